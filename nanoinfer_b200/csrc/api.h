@@ -1,0 +1,55 @@
+// C interface of the kernel library.  Every launcher enqueues on `stream`, allocates
+// nothing, and returns 0 or an error code: a positive value is a cudaError_t, a
+// negative one is one of the NIB_ERR_* codes below.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#define NIB_ERR_BAD_ARGUMENT (-1)
+#define NIB_ERR_UNSUPPORTED_SIZE (-2)
+#define NIB_ERR_DRIVER (-3)
+
+// Values a kernel may leave in the device status word.
+#define NIB_STATUS_OK 0
+#define NIB_STATUS_BAD_PAGE 1
+#define NIB_STATUS_WAIT_TIMEOUT 2
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+int nib_embed(int dtype, const int* tokens, const int* positions, const void* table,
+              const void* pos_table, float* out, int T, int C, cudaStream_t stream);
+
+int nib_layernorm(int out_dtype, const float* x, const int* rows, const float* gamma,
+                  const float* beta, void* out, int n_rows, int C, float eps, cudaStream_t stream);
+
+int nib_kv_append(int dtype, const void* src, int ld, int k_off, int v_off, void* cache,
+                  const int* block_table, int max_blocks, const int* row_entry, const int* positions,
+                  int T, int n_kv_head, int head_dim, int page_size, int n_pages, int* status,
+                  cudaStream_t stream);
+
+// out[M,N] = act(a[M,K] . w[N,K]^T + bias); with `residual` the result is added to the
+// 32-bit `out` in place.  SIMT path: true 32-bit arithmetic for float inputs.
+int nib_linear_simt(int in_dtype, int out_dtype, const void* a, int lda, const void* w, int ldw,
+                    const float* bias, void* out, int ldo, int M, int N, int K, int act,
+                    int residual, cudaStream_t stream);
+
+// Causal attention of T query rows over the paged cache (general SIMT kernel).
+int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
+                       const int* block_table, int max_blocks, const int* row_entry,
+                       const int* positions, int T, int n_head, int n_kv_head, int head_dim,
+                       int page_size, int n_pages, float scale, int window, int* status,
+                       cudaStream_t stream);
+
+int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStream_t stream);
+
+// One token per logits row: argmax where temperature <= 0, else temperature / top-k sampling
+// with the request's own xorshift64* state (rng_state[row_slot[r]], advanced by one draw).
+int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
+               const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
+               cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

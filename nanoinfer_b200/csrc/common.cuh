@@ -1,0 +1,85 @@
+// Shared device helpers for the sm_100a kernels: storage types, conversions and
+// warp/block reductions.  All arithmetic that decides a result's accuracy
+// (statistics, softmax, accumulators, the residual sum) is done in 32-bit.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nib {
+
+using bf16 = __nv_bfloat16;
+
+// dtype codes of the C interface
+enum : int { DT_F32 = 0, DT_BF16 = 1 };
+
+// activation codes of the linear epilogues
+enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2 };
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+// tanh form: 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))); erf form: 0.5 u (1 + erf(u / sqrt 2)).
+// tanhf and erff are the accurate library functions, never the approximate intrinsics.
+__device__ __forceinline__ float gelu_tanh(float u) {
+  const float k = 0.7978845608028654f;
+  return 0.5f * u * (1.0f + tanhf(k * (u + 0.044715f * u * u * u)));
+}
+__device__ __forceinline__ float gelu_erf(float u) {
+  return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
+}
+__device__ __forceinline__ float apply_act(float u, int act) {
+  if (act == ACT_GELU_TANH) return gelu_tanh(u);
+  if (act == ACT_GELU_ERF) return gelu_erf(u);
+  return u;
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats.  The result
+// is the same in every thread, and the order of the additions is fixed.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();  // scratch may still be read from an earlier call
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < n_warps) ? scratch[lane] : 0.0f;
+  return warp_sum(r);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_warps = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float r = (lane < n_warps) ? scratch[lane] : -INFINITY;
+  return warp_max(r);
+}
+
+// Where token `pos` of a request lies in a paged cache layer laid out as
+// [page][K|V][kv_head][slot in page][head_dim].
+__device__ __forceinline__ size_t kv_offset(int page, int kv, int head, int slot, int n_kv_head,
+                                            int page_size, int head_dim) {
+  return ((((size_t)page * 2 + kv) * n_kv_head + head) * page_size + slot) * (size_t)head_dim;
+}
+
+}  // namespace nib
+
+#define NIB_LAUNCH_CHECK() return (int)cudaGetLastError()

@@ -1,0 +1,203 @@
+"""Python faces of the CUDA kernels.
+
+Each function checks shapes and dtypes, then calls one launcher of the kernel
+library through its C symbol on torch's current stream.  Nothing here computes:
+there is no CPU or library fallback, and a missing or unloadable library is an
+error at first use.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF = 0, 1, 2
+ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF}
+
+STATUS_OK, STATUS_BAD_PAGE, STATUS_WAIT_TIMEOUT = 0, 1, 2
+_ERR_NAMES = {-1: "bad argument", -2: "unsupported size", -3: "CUDA driver call failed"}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+_c_int, _c_float, _c_ptr = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+_SIGNATURES = {
+    "nib_embed": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_layernorm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
+    "nib_kv_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                      _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_simt": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                        _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+    "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+}
+
+
+def library() -> ctypes.CDLL:
+    """The loaded kernel library; compiled on first use if the built file is missing."""
+    global _lib
+    if _lib is None:
+        if not torch.cuda.is_available():
+            raise KernelError("nanoinfer_b200 needs a CUDA device: there is no CPU path")
+        path = _build.library_path(build=True)
+        lib = ctypes.CDLL(path)
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                continue
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        _lib = lib
+    return _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: {_ERR_NAMES.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not supported by the kernels")
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _i32(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.int32 or not t.is_contiguous():
+        raise KernelError(f"{name} must be a contiguous int32 tensor")
+
+
+# ------------------------------------------------------------------------------ ops
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] (+ pos_table[positions[t]]), written as 32-bit floats."""
+    T, C = tokens.shape[0], table.shape[1]
+    _i32(tokens, "tokens")
+    if out.dtype != torch.float32 or out.shape[0] < T or out.shape[1] != C or not out.is_contiguous():
+        raise KernelError("embed: out must be contiguous float32 [T, C]")
+    if pos_table is not None:
+        if positions is None or pos_table.dtype != table.dtype or pos_table.shape[1] != C:
+            raise KernelError("embed: pos_table needs positions, the table's dtype and its width")
+        _i32(positions, "positions")
+    _check(library().nib_embed(_dt(table), _ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table),
+                               _ptr(out), T, C, _stream()), "embed")
+
+
+def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, out: torch.Tensor,
+              n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+    """out[r] = LayerNorm(x[rows[r]] if rows is given else x[r]); x is the 32-bit residual stream."""
+    C = x.shape[1]
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise KernelError("layernorm: x must be contiguous float32")
+    if gamma.dtype != torch.float32 or beta.dtype != torch.float32 or gamma.numel() != C or beta.numel() != C:
+        raise KernelError("layernorm: gamma and beta must be float32 [C]")
+    if out.shape[1] != C or out.shape[0] < n_rows or not out.is_contiguous():
+        raise KernelError("layernorm: out must be contiguous [n_rows, C]")
+    if rows is not None:
+        _i32(rows, "rows")
+    _check(library().nib_layernorm(_dt(out), _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
+                                   n_rows, C, float(eps), _stream()), "layernorm")
+
+
+def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+                act: int = ACT_NONE, residual: bool = False) -> None:
+    """out[:M] = act(a[:M] . w^T + bias) on the CUDA cores; with residual, added to the 32-bit out."""
+    N, K = w.shape
+    if a.shape[1] != K or a.dtype != w.dtype or a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("linear: a [M, K] and w [N, K] must share K and dtype, rows contiguous")
+    if out.shape[1] != N or out.shape[0] < M or a.shape[0] < M:
+        raise KernelError("linear: out must be [M, N]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("linear: bias must be float32 [N]")
+    _check(library().nib_linear_simt(_dt(a), _dt(out), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias),
+                                     _ptr(out), out.stride(0), M, N, K, act, int(residual), _stream()),
+           "linear_simt")
+
+
+def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+           act: int = ACT_NONE, residual: bool = False) -> None:
+    """The matrix product of the model: tensor cores for bfloat16 where the shape allows,
+    CUDA cores (true 32-bit) for float32."""
+    linear_simt(a, w, bias, out, M, act, residual)
+
+
+def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, block_table: torch.Tensor,
+              row_entry: torch.Tensor, positions: torch.Tensor, T: int, status: torch.Tensor) -> None:
+    """Copy the key and value columns of src[:T] to their slots in one cache layer
+    [n_pages, 2, n_kv_head, page_size, head_dim]."""
+    n_pages, two, n_kv_head, page_size, head_dim = cache.shape
+    if two != 2 or not cache.is_contiguous() or cache.dtype != src.dtype or src.stride(1) != 1:
+        raise KernelError("kv_append: cache must be contiguous [pages, 2, kv_heads, page, head_dim] of src's dtype")
+    _i32(block_table, "block_table")
+    _check(library().nib_kv_append(_dt(src), _ptr(src), src.stride(0), k_off, v_off, _ptr(cache),
+                                   _ptr(block_table), block_table.shape[1], _ptr(row_entry), _ptr(positions),
+                                   T, n_kv_head, head_dim, page_size, n_pages, _ptr(status), _stream()),
+           "kv_append")
+
+
+def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
+                   row_entry: torch.Tensor, positions: torch.Tensor, T: int, n_head: int, scale: float,
+                   window: int, status: torch.Tensor) -> None:
+    """Causal attention of q[:T] ([T, n_head * head_dim], any row stride) over one cache layer."""
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
+    _check(library().nib_attention_simt(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
+                                        _ptr(block_table), block_table.shape[1], _ptr(row_entry),
+                                        _ptr(positions), T, n_head, n_kv_head, head_dim, page_size, n_pages,
+                                        float(scale), int(window), _ptr(status), _stream()),
+           "attention_simt")
+
+
+def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
+              n_head: int, scale: float, window: int) -> None:
+    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's
+    StepContext (rows, positions, entries)."""
+    attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
+                   window, ctx.status)
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("argmax: logits must be float32 with contiguous rows")
+    _i32(out, "out")
+    _check(library().nib_argmax(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(out), _stream()),
+           "argmax")
+
+
+def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
+           top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor) -> None:
+    """One token per row: greedy where temperature <= 0, else temperature / top-k sampling that
+    advances the xorshift64* word of the row's state slot."""
+    if logits.dtype != torch.float32 or logits.stride(1) != 1:
+        raise KernelError("sample: logits must be float32 with contiguous rows")
+    if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:
+        raise KernelError("sample: rng_state must be int64 words, temperature float32")
+    _i32(row_slot, "row_slot"); _i32(top_k, "top_k"); _i32(out, "out")
+    _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
+                                _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out), _stream()),
+           "sample")

@@ -1,0 +1,163 @@
+"""A model built from a ModelSpec: the parts, the run order, and the forward pass over the
+rows of one step.
+
+The forward pass is the reference's (crates/core/src/stages/kv_cache.rs:25-74): embed the new
+tokens at their positions, run the layers (each appends its keys and values to the cache and
+attends over it), then the final norm and the head on the rows whose logits are wanted only
+(crates/metal/src/shaders/batch.metal:430-452 gathers them the same way).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+from ..parts import base as P
+from ..parts.block import BLOCKS, Block
+from .spec import ModelSpec, PartSpec
+
+
+@dataclass
+class Binding:
+    """One parameter of one part and the checkpoint tensor that feeds it."""
+    part: P.Part
+    spec: P.ParamSpec
+    ref: P.TensorRef
+    where: str          # for messages, e.g. "layers[3].mixer"
+
+
+def _round_up(n: int, m: int) -> int:
+    return (n + m - 1) // m * m
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, config=None):
+        self.spec, self.config = spec, config
+        self.width = spec.width
+        self._bindings: List[Binding] = []
+        self.embedding = self._build(P.EMBEDDINGS, spec.embedding, "embedding")
+        self.position = self._build(P.POSITIONS, spec.position, "position") if spec.position else None
+        self.layers: List[Block] = []
+        for i, ls in enumerate(spec.layers):
+            if ls.arrangement not in BLOCKS:
+                raise KeyError(f"unknown block arrangement {ls.arrangement!r}; registered: {sorted(BLOCKS)}")
+            w = f"layers[{i}]"
+            mixer_args = dict(ls.mixer.args)
+            if ls.mixer_position is not None:
+                mixer_args["position"] = self._build(P.POSITIONS, ls.mixer_position, w + ".mixer_position")
+            mixer = self._build(P.MIXERS, PartSpec(ls.mixer.kind, mixer_args, ls.mixer.tensors), w + ".mixer")
+            self.layers.append(BLOCKS[ls.arrangement](
+                spec.width,
+                self._build(P.NORMS, ls.norm_1, w + ".norm_1"),
+                mixer,
+                self._build(P.NORMS, ls.norm_2, w + ".norm_2"),
+                self._build(P.FEED_FORWARDS, ls.feed_forward, w + ".feed_forward"),
+            ))
+        self.final_norm = self._build(P.NORMS, spec.final_norm, "final_norm")
+        self.head = self._build(P.HEADS, spec.head, "head")
+        self.schedule = list(spec.schedule)
+        self._check_schedule()
+        self.dtype: Optional[torch.dtype] = None
+        self.device: Optional[torch.device] = None
+
+    # ------------------------------------------------------------------ construction
+    def _build(self, registry: P.Registry, ps: PartSpec, where: str) -> P.Part:
+        part = registry.build(ps.kind, **ps.args)
+        wanted = {s.key: s for s in part.param_specs()}
+        unknown = set(ps.tensors) - set(wanted)
+        unmapped = set(wanted) - set(ps.tensors)
+        if unknown or unmapped:
+            raise ValueError(f"{where} ({ps.kind}): tensors mapped to unknown parameters {sorted(unknown)}, "
+                             f"parameters without a tensor {sorted(unmapped)}")
+        for key, s in wanted.items():
+            self._bindings.append(Binding(part, s, ps.tensors[key], where))
+        return part
+
+    def _check_schedule(self) -> None:
+        for i, e in enumerate(self.schedule):
+            if not 0 <= e.layer < len(self.layers):
+                raise ValueError(f"schedule[{i}] names layer {e.layer}, but there are {len(self.layers)} layers")
+            if e.cache_of is not None:
+                if not 0 <= e.cache_of < i or self.schedule[e.cache_of].cache_of is not None:
+                    raise ValueError(f"schedule[{i}].cache_of must name an earlier entry that owns a cache")
+                a = self.layers[e.layer].mixer.kv_spec()
+                b = self.layers[self.schedule[e.cache_of].layer].mixer.kv_spec()
+                if a is None or a != b:
+                    raise ValueError(f"schedule[{i}] cannot read the cache of entry {e.cache_of}: "
+                                     f"their key/value needs differ ({a} vs {b})")
+
+    def bindings(self) -> List[Binding]:
+        return list(self._bindings)
+
+    def parts(self) -> List[P.Part]:
+        seen, out = set(), []
+        for b in self._bindings:
+            if id(b.part) not in seen:
+                seen.add(id(b.part))
+                out.append(b.part)
+        return out
+
+    def all_parts(self) -> List[P.Part]:
+        out: List[P.Part] = [self.embedding]
+        if self.position is not None:
+            out.append(self.position)
+        for blk in self.layers:
+            out.extend(blk.parts().values())
+            pos = getattr(blk.mixer, "position", None)
+            if pos is not None:
+                out.append(pos)
+        out += [self.final_norm, self.head]
+        return out
+
+    def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
+        self.dtype, self.device = dtype, device
+        for part in self.all_parts():
+            part.prepare(dtype, device)
+
+    # ------------------------------------------------------------------ what the cache manager must provide
+    def kv_needs(self) -> List[Tuple[int, P.KVCacheSpec]]:
+        """(schedule index, need) for every run that owns paged keys and values."""
+        out = []
+        for i, e in enumerate(self.schedule):
+            spec = self.layers[e.layer].mixer.kv_spec()
+            if spec is not None and e.cache_of is None:
+                out.append((i, spec))
+        return out
+
+    def state_needs(self) -> List[Tuple[int, P.StateSpec]]:
+        """(schedule index, need) for every run whose mixer keeps per-request state of fixed size."""
+        out = []
+        for i, e in enumerate(self.schedule):
+            spec = self.layers[e.layer].mixer.state_spec()
+            if spec is not None:
+                out.append((i, spec))
+        return out
+
+    @property
+    def vocab_size(self) -> int:
+        return self.head.vocab_size
+
+    @property
+    def max_positions(self) -> Optional[int]:
+        return self.spec.max_positions
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx: P.StepContext, caches: Dict[int, P.KVCacheView], states: Dict[int, torch.Tensor],
+                logit_rows: Optional[torch.Tensor], n_logits: int) -> Optional[torch.Tensor]:
+        """Run the rows of ``ctx`` through the model; return float32 logits [n_logits, vocab] of the
+        rows listed in ``logit_rows`` (None if none are wanted)."""
+        ws = ctx.workspace
+        x = ws.get("model.residual", (ctx.max_rows, self.width), torch.float32)
+        self.embedding.forward(ctx, x, self.position)
+        for i, e in enumerate(self.schedule):
+            owner = i if e.cache_of is None else e.cache_of
+            self.layers[e.layer].forward(x, ctx, caches.get(owner), states.get(i), e.cache_of is None, self.dtype)
+        if n_logits <= 0:
+            return None
+        h = ws.get("model.final", (n_logits, self.width), self.dtype)
+        self.final_norm.forward(x, h, n_logits, rows=logit_rows)
+        pitch = _round_up(self.vocab_size, 16)
+        logits = ws.get("model.logits", (n_logits, pitch), torch.float32)
+        self.head.forward(h, logits[:, :self.vocab_size], n_logits, ctx)
+        return logits[:, :self.vocab_size]

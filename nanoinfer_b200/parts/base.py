@@ -1,0 +1,232 @@
+"""What a model is put together from: the interfaces of the parts and their registries.
+
+A part (norm, mixer, feed-forward, position encoding, embedding, head) takes all of
+its sizes and constants as constructor arguments, declares the parameters it wants
+(``param_specs``), receives them (``bind``) and runs on the rows of one step
+(``forward``).  No part knows which model it is in: the architecture's builder
+chooses a part per layer by its registered name and tells the loader which tensor
+of the checkpoint feeds which parameter.
+
+The reference passes constants as arguments in places (eps to layernorm, head count
+and size to attention: crates/core/src/stages/blocks.rs:43,76) and fixes the rest in
+code (GELU kind, 4C: blocks.rs:113-137); here all of them are parameters.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple, Type
+
+import torch
+
+# ----------------------------------------------------------------------------- parameter specs
+#: kinds of parameters: how the loader stores them for a given engine dtype
+MATRIX = "matrix"   # [out, in] operand of a matrix product: the engine's dtype
+TABLE = "table"     # rows looked up by index (embeddings): the engine's dtype
+VECTOR = "vector"   # biases and norm parameters: always 32-bit
+INT_TABLE = "int_table"  # integer tables: int32
+
+#: how the random-weights mode fills a parameter
+INIT_NORMAL = "normal"              # N(0, std)
+INIT_ONE_PLUS_NORMAL = "one_plus"   # 1 + N(0, std)   (norm scales)
+INIT_ZEROS = "zeros"
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    key: str                 # the part's own name for the parameter
+    shape: Tuple[int, ...]   # the shape the part computes with
+    kind: str = MATRIX
+    init: str = INIT_NORMAL
+
+
+@dataclass(frozen=True)
+class TensorRef:
+    """Where a parameter lives in the checkpoint: the tensor's name, and whether the file
+    stores it transposed ([in, out], as GPT-2's Conv1D does: crates/core/src/weights.rs:1-9)."""
+    name: str
+    transposed: bool = False
+
+
+@dataclass(frozen=True)
+class KVCacheSpec:
+    """A mixer's need of paged keys and values."""
+    n_kv_head: int
+    head_dim: int
+    window: int = 0          # 0: all keys; w > 0: the last w positions only
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """A mixer's need of per-request state of fixed size (one tensor of `shape` per request)."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+# ----------------------------------------------------------------------------- the parts
+class Part:
+    """Base of all parts."""
+
+    def param_specs(self) -> List[ParamSpec]:
+        return []
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        """Receive the loaded parameters, keyed as in ``param_specs``."""
+        self.params = params
+
+    def prepare(self, dtype: torch.dtype, device: torch.device) -> None:
+        """Called once after ``bind`` with the engine's dtype."""
+        self.dtype, self.device = dtype, device
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
+                rows: Optional[torch.Tensor] = None) -> None:
+        """out[:n_rows] = norm(x[rows] or x[:n_rows]); x is the 32-bit residual stream."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Either adds to the embeddings (``additive_table``/``on_embedding``) or transforms
+    queries and keys inside a mixer (``on_qk``); a part may do neither or both."""
+
+    def additive_table(self) -> Optional[torch.Tensor]:
+        """A [positions, width] table to be added to the token embeddings, if that is all it does."""
+        return None
+
+    def max_positions(self) -> Optional[int]:
+        return None
+
+    def on_embedding(self, x: torch.Tensor, ctx: "StepContext") -> None:
+        pass
+
+    def on_qk(self, q: torch.Tensor, k: torch.Tensor, ctx: "StepContext") -> None:
+        pass
+
+
+class Mixer(Part):
+    """Mixes information across positions (attention here).  ``forward`` reads the normed
+    rows ``xn`` and ADDS its output to the 32-bit residual stream ``x`` in place."""
+
+    def kv_spec(self) -> Optional[KVCacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: "StepContext", cache: Optional["KVCacheView"],
+                state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    """Per-row transformation; ``forward`` ADDS its output to the residual stream ``x``."""
+
+    def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: "StepContext") -> None:
+        raise NotImplementedError
+
+
+class Embedding(Part):
+    def forward(self, ctx: "StepContext", x: torch.Tensor, position: Optional[PositionEncoding]) -> None:
+        raise NotImplementedError
+
+
+class Head(Part):
+    def forward(self, h: torch.Tensor, out: torch.Tensor, n_rows: int, ctx: "StepContext") -> None:
+        raise NotImplementedError
+
+    @property
+    def vocab_size(self) -> int:
+        raise NotImplementedError
+
+
+# ----------------------------------------------------------------------------- registries
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._items: Dict[str, Type[Part]] = {}
+
+    def register(self, name: str) -> Callable[[Type[Part]], Type[Part]]:
+        def deco(cls: Type[Part]) -> Type[Part]:
+            if name in self._items and self._items[name] is not cls:
+                raise ValueError(f"{self.what} {name!r} is already registered")
+            self._items[name] = cls
+            return cls
+        return deco
+
+    def build(self, name: str, **kwargs: Any) -> Part:
+        if name not in self._items:
+            raise KeyError(f"unknown {self.what} {name!r}; registered: {sorted(self._items)}")
+        return self._items[name](**kwargs)
+
+    def names(self) -> List[str]:
+        return sorted(self._items)
+
+
+NORMS = Registry("norm")
+POSITIONS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("head")
+
+register_norm = NORMS.register
+register_position = POSITIONS.register
+register_mixer = MIXERS.register
+register_feed_forward = FEED_FORWARDS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register
+
+
+# ----------------------------------------------------------------------------- what a step shows to the parts
+@dataclass
+class KVCacheView:
+    """One cache layer as a mixer sees it during a step."""
+    layer: torch.Tensor          # [n_pages, 2, n_kv_head, page_size, head_dim]
+    block_table: torch.Tensor    # int32 [n_entries, max_blocks]; -1 where no page is held
+    page_size: int
+    window: int
+
+
+@dataclass
+class StepContext:
+    """The rows of one step.  Row t is token ``tokens[t]`` at position ``positions[t]`` of batch
+    entry ``row_entry[t]``; an entry's rows are consecutive and in order."""
+    n_rows: int
+    n_entries: int
+    max_rows: int                # the most rows a step may bring: scratch is sized for it
+    tokens: torch.Tensor         # int32 [n_rows]
+    positions: torch.Tensor      # int32 [n_rows]
+    row_entry: torch.Tensor      # int32 [n_rows]
+    entry_start: torch.Tensor    # int32 [n_entries + 1]: first row of each entry
+    entry_pos0: torch.Tensor     # int32 [n_entries]: position of the entry's first row
+    entry_slot: torch.Tensor     # int32 [n_entries]: the request's state slot
+    status: torch.Tensor         # int32 [1]: device status word (0 = fine)
+    workspace: "Workspace"
+    # the same on the host, for parts that plan their launches
+    host_entry_start: List[int] = field(default_factory=list)
+    host_entry_pos0: List[int] = field(default_factory=list)
+    host_entry_slot: List[int] = field(default_factory=list)
+    max_q_len: int = 0
+    max_kv_len: int = 0
+
+
+class Workspace:
+    """Named scratch buffers that live as long as the engine: a part asks for a buffer by name,
+    shape and dtype and gets the same memory every step (grown if a larger one is asked for)."""
+
+    def __init__(self, device: torch.device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+
+    def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n].view(*shape)
+
+    def nbytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
