@@ -9,7 +9,20 @@ from . import parts as _parts  # registers the built-in parts  # noqa: F401
 from .registry import architectures, get_architecture, load_config, register_architecture
 
 __version__ = "0.1.0"
-__all__ = ["architectures", "get_architecture", "load_config", "register_architecture", "load_model"]
+__all__ = ["architectures", "get_architecture", "load_config", "register_architecture", "load_model",
+           "Engine", "SamplingParams"]
+
+
+def __getattr__(name):
+    # the engine pulls in the kernels; import it on demand so that configuration, weights and the
+    # cache manager can be used where no GPU is present
+    if name == "Engine":
+        from .engine.engine import Engine
+        return Engine
+    if name == "SamplingParams":
+        from .sampling.sampler import SamplingParams
+        return SamplingParams
+    raise AttributeError(name)
 
 
 def load_model(model_dir: str, dtype="bfloat16", device="cuda"):

@@ -1,0 +1,311 @@
+"""Measurement shared by ``bench.py`` and the ``bench`` command: timed decode steps and
+prefill on the engine's own step function, with the byte and FLOP counts of the reference's
+bench (crates/cli/src/bench.rs:261-271, crates/cli/src/metal_batch.rs:113-114,157-160):
+  * decode step bytes = every weight the step uses, once, plus the cached keys and values of
+    the live requests;
+  * matrix FLOPs per token = 2 * (layers * (4 C^2 + 2 C I) + V C), the head counted once per
+    logits row, plus the attention products 4 * C * keys per row and layer.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import subprocess
+import tempfile
+import threading
+import time
+from typing import Dict, List, Optional, Tuple
+
+import torch
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def repo_root() -> str:
+    return os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def measured_peaks() -> Dict[str, float]:
+    path = os.path.join(repo_root(), "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            raw = json.load(fh)
+        out = dict(FALLBACK_PEAKS)
+        for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if isinstance(raw.get(k), (int, float)):
+                out[k] = float(raw[k])
+        out["source"] = "measured"
+        return out
+    except (OSError, ValueError):
+        return dict(FALLBACK_PEAKS)
+
+
+def model_folder(preset: str, seed: int, dtype: torch.dtype, n_layer: Optional[int] = None) -> Tuple[str, object]:
+    """A folder with seeded random weights of the preset's sizes (made once per process tree, in the
+    temporary folder); ``n_layer`` may reduce the depth, never the layer sizes."""
+    from .cli import _preset_path
+    from .config.base import architecture_name
+    from .registry import get_architecture
+    from .weights.random_init import write_random_model
+
+    with open(_preset_path(preset)) as fh:
+        raw = json.load(fh)
+    if n_layer is not None:
+        raw["n_layer"] = int(n_layer)
+    cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
+    key = hashlib.sha1(json.dumps([raw, seed, str(dtype)], sort_keys=True).encode()).hexdigest()[:12]
+    d = os.path.join(tempfile.gettempdir(), f"nanoinfer_b200_model_{os.getuid()}_{key}")
+    if not (os.path.isfile(os.path.join(d, "model.safetensors")) and os.path.isfile(os.path.join(d, "config.json"))):
+        tmp = d + f".tmp{os.getpid()}"
+        write_random_model(cfg, tmp, seed, dtype)
+        if os.path.isdir(d):
+            import shutil
+            shutil.rmtree(tmp)
+        else:
+            os.rename(tmp, d)
+    return d, cfg
+
+
+# ----------------------------------------------------------------------------- counts
+def weight_bytes_per_step(cfg, itemsize: int) -> int:
+    """Bytes of the matrices a decode step streams: the blocks and the head (the position table is
+    touched one row per token and left out, as crates/core/src/config.rs:41-48 does)."""
+    c, i = cfg.n_embd, cfg.inner_dim
+    per_layer = c * 3 * c + c * c + c * i + i * c
+    vectors = cfg.n_layer * (3 * c + c + i + c + 4 * c) + 2 * c
+    return (cfg.n_layer * per_layer + cfg.vocab_size * c) * itemsize + vectors * 4
+
+
+def kv_bytes_per_position(cfg, itemsize: int) -> int:
+    return 2 * cfg.n_layer * cfg.n_embd * itemsize
+
+
+def matrix_flops_per_token(cfg) -> float:
+    c, i = cfg.n_embd, cfg.inner_dim
+    return 2.0 * cfg.n_layer * (4 * c * c + 2 * c * i)
+
+
+def step_flops(cfg, row_contexts: List[int], n_logit_rows: int) -> float:
+    """FLOPs of one step whose rows see ``row_contexts`` keys each."""
+    flops = matrix_flops_per_token(cfg) * len(row_contexts)
+    flops += 2.0 * cfg.vocab_size * cfg.n_embd * n_logit_rows
+    flops += 4.0 * cfg.n_embd * cfg.n_layer * float(sum(row_contexts))
+    return flops
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons in the background during a timed region."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, period_ms: int = 100):
+        self.period_ms = period_ms
+        self.proc: Optional[subprocess.Popen] = None
+        self.lines: List[str] = []
+
+    def start(self) -> None:
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self._t = threading.Thread(target=self._read, daemon=True)
+            self._t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self) -> None:
+        assert self.proc is not None and self.proc.stdout is not None
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> Dict[str, object]:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(self.period_ms / 1000.0)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------- workloads
+class L2Flusher:
+    """Writes a buffer larger than the 126 MB L2 so that the next step starts with a cold cache."""
+
+    def __init__(self, device, nbytes: int = 256 << 20):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def flush(self) -> None:
+        self.buf.zero_()
+
+
+def build_engine(model_dir: str, dtype: str, batch: int, context: int, max_rows: int):
+    from .engine.engine import Engine
+
+    return Engine(model_dir, dtype=dtype, max_tokens=batch * (context + 64), max_batch=max(batch, 1),
+                  max_rows=max_rows, check_status=False)
+
+
+def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
+                flush: bool = True) -> Dict[str, float]:
+    """Device time of decode steps at a fixed batch: ``batch`` requests are prefilled with
+    ``prompt_len`` random tokens, then ``warmup + steps`` greedy decode steps run through the
+    engine's step function and sampler; each timed step is bracketed by CUDA events, with an L2
+    flush between steps."""
+    from .engine.runner import StepItem
+
+    cfg = eng.model.config
+    g = torch.Generator().manual_seed(seed)
+    reqs = [eng.cache.open_request() for _ in range(batch)]
+    from .sampling.sampler import SamplingParams
+    for r in reqs:
+        eng.sampler.set_request(r.slot, SamplingParams(temperature=0.0))
+    last = []
+    budget = max(1, eng.runner.max_rows // max(1, prompt_len))
+    for i in range(0, batch, budget):
+        chunk = reqs[i:i + budget]
+        items = [StepItem(r, torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
+                 for r in chunk]
+        logits = eng.runner.step(items)
+        last += eng.sampler.sample(logits, eng.runner.last_logit_slot).tolist()
+    flusher = L2Flusher(eng.device) if flush else None
+    times = []
+    ctx_sum = 0
+    torch.cuda.synchronize()
+    for s in range(warmup + steps):
+        items = [StepItem(r, [t], [0]) for r, t in zip(reqs, last)]
+        if flusher is not None:
+            flusher.flush()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        logits = eng.runner.step(items)
+        toks = eng.sampler.sample(logits, eng.runner.last_logit_slot)
+        e1.record()
+        last = toks.tolist()
+        if s >= warmup:
+            times.append(e0.elapsed_time(e1))
+            ctx_sum += sum(r.n_tokens for r in reqs)
+    for r in reqs:
+        eng.cache.close_request(r)
+    ms = sum(times) / len(times)
+    return {"ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "mean_context": ctx_sum / (len(times) * batch),
+            "steps": len(times)}
+
+
+def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, seed: int = 1) -> Dict[str, float]:
+    """Device time of ONE step that prefills ``n_prompts`` prompts of ``prompt_len`` tokens."""
+    from .engine.runner import StepItem
+
+    cfg = eng.model.config
+    g = torch.Generator().manual_seed(seed)
+    flusher = L2Flusher(eng.device)
+    times = []
+    for s in range(warmup + runs):
+        reqs = [eng.cache.open_request() for _ in range(n_prompts)]
+        items = [StepItem(r, torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
+                 for r in reqs]
+        flusher.flush()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        eng.runner.step(items)
+        e1.record()
+        torch.cuda.synchronize()
+        if s >= warmup:
+            times.append(e0.elapsed_time(e1))
+        for r in reqs:
+            eng.cache.close_request(r)
+    times.sort()
+    ms = times[len(times) // 2]
+    tokens = n_prompts * prompt_len
+    contexts = [p + 1 for _ in range(n_prompts) for p in range(prompt_len)]
+    return {"ms": ms, "tokens": tokens, "tokens_per_s": tokens / (ms / 1e3),
+            "flops": step_flops(cfg, contexts, n_prompts)}
+
+
+def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 2) -> Dict[str, float]:
+    """Decode throughput through the public entry point: requests are added with host token lists,
+    ``Engine.step`` runs scheduler, step function and sampler, and every step's tokens are read
+    back to the host.  Wall-clock time around the timed steps, device idle before and after."""
+    from .sampling.sampler import SamplingParams
+
+    cfg = eng.model.config
+    g = torch.Generator().manual_seed(seed)
+    params = SamplingParams(max_new_tokens=warmup + steps + 1, temperature=0.0)
+    for _ in range(batch):
+        eng.add_request(torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), params)
+    while any(r.n_pending > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()  # prefill
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        eng.step()
+    torch.cuda.synchronize()
+    dt = time.perf_counter() - t0
+    while eng.has_work():
+        eng.step()
+    return {"tokens_per_s": batch * steps / dt, "ms_per_step": dt / steps * 1e3,
+            "h2d_bytes_per_step": eng.runner.last_meta_bytes, "d2h_bytes_per_step": 4 * batch}
+
+
+# ----------------------------------------------------------------------------- the bench command
+def run_cli_bench(args) -> int:
+    import sys
+
+    peaks = measured_peaks()
+    bw = args.bandwidth_gbs or peaks["hbm_gbs"]
+    batches = [int(b) for b in str(args.batch).split(",") if b]
+    from .registry import load_config
+
+    cfg = load_config(args.weights)
+    itemsize = 2 if args.dtype == "bfloat16" else 4
+    if args.prompt_len + args.tokens + args.warmup > cfg.n_positions:
+        print(f"prompt_len + tokens must be <= {cfg.n_positions}", file=sys.stderr)
+        return 2
+    results = []
+    for b in batches:
+        eng = build_engine(args.weights, args.dtype, b, args.prompt_len + args.tokens + args.warmup,
+                           max_rows=max(2048, b))
+        dec = time_decode(eng, b, args.prompt_len, args.tokens, max(3, args.warmup))
+        pre = time_prefill(eng, 1, args.prompt_len, args.runs, max(1, args.warmup))
+        step_bytes = weight_bytes_per_step(cfg, itemsize) + b * dec["mean_context"] * kv_bytes_per_position(cfg, itemsize)
+        ceiling = bw * 1e9 / step_bytes * b
+        line = {"dtype": args.dtype, "batch": b, "prompt_len": args.prompt_len, "tokens": args.tokens,
+                "decode_tok_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],
+                "decode_gbs": step_bytes / (dec["ms_per_step"] / 1e3) / 1e9,
+                "ceiling_tok_s": ceiling, "pct_of_ceiling": 100.0 * dec["tokens_per_s"] / ceiling,
+                "prefill_tok_s": pre["tokens_per_s"], "note": args.note}
+        print(f"{args.dtype} B={b}: prefill {pre['tokens_per_s']:.0f} tok/s | decode {dec['tokens_per_s']:.1f} tok/s "
+              f"({line['decode_gbs']:.1f} GB/s) | {line['pct_of_ceiling']:.2f}% of {ceiling:.0f} tok/s ceiling")
+        results.append(line)
+        del eng
+        torch.cuda.empty_cache()
+    if args.out:
+        with open(args.out, "a") as fh:
+            for line in results:
+                fh.write(json.dumps(line) + "\n")
+    return 0

@@ -1,0 +1,139 @@
+"""Command line in the manner of the reference's ``nanoinfer`` binary (crates/cli/src/main.rs:28-83):
+
+    python -m nanoinfer_b200 --weights DIR generate --prompt-ids 464,3616 --tokens 40
+    python -m nanoinfer_b200 --weights DIR bench --tokens 64 --prompt-len 64 --batch 1,8,64
+    python -m nanoinfer_b200 random-weights --config gpt2-small --seed 1 --out DIR
+
+``--weights`` is the reference's global option (main.rs:30-32): the folder with
+``model.safetensors`` (and here ``config.json``).  ``generate`` keeps the reference's options
+and defaults (main.rs:48-72): ``--tokens 40 --temperature 0.0 --top-k 40 --seed 42
+--profile``; the prompt is given as token ids.  ``bench`` keeps ``--tokens 64 --prompt-len 64
+--runs 5 --warmup 1 --bandwidth-gbs`` (crates/cli/src/bench.rs:24-58) and ``--batch``/``--dtype``
+of the batch sweep (crates/cli/src/metal_batch.rs:20-58).  The reference chooses a strategy
+with ``--stage``; here the one choice left is ``--dtype``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import time
+from typing import List
+
+
+def _preset_path(name: str) -> str:
+    here = os.path.join(os.path.dirname(os.path.abspath(__file__)), "config", "presets")
+    return name if os.path.isfile(name) else os.path.join(here, name + ".json")
+
+
+def _ids(text: str) -> List[int]:
+    return [int(t) for t in text.replace(" ", ",").split(",") if t]
+
+
+def cmd_random_weights(args) -> int:
+    import torch
+
+    from .registry import get_architecture
+    from .config.base import architecture_name
+    from .weights.random_init import write_random_model
+
+    with open(_preset_path(args.config)) as fh:
+        raw = json.load(fh)
+    cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
+    dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
+    write_random_model(cfg, args.out, args.seed, dtype)
+    print(f"wrote {args.out} ({cfg.n_params() / 1e6:.1f}M params, {args.dtype}, seed {args.seed})", file=sys.stderr)
+    return 0
+
+
+def cmd_generate(args) -> int:
+    import torch
+
+    from .engine.engine import Engine
+    from .sampling.sampler import SamplingParams
+
+    if args.prompt_ids is None:
+        print("generate: give the prompt as --prompt-ids a,b,c (token ids)", file=sys.stderr)
+        return 2
+    prompt = _ids(args.prompt_ids)
+    t0 = time.perf_counter()
+    eng = Engine(args.weights, dtype=args.dtype, max_batch=1, max_rows=max(64, len(prompt)))
+    print(f"loaded {args.weights} ({eng.model.config.n_params() / 1e6:.1f}M params) in "
+          f"{time.perf_counter() - t0:.2f}s", file=sys.stderr)
+    params = SamplingParams(max_new_tokens=args.tokens, temperature=args.temperature, top_k=args.top_k,
+                            seed=args.seed)
+    req = eng.add_request(prompt, params)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    t_first = None
+    printed = 0
+    while eng.has_work():
+        eng.step()
+        if t_first is None and req.output:
+            t_first = time.perf_counter() - t0
+        for tok in req.output[printed:]:
+            print(tok, end=" ", flush=True)
+        printed = len(req.output)
+    total = time.perf_counter() - t0
+    print()
+    n = len(req.output)
+    t_first = t_first or total
+    print(f"[{args.dtype}] prompt {len(prompt)} tok, prefill {t_first * 1e3:.1f} ms "
+          f"({len(prompt) / t_first:.1f} tok/s), decode {(n - 1) / max(total - t_first, 1e-9):.2f} tok/s",
+          file=sys.stderr)
+    if args.profile:
+        from .bench_support import print_profile
+        print_profile(eng, prompt)
+    return 0
+
+
+def cmd_bench(args) -> int:
+    from .bench_support import run_cli_bench
+
+    return run_cli_bench(args)
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="nanoinfer_b200", description="A small LLM inference engine for one B200")
+    ap.add_argument("--weights", default="weights/gpt2",
+                    help="folder with config.json and model.safetensors")
+    sub = ap.add_subparsers(dest="cmd", required=True)
+
+    g = sub.add_parser("generate", help="generate tokens from a prompt")
+    g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--prompt-ids", default=None, help="the prompt as comma-separated token ids")
+    g.add_argument("--tokens", type=int, default=40, help="number of tokens to generate")
+    g.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
+    g.add_argument("--top-k", type=int, default=40)
+    g.add_argument("--seed", type=int, default=42)
+    g.add_argument("--profile", action="store_true", help="print a per-kernel time breakdown afterwards")
+    g.set_defaults(fn=cmd_generate)
+
+    b = sub.add_parser("bench", help="measure prefill and decode throughput")
+    b.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    b.add_argument("--tokens", type=int, default=64, help="decode steps to time per run")
+    b.add_argument("--prompt-len", type=int, default=64)
+    b.add_argument("--batch", default="1", help="batch sizes, e.g. 1,8,64")
+    b.add_argument("--runs", type=int, default=5)
+    b.add_argument("--warmup", type=int, default=1)
+    b.add_argument("--bandwidth-gbs", type=float, default=None,
+                   help="memory bandwidth for the decode ceiling (default: the measured peak)")
+    b.add_argument("--out", default=None, help="append the result line to this file")
+    b.add_argument("--note", default="")
+    b.set_defaults(fn=cmd_bench)
+
+    r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
+    r.add_argument("--config", required=True, help="a preset name (gpt2-small, gpt2-medium, gpt2-xl, "
+                                                   "gpt2-tiny-a, gpt2-tiny-b) or a config.json file")
+    r.add_argument("--seed", type=int, default=0)
+    r.add_argument("--out", required=True)
+    r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.set_defaults(fn=cmd_random_weights)
+
+    args = ap.parse_args(argv)
+    return args.fn(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

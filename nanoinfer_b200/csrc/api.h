@@ -44,8 +44,9 @@ int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, voi
 
 int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStream_t stream);
 
-// One token per logits row: argmax where temperature <= 0, else temperature / top-k sampling
-// with the request's own xorshift64* state (rng_state[row_slot[r]], advanced by one draw).
+// One token per logits row.  temperature, top_k and rng_state are per-slot arrays indexed by
+// row_slot[r]: argmax where temperature <= 0, else temperature / top-k sampling with the
+// request's own xorshift64* state (advanced by one draw).
 int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
                cudaStream_t stream);

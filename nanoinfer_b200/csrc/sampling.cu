@@ -7,8 +7,9 @@
 //     first; r = u * (sum of the kept probabilities); walk the kept tokens subtracting
 //     each probability until r <= 0;
 //   * u comes from a xorshift64* generator: u = (r >> 40) / 2^24.
-// Here the generator's state belongs to the request (one 64-bit word per state slot), so
-// a request's draws do not depend on what else is in the batch.
+// Here the generator's state, the temperature and top_k belong to the request: they live in
+// per-slot arrays indexed by the row's state slot, so a request's draws do not depend on what
+// else is in the batch.
 //
 // Instead of sorting, the walk is a radix select over order-preserving keys of the
 // scaled logits, four passes of eight bits: first by count (which key is the k-th
@@ -150,7 +151,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
   __shared__ SelectShared sh;
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
-  const float temp = temperature[r];
+  const int slot = row_slot[r];
+  const float temp = temperature[slot];
   if (!(temp > 0.0f)) {
     const int best = block_argmax(row, V, best_scratch);
     if (threadIdx.x == 0) out[r] = best;
@@ -159,11 +161,11 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
   // one draw of xorshift64*, kept per request
   __shared__ uint32_t u24_sh;
   if (threadIdx.x == 0) {
-    unsigned long long s = rng_state[row_slot[r]];
+    unsigned long long s = rng_state[slot];
     s ^= s >> 12;
     s ^= s << 25;
     s ^= s >> 27;
-    rng_state[row_slot[r]] = s;
+    rng_state[slot] = s;
     u24_sh = (uint32_t)((s * 0x2545F4914F6CDD1Dull) >> 40);
   }
   float mxl = -INFINITY;
@@ -171,7 +173,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
   const float mx = block_max(mxl, red);  // also orders the write of u24_sh
   const uint32_t u24 = u24_sh;
 
-  int k = top_k[r];
+  int k = top_k[slot];
   bool use_thresh = false;
   uint32_t thresh = 0;
   unsigned long long tie_keep = 0ull, tie_mass = 0ull;

@@ -64,7 +64,7 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
-        cap = 4 * self.max_rows + 4 * self.max_entries + 8 + n_tables
+        cap = 5 * self.max_rows + 4 * self.max_entries + 8 + n_tables
         # A ring of pinned staging buffers: a buffer is written again only after the copy that
         # last read it has finished.
         on_gpu = self.device.type == "cuda"
@@ -77,6 +77,8 @@ class ModelRunner:
         self._ring_next = 0
         self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        self.last_meta_bytes = 0
+        self.last_logit_slot = None
 
     # ------------------------------------------------------------------ checks
     def _validate(self, items: Sequence[StepItem]) -> int:
@@ -121,7 +123,8 @@ class ModelRunner:
         E = len(items)
         M = sum(len(it.want) for it in items)
 
-        # ---- pack the tables: [tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | tables]
+        # ---- pack the tables:
+        # [tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | logit_slot | block tables]
         host, buf, copied = self._ring[self._ring_next]
         self._ring_next = (self._ring_next + 1) % len(self._ring)
         if copied is not None:
@@ -131,7 +134,8 @@ class ModelRunner:
         o_pos0 = o_start + E + 1
         o_slot = o_pos0 + E
         o_lrow = o_slot + E
-        o_tab = o_lrow + M
+        o_lslot = o_lrow + M
+        o_tab = o_lslot + M
         o_tab += (-o_tab) % 4  # keep the tables 16-byte aligned
         row = 0
         lrow = o_lrow
@@ -144,6 +148,7 @@ class ModelRunner:
             buf[o_ent + row:o_ent + row + n] = e
             for w in it.want:
                 buf[lrow] = row + int(w)
+                buf[lrow + M] = it.request.slot
                 lrow += 1
             starts.append(row)
             pos0s.append(p0)
@@ -165,6 +170,7 @@ class ModelRunner:
             tab_offsets.append(o)
             o += E * mb
         n_meta = o
+        self.last_meta_bytes = 4 * n_meta
         dev = self._meta_dev
         dev[:n_meta].copy_(host[:n_meta], non_blocking=True)
         if copied is not None:
@@ -181,6 +187,8 @@ class ModelRunner:
         tables = [dev[off:off + E * mb].view(E, mb) for off, mb in zip(tab_offsets, self.cache.max_blocks)]
         caches = self.cache.layer_views(tables)
         logit_rows = dev[o_lrow:o_lrow + M] if M else None
+        #: the state slot of the request behind each logits row (for the sampler)
+        self.last_logit_slot = dev[o_lslot:o_lslot + M] if M else None
         logits = self.model.forward(ctx, caches, self.cache.state_tensors, logit_rows, M)
 
         for it in items:

@@ -191,8 +191,9 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
 
 def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
            top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor) -> None:
-    """One token per row: greedy where temperature <= 0, else temperature / top-k sampling that
-    advances the xorshift64* word of the row's state slot."""
+    """One token per row.  ``temperature``, ``top_k`` and ``rng_state`` are per-slot arrays and
+    ``row_slot`` names each row's slot: greedy where the slot's temperature <= 0, else
+    temperature / top-k sampling that advances the slot's xorshift64* word."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with contiguous rows")
     if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:

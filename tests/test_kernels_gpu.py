@@ -1,0 +1,258 @@
+"""Each kernel alone against its plain formula, at sizes other than the engine's models:
+widths and vocabularies that are no power of two, head sizes in steps of 8, grouped key/value
+heads, windows, pages scattered over the pool."""
+import math
+
+import pytest
+import torch
+
+import plain_gpt2 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def ops():
+    from nanoinfer_b200.kernels import ops as o
+    return o
+
+
+def gen(seed=0):
+    return torch.Generator().manual_seed(seed)
+
+
+class Ctx:
+    """The few fields of a StepContext that the attention kernels read."""
+
+    def __init__(self, row_entry, positions, starts=None):
+        self.row_entry = torch.tensor(row_entry, dtype=torch.int32, device=DEV)
+        self.positions = torch.tensor(positions, dtype=torch.int32, device=DEV)
+        self.n_rows = len(positions)
+        self.status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        self.n_entries = max(row_entry) + 1
+        starts = starts or [row_entry.index(e) for e in range(self.n_entries)] + [len(row_entry)]
+        self.host_entry_start = starts
+        self.host_entry_pos0 = [positions[s] for s in starts[:-1]]
+        self.entry_start = torch.tensor(starts, dtype=torch.int32, device=DEV)
+        self.entry_pos0 = torch.tensor(self.host_entry_pos0, dtype=torch.int32, device=DEV)
+        self.max_q_len = max(b - a for a, b in zip(starts, starts[1:]))
+        self.max_kv_len = max(positions) + 1
+        self.max_rows = self.n_rows
+        from nanoinfer_b200.parts.base import Workspace
+        self.workspace = Workspace(torch.device(DEV))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("C", [100, 768, 1600])
+def test_embed_adds_positions(dtype, C):
+    V, Pn, T = 777, 300, 37
+    g = gen(1)
+    wte, wpe = torch.randn(V, C, generator=g).to(dtype), torch.randn(Pn, C, generator=g).to(dtype)
+    tok = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    pos = torch.randint(0, Pn, (T,), generator=g, dtype=torch.int32)
+    out = torch.full((T, C), 7.0, device=DEV)
+    ops().embed(tok.to(DEV), wte.to(DEV), out, wpe.to(DEV), pos.to(DEV))
+    want = wte.float()[tok.long()] + wpe.float()[pos.long()]
+    assert torch.equal(out.cpu(), want)
+    ops().embed(tok.to(DEV), wte.to(DEV), out)
+    assert torch.equal(out.cpu(), wte.float()[tok.long()])
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("C, eps", [(120, 1e-6), (768, 1e-5), (1600, 1e-5), (5000, 1e-3)])
+def test_layernorm_two_pass_and_gather(out_dtype, C, eps):
+    g = gen(2)
+    x = (torch.randn(40, C, generator=g) * 3 + 50.0)             # a large mean punishes one-pass variance
+    gamma, beta = torch.randn(C, generator=g), torch.randn(C, generator=g)
+    rows = torch.tensor([39, 0, 7, 7, 21], dtype=torch.int32)
+    out = torch.zeros(40, C, dtype=out_dtype, device=DEV)
+    ops().layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out, 40)
+    want = P.layernorm(x.double(), gamma.double(), beta.double(), eps)
+    tol = 2e-5 if out_dtype == torch.float32 else 3e-2
+    assert (out.cpu().double() - want).abs().max() < tol * max(1.0, float(want.abs().max()))
+    out2 = torch.zeros(5, C, dtype=out_dtype, device=DEV)
+    ops().layernorm(x.to(DEV), gamma.to(DEV), beta.to(DEV), eps, out2, 5, rows.to(DEV))
+    assert torch.equal(out2.cpu(), out.cpu()[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M, N, K", [(1, 96, 768), (37, 70, 3072), (130, 257, 100), (64, 1000, 120)])
+@pytest.mark.parametrize("act", ["none", "tanh", "erf"])
+def test_linear_simt(dtype, M, N, K, act):
+    g = gen(3)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(dtype)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dtype)
+    b = torch.randn(N, generator=g)
+    out = torch.zeros(M, N, dtype=dtype, device=DEV)
+    o = ops()
+    o.linear_simt(a.to(DEV), w.to(DEV), b.to(DEV), out, M, act=o.ACT_CODES[act])
+    y = a.double() @ w.double().T + b.double()
+    want = {"none": lambda u: u, "tanh": P.gelu_tanh, "erf": P.gelu_erf}[act](y)
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert (out.cpu().double() - want).abs().max() < tol
+    # the residual epilogue adds into a 32-bit stream, rows beyond M untouched
+    x = torch.randn(M + 3, N, generator=g)
+    xd = x.to(DEV)
+    o.linear_simt(a.to(DEV), w.to(DEV), b.to(DEV), xd, M, residual=True)
+    assert (xd.cpu().double()[:M] - (x.double()[:M] + y)).abs().max() < tol
+    assert torch.equal(xd.cpu()[M:], x[M:])
+
+
+def test_linear_rows_do_not_depend_on_the_batch():
+    g = gen(4)
+    a, w = torch.randn(70, 200, generator=g), torch.randn(130, 200, generator=g)
+    o = ops()
+    full = torch.zeros(70, 130, device=DEV)
+    o.linear_simt(a.to(DEV), w.to(DEV), None, full, 70)
+    one = torch.zeros(1, 130, device=DEV)
+    o.linear_simt(a[41:42].to(DEV), w.to(DEV), None, one, 1)
+    assert torch.equal(one[0], full[41])
+
+
+def paged_case(dtype, n_head, n_kv_head, hd, page_size, lengths, q_lens, seed):
+    """Requests of the given lengths whose last q_lens tokens are this step's rows; pages are dealt
+    out in a shuffled order so that a request's blocks lie scattered."""
+    g = gen(seed)
+    n_pages = sum(-(-n // page_size) for n in lengths) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    max_blocks = max(-(-n // page_size) for n in lengths) + 1
+    table = torch.full((len(lengths), max_blocks), -1, dtype=torch.int32)
+    cache = torch.zeros(n_pages, 2, n_kv_head, page_size, hd)
+    ks, vs, qs, row_entry, positions = [], [], [], [], []
+    for e, (n, nq) in enumerate(zip(lengths, q_lens)):
+        k, v = torch.randn(n, n_kv_head * hd, generator=g), torch.randn(n, n_kv_head * hd, generator=g)
+        q = torch.randn(nq, n_head * hd, generator=g)
+        k, v, q = k.to(dtype).float(), v.to(dtype).float(), q.to(dtype).float()
+        ks.append(k); vs.append(v); qs.append(q)
+        for b in range(-(-n // page_size)):
+            table[e, b] = perm.pop()
+        for j in range(n):
+            page = int(table[e, j // page_size])
+            cache[page, 0, :, j % page_size] = k[j].view(n_kv_head, hd)
+            cache[page, 1, :, j % page_size] = v[j].view(n_kv_head, hd)
+        row_entry += [e] * nq
+        positions += list(range(n - nq, n))
+    return dict(cache=cache.to(dtype), table=table, ks=ks, vs=vs, qs=qs, row_entry=row_entry, positions=positions)
+
+
+ATT_CASES = [
+    # n_head, n_kv_head, head_dim, page, lengths, q_lens, window
+    (4, 4, 16, 16, [1, 17, 50], [1, 17, 3], 0),
+    (5, 5, 24, 16, [40, 33, 2], [40, 1, 2], 0),
+    (6, 2, 64, 16, [130, 64, 65], [1, 64, 2], 0),
+    (3, 1, 128, 8, [70, 9], [5, 9], 0),
+    (4, 2, 32, 16, [100, 45, 16], [100, 1, 16], 24),
+    (2, 2, 80, 16, [300], [1], 0),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", ATT_CASES)
+def test_attention_over_scattered_pages(dtype, case):
+    n_head, n_kv_head, hd, ps, lengths, q_lens, window = case
+    c = paged_case(dtype, n_head, n_kv_head, hd, ps, lengths, q_lens, seed=hd + len(lengths))
+    scale = 0.7 / math.sqrt(hd)
+    want = torch.cat([
+        P.causal_attention(q.double(), k.double(), v.double(), n_head, n_kv_head, scale=scale, window=window,
+                           q_pos0=len(k) - len(q))
+        for q, k, v in zip(c["qs"], c["ks"], c["vs"])])
+    q = torch.cat(c["qs"]).to(dtype).to(DEV)
+    out = torch.zeros_like(q)
+    ctx = Ctx(c["row_entry"], c["positions"])
+    ops().attention(q, c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, scale, window)
+    assert int(ctx.status.item()) == 0
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    assert (out.cpu().double() - want).abs().max() < tol
+
+
+def test_attention_finds_one_far_key_among_hundreds():
+    """One key far back is made to match the query: the output must be that key's value, whichever
+    page it lies on."""
+    n_head, hd, ps, n = 2, 64, 16, 600
+    for far in (0, 15, 16, 17, 255, 256, 431, 598):
+        c = paged_case(torch.float32, n_head, n_head, hd, ps, [n], [1], seed=far)
+        k, v, q = c["ks"][0], c["vs"][0], c["qs"][0]
+        page = int(c["table"][0, far // ps])
+        for h in range(n_head):
+            c["cache"][page, 0, h, far % ps] = 40.0 * q[0, h * hd:(h + 1) * hd] / q[0, h * hd:(h + 1) * hd].norm()
+        out = torch.zeros(1, n_head * hd, device=DEV)
+        ctx = Ctx(c["row_entry"], c["positions"])
+        ops().attention(q.to(DEV), c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, 1.0, 0)
+        assert (out.cpu() - v[far]).abs().max() < 1e-3, f"key {far} was not found"
+
+
+def test_kv_append_writes_the_right_slots():
+    o = ops()
+    for dtype in (torch.float32, torch.bfloat16):
+        n_kv_head, hd, ps = 3, 24, 16
+        kv = n_kv_head * hd
+        T = 21
+        g = gen(9)
+        src = torch.randn(T, 40 + 2 * kv, generator=g).to(dtype)
+        table = torch.tensor([[5, 2, -1], [0, 7, 3]], dtype=torch.int32)
+        row_entry = [0] * 4 + [1] * 17
+        positions = [14, 15, 16, 17] + list(range(20, 37))
+        cache = torch.zeros(8, 2, n_kv_head, ps, hd, dtype=dtype, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        o.kv_append(src.to(DEV), 40, 40 + kv, cache, table.to(DEV),
+                    torch.tensor(row_entry, dtype=torch.int32, device=DEV),
+                    torch.tensor(positions, dtype=torch.int32, device=DEV), T, status)
+        want = torch.zeros(8, 2, n_kv_head, ps, hd, dtype=dtype)
+        for t in range(T):
+            page = int(table[row_entry[t], positions[t] // ps])
+            want[page, 0, :, positions[t] % ps] = src[t, 40:40 + kv].view(n_kv_head, hd)
+            want[page, 1, :, positions[t] % ps] = src[t, 40 + kv:].view(n_kv_head, hd)
+        assert torch.equal(cache.cpu(), want) and int(status.item()) == 0
+        # a page index outside the pool is reported, not followed
+        bad = table.clone(); bad[1, 1] = 99
+        o.kv_append(src.to(DEV), 40, 40 + kv, cache, bad.to(DEV),
+                    torch.tensor(row_entry, dtype=torch.int32, device=DEV),
+                    torch.tensor(positions, dtype=torch.int32, device=DEV), T, status)
+        assert int(status.item()) == o.STATUS_BAD_PAGE
+
+
+def test_argmax_ties_and_odd_vocabulary():
+    V = 50257
+    lg = torch.randn(5, V, generator=gen(5))
+    lg[1, 40000] = lg[1, 123] = 9.0
+    lg[2, V - 1] = 11.0
+    lg[3, :] = 0.25
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    padded = torch.zeros(5, V + 15, device=DEV)
+    padded[:, :V] = lg.to(DEV)
+    ops().argmax(padded[:, :V], out, 5)
+    assert out.tolist() == [P.argmax(lg[i]) for i in range(5)] and out.tolist()[1:4] == [123, V - 1, 0]
+
+
+@pytest.mark.parametrize("V", [1000, 50257])
+def test_sampling_follows_the_reference_walk(V):
+    o = ops()
+    lg = torch.randn(6, V, generator=gen(6)) * 2.5
+    lg[4, :] = lg[4, 0]                                             # all equal: every walk is a tie
+    temps = [0.8, 1.0, 0.0, 1.3, 1.0, 0.6]
+    topk = [40, 0, 5, 7, 3, V + 5]
+    seeds = [42, 7, 1, 99, 5, 2 ** 40 + 3]
+    slots = torch.tensor([3, 0, 5, 1, 2, 4], dtype=torch.int32, device=DEV)
+    t_dev = torch.zeros(6, device=DEV); k_dev = torch.zeros(6, dtype=torch.int32, device=DEV)
+    rng = torch.zeros(6, dtype=torch.int64, device=DEV)
+    for r, sl in enumerate(slots.tolist()):
+        t_dev[sl], k_dev[sl], rng[sl] = temps[r], topk[r], seeds[r]
+    plain = [P.XorShiftSampler(temps[r], topk[r], seeds[r]) for r in range(6)]
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    dev = lg.to(DEV)
+    agree = total = 0
+    for _ in range(12):
+        o.sample(dev, 6, slots, t_dev, k_dev, rng, out)
+        got = out.tolist()
+        want = [plain[r].sample(lg[r]) for r in range(6)]
+        assert got[2] == want[2]                                    # greedy row
+        assert 0 <= got[4] < 3                                      # ties: the three lowest indices are kept
+        for r in (0, 1, 3, 5):
+            total += 1
+            agree += int(got[r] == want[r])
+    # the walks agree except where r falls within rounding of a boundary between two tokens
+    assert agree >= total - 1
+    for r, sl in enumerate(slots.tolist()):                         # the generator words advanced alike
+        if temps[r] > 0:
+            assert (int(rng[sl].item()) & (2 ** 64 - 1)) == plain[r].rng

@@ -1,0 +1,373 @@
+"""The parts alone and put together in ways GPT-2 does not use, without a change to the
+framework's files: a toy architecture is registered here whose layers differ from one another
+(grouped key/value heads with a window, a mixer with per-request state of its own, a feed-forward
+with routing, a position encoding inside the mixer) and whose run order names a layer twice and
+lets a run read another run's cache.  Everything is compared with a plain whole-sequence
+computation written in this file."""
+import dataclasses
+import json
+import math
+import os
+from typing import ClassVar, List, Tuple
+
+import pytest
+import torch
+
+from conftest import random_tokens
+
+pytestmark = pytest.mark.gpu
+
+
+# ----------------------------------------------------------------------------- toy parts (torch, test only)
+def register_toys():
+    from nanoinfer_b200 import parts as P
+    from nanoinfer_b200.config.base import ModelConfig, field
+    from nanoinfer_b200.models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from nanoinfer_b200.parts.base import MATRIX, VECTOR, ParamSpec, StateSpec, TensorRef
+    from nanoinfer_b200.registry import architectures, register_architecture
+
+    if "ToyMixLM" in architectures():
+        return
+
+    @P.register_mixer("toy_decay_mixer")
+    class DecayMixer(P.Mixer):
+        """s <- decay * s + (1 - decay) * (W xn_t);  x_t += s.  The state s is per request."""
+
+        def __init__(self, width, decay):
+            self.width, self.decay = width, decay
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.width, self.width), MATRIX)]
+
+        def state_spec(self):
+            return StateSpec((self.width,), torch.float32)
+
+        def forward(self, xn, x, ctx, cache, state, writes_cache=True):
+            assert cache is None and state is not None
+            u = xn[:ctx.n_rows].float() @ self.params["weight"].float().T
+            for e in range(ctx.n_entries):
+                a, b, slot = ctx.host_entry_start[e], ctx.host_entry_start[e + 1], ctx.host_entry_slot[e]
+                s = state[slot]
+                for t in range(a, b):
+                    s = self.decay * s + (1.0 - self.decay) * u[t]
+                    x[t] += s
+                state[slot] = s
+
+    @P.register_feed_forward("toy_routed_ffn")
+    class RoutedFFN(P.FeedForward):
+        """Router logits in 32-bit, the best expert per row, x += gate * relu(xn W1_e^T) W2_e^T."""
+
+        def __init__(self, width, inner, n_expert):
+            self.width, self.inner, self.n_expert = width, inner, n_expert
+
+        def param_specs(self):
+            return [ParamSpec("router", (self.n_expert, self.width), MATRIX),
+                    ParamSpec("up", (self.n_expert * self.inner, self.width), MATRIX),
+                    ParamSpec("down", (self.n_expert * self.width, self.inner), MATRIX)]
+
+        def forward(self, xn, x, ctx):
+            T = ctx.n_rows
+            h = xn[:T].float()
+            probs = torch.softmax(h @ self.params["router"].float().T, dim=-1)
+            gate, idx = probs.max(dim=-1)
+            up = self.params["up"].float().view(self.n_expert, self.inner, self.width)
+            down = self.params["down"].float().view(self.n_expert, self.width, self.inner)
+            for e in range(self.n_expert):
+                rows = (idx == e).nonzero().flatten()
+                if rows.numel():
+                    y = torch.relu(h[rows] @ up[e].T) @ down[e].T
+                    x[rows] += gate[rows, None] * y
+
+    @P.register_position("toy_phase")
+    class Phase(P.PositionEncoding):
+        """q and k are multiplied by cos(pos * w_d): a position encoding that acts inside the mixer."""
+
+        def __init__(self, head_dim, base):
+            self.head_dim, self.base = head_dim, base
+
+        def _factor(self, ctx, width, dtype):
+            d = torch.arange(width, device=ctx.positions.device) % self.head_dim
+            w = self.base ** (-d.float() / self.head_dim)
+            return torch.cos(ctx.positions[:ctx.n_rows, None].float() * w[None, :]).to(dtype)
+
+        def on_qk(self, q, k, ctx):
+            q.mul_(self._factor(ctx, q.shape[1], q.dtype))
+            if k is not None:
+                k.mul_(self._factor(ctx, k.shape[1], k.dtype))
+
+    @dataclasses.dataclass
+    class ToyConfig(ModelConfig):
+        architecture_names: ClassVar[Tuple[str, ...]] = ("ToyMixLM",)
+        vocab_size: int = field()
+        width: int = field()
+        n_positions: int = field()
+        eps: float = field()
+        window: int = field()
+        decay: float = field()
+        n_expert: int = field()
+
+        def to_dict(self):
+            return dict(architectures=["ToyMixLM"], **super().to_dict())
+
+    def build(cfg):
+        c = cfg.width
+
+        def norm(name):
+            return PartSpec("layernorm", dict(width=c, eps=cfg.eps),
+                            {"weight": TensorRef(name + ".g"), "bias": TensorRef(name + ".b")})
+
+        def attn(name, n_head, n_kv_head, hd, window, scale):
+            return PartSpec("causal_attention",
+                            dict(width=c, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd, scale=scale, window=window,
+                                 bias=False),
+                            {"qkv_weight": TensorRef(name + ".qkv"), "out_weight": TensorRef(name + ".out")})
+
+        def mlp(name, inner, act):
+            return PartSpec("dense_mlp", dict(width=c, inner=inner, activation=act, bias=True),
+                            {"fc_weight": TensorRef(name + ".fc.w"), "fc_bias": TensorRef(name + ".fc.b"),
+                             "proj_weight": TensorRef(name + ".proj.w"), "proj_bias": TensorRef(name + ".proj.b")})
+
+        layers = [
+            LayerSpec("pre_norm", norm("l0.n1"), attn("l0.att", 4, 2, 16, cfg.window, 0.3), norm("l0.n2"),
+                      mlp("l0.mlp", 96, "tanh")),
+            LayerSpec("pre_norm", norm("l1.n1"),
+                      PartSpec("toy_decay_mixer", dict(width=c, decay=cfg.decay), {"weight": TensorRef("l1.mix.w")}),
+                      norm("l1.n2"),
+                      PartSpec("toy_routed_ffn", dict(width=c, inner=40, n_expert=cfg.n_expert),
+                               {"router": TensorRef("l1.moe.router"), "up": TensorRef("l1.moe.up"),
+                                "down": TensorRef("l1.moe.down")})),
+            LayerSpec("pre_norm", norm("l2.n1"), attn("l2.att", 2, 2, 32, 0, 0.25), norm("l2.n2"),
+                      mlp("l2.mlp", 80, "erf"),
+                      mixer_position=PartSpec("toy_phase", dict(head_dim=32, base=50.0))),
+        ]
+        return ModelSpec(
+            width=c,
+            embedding=PartSpec("token_embedding", dict(vocab_size=cfg.vocab_size, width=c), {"table": TensorRef("emb")}),
+            position=None, layers=layers,
+            schedule=[ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2), ScheduleEntry(0), ScheduleEntry(2, cache_of=2)],
+            final_norm=norm("final"),
+            head=PartSpec("linear_head", dict(vocab_size=cfg.vocab_size, width=c), {"weight": TensorRef("head")}),
+            max_positions=cfg.n_positions)
+
+    register_architecture("ToyMixLM", ToyConfig, build)
+
+
+TOY = dict(architectures=["ToyMixLM"], vocab_size=200, width=64, n_positions=96, eps=1e-5, window=20, decay=0.7,
+           n_expert=3)
+
+
+# ----------------------------------------------------------------------------- the plain toy model
+def plain_toy_logits(folder, tokens):
+    import plain_gpt2 as P
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    cfg = json.load(open(os.path.join(folder, "config.json")))
+    n = len(tokens)
+    pos = torch.arange(n, dtype=torch.float64)
+    x = w["emb"][torch.tensor(tokens)]
+
+    def ln(name, x):
+        return P.layernorm(x, w[name + ".g"], w[name + ".b"], cfg["eps"])
+
+    def phase(t, hd, base):
+        d = torch.arange(t.shape[1]) % hd
+        return t * torch.cos(pos[:, None] * (base ** (-d.double() / hd))[None, :])
+
+    def att(name, x, n_head, n_kv_head, hd, window, scale, kv=None, rotate=False):
+        qkv = x @ w[name + ".qkv"].T
+        q, k, v = qkv[:, :n_head * hd], qkv[:, n_head * hd:(n_head + n_kv_head) * hd], qkv[:, (n_head + n_kv_head) * hd:]
+        if rotate:
+            q, k = phase(q, hd, 50.0), phase(k, hd, 50.0)
+        if kv is not None:
+            k, v = kv
+        o = P.causal_attention(q, k, v, n_head, n_kv_head, scale=scale, window=window)
+        return o @ w[name + ".out"].T, (k, v)
+
+    def mlp(name, x, act):
+        return act(x @ w[name + ".fc.w"].T + w[name + ".fc.b"]) @ w[name + ".proj.w"].T + w[name + ".proj.b"]
+
+    def layer0(x):
+        x = x + att("l0.att", ln("l0.n1", x), 4, 2, 16, cfg["window"], 0.3)[0]
+        return x + mlp("l0.mlp", ln("l0.n2", x), P.gelu_tanh)
+
+    def layer1(x):
+        u = ln("l1.n1", x) @ w["l1.mix.w"].T
+        s = torch.zeros(x.shape[1], dtype=torch.float64)
+        out = []
+        for t in range(n):
+            s = cfg["decay"] * s + (1 - cfg["decay"]) * u[t]
+            out.append(s)
+        x = x + torch.stack(out)
+        h = ln("l1.n2", x)
+        probs = torch.softmax(h @ w["l1.moe.router"].T, dim=-1)
+        gate, idx = probs.max(-1)
+        up, down = w["l1.moe.up"].view(3, 40, -1), w["l1.moe.down"].view(3, -1, 40)
+        y = torch.stack([torch.relu(h[t] @ up[idx[t]].T) @ down[idx[t]].T for t in range(n)])
+        return x + gate[:, None] * y
+
+    def layer2(x, kv=None):
+        a, kv_out = att("l2.att", ln("l2.n1", x), 2, 2, 32, 0, 0.25, kv=kv, rotate=True)
+        x = x + a
+        return x + mlp("l2.mlp", ln("l2.n2", x), P.gelu_erf), kv_out
+
+    x = layer0(x)
+    x = layer1(x)
+    x, kv2 = layer2(x)
+    x = layer0(x)                 # the same weights a second time, with keys and values of its own
+    x, _ = layer2(x, kv=kv2)      # reads the keys and values of the first run of layer 2
+    return (ln("final", x) @ w["head"].T).float()
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    register_toys()
+    from nanoinfer_b200.registry import get_architecture
+    from nanoinfer_b200.weights import write_random_model
+    cfg = get_architecture("ToyMixLM").config_cls.from_dict(TOY)
+    d = str(tmp_path_factory.mktemp("toy"))
+    write_random_model(cfg, d, seed=21, dtype=torch.float32, std=0.08)
+    return d
+
+
+def test_toy_architecture_is_registered_built_and_stepped(toy_folder):
+    """A mixer with state of its own, a routed feed-forward and an in-mixer position encoding are
+    registered from this file; the model is built from config.json, cut into steps every way, and
+    agrees with the plain computation."""
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    m = load_model(toy_folder, torch.float32, "cuda")
+    kinds = [type(l.mixer).__name__ for l in m.layers]
+    assert kinds == ["CausalSelfAttention", "DecayMixer", "CausalSelfAttention"]
+    assert [i for i, _ in m.kv_needs()] == [0, 2, 3] and [i for i, _ in m.state_needs()] == [1]
+    cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=256, max_requests=3, page_size=16,
+                         dtype=torch.float32, device=torch.device("cuda"), max_positions=m.max_positions)
+    # the windowed runs (0 and 3) share one group, the run that keeps all keys has another
+    assert sorted(g.owners for g in cache.groups) == [[0, 3], [2]]
+    runner = ModelRunner(m, cache, max_rows=96, max_entries=3)
+    seqs = [random_tokens(200, n, 300 + i) for i, n in enumerate([96, 61, 40])]
+    want = [plain_toy_logits(toy_folder, s) for s in seqs]
+
+    # whole
+    for s, w in zip(seqs, want):
+        r = cache.open_request()
+        got = runner.step([StepItem(r, s, range(len(s)))]).cpu()
+        assert (got - w).abs().max() < 2e-4
+        cache.close_request(r)
+    # portions of changing size, three requests side by side, state carried from step to step
+    reqs = [cache.open_request() for _ in seqs]
+    prog = [0, 0, 0]
+    got = [[] for _ in seqs]
+    sizes = [[7, 1, 2, 30, 1], [2, 2, 19, 1], [1, 1, 1, 5]]
+    k = 0
+    while any(p < len(s) for p, s in zip(prog, seqs)):
+        items, idx = [], []
+        for i, s in enumerate(seqs):
+            if prog[i] < len(s) and (k + i) % 4 != 3:
+                n = min(sizes[i][k % len(sizes[i])], len(s) - prog[i])
+                items.append(StepItem(reqs[i], s[prog[i]:prog[i] + n], range(n)))
+                idx.append((i, n))
+                prog[i] += n
+        k += 1
+        if not items:
+            continue
+        lg = runner.step(items).cpu()
+        o = 0
+        for i, n in idx:
+            got[i].append(lg[o:o + n].clone())
+            o += n
+    for g, w in zip(got, want):
+        assert (torch.cat(g) - w).abs().max() < 2e-4
+    # the windowed group gave pages back while the other kept all of them
+    win = next(i for i, g in enumerate(cache.groups) if g.spec.window)
+    assert reqs[0].blocks[win][0] == -1 and all(p >= 0 for p in reqs[0].blocks[1 - win])
+    for r in reqs:
+        cache.close_request(r)
+    cache.check()
+    assert cache.pages_used() == [0, 0]
+
+
+def test_state_slot_is_zeroed_for_a_new_request(toy_folder):
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    m = load_model(toy_folder, torch.float32, "cuda")
+    cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=128, max_requests=1, page_size=16,
+                         dtype=torch.float32, device=torch.device("cuda"), max_positions=m.max_positions)
+    runner = ModelRunner(m, cache, max_rows=64, max_entries=1)
+    s = random_tokens(200, 20, 9)
+    r = cache.open_request()
+    first = runner.step([StepItem(r, s, [19])]).cpu().clone()
+    cache.close_request(r)
+    r = cache.open_request()                      # the same slot again
+    again = runner.step([StepItem(r, s, [19])]).cpu()
+    assert torch.equal(first, again)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_norm_embedding_mlp_and_head_parts_alone(dtype):
+    """Each built-in part alone, built through its registry with sizes of its own."""
+    import plain_gpt2 as P
+    from nanoinfer_b200 import parts as NP
+    from nanoinfer_b200.parts.base import StepContext, Workspace
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(4)
+    T, C, I, V = 23, 72, 136, 333
+    tol = 3e-5 if dtype == torch.float32 else 4e-2
+
+    def bind(part, **tensors):
+        part.bind({k: v.to(dev) for k, v in tensors.items()})
+        part.prepare(dtype, dev)
+        return part
+
+    tokens = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    positions = torch.arange(5, 5 + T, dtype=torch.int32)
+    ctx = StepContext(n_rows=T, n_entries=1, max_rows=T, tokens=tokens.to(dev), positions=positions.to(dev),
+                      row_entry=torch.zeros(T, dtype=torch.int32, device=dev),
+                      entry_start=torch.tensor([0, T], dtype=torch.int32, device=dev),
+                      entry_pos0=torch.tensor([5], dtype=torch.int32, device=dev),
+                      entry_slot=torch.zeros(1, dtype=torch.int32, device=dev),
+                      status=torch.zeros(1, dtype=torch.int32, device=dev), workspace=Workspace(dev),
+                      host_entry_start=[0, T], host_entry_pos0=[5], host_entry_slot=[0], max_q_len=T, max_kv_len=5 + T)
+    wte, wpe = torch.randn(V, C, generator=g).to(dtype), torch.randn(64, C, generator=g).to(dtype)
+    emb = bind(NP.EMBEDDINGS.build("token_embedding", vocab_size=V, width=C), table=wte)
+    pos = bind(NP.POSITIONS.build("learned_absolute", n_positions=64, width=C), table=wpe)
+    x = torch.zeros(T, C, device=dev)
+    emb.forward(ctx, x, pos)
+    want_x = P.embed(wte.double(), wpe.double(), tokens.tolist(), 5)
+    assert (x.cpu().double() - want_x).abs().max() < 1e-6
+
+    gamma, beta = 1 + 0.1 * torch.randn(C, generator=g), 0.1 * torch.randn(C, generator=g)
+    norm = bind(NP.NORMS.build("layernorm", width=C, eps=3e-4), weight=gamma, bias=beta)
+    xn = torch.zeros(T, C, dtype=dtype, device=dev)
+    norm.forward(x, xn, T)
+    want_n = P.layernorm(x.cpu().double(), gamma.double(), beta.double(), 3e-4)
+    assert (xn.cpu().double() - want_n).abs().max() < tol
+
+    for act, fn in (("tanh", P.gelu_tanh), ("erf", P.gelu_erf)):
+        w1, b1 = (torch.randn(I, C, generator=g) * 0.1).to(dtype), torch.randn(I, generator=g) * 0.1
+        w2, b2 = (torch.randn(C, I, generator=g) * 0.1).to(dtype), torch.randn(C, generator=g) * 0.1
+        mlp = bind(NP.FEED_FORWARDS.build("dense_mlp", width=C, inner=I, activation=act),
+                   fc_weight=w1, fc_bias=b1, proj_weight=w2, proj_bias=b2)
+        x2 = x.clone()
+        mlp.forward(xn, x2, ctx)
+        h = xn.cpu().double()
+        want = x.cpu().double() + fn(h @ w1.double().T + b1.double()) @ w2.double().T + b2.double()
+        assert (x2.cpu().double() - want).abs().max() < tol
+
+    head = bind(NP.HEADS.build("linear_head", vocab_size=V, width=C), weight=wte)
+    logits = torch.zeros(T, V + 3, device=dev)[:, :V]
+    head.forward(xn, logits, T, ctx)
+    assert (logits.cpu().double() - xn.cpu().double() @ wte.double().T).abs().max() < tol * 4
+
+
+def test_unsupported_sizes_are_refused_with_a_clear_error():
+    from nanoinfer_b200 import parts as NP
+    with pytest.raises(ValueError, match="head_dim"):
+        NP.MIXERS.build("causal_attention", width=60, n_head=5, n_kv_head=5, head_dim=12, scale=1.0)
+    with pytest.raises(ValueError, match="multiple"):
+        NP.MIXERS.build("causal_attention", width=64, n_head=4, n_kv_head=3, head_dim=16, scale=1.0)
+    with pytest.raises(ValueError, match="activation"):
+        NP.FEED_FORWARDS.build("dense_mlp", width=8, inner=8, activation="relu")
+    with pytest.raises(KeyError, match="unknown mixer"):
+        NP.MIXERS.build("no_such_mixer")

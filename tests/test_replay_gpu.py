@@ -1,0 +1,124 @@
+"""Trace replay on the GPU: the same requests replayed whole, with the last 32 tokens one by one,
+in portions of changing size, and mixed with other requests so that pages are used again, in
+32-bit and in bfloat16; every logits row is compared with the plain implementation."""
+import pytest
+import torch
+
+from conftest import TINY, random_tokens
+from trace_util import TraceSession, max_diff
+
+pytestmark = pytest.mark.gpu
+
+# Tolerances on logits of magnitude ~1 (attention sharpened, see conftest.sharpen_attention).
+# 32-bit: the bound the engine is built to.  bfloat16: weights, activations and cache are rounded
+# to 8 bits of mantissa; measured differences on these models stay below 0.04.
+TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+TORCH_DTYPE = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+LENGTHS = {"A": [97, 128, 70, 45, 33, 18], "B": [64, 50, 37, 22, 60, 9]}
+
+
+def round64(n):
+    return -(-n // 64) * 64
+
+
+def requests_of(name):
+    vocab = TINY[name]["vocab_size"]
+    return {f"r{i}": random_tokens(vocab, n, 100 + i) for i, n in enumerate(LENGTHS[name])}
+
+
+def check(session, reqs, model_dir, plain_logits, tol, ids=None):
+    worst = 0.0
+    for rid in (ids or reqs):
+        toks = reqs[rid]
+        got = session.stacked(rid, len(toks))
+        d = max_diff(got, plain_logits(model_dir, toks))
+        worst = max(worst, d)
+        assert d <= tol, f"request {rid} ({len(toks)} tokens): max |logit difference| {d:.3e} > {tol}"
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_alone_whole_tail_and_portions(name, dtype, model_dirs, plain_logits, tmp_path):
+    model_dir = model_dirs(name, TORCH_DTYPE[dtype])
+    vocab = TINY[name]["vocab_size"]
+    reqs = requests_of(name)
+    longest = max(len(t) for t in reqs.values())
+
+    # (1) each request alone and whole, logits at every position
+    s = TraceSession(model_dir, dtype, tmp_path / "whole", round64(longest), vocab)
+    for rid, toks in reqs.items():
+        s.step([(rid, toks, range(len(toks)))], end=[rid])
+    s.close()
+    check(s, reqs, model_dir, plain_logits, TOL[dtype])
+
+    # (2) most of it in one step, the last 32 tokens one by one
+    s = TraceSession(model_dir, dtype, tmp_path / "tail", round64(longest), vocab)
+    for rid, toks in reqs.items():
+        head = max(len(toks) - 32, 1)
+        s.step([(rid, toks[:head], range(head))])
+        for p in range(head, len(toks)):
+            s.step([(rid, toks[p:p + 1], [0])], end=[rid] if p == len(toks) - 1 else [])
+        if head == len(toks):
+            s.step([], end=[rid])
+    s.close()
+    check(s, reqs, model_dir, plain_logits, TOL[dtype])
+
+    # (3) portions of changing size, down to two tokens and one
+    sizes = [5, 2, 16, 3, 1, 17, 2, 31, 4, 1, 2, 9]
+    s = TraceSession(model_dir, dtype, tmp_path / "portions", round64(longest), vocab)
+    for rid, toks in reqs.items():
+        p, k = 0, 0
+        while p < len(toks):
+            n = min(sizes[k % len(sizes)], len(toks) - p)
+            s.step([(rid, toks[p:p + n], range(n))], end=[rid] if p + n == len(toks) else [])
+            p, k = p + n, k + 1
+    s.close()
+    check(s, reqs, model_dir, plain_logits, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_mixed_requests_with_few_pages(name, dtype, model_dirs, plain_logits, tmp_path):
+    """Up to four live requests, portions of some beside single tokens of others, some left out of
+    a step; the pool holds just what the live ones need, so ended requests' pages are used again."""
+    model_dir = model_dirs(name, TORCH_DTYPE[dtype])
+    vocab = TINY[name]["vocab_size"]
+    reqs = requests_of(name)
+    order = list(reqs)
+    # plan: each request has a cut list; a "wave" runs four at a time, the next starts when one ends
+    cuts = {"r0": [30, 1, 1, 7], "r1": [2, 40, 1, 1, 1], "r2": [1, 1, 20, 3], "r3": [17, 2, 1], "r4": [8, 1, 1, 5],
+            "r5": [3, 1, 2]}
+    live, waiting, done_pos = [], list(order), {}
+    peak = 0
+    steps = []
+    progress = {r: 0 for r in order}
+    cut_idx = {r: 0 for r in order}
+    tick = 0
+    while live or waiting:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        entries, ended = [], []
+        for j, rid in enumerate(list(live)):
+            if (tick + j) % 5 == 4 and len(live) > 1:
+                continue                                  # left out of this step, goes on later
+            toks = reqs[rid]
+            c = cuts[rid]
+            n = min(c[cut_idx[rid] % len(c)], len(toks) - progress[rid])
+            entries.append((rid, toks[progress[rid]:progress[rid] + n], range(n)))
+            progress[rid] += n
+            cut_idx[rid] += 1
+            if progress[rid] == len(toks):
+                ended.append(rid)
+                live.remove(rid)
+        peak = max(peak, sum(round64(progress[r]) for r in set(live) | set(ended)))
+        steps.append((entries, ended))
+        tick += 1
+    s = TraceSession(model_dir, dtype, tmp_path / "mixed", peak, vocab)
+    for entries, ended in steps:
+        s.step(entries, end=ended)
+    s.close()
+    assert any(len(e) >= 3 and min(len(t) for _, t, _ in e) == 1 and max(len(t) for _, t, _ in e) > 1
+               for e, _ in steps), "the plan must mix portions with single tokens"
+    check(s, reqs, model_dir, plain_logits, TOL[dtype])

@@ -1,0 +1,153 @@
+"""The scheduler's decisions (no GPU): admission, portions under the token budget, decoding,
+finishing and freeing, and what happens when pages run out."""
+import random
+
+from nanoinfer_b200.cache import CacheManager
+from nanoinfer_b200.engine.scheduler import FINISHED, RUNNING, WAITING, Scheduler
+from nanoinfer_b200.parts.base import KVCacheSpec
+from nanoinfer_b200.sampling import SamplingParams
+
+SPEC = KVCacheSpec(2, 16)
+
+
+def setup(max_tokens, max_batch=4, max_rows=64, budget=32, max_positions=128, **kw):
+    cache = CacheManager([(0, SPEC), (1, SPEC)], [], max_tokens=max_tokens, max_requests=max_batch, page_size=16,
+                         device=None, max_positions=max_positions)
+    return cache, Scheduler(cache, max_batch=max_batch, max_rows=max_rows, prefill_budget=budget,
+                            max_positions=max_positions, **kw)
+
+
+def run_step(cache, s, token=7):
+    """What the engine does around a step, without a model."""
+    items = s.schedule()
+    if items:
+        cache.append([(i.request.cache, i.n_tokens) for i in items])    # must never fail
+        for i in items:
+            cache.commit(i.request.cache, i.n_tokens)
+    ended = s.on_step_done(items, [token] * sum(1 for i in items if i.samples))
+    cache.check()
+    return items, ended + s.ended_without_step
+
+
+def test_prompt_is_cut_under_the_budget_then_decoded():
+    cache, s = setup(max_tokens=256, budget=32)
+    r = s.add(list(range(70)), SamplingParams(max_new_tokens=3))
+    sizes = []
+    while s.has_work():
+        items, _ = run_step(cache, s)
+        sizes.append([(i.n_tokens, i.samples) for i in items])
+    # 70 tokens as 32 + 32 + 6; only the last portion yields a token; then two single-token steps
+    assert sizes == [[(32, False)], [(32, False)], [(6, True)], [(1, True)], [(1, True)]]
+    assert r.output == [7, 7, 7] and r.finish_reason == "length" and r.state == FINISHED
+    assert cache.pages_used() == [0] and cache.slots.n_free == 4
+
+
+def test_decode_rows_first_and_prompts_share_the_rest():
+    cache, s = setup(max_tokens=512, budget=40, max_rows=42)
+    a = s.add([1] * 5, SamplingParams(max_new_tokens=10))
+    run_step(cache, s)                                             # a is prefilled
+    b = s.add([2] * 30, SamplingParams(max_new_tokens=2))
+    c = s.add([3] * 30, SamplingParams(max_new_tokens=2))
+    items, _ = run_step(cache, s)
+    got = [(i.request.id, i.n_tokens) for i in items]
+    assert got == [(a.id, 1), (b.id, 30), (c.id, 10)]              # one decode row, then 40 prompt tokens
+    items, _ = run_step(cache, s)
+    assert [(i.request.id, i.n_tokens, i.samples) for i in items] == [(a.id, 1, True), (b.id, 1, True), (c.id, 20, True)]
+
+
+def test_row_limit_bounds_the_budget():
+    cache, s = setup(max_tokens=1024, max_batch=4, max_rows=10, budget=100)
+    a = s.add([1] * 3, SamplingParams(max_new_tokens=50))
+    b = s.add([1] * 3, SamplingParams(max_new_tokens=50))
+    run_step(cache, s)
+    s.add([2] * 40, SamplingParams(max_new_tokens=1))
+    items, _ = run_step(cache, s)
+    assert sum(i.n_tokens for i in items) == 10 and [i.n_tokens for i in items] == [1, 1, 8]
+
+
+def test_admission_is_first_come_first_served_with_headroom():
+    cache, s = setup(max_tokens=96, max_batch=4)                   # 6 pages
+    a = s.add([1] * 40, SamplingParams(max_new_tokens=4))          # pages(41) = 3
+    b = s.add([1] * 40, SamplingParams(max_new_tokens=4))          # needs 3 + 1 headroom: 3 free after a -> waits
+    c = s.add([1] * 2, SamplingParams(max_new_tokens=4))           # would fit, but may not overtake b
+    run_step(cache, s)
+    assert a.state == RUNNING and b.state == WAITING and c.state == WAITING
+    while a.state != FINISHED:
+        run_step(cache, s)
+    run_step(cache, s)
+    assert b.state == RUNNING and c.state == RUNNING and b.admitted_order < c.admitted_order
+
+
+def test_eos_and_context_full_end_a_request():
+    cache, s = setup(max_tokens=512, max_positions=20)
+    a = s.add([1] * 4, SamplingParams(max_new_tokens=50, eos_token_id=9))
+    b = s.add([1] * 15, SamplingParams(max_new_tokens=50))
+    run_step(cache, s, token=5)
+    items, ended = run_step(cache, s, token=9)
+    assert a in ended and a.finish_reason == "eos" and a.output == [5, 9]
+    while b.state != FINISHED:
+        run_step(cache, s, token=5)
+    assert b.finish_reason == "context_full" and len(b.prompt) + len(b.output) == 21
+    assert cache.pages_used() == [0]
+
+
+def test_when_pages_run_out_the_newest_request_is_preempted_and_recomputed():
+    cache, s = setup(max_tokens=64, max_batch=3, headroom_pages=0)          # 4 pages
+    a = s.add([1] * 14, SamplingParams(max_new_tokens=40))
+    b = s.add([2] * 14, SamplingParams(max_new_tokens=40))
+    c = s.add([3] * 14, SamplingParams(max_new_tokens=40))
+    run_step(cache, s)                                                      # a, b, c hold a page each; one spare
+    assert [r.state for r in (a, b, c)] == [RUNNING] * 3
+    preempted_seen = False
+    for _ in range(400):
+        if not s.has_work():
+            break
+        items, _ = run_step(cache, s)
+        assert items, "a step must always make progress"
+        if c.n_preemptions and not preempted_seen:
+            preempted_seen = True
+            assert c.state == WAITING and c.cache is None and c.n_computed == 0 and s.waiting[0] is c
+            kept = len(c.output)
+    assert preempted_seen and s.stats.preemptions >= 1
+    assert a.n_preemptions == 0                                             # the oldest never loses its pages
+    for r in (a, b, c):
+        assert r.finish_reason == "length" and len(r.output) == 40         # nothing is lost by recomputing
+    assert kept >= 1 and cache.pages_used() == [0] and cache.slots.n_free == 3
+
+
+def test_a_request_that_can_never_fit_ends_with_too_long():
+    cache, s = setup(max_tokens=32, max_batch=2)                            # 2 pages
+    a = s.add([1] * 40, SamplingParams(max_new_tokens=4))                   # pages(41) = 3 > 2
+    b = s.add([1] * 20, SamplingParams(max_new_tokens=30))                  # fits, then outgrows the pool alone
+    items, ended = run_step(cache, s)
+    assert a in ended and a.finish_reason == "too_long" and a.output == []
+    while s.has_work():
+        run_step(cache, s)
+    assert b.finish_reason == "too_long" and len(b.prompt) + len(b.output) - 1 <= 32
+    assert cache.pages_used() == [0]
+
+
+def test_portions_shrink_to_the_pages_that_are_left():
+    cache, s = setup(max_tokens=64, max_batch=2, budget=64, headroom_pages=0)   # 4 pages
+    a = s.add([1] * 30, SamplingParams(max_new_tokens=20))
+    run_step(cache, s)                                                          # a holds 2 pages
+    b = s.add([2] * 30, SamplingParams(max_new_tokens=1))                       # admitted: pages(31) = 2 free
+    items, _ = run_step(cache, s)
+    # a's decode row crosses no page edge (token 31 of page 2); b gets the two free pages
+    assert [(i.request.id, i.n_tokens) for i in items] == [(a.id, 1), (b.id, 30)]
+
+
+def test_random_traffic_always_finishes_everything():
+    for seed in range(5):
+        rng = random.Random(seed)
+        cache, s = setup(max_tokens=rng.choice([112, 160, 256]), max_batch=rng.choice([2, 4]),
+                         budget=rng.choice([8, 32, 64]), max_rows=64)
+        reqs = [s.add([1] * rng.randint(1, 60), SamplingParams(max_new_tokens=rng.randint(1, 40))) for _ in range(15)]
+        for _ in range(3000):
+            if not s.has_work():
+                break
+            run_step(cache, s)
+        assert not s.has_work()
+        for r in reqs:
+            assert r.state == FINISHED and r.finish_reason == "length" and len(r.output) == r.params.max_new_tokens
+        assert cache.pages_used() == [0]
