@@ -78,14 +78,14 @@ def test_step_refuses_bad_input_and_changes_nothing(model_dirs):
     m = load_model(d, torch.float32, "cuda")
     cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=64, max_requests=3, page_size=16,
                          dtype=torch.float32, device=torch.device("cuda"), max_positions=m.max_positions)
-    runner = ModelRunner(m, cache, max_rows=48, max_entries=3)
+    runner = ModelRunner(m, cache, max_rows=80, max_entries=3)
     a, b = cache.open_request(), cache.open_request()
     runner.step([StepItem(a, [1, 2, 3], [2])])
     state = (a.n_tokens, list(a.blocks[0]), cache.pages_free())
     for items, err in [
         ([StepItem(a, [512], [0])], BadToken), ([StepItem(a, [], [])], StepError),
         ([StepItem(a, [1], [1])], StepError), ([StepItem(a, [1], []), StepItem(a, [2], [])], StepError),
-        ([StepItem(a, [1] * 49, [])], TooManyRows), ([StepItem(a, [1] * 30, []), StepItem(b, [1] * 40, [])], PoolExhausted),
+        ([StepItem(a, [1] * 81, [])], TooManyRows), ([StepItem(a, [1] * 30, []), StepItem(b, [1] * 40, [])], PoolExhausted),
     ]:
         with pytest.raises(err):
             runner.step(items)
