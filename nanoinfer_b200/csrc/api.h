@@ -35,6 +35,13 @@ int nib_linear_simt(int in_dtype, int out_dtype, const void* a, int lda, const v
                     const float* bias, void* out, int ldo, int M, int N, int K, int act,
                     int residual, cudaStream_t stream);
 
+// The same product for bfloat16 inputs on the tensor cores (tcgen05 + TMA); out is bfloat16 or
+// float32.  nib_linear_tc_supported says whether the shape and alignment are taken.
+int nib_linear_tc_supported(const void* a, int lda, const void* w, int ldw, int K);
+int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                  void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
+                  cudaStream_t stream);
+
 // Causal attention of T query rows over the paged cache (general SIMT kernel).
 int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
                        const int* block_table, int max_blocks, const int* row_entry,

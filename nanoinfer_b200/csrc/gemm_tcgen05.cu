@@ -1,0 +1,397 @@
+// out = act(a . w^T + bias) in bfloat16 on the 5th-generation tensor cores (sm_100a):
+// TMA loads into 128-byte-swizzled shared memory, tcgen05.mma with the accumulator in tensor
+// memory, tcgen05.ld back to registers for a fused epilogue (bias, GELU, residual add).
+//
+// Both operands are K-major ([rows, K], K contiguous): activations a [M, K] and weights w [N, K],
+// the "out, in" layout the reference transposes to at load (crates/core/src/weights.rs:1-9), so
+// out = a . w^T is the reference's matmul (crates/core/src/kernels/reference.rs:26-37).  The tile
+// that feeds the MMA's M side ("P", 128 rows) and the one that feeds its N side ("Q", 16..256
+// rows) are interchangeable:
+//   * many rows (prefill): P = activations, Q = weights;
+//   * few rows (decode):   P = weights, Q = activations ("swap-AB"), so a step of 1..128 tokens
+//     still fills the 128-row MMA and every weight byte is read exactly once.
+//
+// One CTA computes one P x Q tile: warp 0 issues the TMA loads, warp 1 allocates tensor memory
+// and issues the MMAs, warps 2..5 run the epilogue (each owns the 32 TMEM lanes of its quarter).
+// Every wait on an mbarrier is bounded: if it runs out, the kernel records
+// NIB_STATUS_WAIT_TIMEOUT, stops issuing work, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace nib {
+
+constexpr int TC_BP = 128;        // rows of the P tile = MMA M
+constexpr int TC_BK = 64;         // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int TC_MAX_STAGES = 8;
+constexpr int TC_THREADS = 192;
+constexpr long long TC_WAIT_CYCLES = 4000000000ll;  // about two seconds
+
+struct TcParams {
+  int p_rows, q_rows, K;
+  int bq;            // rows of the Q tile = MMA N (multiple of 16)
+  int stages;
+  int swap;          // 0: P = activations (out[p, q]); 1: P = weights (out[q, p])
+  void* out;
+  int ldo;
+  int out_f32;
+  const float* bias;
+  int act;
+  int residual;
+  int vec_ok;        // out is 16-byte aligned and its row pitch keeps rows so: vector stores allowed
+  int* status;
+};
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the barrier did not flip in time or another role gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (*abort_flag) return false;
+    if (clock64() - t0 > TC_WAIT_CYCLES) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(cols));
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                          uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+  uint32_t r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile [rows][64 bf16] in the 128-byte swizzle:
+// start address >> 4, leading byte offset 1 (unused with a swizzle), stride byte offset 1024 >> 4
+// (eight 128-byte rows), descriptor version 1, layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  return (uint64_t)((smem_addr >> 4) & 0x3fffu) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+// Instruction descriptor for kind::f16: D = f32 (bits 4-5 = 1), A = B = bf16 (bits 7-9, 10-12 = 1),
+// both K-major (bits 15, 16 = 0), N >> 3 at bits 17-22, M >> 4 at bits 24-28.
+__device__ __forceinline__ uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ------------------------------------------------------------------ the kernel
+__global__ void __launch_bounds__(TC_THREADS, 1)
+linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                 const TcParams prm) {
+  extern __shared__ uint8_t smem_raw[];
+  // tiles must start on a 1024-byte boundary for the 128-byte swizzle
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ uint64_t full_bar[TC_MAX_STAGES];
+  __shared__ uint64_t empty_bar[TC_MAX_STAGES];
+  __shared__ uint64_t tmem_full_bar;
+  __shared__ uint32_t tmem_base_sh;
+  __shared__ int abort_sh;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int stages = prm.stages, bq = prm.bq;
+  const uint32_t p_bytes = TC_BP * TC_BK * 2, q_bytes = (uint32_t)bq * TC_BK * 2;
+  const uint32_t stage_bytes = p_bytes + q_bytes;  // both multiples of 1024 (bq is a multiple of 16: 2 KB)
+  const int p0 = blockIdx.x * TC_BP, q0 = blockIdx.y * bq;
+  const int num_kb = (prm.K + TC_BK - 1) / TC_BK;
+  uint32_t tmem_cols = 32;
+  while ((int)tmem_cols < bq) tmem_cols <<= 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tmem_full_bar, 1);
+    abort_sh = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(&tmem_base_sh, tmem_cols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_base_sh;
+  volatile int* abort_flag = &abort_sh;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (one lane)
+    if (lane == 0) {
+      int issued = 0;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        const int s = kb % stages;
+        const uint32_t parity = ((kb / stages) & 1) ^ 1;  // a fresh barrier passes the first round
+        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) break;
+        uint8_t* sp = smem + (size_t)s * stage_bytes;
+        mbar_expect_tx(&full_bar[s], stage_bytes);
+        tma_load_2d(sp, &map_p, &full_bar[s], kb * TC_BK, p0);
+        tma_load_2d(sp + p_bytes, &map_q, &full_bar[s], kb * TC_BK, q0);
+        ++issued;
+      }
+      if (*abort_flag) {
+        // let the copies that are still in flight land before the block's shared memory goes away
+        const int first = issued > stages ? issued - stages : 0;
+        for (int kb = first; kb < issued; ++kb) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full_bar[kb % stages], (kb / stages) & 1) && clock64() - t0 < 200000000ll) {
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (one lane)
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(TC_BP, bq);
+      bool ok = true;
+      for (int kb = 0; kb < num_kb && ok; ++kb) {
+        const int s = kb % stages;
+        ok = mbar_wait(&full_bar[s], (kb / stages) & 1, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t pa = smem_u32(smem + (size_t)s * stage_bytes);
+        const uint32_t qa = pa + p_bytes;
+#pragma unroll
+        for (int k = 0; k < TC_BK / 16; ++k) {
+          // 16 bf16 = 32 bytes further along K inside the swizzled row
+          umma_bf16(tmem_base, umma_desc(pa + k * 32), umma_desc(qa + k * 32), idesc, (kb | k) != 0);
+        }
+        umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
+      }
+      umma_commit(&tmem_full_bar);   // arrives when every MMA above has finished
+    }
+  } else {
+    // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +32
+    const int quarter = warp & 3;
+    const int p = p0 + quarter * 32 + lane;  // this thread's row of the P tile
+    const bool ok = mbar_wait(&tmem_full_bar, 0, abort_flag);
+    tc_fence_after();
+    if (ok) {
+      const bool p_ok = p < prm.p_rows;
+      for (int c0 = 0; c0 < bq; c0 += 16) {
+        if (q0 + c0 >= prm.q_rows) break;  // uniform over the warp
+        float v[16];
+        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        if (!p_ok) continue;
+        if (!prm.swap) {
+          // out[p, q0 + c0 + j]: this thread writes 16 consecutive features of its own row
+          const int n0 = q0 + c0;
+          const int nv = min(16, prm.q_rows - n0);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (j < nv) {
+              float x = v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f);
+              v[j] = apply_act(x, prm.act);
+            }
+          }
+          if (prm.out_f32) {
+            float* o = (float*)prm.out + (size_t)p * prm.ldo + n0;
+            if (nv == 16 && prm.vec_ok) {
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (prm.residual) {
+                  const float4 old = *reinterpret_cast<const float4*>(o + j);
+                  r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
+                }
+                *reinterpret_cast<float4*>(o + j) = r;
+              }
+            } else {
+              for (int j = 0; j < nv; ++j) o[j] = prm.residual ? o[j] + v[j] : v[j];
+            }
+          } else {
+            bf16* o = (bf16*)prm.out + (size_t)p * prm.ldo + n0;
+            if (nv == 16 && prm.vec_ok) {
+              uint4 a = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
+                                   pack_bf16(v[6], v[7]));
+              uint4 b = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]),
+                                   pack_bf16(v[14], v[15]));
+              *reinterpret_cast<uint4*>(o) = a;
+              *reinterpret_cast<uint4*>(o + 8) = b;
+            } else {
+              for (int j = 0; j < nv; ++j) o[j] = __float2bfloat16_rn(v[j]);
+            }
+          }
+        } else {
+          // out[q0 + c0 + j, p]: the warp's lanes hold consecutive features of one token's row
+          const float b = prm.bias ? prm.bias[p] : 0.0f;
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int m = q0 + c0 + j;
+            if (m < prm.q_rows) {
+              const float x = apply_act(v[j] + b, prm.act);
+              if (prm.out_f32) {
+                float* o = (float*)prm.out + (size_t)m * prm.ldo + p;
+                *o = prm.residual ? *o + x : x;
+              } else {
+                ((bf16*)prm.out)[(size_t)m * prm.ldo + p] = __float2bfloat16_rn(x);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+  if (threadIdx.x == 0 && abort_sh) *prm.status = NIB_STATUS_WAIT_TIMEOUT;
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// A [rows, K] bf16 matrix with `ld` elements between rows, read in boxes of box_rows x 64 with the
+// 128-byte swizzle; parts of a box outside the matrix are filled with zeros.
+static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace nib
+
+using namespace nib;
+
+// 1 if the tensor-core path takes this problem, 0 if the caller must use the SIMT kernel.
+extern "C" int nib_linear_tc_supported(const void* a, int lda, const void* w, int ldw, int K) {
+  if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return 0;  // TMA: 16-byte row strides
+  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return 0;
+  return 1;
+}
+
+extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                             void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
+                             cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (!nib_linear_tc_supported(a, lda, w, ldw, K)) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (residual && out_dtype != DT_F32) return NIB_ERR_BAD_ARGUMENT;
+  TcParams prm;
+  prm.K = K;
+  prm.out = out;
+  prm.ldo = ldo;
+  prm.out_f32 = out_dtype == DT_F32;
+  prm.bias = bias;
+  prm.act = act;
+  prm.residual = residual;
+  prm.status = status;
+  prm.vec_ok = ((uintptr_t)out & 15) == 0 && (ldo % (out_dtype == DT_F32 ? 4 : 8)) == 0;
+  prm.swap = M <= 128;
+  const void *p_base, *q_base;
+  int p_ld, q_ld;
+  if (prm.swap) {
+    prm.p_rows = N; prm.q_rows = M; p_base = w; p_ld = ldw; q_base = a; q_ld = lda;
+    prm.bq = (M + 15) / 16 * 16;
+  } else {
+    prm.p_rows = M; prm.q_rows = N; p_base = a; p_ld = lda; q_base = w; q_ld = ldw;
+    const long tiles128 = (long)((M + TC_BP - 1) / TC_BP) * ((N + 127) / 128);
+    prm.bq = (tiles128 >= 148 && N >= 128) ? 128 : 64;
+    if (N < prm.bq) prm.bq = (N + 15) / 16 * 16;
+  }
+  const int stage_bytes = TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2;
+  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  int stages = (200 * 1024) / stage_bytes;
+  if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
+  if (stages > num_kb) stages = num_kb;
+  if (stages < 1) stages = 1;
+  prm.stages = stages;
+  const size_t smem = (size_t)stages * stage_bytes + 1024;
+
+  CUtensorMap map_p, map_q;
+  if (!make_map(&map_p, p_base, prm.p_rows, K, p_ld, TC_BP)) return NIB_ERR_DRIVER;
+  if (!make_map(&map_q, q_base, prm.q_rows, K, q_ld, prm.bq)) return NIB_ERR_DRIVER;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq);
+  if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
+  linear_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, prm);
+  NIB_LAUNCH_CHECK();
+}

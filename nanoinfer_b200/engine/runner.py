@@ -62,7 +62,7 @@ class ModelRunner:
         self.max_rows, self.max_entries = int(max_rows), int(max_entries)
         self.check_status = check_status
         self.workspace = Workspace(self.device)
-        self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.status = ops.status_word() if self.device.type == "cuda" else torch.zeros(1, dtype=torch.int32)
         n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
         cap = 5 * self.max_rows + 4 * self.max_entries + 8 + n_tables
         # A ring of pinned staging buffers: a buffer is written again only after the copy that

@@ -36,6 +36,9 @@ _SIGNATURES = {
                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_linear_simt": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                         _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_linear_tc_supported": [_c_ptr, _c_int, _c_ptr, _c_int, _c_int],
+    "nib_linear_tc": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                      _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -138,11 +141,48 @@ def linear_simt(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], 
            "linear_simt")
 
 
+_status: Optional[torch.Tensor] = None
+
+
+def status_word() -> torch.Tensor:
+    """The device status word (int32 [1]) that kernels write when they meet a fault they can
+    name (a page index outside its pool, a wait that ran out).  0 means fine."""
+    global _status
+    if _status is None:
+        _status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    return _status
+
+
+def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+              act: int = ACT_NONE, residual: bool = False) -> None:
+    """out[:M] = act(a[:M] . w^T + bias) for bfloat16 a and w on the tensor cores (tcgen05, TMA)."""
+    N, K = w.shape
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[1] != K:
+        raise KernelError("linear_tc: a [M, K] and w [N, K] must be bfloat16 and share K")
+    if a.stride(1) != 1 or w.stride(1) != 1 or out.stride(1) != 1 or out.shape[1] != N or out.shape[0] < M:
+        raise KernelError("linear_tc: rows must be contiguous and out [M, N]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != N):
+        raise KernelError("linear_tc: bias must be float32 [N]")
+    _check(library().nib_linear_tc(_dt(out), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                   out.stride(0), M, N, K, act, int(residual), _ptr(status_word()), _stream()),
+           "linear_tc")
+
+
+def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
+    return bool(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and library().nib_linear_tc_supported(
+        _ptr(a), a.stride(0), _ptr(w), w.stride(0), w.shape[1]))
+
+
 def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
            act: int = ACT_NONE, residual: bool = False) -> None:
-    """The matrix product of the model: tensor cores for bfloat16 where the shape allows,
-    CUDA cores (true 32-bit) for float32."""
-    linear_simt(a, w, bias, out, M, act, residual)
+    """The matrix product of the model: out[:M] = act(a[:M] . w^T + bias), added to the 32-bit
+    ``out`` with ``residual``.  bfloat16 runs on the tensor cores where shape and alignment allow
+    (rows of 16-byte multiples), else on the CUDA cores; float32 always runs on the CUDA cores in
+    true 32-bit arithmetic."""
+    if linear_tc_supported(a, w):
+        linear_tc(a, w, bias, out, M, act, residual)
+    else:
+        linear_simt(a, w, bias, out, M, act, residual)
 
 
 def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, block_table: torch.Tensor,

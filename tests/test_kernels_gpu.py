@@ -256,3 +256,55 @@ def test_sampling_follows_the_reference_walk(V):
     for r, sl in enumerate(slots.tolist()):                         # the generator words advanced alike
         if temps[r] > 0:
             assert (int(rng[sl].item()) & (2 ** 64 - 1)) == plain[r].rng
+
+
+TC_SHAPES = [
+    # M, N, K: few rows take the swapped orientation (weights on the MMA's M side), many rows the plain one
+    (1, 96, 768), (8, 2304, 768), (37, 70, 3072), (64, 1000, 120), (128, 257, 64), (16, 50257, 64),
+    (129, 768, 768), (300, 200, 200), (2048, 2304, 768), (515, 1000, 3072), (130, 50, 72),
+]
+
+
+@pytest.mark.parametrize("M, N, K", TC_SHAPES)
+def test_linear_tensor_cores(M, N, K):
+    """tcgen05 GEMM against a float64 product of the same bfloat16 inputs: every epilogue, both
+    output types, sizes that are no multiple of any tile."""
+    o = ops()
+    g = gen(M * 7 + N)
+    a = (torch.randn(M + 2, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    ad, wd, bd = a.to(DEV), w.to(DEV), b.to(DEV)
+    assert o.linear_tc_supported(ad, wd)
+    y = a[:M].double() @ w.double().T + b.double()
+    scale = float(y.abs().max())
+    for act, fn in (("none", lambda u: u), ("tanh", P.gelu_tanh), ("erf", P.gelu_erf)):
+        out = torch.full((M + 2, N), 3.0, dtype=torch.bfloat16, device=DEV)
+        o.linear_tc(ad, wd, bd, out, M, act=o.ACT_CODES[act])
+        want = fn(y)
+        assert (out.cpu().double()[:M] - want).abs().max() < 1e-2 * max(1.0, scale), act
+        assert (out.cpu()[M:] == 3.0).all()                          # rows beyond M are untouched
+    # 32-bit output into a pitched buffer (the logits), without bias
+    pitch = (N + 15) // 16 * 16 + 16
+    buf = torch.full((M, pitch), -7.0, device=DEV)
+    o.linear_tc(ad, wd, None, buf[:, :N], M)
+    assert (buf.cpu().double()[:, :N] - (y - b.double())).abs().max() < 2e-3 * max(1.0, scale)
+    assert (buf.cpu()[:, N:] == -7.0).all()
+    # residual: added into the 32-bit stream
+    x = torch.randn(M + 2, N, generator=g)
+    xd = x.to(DEV)
+    o.linear_tc(ad, wd, bd, xd, M, residual=True)
+    assert (xd.cpu().double()[:M] - (x.double()[:M] + y)).abs().max() < 2e-3 * max(1.0, scale)
+    assert torch.equal(xd.cpu()[M:], x[M:])
+    assert int(o.status_word().item()) == 0
+
+
+def test_linear_falls_back_when_rows_are_not_16_byte_multiples():
+    o = ops()
+    g = gen(11)
+    a, w = torch.randn(5, 36, generator=g).to(torch.bfloat16), torch.randn(20, 36, generator=g).to(torch.bfloat16)
+    ad, wd = a.to(DEV), w.to(DEV)
+    assert not o.linear_tc_supported(ad, wd)                         # K = 36: 72-byte rows
+    out = torch.zeros(5, 20, dtype=torch.bfloat16, device=DEV)
+    o.linear(ad, wd, None, out, 5)
+    assert (out.cpu().double() - a.double() @ w.double().T).abs().max() < 0.1
