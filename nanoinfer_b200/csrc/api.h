@@ -42,12 +42,29 @@ int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw,
                   void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
                   cudaStream_t stream);
 
-// Causal attention of T query rows over the paged cache (general SIMT kernel).
+// Causal attention of T query rows over the paged cache (general SIMT kernel).  rows: the
+// step's rows to process (nullptr: rows 0..T-1).
 int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
-                       const int* block_table, int max_blocks, const int* row_entry,
+                       const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                        const int* positions, int T, int n_head, int n_kv_head, int head_dim,
                        int page_size, int n_pages, float scale, int window, int* status,
                        cudaStream_t stream);
+
+// Split-KV attention for single decoded tokens (float32 or bfloat16) and its scratch need.
+long long nib_attention_decode_scratch(int n_rows, int n_head, int head_dim, int n_splits);
+int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, float* scratch, void* out,
+                         int ldo, const int* block_table, int max_blocks, const int* rows,
+                         const int* row_entry, const int* positions, int n_rows, int n_head, int n_kv_head,
+                         int head_dim, int page_size, int n_pages, float scale, int window, int chunk,
+                         int n_splits, int* status, cudaStream_t stream);
+
+// Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16).
+int nib_attention_prefill_supported(int head_dim);
+int nib_attention_prefill(const void* q, int ldq, const void* cache, void* out, int ldo,
+                          const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                          const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
+                          int head_dim, int page_size, int n_pages, float scale, int window, int* status,
+                          cudaStream_t stream);
 
 int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStream_t stream);
 

@@ -19,13 +19,13 @@ template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
                       T* __restrict__ out, int ldo, const int* __restrict__ block_table,
-                      int max_blocks, const int* __restrict__ row_entry,
+                      int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                       const int* __restrict__ positions, int n_head, int n_kv_head, int head_dim,
                       int page_size, int n_pages, float scale, int window, int* __restrict__ status) {
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x * ATT_WARPS + warp;
-  const int t = blockIdx.y;
+  const int t = rows ? rows[blockIdx.y] : blockIdx.y;
   if (h >= n_head) return;  // whole warps leave; no block-wide barrier follows
   float* qs = smem + (size_t)warp * (head_dim + 32 + 64);
   float* pj = qs + head_dim;                                   // 32 probabilities
@@ -97,7 +97,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
 using namespace nib;
 
 extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out,
-                                  int ldo, const int* block_table, int max_blocks,
+                                  int ldo, const int* block_table, int max_blocks, const int* rows,
                                   const int* row_entry, const int* positions, int T, int n_head,
                                   int n_kv_head, int head_dim, int page_size, int n_pages,
                                   float scale, int window, int* status, cudaStream_t stream) {
@@ -109,11 +109,11 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
   const size_t smem = (size_t)ATT_WARPS * (head_dim + 32 + 64) * sizeof(float);
   if (dtype == DT_F32)
     attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
-        (const float*)q, ldq, (const float*)cache, (float*)out, ldo, block_table, max_blocks, row_entry,
+        (const float*)q, ldq, (const float*)cache, (float*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
   else if (dtype == DT_BF16)
     attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, smem, stream>>>(
-        (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, row_entry,
+        (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
   else
     return NIB_ERR_BAD_ARGUMENT;

@@ -64,7 +64,7 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.status = ops.status_word() if self.device.type == "cuda" else torch.zeros(1, dtype=torch.int32)
         n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
-        cap = 5 * self.max_rows + 4 * self.max_entries + 8 + n_tables
+        cap = 7 * self.max_rows + 8 * self.max_entries + 16 + n_tables
         # A ring of pinned staging buffers: a buffer is written again only after the copy that
         # last read it has finished.
         on_gpu = self.device.type == "cuda"
@@ -124,7 +124,8 @@ class ModelRunner:
         M = sum(len(it.want) for it in items)
 
         # ---- pack the tables:
-        # [tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | logit_slot | block tables]
+        # [tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | logit_slot | attention plan |
+        #  block tables]
         host, buf, copied = self._ring[self._ring_next]
         self._ring_next = (self._ring_next + 1) % len(self._ring)
         if copied is not None:
@@ -135,8 +136,7 @@ class ModelRunner:
         o_slot = o_pos0 + E
         o_lrow = o_slot + E
         o_lslot = o_lrow + M
-        o_tab = o_lslot + M
-        o_tab += (-o_tab) % 4  # keep the tables 16-byte aligned
+        o_plan = o_lslot + M
         row = 0
         lrow = o_lrow
         starts, pos0s, slots = [], [], []
@@ -159,6 +159,12 @@ class ModelRunner:
         buf[o_start:o_start + E + 1] = starts
         buf[o_pos0:o_pos0 + E] = pos0s
         buf[o_slot:o_slot + E] = slots
+        # which rows are single decoded tokens, which are prompt portions (64-row tiles)
+        plan = ops.AttentionPlan(starts, pos0s, self.device, into=buf)
+        n_plan = len(plan.host)
+        buf[o_plan:o_plan + n_plan] = plan.host
+        o_tab = o_plan + n_plan
+        o_tab += (-o_tab) % 4  # keep the tables 16-byte aligned
         tab_offsets = []
         o = o_tab
         for gi, mb in enumerate(self.cache.max_blocks):
@@ -184,6 +190,8 @@ class ModelRunner:
             host_entry_start=starts, host_entry_pos0=pos0s, host_entry_slot=slots,
             max_q_len=max_q, max_kv_len=max_kv,
         )
+        plan.bind(dev[o_plan:o_plan + n_plan])
+        ctx.attention_plan = plan
         tables = [dev[off:off + E * mb].view(E, mb) for off, mb in zip(tab_offsets, self.cache.max_blocks)]
         caches = self.cache.layer_views(tables)
         logit_rows = dev[o_lrow:o_lrow + M] if M else None

@@ -39,8 +39,14 @@ _SIGNATURES = {
     "nib_linear_tc_supported": [_c_ptr, _c_int, _c_ptr, _c_int, _c_int],
     "nib_linear_tc": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr, _c_ptr],
-    "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
+    "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+    "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                             _c_int, _c_ptr, _c_ptr],
+    "nib_attention_prefill_supported": [_c_int],
+    "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
 }
@@ -201,24 +207,120 @@ def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, bl
 
 def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                    row_entry: torch.Tensor, positions: torch.Tensor, T: int, n_head: int, scale: float,
-                   window: int, status: torch.Tensor) -> None:
-    """Causal attention of q[:T] ([T, n_head * head_dim], any row stride) over one cache layer."""
+                   window: int, status: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+    """Causal attention of T rows of q ([*, n_head * head_dim], any row stride) over one cache layer, with
+    the general kernel (any head size up to 256, any page size).  ``rows`` lists the rows to process."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
     _check(library().nib_attention_simt(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
-                                        _ptr(block_table), block_table.shape[1], _ptr(row_entry),
+                                        _ptr(block_table), block_table.shape[1], _ptr(rows), _ptr(row_entry),
                                         _ptr(positions), T, n_head, n_kv_head, head_dim, page_size, n_pages,
                                         float(scale), int(window), _ptr(status), _stream()),
            "attention_simt")
 
 
+def decode_split(n_rows: int, n_head: int, max_keys: int) -> tuple:
+    """(chunk, n_splits): keys per split (a multiple of 64) so that about four blocks per SM are in flight."""
+    want = max(1, -(-592 // max(1, n_rows * n_head)))
+    chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
+    return chunk, max(1, -(-max_keys // chunk))
+
+
+def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
+                     row_entry: torch.Tensor, positions: torch.Tensor, n_rows: int, n_head: int, scale: float,
+                     window: int, status: torch.Tensor, max_keys: int, workspace,
+                     rows: Optional[torch.Tensor] = None) -> None:
+    """Split-KV attention for rows that are single decoded tokens.  ``max_keys``: the longest key
+    range among them; partial results go through ``workspace``."""
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
+    chunk, n_splits = decode_split(n_rows, n_head, max_keys)
+    scratch = None
+    if n_splits > 1:
+        scratch = workspace.get("attention.partials", (n_rows * n_head * n_splits * (head_dim + 2),), torch.float32)
+    _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
+                                          out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
+                                          _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
+                                          page_size, n_pages, float(scale), int(window), chunk, n_splits,
+                                          _ptr(status), _stream()), "attention_decode")
+
+
+def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
+                      tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
+                      n_head: int, scale: float, window: int, status: torch.Tensor) -> None:
+    """Tiled tensor-core attention for prompt portions: ``tiles`` holds (entry, first row within the
+    entry) pairs of 64 rows each."""
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill: bfloat16 only")
+    _check(library().nib_attention_prefill(_ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
+                                           _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
+                                           _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
+                                           page_size, n_pages, float(scale), int(window), _ptr(status), _stream()),
+           "attention_prefill")
+
+
+class AttentionPlan:
+    """Which rows of a step are single decoded tokens and which belong to prompt portions; the
+    same for every layer of the step."""
+
+    def __init__(self, entry_start, entry_pos0, device, into=None):
+        dec, pre, tiles = [], [], []
+        self.max_decode_keys = 0
+        for e in range(len(entry_start) - 1):
+            a, b = entry_start[e], entry_start[e + 1]
+            if b - a == 1:
+                dec.append(a)
+                self.max_decode_keys = max(self.max_decode_keys, entry_pos0[e] + 1)
+            else:
+                pre.extend(range(a, b))
+                tiles.extend((e, off) for off in range(0, b - a, 64))
+        self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
+        flat = dec + pre + [v for t in tiles for v in t]
+        self.host = flat
+        if into is None:
+            buf = torch.tensor(flat, dtype=torch.int32, device=device) if flat else None
+            self.bind(buf)
+
+    def bind(self, buf) -> None:
+        """``buf``: a device int32 tensor holding ``self.host``."""
+        nd, npre = self.n_decode, self.n_prefill_rows
+        all_decode = npre == 0
+        # rows 0..n-1 in order need no index list
+        self.decode_rows = None if all_decode or nd == 0 else buf[:nd]
+        self.prefill_rows = None if nd == 0 or npre == 0 else buf[nd:nd + npre]
+        self.tiles = buf[nd + npre:nd + npre + 2 * self.n_tiles] if self.n_tiles else None
+
+
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
               n_head: int, scale: float, window: int) -> None:
-    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's
-    StepContext (rows, positions, entries)."""
-    attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
-                   window, ctx.status)
+    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's StepContext.
+    Single decoded tokens go to the split-KV kernel; prompt portions go to the tiled tensor-core
+    kernel in bfloat16 (head sizes 16..128 in steps of 16) and to the general kernel otherwise."""
+    plan = getattr(ctx, "attention_plan", None)
+    if plan is None:
+        plan = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, q.device)
+        ctx.attention_plan = plan
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    fast_pages = page_size % 16 == 0 and head_dim % 8 == 0
+    if not fast_pages:
+        attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
+                       window, ctx.status)
+        return
+    if plan.n_decode:
+        keys = plan.max_decode_keys if window <= 0 else min(plan.max_decode_keys, window)
+        attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
+                         window, ctx.status, keys, ctx.workspace, plan.decode_rows)
+    if plan.n_prefill_rows:
+        if q.dtype == torch.bfloat16 and library().nib_attention_prefill_supported(head_dim) \
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+            attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
+                              n_head, scale, window, ctx.status)
+        else:
+            attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_prefill_rows, n_head,
+                           scale, window, ctx.status, plan.prefill_rows)
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:

@@ -208,6 +208,9 @@ class StepContext:
     host_entry_slot: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
+    #: which rows are single decoded tokens and which are prompt portions (set by the step function;
+    #: the attention kernels build it themselves when it is absent)
+    attention_plan: Optional[object] = None
 
 
 class Workspace:

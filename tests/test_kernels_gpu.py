@@ -144,6 +144,15 @@ ATT_CASES = [
     (3, 1, 128, 8, [70, 9], [5, 9], 0),
     (4, 2, 32, 16, [100, 45, 16], [100, 1, 16], 24),
     (2, 2, 80, 16, [300], [1], 0),
+    # single tokens over long ranges: many splits per (row, head); with and without a window
+    (12, 12, 64, 16, [1024, 1000, 513], [1, 1, 1], 0),
+    (4, 2, 64, 16, [700, 300, 5], [1, 1, 1], 100),
+    (1, 1, 256, 16, [90], [1], 0),
+    # prompt portions of several 64-row tiles that continue an earlier part of the request
+    (2, 2, 64, 16, [200], [130], 0),
+    (4, 1, 32, 32, [260, 90], [200, 90], 50),
+    (2, 2, 128, 16, [150, 64, 65], [150, 64, 2], 0),
+    (3, 3, 48, 16, [100, 31], [37, 1], 0),
 ]
 
 
