@@ -82,7 +82,7 @@ def main() -> int:
     clocks.start()
     eng = bs.build_engine(model_dir, "bfloat16", args.batch, context, max_rows=2048)
     dec = bs.time_decode(eng, args.batch, prompt_len, steps, warmup)
-    launches = getattr(eng.runner, "launches_last_step", None)
+    launches = dec["launches_per_step"]
     clock_record = clocks.stop()
     e2e = bs.time_e2e_decode(eng, args.batch, prompt_len, steps, warmup)
     pre = bs.time_prefill(eng, 2, 1024, runs=5, warmup=3)

@@ -188,8 +188,7 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
         chunk = reqs[i:i + budget]
         items = [StepItem(r, torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
                  for r in chunk]
-        logits = eng.runner.step(items)
-        last += eng.sampler.sample(logits, eng.runner.last_logit_slot).tolist()
+        last += eng.runner.step(items, sampler=eng.sampler).tolist()
     flusher = L2Flusher(eng.device) if flush else None
     times = []
     ctx_sum = 0
@@ -200,8 +199,7 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
             flusher.flush()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        logits = eng.runner.step(items)
-        toks = eng.sampler.sample(logits, eng.runner.last_logit_slot)
+        toks = eng.runner.step(items, sampler=eng.sampler)
         e1.record()
         last = toks.tolist()
         if s >= warmup:
@@ -211,7 +209,8 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
         eng.cache.close_request(r)
     ms = sum(times) / len(times)
     return {"ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "mean_context": ctx_sum / (len(times) * batch),
-            "steps": len(times)}
+            "steps": len(times), "launches_per_step": eng.runner.launches_last_step,
+            "graph_replays": eng.runner.graph_replays}
 
 
 def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, seed: int = 1) -> Dict[str, float]:
@@ -270,6 +269,58 @@ def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, s
         eng.step()
     return {"tokens_per_s": batch * steps / dt, "ms_per_step": dt / steps * 1e3,
             "h2d_bytes_per_step": eng.runner.last_meta_bytes, "d2h_bytes_per_step": 4 * batch}
+
+
+def profile_step(eng, items, sampler=None, repeats: int = 3):
+    """Per-kernel device time of one step, run eagerly ``repeats`` times (the requests are cut back
+    after each run, so the same step is measured); returns {(launcher, label): (ms per step, calls)}."""
+    from .kernels import ops
+
+    graphs = eng.runner.use_graphs
+    eng.runner.use_graphs = False
+    lens = [it.request.n_tokens for it in items]
+    try:
+        eng.runner.step(items, sampler=sampler)
+        for it, n in zip(items, lens):
+            eng.cache.truncate(it.request, n)
+        prof = ops.start_profile()
+        for _ in range(repeats):
+            eng.runner.step(items, sampler=sampler)
+            for it, n in zip(items, lens):
+                eng.cache.truncate(it.request, n)
+        out = prof.summary()
+    finally:
+        ops.stop_profile()
+        eng.runner.use_graphs = graphs
+    return {k: (ms / repeats, n // repeats) for k, (ms, n) in out.items()}
+
+
+def format_profile(table) -> str:
+    total = sum(ms for ms, _ in table.values())
+    lines = [f"{'kernel':<28}{'shape':<26}{'calls':>6}{'ms':>10}{'%':>7}"]
+    for (name, label), (ms, n) in sorted(table.items(), key=lambda kv: -kv[1][0]):
+        lines.append(f"{name[4:]:<28}{label if 'linear' in name else '':<26}{n:>6}{ms:>10.4f}{100 * ms / total:>7.1f}")
+    lines.append(f"{'total':<60}{total:>10.4f}")
+    return "\n".join(lines)
+
+
+def print_profile(eng, prompt) -> None:
+    """The per-kernel breakdown of a prefill of ``prompt`` and of one decode step after it."""
+    import sys
+
+    from .engine.runner import StepItem
+    from .sampling.sampler import SamplingParams
+
+    r = eng.cache.open_request()
+    eng.sampler.set_request(r.slot, SamplingParams(temperature=0.0))
+    pre = profile_step(eng, [StepItem(r, list(prompt), [len(prompt) - 1])], eng.sampler)
+    print(f"-- prefill of {len(prompt)} tokens", file=sys.stderr)
+    print(format_profile(pre), file=sys.stderr)
+    eng.runner.step([StepItem(r, list(prompt), [len(prompt) - 1])], sampler=eng.sampler)
+    dec = profile_step(eng, [StepItem(r, [int(prompt[-1])], [0])], eng.sampler)
+    print(f"-- one decode step at context {len(prompt) + 1}", file=sys.stderr)
+    print(format_profile(dec), file=sys.stderr)
+    eng.cache.close_request(r)
 
 
 # ----------------------------------------------------------------------------- the bench command

@@ -22,6 +22,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import KVCacheSpec, KVCacheView, StateSpec
@@ -104,6 +105,9 @@ class RequestCache:
     n_tokens: int = 0
     blocks: List[List[int]] = field(default_factory=list)
     live: bool = True
+    #: per group, the block table row as the device wants it (int32 [max_blocks], -1 = no page):
+    #: a mirror of ``blocks`` kept by the manager so that a step copies it in one piece
+    table_rows: List[np.ndarray] = field(default_factory=list)
 
     def pages_held(self) -> int:
         return sum(1 for g in self.blocks for p in g if p >= 0)
@@ -203,18 +207,20 @@ class CacheManager:
     def open_request(self) -> RequestCache:
         slot = self.slots.take()
         self.slots.reset(slot, self._state_keys)
-        req = RequestCache(slot=slot, blocks=[[] for _ in self.groups])
+        req = RequestCache(slot=slot, blocks=[[] for _ in self.groups],
+                           table_rows=[np.full(mb, -1, dtype=np.int32) for mb in self.max_blocks])
         self._live.append(req)
         return req
 
     def close_request(self, req: RequestCache) -> None:
         """Give back everything the request holds."""
         self._require_live(req)
-        for g, blocks in zip(self.groups, req.blocks):
+        for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
             for p in blocks:
                 if p >= 0:
                     g.pool.give_back(p)
             blocks.clear()
+            row.fill(-1)
         self.slots.give_back(req.slot)
         req.live = False
         req.n_tokens = 0
@@ -260,21 +266,24 @@ class CacheManager:
             raise PoolExhausted("KV cache pool exhausted: the step needs more pages than are free")
         for req, n in work:
             n_blocks = -(-(req.n_tokens + n) // self.page_size)
-            for g, blocks in zip(self.groups, req.blocks):
+            for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
                 while len(blocks) < n_blocks:
-                    blocks.append(g.pool.take())
+                    page = g.pool.take()
+                    row[len(blocks)] = page
+                    blocks.append(page)
 
     def commit(self, req: RequestCache, n_new: int) -> None:
         """The step ran: the request is ``n_new`` tokens longer; pages a window has passed go back."""
         self._require_live(req)
         req.n_tokens += n_new
-        for g, blocks in zip(self.groups, req.blocks):
+        for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
             if g.spec.window > 0:
                 first = self._first_needed_block(g, req.n_tokens)  # the next query stands at n_tokens
                 for b in range(min(first, len(blocks))):
                     if blocks[b] >= 0:
                         g.pool.give_back(blocks[b])
                         blocks[b] = -1
+                        row[b] = -1
 
     def truncate(self, req: RequestCache, n_tokens: int) -> None:
         """Forget positions from ``n_tokens`` on; pages wholly past it go back
@@ -285,13 +294,14 @@ class CacheManager:
         if self._state_keys and n_tokens != req.n_tokens:
             raise CacheError("truncate: a mixer keeps per-request state, which cannot be rolled back")
         keep = -(-n_tokens // self.page_size)
-        for g, blocks in zip(self.groups, req.blocks):
+        for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
             if g.spec.window > 0 and n_tokens < req.n_tokens:
                 first = self._first_needed_block(g, n_tokens)
                 if any(blocks[b] < 0 for b in range(first, min(keep, len(blocks)))):
                     raise CacheError("truncate: pages behind the window were already given back")
             while len(blocks) > keep:
                 p = blocks.pop()
+                row[len(blocks)] = -1
                 if p >= 0:
                     g.pool.give_back(p)
         req.n_tokens = n_tokens
@@ -330,6 +340,10 @@ class CacheManager:
                 raise CacheError(f"group {gi}: a page is held twice")
             if len(held) != g.pool.n_used:
                 raise CacheError(f"group {gi}: {g.pool.n_used} pages are out but requests hold {len(held)}")
+            for r in self._live:
+                row = r.table_rows[gi]
+                if list(row[:len(r.blocks[gi])]) != r.blocks[gi] or (row[len(r.blocks[gi]):] != -1).any():
+                    raise CacheError(f"group {gi}: a block table row does not mirror the request's pages")
         self.slots.check()
         if len({r.slot for r in self._live}) != len(self._live):
             raise CacheError("two live requests share a slot")

@@ -13,6 +13,10 @@
 //
 // One CTA computes one P x Q tile: warp 0 issues the TMA loads, warp 1 allocates tensor memory
 // and issues the MMAs, warps 2..5 run the epilogue (each owns the 32 TMEM lanes of its quarter).
+// The epilogue writes the finished tile into the (by then idle) pipeline buffers and hands it
+// to TMA: a tiled store, or for the residual sum a tiled reduce-add, so that x += tile happens in
+// the L2 without the SM reading x.  Outputs whose pitch or address TMA cannot take (rows not a
+// multiple of 16 bytes) are written with plain stores instead.
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records
 // NIB_STATUS_WAIT_TIMEOUT, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
@@ -39,7 +43,7 @@ struct TcParams {
   const float* bias;
   int act;
   int residual;
-  int vec_ok;        // out is 16-byte aligned and its row pitch keeps rows so: vector stores allowed
+  int tma_store;     // 1: the epilogue stages the tile in shared memory and stores it with TMA
   int* status;
 };
 
@@ -107,6 +111,14 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
                : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const void* src, int x, int y) {
+  asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -137,9 +149,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 }
 
 // ------------------------------------------------------------------ the kernel
+// Waits by one lane for the whole warp: 32 lanes polling one barrier only queue up behind each other.
+__device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+  int ok = 1;
+  if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
-                 const TcParams prm) {
+                 const __grid_constant__ CUtensorMap map_o, const TcParams prm) {
   extern __shared__ uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -148,6 +167,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   __shared__ uint64_t tmem_full_bar;
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
+  __shared__ int epi_ok_sh[4];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = prm.stages, bq = prm.bq;
@@ -167,6 +187,9 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     abort_sh = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_p) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
+    if (prm.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_o) : "memory");
   }
   if (warp == 1) tmem_alloc(&tmem_base_sh, tmem_cols);
   tc_fence_before();
@@ -176,39 +199,42 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   volatile int* abort_flag = &abort_sh;
 
   if (warp == 0) {
-    // ---------------- TMA producer (one lane)
-    if (lane == 0) {
-      int issued = 0;
-      for (int kb = 0; kb < num_kb; ++kb) {
-        const int s = kb % stages;
-        const uint32_t parity = ((kb / stages) & 1) ^ 1;  // a fresh barrier passes the first round
-        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) break;
+    // ---------------- TMA producer: the warp walks the loop together, lane 0 waits and issues
+    int issued = 0, s = 0;
+    uint32_t parity = 1;  // a fresh barrier passes a wait on the phase before its first
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (!warp_mbar_wait(&empty_bar[s], parity, abort_flag, lane)) break;
+      if (lane == 0) {
         uint8_t* sp = smem + (size_t)s * stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
         tma_load_2d(sp, &map_p, &full_bar[s], kb * TC_BK, p0);
         tma_load_2d(sp + p_bytes, &map_q, &full_bar[s], kb * TC_BK, q0);
-        ++issued;
       }
-      if (*abort_flag) {
-        // let the copies that are still in flight land before the block's shared memory goes away
-        const int first = issued > stages ? issued - stages : 0;
-        for (int kb = first; kb < issued; ++kb) {
-          const long long t0 = clock64();
-          while (!mbar_try_wait(&full_bar[kb % stages], (kb / stages) & 1) && clock64() - t0 < 200000000ll) {
-          }
+      ++issued;
+      if (++s == stages) {
+        s = 0;
+        parity ^= 1;
+      }
+    }
+    if (*abort_flag && lane == 0) {
+      // let the copies that are still in flight land before the block's shared memory goes away
+      const int first = issued > stages ? issued - stages : 0;
+      for (int kb = first; kb < issued; ++kb) {
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full_bar[kb % stages], (kb / stages) & 1) && clock64() - t0 < 200000000ll) {
         }
       }
     }
+    __syncwarp();
   } else if (warp == 1) {
-    // ---------------- MMA issuer (one lane)
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc(TC_BP, bq);
-      bool ok = true;
-      for (int kb = 0; kb < num_kb && ok; ++kb) {
-        const int s = kb % stages;
-        ok = mbar_wait(&full_bar[s], (kb / stages) & 1, abort_flag);
-        if (!ok) break;
-        tc_fence_after();
+    // ---------------- MMA issuer: lane 0 waits and issues
+    const uint32_t idesc = umma_idesc(TC_BP, bq);
+    int s = 0;
+    uint32_t parity = 0;
+    for (int kb = 0; kb < num_kb; ++kb) {
+      if (!warp_mbar_wait(&full_bar[s], parity, abort_flag, lane)) break;
+      tc_fence_after();
+      if (lane == 0) {
         const uint32_t pa = smem_u32(smem + (size_t)s * stage_bytes);
         const uint32_t qa = pa + p_bytes;
 #pragma unroll
@@ -218,58 +244,101 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         }
         umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
       }
-      umma_commit(&tmem_full_bar);   // arrives when every MMA above has finished
+      if (++s == stages) {
+        s = 0;
+        parity ^= 1;
+      }
     }
+    if (lane == 0) umma_commit(&tmem_full_bar);  // arrives when every MMA above has finished
+    __syncwarp();
   } else {
     // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +32
     const int quarter = warp & 3;
-    const int p = p0 + quarter * 32 + lane;  // this thread's row of the P tile
-    const bool ok = mbar_wait(&tmem_full_bar, 0, abort_flag);
+    const int pl = quarter * 32 + lane;      // this thread's row within the P tile
+    const int p = p0 + pl;
+    // the four epilogue warps go on only if all of them saw the accumulator complete
+    if (lane == 0) epi_ok_sh[quarter] = mbar_wait(&tmem_full_bar, 0, abort_flag) ? 1 : 0;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    const bool ok = (epi_ok_sh[0] & epi_ok_sh[1] & epi_ok_sh[2] & epi_ok_sh[3]) != 0;
     tc_fence_after();
-    if (ok) {
-      const bool p_ok = p < prm.p_rows;
+    const bool p_ok = p < prm.p_rows;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    if (ok && prm.tma_store) {
+      // Every MMA has finished, so every pipeline buffer is idle: the tile is staged there.
+      const float bias_p = (prm.swap && prm.bias && p_ok) ? prm.bias[p] : 0.0f;
+      for (int c0 = 0; c0 < bq; c0 += 16) {
+        float v[16];
+        tmem_ld16(lane_addr + (uint32_t)c0, v);
+        if (!prm.swap) {
+          // normal orientation: blocks of [128 rows][128 bytes] in the 128-byte swizzle
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int n = q0 + c0 + j;
+            v[j] = apply_act(v[j] + ((prm.bias && n < prm.q_rows) ? prm.bias[n] : 0.0f), prm.act);
+          }
+          if (prm.out_f32) {
+            uint8_t* blk = smem + (size_t)(c0 / 32) * 16384 + (size_t)pl * 128;
+#pragma unroll
+            for (int j = 0; j < 16; j += 4) {
+              const int chunk = ((c0 % 32 + j) / 4) ^ (pl & 7);
+              *reinterpret_cast<float4*>(blk + chunk * 16) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+          } else {
+            uint8_t* blk = smem + (size_t)(c0 / 64) * 16384 + (size_t)pl * 128;
+#pragma unroll
+            for (int j = 0; j < 16; j += 8) {
+              const int chunk = ((c0 % 64 + j) / 8) ^ (pl & 7);
+              *reinterpret_cast<uint4*>(blk + chunk * 16) =
+                  make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]), pack_bf16(v[j + 4], v[j + 5]),
+                             pack_bf16(v[j + 6], v[j + 7]));
+            }
+          }
+        } else {
+          // swapped orientation: a dense [tokens][128 features] tile, lanes along the features
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float x = apply_act(v[j] + bias_p, prm.act);
+            if (prm.out_f32)
+              reinterpret_cast<float*>(smem)[(c0 + j) * TC_BP + pl] = x;
+            else
+              reinterpret_cast<bf16*>(smem)[(c0 + j) * TC_BP + pl] = __float2bfloat16_rn(x);
+          }
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
+      asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
+      if (warp == 2 && lane == 0) {
+        if (!prm.swap) {
+          const int cols = prm.out_f32 ? 32 : 64;
+          for (int c = 0; c < bq && q0 + c < prm.q_rows; c += cols) {
+            const void* src = smem + (size_t)(c / cols) * 16384;
+            if (prm.residual) tma_reduce_add_2d(&map_o, src, q0 + c, p0);
+            else tma_store_2d(&map_o, src, q0 + c, p0);
+          }
+        } else {
+          if (prm.residual) tma_reduce_add_2d(&map_o, smem, p0, q0);
+          else tma_store_2d(&map_o, smem, p0, q0);
+        }
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
+      }
+    } else if (ok) {
       for (int c0 = 0; c0 < bq; c0 += 16) {
         if (q0 + c0 >= prm.q_rows) break;  // uniform over the warp
         float v[16];
-        tmem_ld16(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, v);
+        tmem_ld16(lane_addr + (uint32_t)c0, v);
         if (!p_ok) continue;
         if (!prm.swap) {
           // out[p, q0 + c0 + j]: this thread writes 16 consecutive features of its own row
           const int n0 = q0 + c0;
           const int nv = min(16, prm.q_rows - n0);
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            if (j < nv) {
-              float x = v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f);
-              v[j] = apply_act(x, prm.act);
-            }
-          }
-          if (prm.out_f32) {
-            float* o = (float*)prm.out + (size_t)p * prm.ldo + n0;
-            if (nv == 16 && prm.vec_ok) {
-#pragma unroll
-              for (int j = 0; j < 16; j += 4) {
-                float4 r = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                if (prm.residual) {
-                  const float4 old = *reinterpret_cast<const float4*>(o + j);
-                  r.x += old.x; r.y += old.y; r.z += old.z; r.w += old.w;
-                }
-                *reinterpret_cast<float4*>(o + j) = r;
-              }
+          for (int j = 0; j < nv; ++j) {
+            const float x = apply_act(v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f), prm.act);
+            if (prm.out_f32) {
+              float* o = (float*)prm.out + (size_t)p * prm.ldo + n0 + j;
+              *o = prm.residual ? *o + x : x;
             } else {
-              for (int j = 0; j < nv; ++j) o[j] = prm.residual ? o[j] + v[j] : v[j];
-            }
-          } else {
-            bf16* o = (bf16*)prm.out + (size_t)p * prm.ldo + n0;
-            if (nv == 16 && prm.vec_ok) {
-              uint4 a = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]), pack_bf16(v[4], v[5]),
-                                   pack_bf16(v[6], v[7]));
-              uint4 b = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]), pack_bf16(v[12], v[13]),
-                                   pack_bf16(v[14], v[15]));
-              *reinterpret_cast<uint4*>(o) = a;
-              *reinterpret_cast<uint4*>(o + 8) = b;
-            } else {
-              for (int j = 0; j < nv; ++j) o[j] = __float2bfloat16_rn(v[j]);
+              ((bf16*)prm.out)[(size_t)p * prm.ldo + n0 + j] = __float2bfloat16_rn(x);
             }
           }
         } else {
@@ -318,18 +387,21 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// A [rows, K] bf16 matrix with `ld` elements between rows, read in boxes of box_rows x 64 with the
-// 128-byte swizzle; parts of a box outside the matrix are filled with zeros.
-static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+// A row-major [rows, cols] matrix with `ld` elements between rows, moved in boxes of
+// box_rows x box_cols; parts of a box outside the matrix read as zeros and are not written.
+static bool make_map(CUtensorMap* map, const void* base, bool f32, int rows, int cols, int ld, int box_rows,
+                     int box_cols, bool swizzle128) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  const int esz = f32 ? 4 : 2;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * esz};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+            const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 }  // namespace nib
@@ -358,7 +430,6 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   prm.act = act;
   prm.residual = residual;
   prm.status = status;
-  prm.vec_ok = ((uintptr_t)out & 15) == 0 && (ldo % (out_dtype == DT_F32 ? 4 : 8)) == 0;
   prm.swap = M <= 128;
   const void *p_base, *q_base;
   int p_ld, q_ld;
@@ -371,6 +442,12 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
     prm.bq = (tiles128 >= 148 && N >= 128) ? 128 : 64;
     if (N < prm.bq) prm.bq = (N + 15) / 16 * 16;
   }
+  // TMA can store the tile if the output's rows are 16-byte multiples; the plain orientation
+  // also needs whole 128-byte blocks across the tile
+  const int esz = prm.out_f32 ? 4 : 2;
+  // (TMA clips a store at the tensor's edge in 16-byte pieces, so the row length must be a multiple too)
+  prm.tma_store = ((uintptr_t)out & 15) == 0 && ((long)ldo * esz) % 16 == 0 && ((long)N * esz) % 16 == 0 &&
+                  (prm.swap || prm.bq % 64 == 0);
   const int stage_bytes = TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2;
   const int num_kb = (K + TC_BK - 1) / TC_BK;
   int stages = (200 * 1024) / stage_bytes;
@@ -378,11 +455,21 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   if (stages > num_kb) stages = num_kb;
   if (stages < 1) stages = 1;
   prm.stages = stages;
-  const size_t smem = (size_t)stages * stage_bytes + 1024;
+  size_t tile_bytes = (size_t)stages * stage_bytes;
+  const size_t staging = (size_t)TC_BP * prm.bq * esz;
+  if (prm.tma_store && staging > tile_bytes) tile_bytes = staging;
+  const size_t smem = tile_bytes + 1024;
 
-  CUtensorMap map_p, map_q;
-  if (!make_map(&map_p, p_base, prm.p_rows, K, p_ld, TC_BP)) return NIB_ERR_DRIVER;
-  if (!make_map(&map_q, q_base, prm.q_rows, K, q_ld, prm.bq)) return NIB_ERR_DRIVER;
+  CUtensorMap map_p, map_q, map_o;
+  if (!make_map(&map_p, p_base, false, prm.p_rows, K, p_ld, TC_BP, TC_BK, true)) return NIB_ERR_DRIVER;
+  if (!make_map(&map_q, q_base, false, prm.q_rows, K, q_ld, prm.bq, TC_BK, true)) return NIB_ERR_DRIVER;
+  if (prm.tma_store) {
+    const bool ok = prm.swap ? make_map(&map_o, out, prm.out_f32, M, N, ldo, prm.bq, TC_BP, false)
+                             : make_map(&map_o, out, prm.out_f32, M, N, ldo, TC_BP, prm.out_f32 ? 32 : 64, true);
+    if (!ok) return NIB_ERR_DRIVER;
+  } else {
+    map_o = map_p;  // unused
+  }
 
   static bool attr_set = false;
   if (!attr_set) {
@@ -392,6 +479,6 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   }
   dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq);
   if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
-  linear_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, prm);
+  linear_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
   NIB_LAUNCH_CHECK();
 }

@@ -24,7 +24,8 @@ _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.
 class Engine:
     def __init__(self, model_dir: str, dtype: Union[str, torch.dtype] = "bfloat16", device: str = "cuda",
                  max_tokens: Optional[int] = None, max_batch: int = 64, max_rows: int = 2048,
-                 prefill_budget: Optional[int] = None, page_size: int = 16, check_status: bool = False):
+                 prefill_budget: Optional[int] = None, page_size: int = 16, check_status: bool = False,
+                 use_graphs: bool = True):
         """``max_tokens``: how many tokens all live requests may hold in the cache together
         (default: ``max_batch`` full contexts).  ``prefill_budget``: most prompt tokens per step
         (default ``max_rows``)."""
@@ -41,7 +42,7 @@ class Engine:
                                   max_requests=max_batch, page_size=page_size, dtype=dtype, device=self.device,
                                   max_positions=limit)
         self.runner = ModelRunner(self.model, self.cache, max_rows=max_rows, max_entries=max_batch,
-                                  check_status=check_status)
+                                  check_status=check_status, use_graphs=use_graphs)
         self.sampler = Sampler(self.cache.slots)
         self.scheduler = Scheduler(self.cache, max_batch=max_batch, max_rows=max_rows,
                                    prefill_budget=prefill_budget or max_rows, max_positions=limit)
@@ -73,10 +74,8 @@ class Engine:
             r = it.request
             toks = r.tokens[r.n_computed:r.n_computed + it.n_tokens]
             step_items.append(StepItem(r.cache, toks, [it.n_tokens - 1] if it.samples else []))
-        logits = self.runner.step(step_items)
-        sampled: List[int] = []
-        if logits is not None:
-            sampled = self.sampler.sample(logits, self.runner.last_logit_slot).tolist()
+        tokens = self.runner.step(step_items, sampler=self.sampler)
+        sampled: List[int] = tokens.tolist() if tokens is not None else []
         ended += self.scheduler.on_step_done(items, sampled)
         return ended
 

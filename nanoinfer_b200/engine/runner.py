@@ -12,17 +12,23 @@ batch engine (crates/metal/src/batch.rs:1-15, ``Batch::step`` batch.rs:259-315).
      the device in one copy;
   3. runs the model on exactly these rows;
   4. commits the new lengths (batch.rs:270) and returns float32 logits [wanted, vocab] in the
-     order of the items and of their ``want`` lists.  Sampling is a separate call on them.
+     order of the items and of their ``want`` lists, or, when a sampler is given, one sampled
+     token per logits row.
+
+Steps made of single decoded tokens only are launch-bound, so their kernels are captured once
+per shape in a CUDA graph and replayed (the reference keeps its decode loop on the GPU for the
+same reason, ``decode_resident``, batch.rs:322-363).  What a graph bakes in is only the shape of
+the step: the tables it reads are rewritten before every replay.
 """
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
 
-from ..cache.manager import CacheManager, PoolExhausted, RequestCache
+from ..cache.manager import CacheManager, RequestCache
 from ..kernels import ops
 from ..models.model import Model
 from ..parts.base import StepContext, Workspace
@@ -52,22 +58,57 @@ class StepItem:
     want: Sequence[int] = field(default_factory=list)
 
 
+@dataclass
+class _Layout:
+    """Where each table of a step lies in the packed int32 buffer."""
+    T: int
+    E: int
+    M: int
+    n_plan: int
+    tok: int = 0
+    pos: int = 0
+    ent: int = 0
+    start: int = 0
+    pos0: int = 0
+    slot: int = 0
+    lrow: int = 0
+    lslot: int = 0
+    plan: int = 0
+    tabs: Tuple[int, ...] = ()
+    total: int = 0
+
+
+@dataclass
+class _Captured:
+    graph: "torch.cuda.CUDAGraph"
+    logits: Optional[torch.Tensor]
+    tokens: Optional[torch.Tensor]
+    launches: int
+
+
+#: decode graphs are shaped by the longest key range rounded up to this many positions
+GRAPH_KEY_BUCKET = 256
+
+
 class ModelRunner:
     def __init__(self, model: Model, cache: CacheManager, max_rows: int = 2048, max_entries: int = 64,
-                 check_status: bool = True):
+                 check_status: bool = True, use_graphs: bool = True, max_graphs: int = 96):
         if model.device is None:
             raise ValueError("the model has no weights yet: load them first")
         self.model, self.cache = model, cache
         self.device = model.device
         self.max_rows, self.max_entries = int(max_rows), int(max_entries)
         self.check_status = check_status
+        on_gpu = self.device.type == "cuda"
+        # a mixer with state of its own may plan its work on the host, which a graph would freeze
+        self.use_graphs = bool(use_graphs) and on_gpu and not model.state_needs()
+        self.max_graphs = max_graphs
         self.workspace = Workspace(self.device)
-        self.status = ops.status_word() if self.device.type == "cuda" else torch.zeros(1, dtype=torch.int32)
+        self.status = ops.status_word() if on_gpu else torch.zeros(1, dtype=torch.int32)
         n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
         cap = 7 * self.max_rows + 8 * self.max_entries + 16 + n_tables
         # A ring of pinned staging buffers: a buffer is written again only after the copy that
         # last read it has finished.
-        on_gpu = self.device.type == "cuda"
         self._ring = []
         for _ in range(4):
             host = torch.empty(cap, dtype=torch.int32)
@@ -76,9 +117,15 @@ class ModelRunner:
             self._ring.append((host, host.numpy(), torch.cuda.Event() if on_gpu else None))
         self._ring_next = 0
         self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
+        self._arange = np.arange(self.max_entries + 1, dtype=np.int32)
+        self._graphs: Dict[tuple, _Captured] = {}
+        self._seen: Dict[tuple, int] = {}
         self.steps_run = 0
+        self.graph_replays = 0
         self.last_meta_bytes = 0
         self.last_logit_slot = None
+        #: kernel launches of the last step (counted by the kernel interface)
+        self.launches_last_step = 0
 
     # ------------------------------------------------------------------ checks
     def _validate(self, items: Sequence[StepItem]) -> int:
@@ -112,99 +159,155 @@ class ModelRunner:
             raise TooManyRows(f"{n_rows} rows > max_rows {self.max_rows}")
         return n_rows
 
-    # ------------------------------------------------------------------ the step
-    def step(self, items: Sequence[StepItem]) -> Optional[torch.Tensor]:
-        T = self._validate(items)
-        work = [(it.request, len(it.tokens)) for it in items]
-        try:
-            self.cache.append(work)  # all pages of the step, or none
-        except PoolExhausted:
-            raise
-        E = len(items)
-        M = sum(len(it.want) for it in items)
+    # ------------------------------------------------------------------ packing
+    def _layout(self, T: int, E: int, M: int, n_plan: int) -> _Layout:
+        """[tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | logit_slot |
+        attention plan | block tables], the tables 16-byte aligned."""
+        lay = _Layout(T, E, M, n_plan)
+        lay.tok, lay.pos, lay.ent = 0, T, 2 * T
+        lay.start = 3 * T
+        lay.pos0 = lay.start + E + 1
+        lay.slot = lay.pos0 + E
+        lay.lrow = lay.slot + E
+        lay.lslot = lay.lrow + M
+        lay.plan = lay.lslot + M
+        o = lay.plan + n_plan
+        o += (-o) % 4
+        tabs = []
+        for mb in self.cache.max_blocks:
+            tabs.append(o)
+            o += E * mb
+        lay.tabs, lay.total = tuple(tabs), o
+        return lay
 
-        # ---- pack the tables:
-        # [tokens | positions | row_entry | entry_start | pos0 | slot | logit_rows | logit_slot | attention plan |
-        #  block tables]
+    def _context(self, lay: _Layout, plan, starts, pos0s, slots, max_q: int, max_kv: int):
+        dev = self._meta_dev
+        T, E, M = lay.T, lay.E, lay.M
+        ctx = StepContext(
+            n_rows=T, n_entries=E, max_rows=self.max_rows,
+            tokens=dev[lay.tok:lay.tok + T], positions=dev[lay.pos:lay.pos + T], row_entry=dev[lay.ent:lay.ent + T],
+            entry_start=dev[lay.start:lay.start + E + 1], entry_pos0=dev[lay.pos0:lay.pos0 + E],
+            entry_slot=dev[lay.slot:lay.slot + E], status=self.status, workspace=self.workspace,
+            host_entry_start=starts, host_entry_pos0=pos0s, host_entry_slot=slots,
+            max_q_len=max_q, max_kv_len=max_kv,
+        )
+        plan.bind(dev[lay.plan:lay.plan + lay.n_plan])
+        ctx.attention_plan = plan
+        tables = [dev[off:off + E * mb].view(E, mb) for off, mb in zip(lay.tabs, self.cache.max_blocks)]
+        caches = self.cache.layer_views(tables)
+        logit_rows = dev[lay.lrow:lay.lrow + M] if M else None
+        logit_slot = dev[lay.lslot:lay.lslot + M] if M else None
+        return ctx, caches, logit_rows, logit_slot
+
+    def _run(self, ctx, caches, logit_rows, logit_slot, M: int, sampler):
+        logits = self.model.forward(ctx, caches, self.cache.state_tensors, logit_rows, M)
+        tokens = sampler.sample(logits, logit_slot) if (sampler is not None and logits is not None) else None
+        return logits, tokens
+
+    # ------------------------------------------------------------------ the step
+    def step(self, items: Sequence[StepItem], sampler=None) -> Optional[torch.Tensor]:
+        """Run one step.  Returns float32 logits [wanted, vocab] (None if nothing is wanted), or with
+        ``sampler`` the sampled tokens, int32 [wanted].  Either lives in the engine's scratch memory
+        and is valid until the next step."""
+        T = self._validate(items)
+        self.cache.append([(it.request, len(it.tokens)) for it in items])  # all pages of the step, or none
+        E = len(items)
+        decode_only = T == E
         host, buf, copied = self._ring[self._ring_next]
         self._ring_next = (self._ring_next + 1) % len(self._ring)
         if copied is not None:
             copied.synchronize()  # returns at once unless the GPU is four steps behind
-        o_tok, o_pos, o_ent = 0, T, 2 * T
-        o_start = 3 * T
-        o_pos0 = o_start + E + 1
-        o_slot = o_pos0 + E
-        o_lrow = o_slot + E
-        o_lslot = o_lrow + M
-        o_plan = o_lslot + M
-        row = 0
-        lrow = o_lrow
-        starts, pos0s, slots = [], [], []
-        max_q = max_kv = 0
-        for e, it in enumerate(items):
-            n, p0 = len(it.tokens), it.request.n_tokens
-            buf[o_tok + row:o_tok + row + n] = it.tokens
-            buf[o_pos + row:o_pos + row + n] = np.arange(p0, p0 + n, dtype=np.int32)
-            buf[o_ent + row:o_ent + row + n] = e
-            for w in it.want:
-                buf[lrow] = row + int(w)
-                buf[lrow + M] = it.request.slot
-                lrow += 1
-            starts.append(row)
-            pos0s.append(p0)
-            slots.append(it.request.slot)
-            max_q, max_kv = max(max_q, n), max(max_kv, p0 + n)
-            row += n
-        starts.append(row)
-        buf[o_start:o_start + E + 1] = starts
-        buf[o_pos0:o_pos0 + E] = pos0s
-        buf[o_slot:o_slot + E] = slots
-        # which rows are single decoded tokens, which are prompt portions (64-row tiles)
-        plan = ops.AttentionPlan(starts, pos0s, self.device, into=buf)
-        n_plan = len(plan.host)
-        buf[o_plan:o_plan + n_plan] = plan.host
-        o_tab = o_plan + n_plan
-        o_tab += (-o_tab) % 4  # keep the tables 16-byte aligned
-        tab_offsets = []
-        o = o_tab
-        for gi, mb in enumerate(self.cache.max_blocks):
-            tab = buf[o:o + E * mb].reshape(E, mb)
-            tab.fill(-1)
+
+        want_rows: List[int] = []
+        if decode_only:
+            pos0s = [it.request.n_tokens for it in items]
+            starts = self._arange[:E + 1].tolist()
+            slots = [it.request.slot for it in items]
+            want_rows = [e for e, it in enumerate(items) if len(it.want)]
+            M = len(want_rows)
+            max_q, max_kv = 1, max(pos0s) + 1
+            plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
+            if self.use_graphs:  # the split of the keys must not change from step to step of a graph
+                plan.max_decode_keys = -(-plan.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
+            lay = self._layout(T, E, M, len(plan.host))
+            buf[lay.tok:lay.tok + T] = [it.tokens[0] for it in items]
+            buf[lay.pos:lay.pos + T] = pos0s
+            buf[lay.ent:lay.ent + T] = self._arange[:E]
+            buf[lay.lrow:lay.lrow + M] = want_rows
+            buf[lay.lslot:lay.lslot + M] = [slots[e] for e in want_rows]
+        else:
+            M = sum(len(it.want) for it in items)
+            starts, pos0s, slots = [0], [], []
+            max_q = max_kv = 0
+            for it in items:
+                n, p0 = len(it.tokens), it.request.n_tokens
+                starts.append(starts[-1] + n)
+                pos0s.append(p0)
+                slots.append(it.request.slot)
+                max_q, max_kv = max(max_q, n), max(max_kv, p0 + n)
+            plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
+            lay = self._layout(T, E, M, len(plan.host))
+            lrow = lay.lrow
             for e, it in enumerate(items):
-                blocks = it.request.blocks[gi]
-                tab[e, :len(blocks)] = blocks
-            tab_offsets.append(o)
-            o += E * mb
-        n_meta = o
-        self.last_meta_bytes = 4 * n_meta
-        dev = self._meta_dev
-        dev[:n_meta].copy_(host[:n_meta], non_blocking=True)
+                a, n, p0 = starts[e], len(it.tokens), pos0s[e]
+                buf[lay.tok + a:lay.tok + a + n] = it.tokens
+                buf[lay.pos + a:lay.pos + a + n] = np.arange(p0, p0 + n, dtype=np.int32)
+                buf[lay.ent + a:lay.ent + a + n] = e
+                for w in it.want:
+                    buf[lrow] = a + int(w)
+                    buf[lrow + M] = slots[e]
+                    lrow += 1
+        buf[lay.start:lay.start + E + 1] = starts
+        buf[lay.pos0:lay.pos0 + E] = pos0s
+        buf[lay.slot:lay.slot + E] = slots
+        if lay.n_plan:
+            buf[lay.plan:lay.plan + lay.n_plan] = plan.host
+        for gi, (off, mb) in enumerate(zip(lay.tabs, self.cache.max_blocks)):
+            tab = buf[off:off + E * mb].reshape(E, mb)
+            for e, it in enumerate(items):
+                tab[e] = it.request.table_rows[gi]
+        self.last_meta_bytes = 4 * lay.total
+        self._meta_dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         if copied is not None:
             copied.record()
+        self.last_logit_slot = self._meta_dev[lay.lslot:lay.lslot + M] if M else None
 
-        ctx = StepContext(
-            n_rows=T, n_entries=E, max_rows=self.max_rows,
-            tokens=dev[o_tok:o_tok + T], positions=dev[o_pos:o_pos + T], row_entry=dev[o_ent:o_ent + T],
-            entry_start=dev[o_start:o_start + E + 1], entry_pos0=dev[o_pos0:o_pos0 + E],
-            entry_slot=dev[o_slot:o_slot + E], status=self.status, workspace=self.workspace,
-            host_entry_start=starts, host_entry_pos0=pos0s, host_entry_slot=slots,
-            max_q_len=max_q, max_kv_len=max_kv,
-        )
-        plan.bind(dev[o_plan:o_plan + n_plan])
-        ctx.attention_plan = plan
-        tables = [dev[off:off + E * mb].view(E, mb) for off, mb in zip(tab_offsets, self.cache.max_blocks)]
-        caches = self.cache.layer_views(tables)
-        logit_rows = dev[o_lrow:o_lrow + M] if M else None
-        #: the state slot of the request behind each logits row (for the sampler)
-        self.last_logit_slot = dev[o_lslot:o_lslot + M] if M else None
-        logits = self.model.forward(ctx, caches, self.cache.state_tensors, logit_rows, M)
+        key = None
+        if decode_only and self.use_graphs:
+            key = (T, M, lay.n_plan, plan.max_decode_keys, id(sampler), tuple(want_rows) if M != E else None)
+        cap = self._graphs.get(key) if key is not None else None
+        if cap is not None:
+            cap.graph.replay()
+            self.graph_replays += 1
+            logits, tokens = cap.logits, cap.tokens
+            self.launches_last_step = cap.launches
+        else:
+            args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv)
+            n_seen = self._seen.get(key, 0) if key is not None else 0
+            if key is not None and n_seen >= 1 and len(self._graphs) < self.max_graphs:
+                # the shape was run once already (scratch is sized, attributes are set): capture it
+                graph = torch.cuda.CUDAGraph()
+                before = ops.launch_count()
+                with torch.cuda.graph(graph):
+                    logits, tokens = self._run(*args, M, sampler)
+                cap = _Captured(graph, logits, tokens, ops.launch_count() - before)
+                self._graphs[key] = cap
+                graph.replay()
+                self.graph_replays += 1
+                self.launches_last_step = cap.launches
+            else:
+                before = ops.launch_count()
+                logits, tokens = self._run(*args, M, sampler)
+                self.launches_last_step = ops.launch_count() - before
+                if key is not None:
+                    self._seen[key] = n_seen + 1
 
         for it in items:
             self.cache.commit(it.request, len(it.tokens))
         self.steps_run += 1
         if self.check_status:
             self.raise_on_status()
-        return logits
+        return tokens if sampler is not None else logits
 
     def raise_on_status(self) -> None:
         """Read the device status word (this waits for the step) and raise if a kernel flagged a fault."""

@@ -25,7 +25,7 @@ class KernelError(RuntimeError):
     pass
 
 
-_lib: Optional[ctypes.CDLL] = None
+_lib = None
 
 _c_int, _c_float, _c_ptr = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -52,22 +52,72 @@ _SIGNATURES = {
 }
 
 
-def library() -> ctypes.CDLL:
+class Profiler:
+    """Per-kernel device time, measured with CUDA events around every launcher call while active
+    (the per-op breakdown of the reference's ``--profile``, crates/cli/src/report.rs:22-58)."""
+
+    def __init__(self):
+        self.records = []   # (launcher name, label, start event, end event)
+        self.label = ""
+
+    def summary(self):
+        torch.cuda.synchronize()
+        out = {}
+        for name, label, e0, e1 in self.records:
+            key = (name, label)
+            ms, n = out.get(key, (0.0, 0))
+            out[key] = (ms + e0.elapsed_time(e1), n + 1)
+        return out
+
+
+_profiler: Optional[Profiler] = None
+
+
+def start_profile() -> Profiler:
+    global _profiler
+    _profiler = Profiler()
+    return _profiler
+
+
+def stop_profile() -> None:
+    global _profiler
+    _profiler = None
+
+
+class _Library:
+    """The launchers of the kernel library; with a profiler active each call is bracketed by events."""
+
+    def __init__(self, lib: ctypes.CDLL):
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+            setattr(self, name, self._wrap(name, fn))
+        self.raw = lib
+
+    @staticmethod
+    def _wrap(name, fn):
+        def call(*args):
+            prof = _profiler
+            if prof is None:
+                return fn(*args)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            code = fn(*args)
+            e1.record()
+            prof.records.append((name, prof.label, e0, e1))
+            return code
+        return call
+
+
+def library() -> _Library:
     """The loaded kernel library; compiled on first use if the built file is missing."""
     global _lib
     if _lib is None:
         if not torch.cuda.is_available():
             raise KernelError("nanoinfer_b200 needs a CUDA device: there is no CPU path")
         path = _build.library_path(build=True)
-        lib = ctypes.CDLL(path)
-        for name, argtypes in _SIGNATURES.items():
-            try:
-                fn = getattr(lib, name)
-            except AttributeError:
-                continue
-            fn.argtypes = argtypes
-            fn.restype = _c_int
-        _lib = lib
+        _lib = _Library(ctypes.CDLL(path))
     return _lib
 
 
@@ -75,8 +125,18 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _check(code: int, what: str) -> None:
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernels this process has enqueued through this interface (captured launches count once)."""
+    return _launches
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global _launches
     if code == 0:
+        _launches += kernels
         return
     if code < 0:
         raise KernelError(f"{what}: {_ERR_NAMES.get(code, code)}")
@@ -185,6 +245,8 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
     ``out`` with ``residual``.  bfloat16 runs on the tensor cores where shape and alignment allow
     (rows of 16-byte multiples), else on the CUDA cores; float32 always runs on the CUDA cores in
     true 32-bit arithmetic."""
+    if _profiler is not None:
+        _profiler.label = f"M={M} N={w.shape[0]} K={w.shape[1]}"
     if linear_tc_supported(a, w):
         linear_tc(a, w, bias, out, M, act, residual)
     else:
@@ -244,7 +306,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
                                           page_size, n_pages, float(scale), int(window), chunk, n_splits,
-                                          _ptr(status), _stream()), "attention_decode")
+                                          _ptr(status), _stream()), "attention_decode", 2 if n_splits > 1 else 1)
 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
@@ -266,7 +328,7 @@ class AttentionPlan:
     """Which rows of a step are single decoded tokens and which belong to prompt portions; the
     same for every layer of the step."""
 
-    def __init__(self, entry_start, entry_pos0, device, into=None):
+    def __init__(self, entry_start, entry_pos0, device, bind=True):
         dec, pre, tiles = [], [], []
         self.max_decode_keys = 0
         for e in range(len(entry_start) - 1):
@@ -280,9 +342,8 @@ class AttentionPlan:
         self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
         flat = dec + pre + [v for t in tiles for v in t]
         self.host = flat
-        if into is None:
-            buf = torch.tensor(flat, dtype=torch.int32, device=device) if flat else None
-            self.bind(buf)
+        if bind:
+            self.bind(torch.tensor(flat, dtype=torch.int32, device=device) if flat else None)
 
     def bind(self, buf) -> None:
         """``buf``: a device int32 tensor holding ``self.host``."""
