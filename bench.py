@@ -34,7 +34,7 @@ REFERENCE_B8_TOK_S = 2205.0
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
@@ -78,12 +78,10 @@ def main() -> int:
         torch.cuda.empty_cache()
         return d
 
-    clocks = bs.ClockSampler()
-    clocks.start()
     eng = bs.build_engine(model_dir, "bfloat16", args.batch, context, max_rows=2048)
-    dec = bs.time_decode(eng, args.batch, prompt_len, steps, warmup)
+    dec = bs.time_decode(eng, args.batch, prompt_len, steps, warmup, clocks=bs.ClockSampler())
     launches = dec["launches_per_step"]
-    clock_record = clocks.stop()
+    clock_record = dec["clocks"]
     e2e = bs.time_e2e_decode(eng, args.batch, prompt_len, steps, warmup)
     pre = bs.time_prefill(eng, 2, 1024, runs=5, warmup=3)
     del eng

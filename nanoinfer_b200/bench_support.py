@@ -102,7 +102,7 @@ class ClockSampler:
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, period_ms: int = 100):
+    def __init__(self, period_ms: int = 10):
         self.period_ms = period_ms
         self.proc: Optional[subprocess.Popen] = None
         self.lines: List[str] = []
@@ -125,7 +125,6 @@ class ClockSampler:
     def stop(self) -> Dict[str, object]:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(self.period_ms / 1000.0)
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
@@ -169,7 +168,7 @@ def build_engine(model_dir: str, dtype: str, batch: int, context: int, max_rows:
 
 
 def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 0,
-                flush: bool = True) -> Dict[str, float]:
+                flush: bool = True, clocks: Optional["ClockSampler"] = None) -> Dict[str, float]:
     """Device time of decode steps at a fixed batch: ``batch`` requests are prefilled with
     ``prompt_len`` random tokens, then ``warmup + steps`` greedy decode steps run through the
     engine's step function and sampler; each timed step is bracketed by CUDA events, with an L2
@@ -194,6 +193,8 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     ctx_sum = 0
     torch.cuda.synchronize()
     for s in range(warmup + steps):
+        if s == warmup and clocks is not None:
+            clocks.start()  # sample clocks and throttle reasons during the timed steps only
         items = [StepItem(r, [t], [0]) for r, t in zip(reqs, last)]
         if flusher is not None:
             flusher.flush()
@@ -205,10 +206,11 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
         if s >= warmup:
             times.append(e0.elapsed_time(e1))
             ctx_sum += sum(r.n_tokens for r in reqs)
+    clock_record = clocks.stop() if clocks is not None else None
     for r in reqs:
         eng.cache.close_request(r)
     ms = sum(times) / len(times)
-    return {"ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "mean_context": ctx_sum / (len(times) * batch),
+    return {"clocks": clock_record, "ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "mean_context": ctx_sum / (len(times) * batch),
             "steps": len(times), "launches_per_step": eng.runner.launches_last_step,
             "graph_replays": eng.runner.graph_replays}
 

@@ -50,7 +50,8 @@ int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, voi
                        int page_size, int n_pages, float scale, int window, int* status,
                        cudaStream_t stream);
 
-// Split-KV attention for single decoded tokens (float32 or bfloat16) and its scratch need.
+// Split-KV attention for single decoded tokens (float32 or bfloat16, head sizes up to 128 in steps
+// of 8, pages of a multiple of 16 positions) and its scratch need.
 long long nib_attention_decode_scratch(int n_rows, int n_head, int head_dim, int n_splits);
 int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, float* scratch, void* out,
                          int ldo, const int* block_table, int max_blocks, const int* rows,

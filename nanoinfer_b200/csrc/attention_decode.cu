@@ -9,47 +9,44 @@
 // a small batch still fills the GPU.  Scores are (q . k) * scale for the keys lo..pos, in 32-bit
 // (crates/core/src/kernels/reference.rs:109-142).
 //
-// Inside a block each warp takes 16 keys at a time: two lanes share a key for the dot product
-// (each reads alternate 16-byte pieces of the key row), then the lanes turn to the head
-// dimensions for the weighted sum of the values.
 #include "api.h"
 #include "common.cuh"
 
 namespace nib {
 
 constexpr int DEC_WARPS = 4;
-constexpr int DEC_MAX_PAIRS = 4;  // head_dim <= 256: lane owns dims 2*lane + 64*i, +1
+constexpr int DEC_MAX_HD = 128;
 
-template <typename T> struct Vec16;  // one 16-byte piece of a row
-template <> struct Vec16<float> {
+template <typename T> struct Piece;  // one 16-byte piece of a key or value row
+template <> struct Piece<float> {
   static constexpr int N = 4;
-  static __device__ __forceinline__ float dot(const float* __restrict__ k, const float* q) {
-    const float4 v = *reinterpret_cast<const float4*>(k);
-    return v.x * q[0] + v.y * q[1] + v.z * q[2] + v.w * q[3];
-  }
+  float4 raw;
+  __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void unpack(float* f) const { f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w; }
 };
-template <> struct Vec16<bf16> {
+template <> struct Piece<bf16> {
   static constexpr int N = 8;
-  static __device__ __forceinline__ float dot(const bf16* __restrict__ k, const float* q) {
-    const uint4 raw = *reinterpret_cast<const uint4*>(k);
+  uint4 raw;
+  __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void unpack(float* f) const {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    float s = 0.0f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const float2 f = __bfloat1622float2(h[i]);
-      s = fmaf(f.x, q[2 * i], s);
-      s = fmaf(f.y, q[2 * i + 1], s);
+      const float2 t = __bfloat1622float2(h[i]);
+      f[2 * i] = t.x;
+      f[2 * i + 1] = t.y;
     }
-    return s;
   }
 };
-__device__ __forceinline__ float2 load2(const float* p) { return *reinterpret_cast<const float2*>(p); }
-__device__ __forceinline__ float2 load2(const bf16* p) {
-  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
-}
 
 // partial layout: o [row][head][split][head_dim], ml [row][head][split][2]
-template <typename T>
+//
+// Inside a warp, lanes 2s and 2s+1 own key slot s of every 16-key unit: they split the 16-byte
+// pieces of the key row (and of the value row) between them, so a unit is 32 lanes x several
+// independent 16-byte loads.  Each lane pair keeps an online softmax of its own over its keys
+// (no exchange between lanes inside the loop but the one that completes the dot product); the
+// sixteen pairs, then the four warps, are merged once at the end, in a fixed order.
+template <typename T, int HD_MAX>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* __restrict__ part_o,
                         float* __restrict__ part_ml, T* __restrict__ out, int ldo,
@@ -57,6 +54,8 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
                         int chunk, int n_splits, int* __restrict__ status) {
+  constexpr int VN = Piece<T>::N;
+  constexpr int MAXP = HD_MAX / VN / 2;   // pieces per lane
   extern __shared__ float smem[];
   float* qs = smem;                                  // head_dim
   float* wo = smem + head_dim;                       // DEC_WARPS * head_dim
@@ -83,12 +82,11 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_float(q[(size_t)t * ldq + h * head_dim + d]);
   __syncthreads();
 
-  constexpr int VN = Vec16<T>::N;
-  const int n_pieces = head_dim / VN;  // 16-byte pieces per key row
-  const int key_in_unit = lane >> 1, half = lane & 1;
-  float o[2 * DEC_MAX_PAIRS];
+  const int n_pieces = head_dim / VN;  // 16-byte pieces per row
+  const int slot_in_unit = lane >> 1, half = lane & 1;
+  float o[MAXP * VN];
 #pragma unroll
-  for (int i = 0; i < 2 * DEC_MAX_PAIRS; ++i) o[i] = 0.0f;
+  for (int i = 0; i < MAXP * VN; ++i) o[i] = 0.0f;
   float m = -INFINITY, l = 0.0f;
 
   // units of 16 consecutive keys that lie in one page (page_size is a multiple of 16)
@@ -100,55 +98,81 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
       if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
       continue;
     }
-    const int slot0 = j0 % page_size;
-    const T* kbase = cache + kv_offset(page, 0, hk, slot0, n_kv_head, page_size, head_dim);
-    const T* vbase = cache + kv_offset(page, 1, hk, slot0, n_kv_head, page_size, head_dim);
-    const int j = j0 + key_in_unit;
-    const bool valid = j >= k_begin && j < k_end;
-    float dot = 0.0f;
-    if (valid) {
-      const T* kr = kbase + (size_t)key_in_unit * head_dim;
-      for (int c = half; c < n_pieces; c += 2) dot += Vec16<T>::dot(kr + c * VN, qs + c * VN);
-    }
-    dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-    const float s = valid ? dot * scale : -INFINITY;
-    const float m_new = fmaxf(m, warp_max(s));
-    const float p = valid ? expf(s - m_new) : 0.0f;
-    const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
-    // every key's p sits in two lanes: halve the warp sum
-    l = l * corr + 0.5f * warp_sum(p);
+    const int j = j0 + slot_in_unit;
+    if (j < k_begin || j >= k_end) continue;  // this lane pair's key is outside the range
+    const int slot = j % page_size;
+    const T* kr = cache + kv_offset(page, 0, hk, slot, n_kv_head, page_size, head_dim);
+    const T* vr = cache + kv_offset(page, 1, hk, slot, n_kv_head, page_size, head_dim);
+    Piece<T> kp[MAXP], vp[MAXP];
 #pragma unroll
-    for (int i = 0; i < 2 * DEC_MAX_PAIRS; ++i) o[i] *= corr;
-    const int jj_lo = max(k_begin - j0, 0), jj_hi = min(k_end - j0, 16);
-    for (int jj = jj_lo; jj < jj_hi; ++jj) {
-      const float pj = __shfl_sync(0xffffffffu, p, jj * 2);
-      const T* vr = vbase + (size_t)jj * head_dim;
-#pragma unroll
-      for (int i = 0; i < DEC_MAX_PAIRS; ++i) {
-        const int d = 2 * lane + 64 * i;
-        if (d < head_dim) {
-          const float2 v = load2(vr + d);
-          o[2 * i] = fmaf(pj, v.x, o[2 * i]);
-          o[2 * i + 1] = fmaf(pj, v.y, o[2 * i + 1]);
-        }
+    for (int i = 0; i < MAXP; ++i) {
+      const int c = half + 2 * i;
+      if (c < n_pieces) {
+        kp[i].load(kr + c * VN);
+        vp[i].load(vr + c * VN);
       }
     }
-    m = m_new;
-  }
-  // merge the warps of the block, in warp order
-  if (lane == 0) {
-    wm[warp] = m;
-    wl[warp] = l;
-  }
+    float dot = 0.0f;
 #pragma unroll
-  for (int i = 0; i < DEC_MAX_PAIRS; ++i) {
-    const int d = 2 * lane + 64 * i;
-    if (d < head_dim) {
-      wo[warp * head_dim + d] = o[2 * i];
-      wo[warp * head_dim + d + 1] = o[2 * i + 1];
+    for (int i = 0; i < MAXP; ++i) {
+      const int c = half + 2 * i;
+      if (c < n_pieces) {
+        float f[VN];
+        kp[i].unpack(f);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) dot = fmaf(f[e], qs[c * VN + e], dot);
+      }
+    }
+    // both lanes of the pair are here together (the range test above depends on the pair only)
+    dot += __shfl_xor_sync(0x3u << (lane & ~1), dot, 1);
+    const float s = dot * scale;
+    const float m_new = fmaxf(m, s);
+    const float p = expf(s - m_new);
+    const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+    l = l * corr + p;
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int c = half + 2 * i;
+      if (c < n_pieces) {
+        float f[VN];
+        vp[i].unpack(f);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) o[i * VN + e] = fmaf(p, f[e], o[i * VN + e] * corr);
+      } 
+    }
+  }
+  __syncwarp();
+  // ---- merge the sixteen lane pairs of the warp
+  const float mw = warp_max(m);
+  const float f_lane = (m == -INFINITY) ? 0.0f : expf(m - mw);
+  float lw = (half == 0) ? l * f_lane : 0.0f;
+  lw = warp_sum(lw);
+#pragma unroll
+  for (int i = 0; i < MAXP * VN; ++i) {
+    float v = o[i] * f_lane;
+    v += __shfl_xor_sync(0xffffffffu, v, 2);
+    v += __shfl_xor_sync(0xffffffffu, v, 4);
+    v += __shfl_xor_sync(0xffffffffu, v, 8);
+    v += __shfl_xor_sync(0xffffffffu, v, 16);
+    o[i] = v;
+  }
+  if (lane == 0) {
+    wm[warp] = mw;
+    wl[warp] = lw;
+  }
+  if (slot_in_unit == 0) {
+#pragma unroll
+    for (int i = 0; i < MAXP; ++i) {
+      const int c = half + 2 * i;
+      if (c < n_pieces) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) wo[warp * head_dim + c * VN + e] = o[i * VN + e];
+      }
     }
   }
   __syncthreads();
+  // ---- merge the warps of the block, in warp order
   float M = -INFINITY;
 #pragma unroll
   for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w]);
@@ -206,9 +230,14 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
                          int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
   const size_t smem = (size_t)(head_dim + DEC_WARPS * head_dim + 2 * DEC_WARPS) * sizeof(float);
-  attention_decode_kernel<T><<<grid, DEC_WARPS * 32, smem, stream>>>(
-      (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
-      positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, status);
+  if (head_dim <= 64)
+    attention_decode_kernel<T, 64><<<grid, DEC_WARPS * 32, smem, stream>>>(
+        (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, status);
+  else
+    attention_decode_kernel<T, DEC_MAX_HD><<<grid, DEC_WARPS * 32, smem, stream>>>(
+        (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, status);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return (int)e;
   if (n_splits > 1) {
@@ -238,7 +267,7 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
                                     int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
                                     int window, int chunk, int n_splits, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  if (head_dim <= 0 || head_dim > 64 * DEC_MAX_PAIRS || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (head_dim <= 0 || head_dim > DEC_MAX_HD || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (page_size % 16 != 0 || chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows > 65535 || n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;

@@ -34,8 +34,10 @@ constexpr long long TC_WAIT_CYCLES = 4000000000ll;  // about two seconds
 
 struct TcParams {
   int p_rows, q_rows, K;
-  int bq;            // rows of the Q tile = MMA N (multiple of 16)
+  int bq;            // rows of the Q tile = MMA N (multiple of 16, at most 256)
   int stages;
+  int k_sub;         // 64-wide K blocks per pipeline stage (1 or 2)
+  int kb_per_split;  // 64-wide K blocks per split of K (grid.z splits; their tiles are summed by reduce-add)
   int swap;          // 0: P = activations (out[p, q]); 1: P = weights (out[q, p])
   void* out;
   int ldo;
@@ -171,10 +173,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = prm.stages, bq = prm.bq;
-  const uint32_t p_bytes = TC_BP * TC_BK * 2, q_bytes = (uint32_t)bq * TC_BK * 2;
-  const uint32_t stage_bytes = p_bytes + q_bytes;  // both multiples of 1024 (bq is a multiple of 16: 2 KB)
+  const int k_sub = prm.k_sub;
+  const uint32_t p_bytes = TC_BP * TC_BK * 2, q_bytes = (uint32_t)bq * TC_BK * 2;  // one 64-wide block each
+  const uint32_t stage_bytes = (uint32_t)k_sub * (p_bytes + q_bytes);  // multiples of 1024 (bq % 16 == 0)
   const int p0 = blockIdx.x * TC_BP, q0 = blockIdx.y * bq;
-  const int num_kb = (prm.K + TC_BK - 1) / TC_BK;
+  // this block's share of K, in 64-wide blocks, and in pipeline stages
+  const int kb_begin = blockIdx.z * prm.kb_per_split;
+  const int kb_end = min((prm.K + TC_BK - 1) / TC_BK, kb_begin + prm.kb_per_split);
+  const int num_kb = (kb_end - kb_begin + k_sub - 1) / k_sub;
+  const bool first_split = blockIdx.z == 0;
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < bq) tmem_cols <<= 1;
 
@@ -207,8 +214,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
       if (lane == 0) {
         uint8_t* sp = smem + (size_t)s * stage_bytes;
         mbar_expect_tx(&full_bar[s], stage_bytes);
-        tma_load_2d(sp, &map_p, &full_bar[s], kb * TC_BK, p0);
-        tma_load_2d(sp + p_bytes, &map_q, &full_bar[s], kb * TC_BK, q0);
+        for (int sub = 0; sub < k_sub; ++sub) {
+          // a block past this split's end is asked for past the end of K: it arrives as zeros
+          const int kb64 = kb_begin + kb * k_sub + sub;
+          const int kx = (kb64 < kb_end ? kb64 : (prm.K + TC_BK - 1) / TC_BK) * TC_BK;
+          tma_load_2d(sp + sub * p_bytes, &map_p, &full_bar[s], kx, p0);
+          tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[s], kx, q0);
+        }
       }
       ++issued;
       if (++s == stages) {
@@ -235,12 +247,15 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
       if (!warp_mbar_wait(&full_bar[s], parity, abort_flag, lane)) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t pa = smem_u32(smem + (size_t)s * stage_bytes);
-        const uint32_t qa = pa + p_bytes;
+        const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
+        for (int sub = 0; sub < k_sub; ++sub) {
+          const uint32_t pa = base + sub * p_bytes;
+          const uint32_t qa = base + k_sub * p_bytes + sub * q_bytes;
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          // 16 bf16 = 32 bytes further along K inside the swizzled row
-          umma_bf16(tmem_base, umma_desc(pa + k * 32), umma_desc(qa + k * 32), idesc, (kb | k) != 0);
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            // 16 bf16 = 32 bytes further along K inside the swizzled row
+            umma_bf16(tmem_base, umma_desc(pa + k * 32), umma_desc(qa + k * 32), idesc, (kb | sub | k) != 0);
+          }
         }
         umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
       }
@@ -265,7 +280,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     if (ok && prm.tma_store) {
       // Every MMA has finished, so every pipeline buffer is idle: the tile is staged there.
-      const float bias_p = (prm.swap && prm.bias && p_ok) ? prm.bias[p] : 0.0f;
+      const float bias_p = (prm.swap && prm.bias && p_ok && first_split) ? prm.bias[p] : 0.0f;
       for (int c0 = 0; c0 < bq; c0 += 16) {
         float v[16];
         tmem_ld16(lane_addr + (uint32_t)c0, v);
@@ -274,7 +289,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int n = q0 + c0 + j;
-            v[j] = apply_act(v[j] + ((prm.bias && n < prm.q_rows) ? prm.bias[n] : 0.0f), prm.act);
+            v[j] = apply_act(v[j] + ((prm.bias && first_split && n < prm.q_rows) ? prm.bias[n] : 0.0f), prm.act);
           }
           if (prm.out_f32) {
             uint8_t* blk = smem + (size_t)(c0 / 32) * 16384 + (size_t)pl * 128;
@@ -431,28 +446,58 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   prm.residual = residual;
   prm.status = status;
   prm.swap = M <= 128;
+  const int esz = prm.out_f32 ? 4 : 2;
+  // TMA can store the tile if the output's rows are 16-byte multiples (it also clips a store at the
+  // tensor's edge in 16-byte pieces, so the row length must be a multiple too)
+  const bool tma_ok = ((uintptr_t)out & 15) == 0 && ((long)ldo * esz) % 16 == 0 && ((long)N * esz) % 16 == 0;
+  const int num_kb64 = (K + TC_BK - 1) / TC_BK;
   const void *p_base, *q_base;
-  int p_ld, q_ld;
+  int p_ld, q_ld, splits = 1;
   if (prm.swap) {
     prm.p_rows = N; prm.q_rows = M; p_base = w; p_ld = ldw; q_base = a; q_ld = lda;
     prm.bq = (M + 15) / 16 * 16;
+    prm.tma_store = tma_ok;
+    // few tiles cannot pull the weights at full bandwidth: split K where the tiles can be summed
+    // in memory (the residual add), at least two 64-wide blocks per split
+    const int tiles = (N + TC_BP - 1) / TC_BP;
+    if (residual && tma_ok && tiles < 148) {
+      splits = (148 + tiles - 1) / tiles;
+      if (splits > num_kb64 / 2) splits = num_kb64 / 2;
+      if (splits < 1) splits = 1;
+    }
   } else {
     prm.p_rows = M; prm.q_rows = N; p_base = a; p_ld = lda; q_base = w; q_ld = ldw;
-    const long tiles128 = (long)((M + TC_BP - 1) / TC_BP) * ((N + 127) / 128);
-    prm.bq = (tiles128 >= 148 && N >= 128) ? 128 : 64;
-    if (N < prm.bq) prm.bq = (N + 15) / 16 * 16;
+    // pick the Q tile (and a split of K for residual outputs) that fills the 148 SMs best
+    const int p_tiles = (M + TC_BP - 1) / TC_BP;
+    double best = 1e30;
+    int best_bq = 64, best_splits = 1;
+    for (int bq = 256; bq >= 64; bq >>= 1) {
+      if (bq > 64 && N < bq) continue;
+      const int tiles = p_tiles * ((N + bq - 1) / bq);
+      const int max_splits = (residual && tma_ok) ? (num_kb64 >= 8 ? num_kb64 / 4 : 1) : 1;
+      for (int sp = 1; sp <= max_splits && sp <= 8; ++sp) {
+        const long ctas = (long)tiles * sp;
+        const long waves = (ctas + 147) / 148;
+        const double kb = (double)((num_kb64 + sp - 1) / sp);
+        const double per_kb = 2.0 * bq > 300.0 ? 2.0 * bq : 300.0;   // MMA cycles vs issue cycles
+        const double cost = waves * (kb * per_kb + 2500.0 + 14.0 * bq);
+        if (cost < best) { best = cost; best_bq = bq; best_splits = sp; }
+      }
+    }
+    prm.bq = best_bq;
+    splits = best_splits;
+    if (N < 64) prm.bq = (N + 15) / 16 * 16;
+    prm.tma_store = tma_ok && prm.bq % 64 == 0;
+    if (!prm.tma_store) splits = 1;
   }
-  // TMA can store the tile if the output's rows are 16-byte multiples; the plain orientation
-  // also needs whole 128-byte blocks across the tile
-  const int esz = prm.out_f32 ? 4 : 2;
-  // (TMA clips a store at the tensor's edge in 16-byte pieces, so the row length must be a multiple too)
-  prm.tma_store = ((uintptr_t)out & 15) == 0 && ((long)ldo * esz) % 16 == 0 && ((long)N * esz) % 16 == 0 &&
-                  (prm.swap || prm.bq % 64 == 0);
-  const int stage_bytes = TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2;
-  const int num_kb = (K + TC_BK - 1) / TC_BK;
+  prm.kb_per_split = (num_kb64 + splits - 1) / splits;
+  splits = (num_kb64 + prm.kb_per_split - 1) / prm.kb_per_split;
+  prm.k_sub = (prm.bq <= 128 && prm.kb_per_split >= 4) ? 2 : 1;
+  const int stage_bytes = prm.k_sub * (TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2);
+  const int num_stage_steps = (prm.kb_per_split + prm.k_sub - 1) / prm.k_sub;
   int stages = (200 * 1024) / stage_bytes;
   if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
-  if (stages > num_kb) stages = num_kb;
+  if (stages > num_stage_steps) stages = num_stage_steps;
   if (stages < 1) stages = 1;
   prm.stages = stages;
   size_t tile_bytes = (size_t)stages * stage_bytes;
@@ -477,7 +522,7 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq);
+  dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq, splits);
   if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   linear_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
   NIB_LAUNCH_CHECK();

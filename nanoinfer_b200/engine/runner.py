@@ -15,10 +15,11 @@ batch engine (crates/metal/src/batch.rs:1-15, ``Batch::step`` batch.rs:259-315).
      order of the items and of their ``want`` lists, or, when a sampler is given, one sampled
      token per logits row.
 
-Steps made of single decoded tokens only are launch-bound, so their kernels are captured once
-per shape in a CUDA graph and replayed (the reference keeps its decode loop on the GPU for the
-same reason, ``decode_resident``, batch.rs:322-363).  What a graph bakes in is only the shape of
-the step: the tables it reads are rewritten before every replay.
+Steps are launch-bound (a decode step is a hundred small kernels), so the kernels of a step are
+captured in a CUDA graph the second time its shape is seen, and replayed from then on (the
+reference keeps its decode loop on the GPU for the same reason, ``decode_resident``,
+batch.rs:322-363).  What a graph bakes in is only the shape of the step: the tables it reads are
+rewritten before every replay.
 """
 from __future__ import annotations
 
@@ -246,6 +247,8 @@ class ModelRunner:
                 slots.append(it.request.slot)
                 max_q, max_kv = max(max_q, n), max(max_kv, p0 + n)
             plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
+            if self.use_graphs:
+                plan.max_decode_keys = -(-plan.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
             lay = self._layout(T, E, M, len(plan.host))
             lrow = lay.lrow
             for e, it in enumerate(items):
@@ -272,9 +275,11 @@ class ModelRunner:
             copied.record()
         self.last_logit_slot = self._meta_dev[lay.lslot:lay.lslot + M] if M else None
 
+        # a graph bakes in the shape of the step only: row, entry and logits counts, how the rows
+        # split into single tokens and 64-row prompt tiles, and the split of the decode keys
         key = None
-        if decode_only and self.use_graphs:
-            key = (T, M, lay.n_plan, plan.max_decode_keys, id(sampler), tuple(want_rows) if M != E else None)
+        if self.use_graphs:
+            key = (T, E, M, plan.n_decode, plan.n_prefill_rows, plan.n_tiles, plan.max_decode_keys, id(sampler))
         cap = self._graphs.get(key) if key is not None else None
         if cap is not None:
             cap.graph.replay()

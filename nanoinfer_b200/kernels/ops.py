@@ -365,7 +365,7 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         plan = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, q.device)
         ctx.attention_plan = plan
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
-    fast_pages = page_size % 16 == 0 and head_dim % 8 == 0
+    fast_pages = page_size % 16 == 0 and head_dim % 8 == 0 and head_dim <= 128
     if not fast_pages:
         attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
                        window, ctx.status)
