@@ -42,6 +42,13 @@ int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw,
                   void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
                   cudaStream_t stream);
 
+// The fused query/key/value projection for steps of at most 128 rows (bfloat16): queries go to
+// out, keys and values straight into one layer of the paged cache.
+int nib_linear_tc_qkv(const void* a, int lda, const void* w, int ldw, const float* bias, void* out, int ldo,
+                      int M, int N, int K, void* cache, const int* block_table, int max_blocks,
+                      const int* row_entry, const int* positions, int q_dim, int n_kv_head, int head_dim,
+                      int page_size, int n_pages, int* status, cudaStream_t stream);
+
 // Causal attention of T query rows over the paged cache (general SIMT kernel).  rows: the
 // step's rows to process (nullptr: rows 0..T-1).
 int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
@@ -57,7 +64,7 @@ int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, f
                          int ldo, const int* block_table, int max_blocks, const int* rows,
                          const int* row_entry, const int* positions, int n_rows, int n_head, int n_kv_head,
                          int head_dim, int page_size, int n_pages, float scale, int window, int chunk,
-                         int n_splits, int* status, cudaStream_t stream);
+                         int n_splits, int* counters, int* status, cudaStream_t stream);
 
 // Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16).
 int nib_attention_prefill_supported(int head_dim);
@@ -72,9 +79,10 @@ int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStr
 // One token per logits row.  temperature, top_k and rng_state are per-slot arrays indexed by
 // row_slot[r]: argmax where temperature <= 0, else temperature / top-k sampling with the
 // request's own xorshift64* state (advanced by one draw).
+// scratch: 2 * n_rows 64-bit words that are zero before the first call (the kernel leaves them zero).
 int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
-               cudaStream_t stream);
+               unsigned long long* scratch, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

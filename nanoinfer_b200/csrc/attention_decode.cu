@@ -2,8 +2,8 @@
 //
 // One block handles one (row, head, split of the keys): it streams its share of the paged keys
 // and values once, keeps an online softmax (running maximum m, sum l, unnormalised output o) and
-// writes the partial (m, l, o); a second kernel merges the splits of a (row, head) in a fixed
-// order:  M = max m_s;  L = sum l_s e^(m_s - M);  out = sum o_s e^(m_s - M) / L.
+// writes the partial (m, l, o); the block of a (row, head) that finishes last merges its splits in
+// split order:  M = max m_s;  L = sum l_s e^(m_s - M);  out = sum o_s e^(m_s - M) / L.
 // This is the reference's b_attn_split / b_attn_merge pair
 // (crates/metal/src/shaders/batch.metal:349-424) with the split size chosen by the host so that
 // a small batch still fills the GPU.  Scores are (q . k) * scale for the keys lo..pos, in 32-bit
@@ -53,7 +53,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
-                        int chunk, int n_splits, int* __restrict__ status) {
+                        int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status) {
   constexpr int VN = Piece<T>::N;
   constexpr int MAXP = HD_MAX / VN / 2;   // pieces per lane
   extern __shared__ float smem[];
@@ -72,13 +72,14 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   const int hk = h / (n_head / n_kv_head);
   const size_t pidx = ((size_t)r * n_head + h) * n_splits + split;
 
-  if (k_begin >= k_end) {  // nothing in this split: the merge skips l == 0
+  __shared__ int is_last_sh;
+  const bool empty = k_begin >= k_end;  // nothing in this split: the merge skips l == 0
+  if (empty) {
     if (threadIdx.x == 0) {
       part_ml[2 * pidx] = -INFINITY;
       part_ml[2 * pidx + 1] = 0.0f;
     }
-    return;
-  }
+  } else {
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_float(q[(size_t)t * ldq + h * head_dim + d]);
   __syncthreads();
 
@@ -196,29 +197,34 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
     part_ml[2 * pidx] = M;
     part_ml[2 * pidx + 1] = L;
   }
-}
-
-template <typename T>
-__global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                       T* __restrict__ out, int ldo, const int* __restrict__ rows, int n_head,
-                                       int head_dim, int n_splits) {
-  const int h = blockIdx.x, r = blockIdx.y;
-  const int t = rows ? rows[r] : r;
+  }  // !empty
+  if (n_splits == 1) return;
+  // ---- the block that finishes last merges the splits of its (row, head), in split order
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(&counters[r * n_head + h], 1);
+    is_last_sh = arrived == n_splits - 1;
+    if (is_last_sh) counters[r * n_head + h] = 0;  // zero again for the next launch
+  }
+  __syncthreads();
+  if (!is_last_sh) return;
+  __threadfence();
   const size_t base = ((size_t)r * n_head + h) * n_splits;
-  float M = -INFINITY;
-  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[2 * (base + s)]);
-  float L = 0.0f;
-  for (int s = 0; s < n_splits; ++s) {
-    const float ls = part_ml[2 * (base + s) + 1];
-    if (ls > 0.0f) L += ls * expf(part_ml[2 * (base + s)] - M);
+  float Mx = -INFINITY;
+  for (int sp = 0; sp < n_splits; ++sp) Mx = fmaxf(Mx, part_ml[2 * (base + sp)]);
+  float Lx = 0.0f;
+  for (int sp = 0; sp < n_splits; ++sp) {
+    const float ls = part_ml[2 * (base + sp) + 1];
+    if (ls > 0.0f) Lx += ls * expf(part_ml[2 * (base + sp)] - Mx);
   }
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
-    for (int s = 0; s < n_splits; ++s) {
-      const float ls = part_ml[2 * (base + s) + 1];
-      if (ls > 0.0f) acc += part_o[(base + s) * head_dim + d] * expf(part_ml[2 * (base + s)] - M);
+    for (int sp = 0; sp < n_splits; ++sp) {
+      const float ls = part_ml[2 * (base + sp) + 1];
+      if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * expf(part_ml[2 * (base + sp)] - Mx);
     }
-    out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L);
+    out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / Lx);
   }
 }
 
@@ -227,24 +233,17 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
                          int ldo, const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                          const int* positions, int n_rows, int n_head, int n_kv_head, int head_dim,
                          int page_size, int n_pages, float scale, int window, int chunk, int n_splits,
-                         int* status, cudaStream_t stream) {
+                         int* counters, int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
   const size_t smem = (size_t)(head_dim + DEC_WARPS * head_dim + 2 * DEC_WARPS) * sizeof(float);
   if (head_dim <= 64)
     attention_decode_kernel<T, 64><<<grid, DEC_WARPS * 32, smem, stream>>>(
         (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, status);
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
   else
     attention_decode_kernel<T, DEC_MAX_HD><<<grid, DEC_WARPS * 32, smem, stream>>>(
         (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, status);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return (int)e;
-  if (n_splits > 1) {
-    dim3 mgrid(n_head, n_rows);
-    attention_merge_kernel<T><<<mgrid, 64, 0, stream>>>(part_o, part_ml, (T*)out, ldo, rows, n_head, head_dim,
-                                                         n_splits);
-  }
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
   NIB_LAUNCH_CHECK();
 }
 
@@ -260,27 +259,29 @@ extern "C" long long nib_attention_decode_scratch(int n_rows, int n_head, int he
 
 // rows: indices of the step's rows to process (nullptr: rows 0..n_rows-1).  Keys are split into
 // chunks of `chunk` positions (a multiple of 16); n_splits = ceil(longest key range / chunk).
-// scratch holds nib_attention_decode_scratch(...) floats.
+// scratch holds nib_attention_decode_scratch(...) floats; counters holds n_rows * n_head ints that are
+// zero before the first call (the kernel leaves them zero).
 extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, float* scratch,
                                     void* out, int ldo, const int* block_table, int max_blocks, const int* rows,
                                     const int* row_entry, const int* positions, int n_rows, int n_head,
                                     int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
-                                    int window, int chunk, int n_splits, int* status, cudaStream_t stream) {
+                                    int window, int chunk, int n_splits, int* counters, int* status,
+                                    cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (head_dim <= 0 || head_dim > DEC_MAX_HD || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (page_size % 16 != 0 || chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows > 65535 || n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (n_splits > 1 && scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  if (n_splits > 1 && (scratch == nullptr || counters == nullptr)) return NIB_ERR_BAD_ARGUMENT;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)n_rows * n_head * n_splits * head_dim : nullptr;
   if (dtype == DT_F32)
     return launch_decode<float>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                 positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                                chunk, n_splits, status, stream);
+                                chunk, n_splits, counters, status, stream);
   if (dtype == DT_BF16)
     return launch_decode<bf16>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                               chunk, n_splits, status, stream);
+                               chunk, n_splits, counters, status, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }

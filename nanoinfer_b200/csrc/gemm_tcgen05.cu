@@ -47,6 +47,14 @@ struct TcParams {
   int residual;
   int tma_store;     // 1: the epilogue stages the tile in shared memory and stores it with TMA
   int* status;
+  // Optional (swapped orientation only): output features from q_dim on are keys and values, which go
+  // straight to their slots in the paged cache instead of to `out` (the reference's QKV epilogue,
+  // crates/metal/src/shaders/batch.metal:155-164)
+  bf16* kv_cache;
+  const int* kv_block_table;
+  const int* kv_row_entry;
+  const int* kv_positions;
+  int kv_max_blocks, kv_q_dim, kv_heads, kv_head_dim, kv_page_size, kv_n_pages;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -121,6 +129,26 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, const 
   asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.bulk_group [%0, {%2, %3}], [%1];"
                ::"l"((uint64_t)map), "r"(smem_u32(src)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16_issue(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+// The epilogue's activation.  The result is rounded to bfloat16 (8 bits of mantissa), so the tanh
+// form uses the hardware tanh (relative error about 2^-11); the erf form keeps the accurate erff.
+template <int ACT>
+__device__ __forceinline__ float epilogue_act(float u) {
+  if (ACT == ACT_GELU_TANH) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.7978845608028654f * (u + 0.044715f * u * u * u)));
+    return 0.5f * u * (1.0f + t);
+  }
+  if (ACT == ACT_GELU_ERF) return gelu_erf(u);
+  return u;
+}
 __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
   uint32_t r[16];
   asm volatile(
@@ -158,6 +186,9 @@ __device__ __forceinline__ bool warp_mbar_wait(uint64_t* bar, uint32_t parity, v
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
+// ACT is a template parameter so that each instantiation carries the code of its own activation only
+// (the unrolled epilogue would otherwise hold dozens of copies of erff).
+template <int ACT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                  const __grid_constant__ CUtensorMap map_o, const TcParams prm) {
@@ -281,42 +312,61 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     if (ok && prm.tma_store) {
       // Every MMA has finished, so every pipeline buffer is idle: the tile is staged there.
       const float bias_p = (prm.swap && prm.bias && p_ok && first_split) ? prm.bias[p] : 0.0f;
-      for (int c0 = 0; c0 < bq; c0 += 16) {
-        float v[16];
-        tmem_ld16(lane_addr + (uint32_t)c0, v);
-        if (!prm.swap) {
-          // normal orientation: blocks of [128 rows][128 bytes] in the 128-byte swizzle
+      // 64 columns at a time: four tensor-memory loads in flight, one wait
+      for (int g0 = 0; g0 < bq; g0 += 64) {
+        uint32_t raw[4][16];
+        const int n_sub = min(4, (bq - g0) / 16);  // uniform over the block
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int n = q0 + c0 + j;
-            v[j] = apply_act(v[j] + ((prm.bias && first_split && n < prm.q_rows) ? prm.bias[n] : 0.0f), prm.act);
-          }
-          if (prm.out_f32) {
-            uint8_t* blk = smem + (size_t)(c0 / 32) * 16384 + (size_t)pl * 128;
+        for (int sub = 0; sub < 4; ++sub)
+          if (sub < n_sub) tmem_ld16_issue(lane_addr + (uint32_t)(g0 + sub * 16), raw[sub]);
+        tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; j += 4) {
-              const int chunk = ((c0 % 32 + j) / 4) ^ (pl & 7);
-              *reinterpret_cast<float4*>(blk + chunk * 16) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        for (int sub = 0; sub < 4; ++sub) {
+          if (sub >= n_sub) continue;
+          const int c0 = g0 + sub * 16;
+          float v[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[sub][j]);
+          if (!prm.swap) {
+            // normal orientation: blocks of [128 rows][128 bytes] in the 128-byte swizzle
+            if (prm.bias && first_split) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) {
+                const int n = q0 + c0 + j;
+                v[j] += (n < prm.q_rows) ? prm.bias[n] : 0.0f;
+              }
+            }
+            if (ACT != ACT_NONE) {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) v[j] = epilogue_act<ACT>(v[j]);
+            }
+            if (prm.out_f32) {
+              uint8_t* blk = smem + (size_t)(c0 / 32) * 16384 + (size_t)pl * 128;
+#pragma unroll
+              for (int j = 0; j < 16; j += 4) {
+                const int chunk = ((c0 % 32 + j) / 4) ^ (pl & 7);
+                *reinterpret_cast<float4*>(blk + chunk * 16) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              }
+            } else {
+              uint8_t* blk = smem + (size_t)(c0 / 64) * 16384 + (size_t)pl * 128;
+#pragma unroll
+              for (int j = 0; j < 16; j += 8) {
+                const int chunk = ((c0 % 64 + j) / 8) ^ (pl & 7);
+                *reinterpret_cast<uint4*>(blk + chunk * 16) =
+                    make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]),
+                               pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
+              }
             }
           } else {
-            uint8_t* blk = smem + (size_t)(c0 / 64) * 16384 + (size_t)pl * 128;
+            // swapped orientation: a dense [tokens][128 features] tile, lanes along the features
 #pragma unroll
-            for (int j = 0; j < 16; j += 8) {
-              const int chunk = ((c0 % 64 + j) / 8) ^ (pl & 7);
-              *reinterpret_cast<uint4*>(blk + chunk * 16) =
-                  make_uint4(pack_bf16(v[j], v[j + 1]), pack_bf16(v[j + 2], v[j + 3]), pack_bf16(v[j + 4], v[j + 5]),
-                             pack_bf16(v[j + 6], v[j + 7]));
+            for (int j = 0; j < 16; ++j) {
+              const float x = epilogue_act<ACT>(v[j] + bias_p);
+              if (prm.out_f32)
+                reinterpret_cast<float*>(smem)[(c0 + j) * TC_BP + pl] = x;
+              else
+                reinterpret_cast<bf16*>(smem)[(c0 + j) * TC_BP + pl] = __float2bfloat16_rn(x);
             }
-          }
-        } else {
-          // swapped orientation: a dense [tokens][128 features] tile, lanes along the features
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float x = apply_act(v[j] + bias_p, prm.act);
-            if (prm.out_f32)
-              reinterpret_cast<float*>(smem)[(c0 + j) * TC_BP + pl] = x;
-            else
-              reinterpret_cast<bf16*>(smem)[(c0 + j) * TC_BP + pl] = __float2bfloat16_rn(x);
           }
         }
       }
@@ -347,24 +397,46 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           // out[p, q0 + c0 + j]: this thread writes 16 consecutive features of its own row
           const int n0 = q0 + c0;
           const int nv = min(16, prm.q_rows - n0);
-          for (int j = 0; j < nv; ++j) {
-            const float x = apply_act(v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f), prm.act);
-            if (prm.out_f32) {
-              float* o = (float*)prm.out + (size_t)p * prm.ldo + n0 + j;
-              *o = prm.residual ? *o + x : x;
-            } else {
-              ((bf16*)prm.out)[(size_t)p * prm.ldo + n0 + j] = __float2bfloat16_rn(x);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {  // unrolled with a guard: v[] must stay in registers
+            if (j < nv) {
+              const float x = epilogue_act<ACT>(v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f));
+              if (prm.out_f32) {
+                float* o = (float*)prm.out + (size_t)p * prm.ldo + n0 + j;
+                *o = prm.residual ? *o + x : x;
+              } else {
+                ((bf16*)prm.out)[(size_t)p * prm.ldo + n0 + j] = __float2bfloat16_rn(x);
+              }
             }
           }
         } else {
           // out[q0 + c0 + j, p]: the warp's lanes hold consecutive features of one token's row
           const float b = prm.bias ? prm.bias[p] : 0.0f;
+          const bool to_cache = prm.kv_cache != nullptr && p >= prm.kv_q_dim;
+          int kv_which = 0, kv_head = 0, kv_d = 0;
+          if (to_cache) {
+            const int kv_dim = prm.kv_heads * prm.kv_head_dim;
+            const int rem = p - prm.kv_q_dim;
+            kv_which = rem / kv_dim;
+            kv_head = (rem % kv_dim) / prm.kv_head_dim;
+            kv_d = rem % prm.kv_head_dim;
+          }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = q0 + c0 + j;
             if (m < prm.q_rows) {
-              const float x = apply_act(v[j] + b, prm.act);
-              if (prm.out_f32) {
+              const float x = epilogue_act<ACT>(v[j] + b);
+              if (to_cache) {
+                const int pos = prm.kv_positions[m];
+                const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks +
+                                                    pos / prm.kv_page_size];
+                if (page < 0 || page >= prm.kv_n_pages) {
+                  *prm.status = NIB_STATUS_BAD_PAGE;
+                } else {
+                  prm.kv_cache[kv_offset(page, kv_which, kv_head, pos % prm.kv_page_size, prm.kv_heads,
+                                         prm.kv_page_size, prm.kv_head_dim) + kv_d] = __float2bfloat16_rn(x);
+                }
+              } else if (prm.out_f32) {
                 float* o = (float*)prm.out + (size_t)m * prm.ldo + p;
                 *o = prm.residual ? *o + x : x;
               } else {
@@ -430,9 +502,17 @@ extern "C" int nib_linear_tc_supported(const void* a, int lda, const void* w, in
   return 1;
 }
 
-extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
-                             void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
-                             cudaStream_t stream) {
+struct KvTarget {
+  void* cache;
+  const int* block_table;
+  const int* row_entry;
+  const int* positions;
+  int max_blocks, q_dim, heads, head_dim, page_size, n_pages;
+};
+
+static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
+                     int ldo, int M, int N, int K, int act, int residual, const KvTarget* kv, int* status,
+                     cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (!nib_linear_tc_supported(a, lda, w, ldw, K)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (residual && out_dtype != DT_F32) return NIB_ERR_BAD_ARGUMENT;
@@ -445,6 +525,19 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   prm.act = act;
   prm.residual = residual;
   prm.status = status;
+  prm.kv_cache = nullptr;
+  prm.kv_block_table = prm.kv_row_entry = prm.kv_positions = nullptr;
+  prm.kv_max_blocks = prm.kv_q_dim = prm.kv_heads = prm.kv_head_dim = prm.kv_page_size = prm.kv_n_pages = 0;
+  if (kv != nullptr) {
+    if (M > 128 || out_dtype != DT_BF16 || act != ACT_NONE || residual) return NIB_ERR_BAD_ARGUMENT;
+    if (N != kv->q_dim + 2 * kv->heads * kv->head_dim) return NIB_ERR_BAD_ARGUMENT;
+    prm.kv_cache = (bf16*)kv->cache;
+    prm.kv_block_table = kv->block_table;
+    prm.kv_row_entry = kv->row_entry;
+    prm.kv_positions = kv->positions;
+    prm.kv_max_blocks = kv->max_blocks; prm.kv_q_dim = kv->q_dim; prm.kv_heads = kv->heads;
+    prm.kv_head_dim = kv->head_dim; prm.kv_page_size = kv->page_size; prm.kv_n_pages = kv->n_pages;
+  }
   prm.swap = M <= 128;
   const int esz = prm.out_f32 ? 4 : 2;
   // TMA can store the tile if the output's rows are 16-byte multiples (it also clips a store at the
@@ -456,7 +549,7 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   if (prm.swap) {
     prm.p_rows = N; prm.q_rows = M; p_base = w; p_ld = ldw; q_base = a; q_ld = lda;
     prm.bq = (M + 15) / 16 * 16;
-    prm.tma_store = tma_ok;
+    prm.tma_store = tma_ok && kv == nullptr;
     // few tiles cannot pull the weights at full bandwidth: split K where the tiles can be summed
     // in memory (the residual add), at least two 64-wide blocks per split
     const int tiles = (N + TC_BP - 1) / TC_BP;
@@ -495,7 +588,12 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
   prm.k_sub = (prm.bq <= 128 && prm.kb_per_split >= 4) ? 2 : 1;
   const int stage_bytes = prm.k_sub * (TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2);
   const int num_stage_steps = (prm.kb_per_split + prm.k_sub - 1) / prm.k_sub;
-  int stages = (200 * 1024) / stage_bytes;
+  // A deep pipeline (one block per SM) unless the grid is several waves of bandwidth-bound blocks
+  // (the head's 393 tiles of a decode step): then about 72 KB per block, so that three blocks share
+  // an SM and one's prologue and epilogue hide behind the others' loads.
+  const long n_ctas = (long)((prm.p_rows + TC_BP - 1) / TC_BP) * ((prm.q_rows + prm.bq - 1) / prm.bq) * splits;
+  int stages = ((prm.swap && n_ctas > 2 * 148 ? 72 : 200) * 1024) / stage_bytes;
+  if (stages < 2) stages = 2;
   if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
   if (stages > num_stage_steps) stages = num_stage_steps;
   if (stages < 1) stages = 1;
@@ -518,12 +616,44 @@ extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* 
 
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 225 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(linear_tc_kernel<ACT_NONE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         225 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(linear_tc_kernel<ACT_GELU_TANH>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               225 * 1024);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(linear_tc_kernel<ACT_GELU_ERF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               225 * 1024);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq, splits);
   if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
-  linear_tc_kernel<<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+  if (act == ACT_GELU_TANH)
+    linear_tc_kernel<ACT_GELU_TANH><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+  else if (act == ACT_GELU_ERF)
+    linear_tc_kernel<ACT_GELU_ERF><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+  else if (act == ACT_NONE)
+    linear_tc_kernel<ACT_NONE><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                             void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
+                             cudaStream_t stream) {
+  return launch_tc(out_dtype, a, lda, w, ldw, bias, out, ldo, M, N, K, act, residual, nullptr, status, stream);
+}
+
+// The fused query/key/value projection of a step of at most 128 rows: out[m, n] for the first q_dim
+// features (the queries, bfloat16), the rest written to the rows' slots in one cache layer
+// [n_pages, 2, n_kv_head, page_size, head_dim] through the block tables.
+extern "C" int nib_linear_tc_qkv(const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
+                                 int ldo, int M, int N, int K, void* cache, const int* block_table,
+                                 int max_blocks, const int* row_entry, const int* positions, int q_dim,
+                                 int n_kv_head, int head_dim, int page_size, int n_pages, int* status,
+                                 cudaStream_t stream) {
+  KvTarget kv{cache, block_table, row_entry, positions, max_blocks, q_dim, n_kv_head, head_dim, page_size, n_pages};
+  return launch_tc(DT_BF16, a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE, 0, &kv, status, stream);
 }

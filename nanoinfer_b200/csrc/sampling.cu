@@ -21,6 +21,7 @@
 namespace nib {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_CHUNKS = 16;   // blocks that share a greedy row
 
 __device__ __forceinline__ uint32_t float_key(float f) {
   const uint32_t b = __float_as_uint(f);
@@ -142,22 +143,48 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
   resid_out = target;
 }
 
+// Grid (SAMPLE_CHUNKS, rows).  A greedy row is spread over the chunks: every block takes a slice of
+// the vocabulary, folds (value, index) into one 64-bit word per row with atomicMax (the value's
+// order-preserving key in the high half, ~index in the low half: the largest value wins, ties go
+// to the lowest index), and the block that arrives last writes the token and clears the words.
+// A sampled row is the work of block 0 of its row alone.  `scratch` holds 2 words per row
+// (the folded maximum and the arrival count), zero between launches.
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
-              unsigned long long* __restrict__ rng_state, int* __restrict__ out) {
+              unsigned long long* __restrict__ rng_state, int* __restrict__ out,
+              unsigned long long* __restrict__ scratch) {
   __shared__ BestPair best_scratch[32];
   __shared__ float red[32];
   __shared__ SelectShared sh;
-  const int r = blockIdx.x;
+  const int r = blockIdx.y;
   const float* row = logits + (size_t)r * ld;
   const int slot = row_slot[r];
   const float temp = temperature[slot];
   if (!(temp > 0.0f)) {
-    const int best = block_argmax(row, V, best_scratch);
-    if (threadIdx.x == 0) out[r] = best;
+    const int per = (V + gridDim.x - 1) / gridDim.x;
+    const int begin = blockIdx.x * per, n = min(per, V - begin);
+    if (n > 0) {
+      const int best = begin + block_argmax(row + begin, n, best_scratch);
+      if (threadIdx.x == 0) {
+        const unsigned long long word =
+            ((unsigned long long)float_key(row[best]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)best);
+        atomicMax(&scratch[2 * r], word);
+      }
+    }
+    if (threadIdx.x == 0) {
+      __threadfence();
+      const unsigned long long arrived = atomicAdd(&scratch[2 * r + 1], 1ull);
+      if (arrived == gridDim.x - 1) {
+        __threadfence();
+        const unsigned long long word = atomicExch(&scratch[2 * r], 0ull);
+        scratch[2 * r + 1] = 0ull;
+        out[r] = (int)(0xffffffffu - (uint32_t)(word & 0xffffffffull));
+      }
+    }
     return;
   }
+  if (blockIdx.x != 0) return;
   // one draw of xorshift64*, kept per request
   __shared__ uint32_t u24_sh;
   if (threadIdx.x == 0) {
@@ -232,9 +259,11 @@ extern "C" int nib_argmax(const float* logits, int ld, int n_rows, int V, int* o
 
 extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                           const float* temperature, const int* top_k, unsigned long long* rng_state,
-                          int* out, cudaStream_t stream) {
+                          int* out, unsigned long long* scratch, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  sample_kernel<<<n_rows, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, row_slot, temperature, top_k,
-                                                       rng_state, out);
+  if (n_rows > 65535 || scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  dim3 grid(SAMPLE_CHUNKS, n_rows);
+  sample_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, row_slot, temperature, top_k, rng_state, out,
+                                                     scratch);
   NIB_LAUNCH_CHECK();
 }

@@ -39,16 +39,18 @@ _SIGNATURES = {
     "nib_linear_tc_supported": [_c_ptr, _c_int, _c_ptr, _c_int, _c_int],
     "nib_linear_tc": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_tc_qkv": [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                          _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                              _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
-                             _c_int, _c_ptr, _c_ptr],
+                             _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
 }
 
 
@@ -253,6 +255,29 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         linear_simt(a, w, bias, out, M, act, residual)
 
 
+QKV_FUSED_MAX_ROWS = 128
+
+
+def linear_qkv(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+               q_dim: int, cache: torch.Tensor, block_table: torch.Tensor, row_entry: torch.Tensor,
+               positions: torch.Tensor, status: torch.Tensor) -> bool:
+    """The fused q/k/v projection with the cache append in its epilogue: queries to out[:M, :q_dim],
+    keys and values to their slots of ``cache``.  Returns False (and does nothing) where the fused
+    kernel does not apply: more than 128 rows, float32, or a shape the tensor cores refuse."""
+    if M > QKV_FUSED_MAX_ROWS or not linear_tc_supported(a, w) or cache.dtype != torch.bfloat16 \
+            or out.dtype != torch.bfloat16:
+        return False
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    N, K = w.shape
+    if _profiler is not None:
+        _profiler.label = f"M={M} N={N} K={K} qkv"
+    _check(library().nib_linear_tc_qkv(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                       out.stride(0), M, N, K, _ptr(cache), _ptr(block_table),
+                                       block_table.shape[1], _ptr(row_entry), _ptr(positions), q_dim, n_kv_head,
+                                       head_dim, page_size, n_pages, _ptr(status), _stream()), "linear_tc_qkv")
+    return True
+
+
 def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, block_table: torch.Tensor,
               row_entry: torch.Tensor, positions: torch.Tensor, T: int, status: torch.Tensor) -> None:
     """Copy the key and value columns of src[:T] to their slots in one cache layer
@@ -299,14 +324,15 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
     chunk, n_splits = decode_split(n_rows, n_head, max_keys)
-    scratch = None
+    scratch = counters = None
     if n_splits > 1:
         scratch = workspace.get("attention.partials", (n_rows * n_head * n_splits * (head_dim + 2),), torch.float32)
+        counters = workspace.get_zeroed("attention.arrivals", (n_rows * n_head,), torch.int32)
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
                                           page_size, n_pages, float(scale), int(window), chunk, n_splits,
-                                          _ptr(status), _stream()), "attention_decode", 2 if n_splits > 1 else 1)
+                                          _ptr(counters), _ptr(status), _stream()), "attention_decode")
 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
@@ -392,6 +418,9 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
            "argmax")
 
 
+_sample_scratch: Optional[torch.Tensor] = None
+
+
 def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
            top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor) -> None:
     """One token per row.  ``temperature``, ``top_k`` and ``rng_state`` are per-slot arrays and
@@ -402,6 +431,10 @@ def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperatur
     if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:
         raise KernelError("sample: rng_state must be int64 words, temperature float32")
     _i32(row_slot, "row_slot"); _i32(top_k, "top_k"); _i32(out, "out")
+    global _sample_scratch
+    if _sample_scratch is None or _sample_scratch.numel() < 2 * n_rows:
+        # two words per row that the kernel finds zero and leaves zero
+        _sample_scratch = torch.zeros(2 * max(n_rows, 256), dtype=torch.int64, device=logits.device)
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
-                                _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out), _stream()),
-           "sample")
+                                _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
+                                _ptr(_sample_scratch), _stream()), "sample")

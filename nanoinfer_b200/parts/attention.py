@@ -54,11 +54,16 @@ class CausalSelfAttention(Mixer):
         ws = ctx.workspace
         if writes_cache:
             qkv = ws.get("attention.qkv", (ctx.max_rows, self.q_dim + 2 * self.kv_dim), self.dtype)
-            ops.linear(xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T)
-            if self.position is not None:
-                self.position.on_qk(qkv[:T, :self.q_dim], qkv[:T, self.q_dim:self.q_dim + self.kv_dim], ctx)
-            ops.kv_append(qkv, self.q_dim, self.q_dim + self.kv_dim, cache.layer, cache.block_table,
-                          ctx.row_entry, ctx.positions, T, ctx.status)
+            # small steps: keys and values go to the cache from the projection's epilogue
+            fused = self.position is None and ops.linear_qkv(
+                xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T, self.q_dim, cache.layer, cache.block_table,
+                ctx.row_entry, ctx.positions, ctx.status)
+            if not fused:
+                ops.linear(xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T)
+                if self.position is not None:
+                    self.position.on_qk(qkv[:T, :self.q_dim], qkv[:T, self.q_dim:self.q_dim + self.kv_dim], ctx)
+                ops.kv_append(qkv, self.q_dim, self.q_dim + self.kv_dim, cache.layer, cache.block_table,
+                              ctx.row_entry, ctx.positions, T, ctx.status)
             q = qkv[:, :self.q_dim]
         else:
             # this layer reads another layer's keys and values: only the queries are projected

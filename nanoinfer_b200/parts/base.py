@@ -231,5 +231,17 @@ class Workspace:
             self._bufs[name] = buf
         return buf[:n].view(*shape)
 
+    def get_zeroed(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        """Like ``get``, but the memory is zero when first handed out (and whenever it has to grow);
+        for counters that a kernel finds zero and leaves zero."""
+        n = 1
+        for s in shape:
+            n *= int(s)
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+        return buf[:n].view(*shape)
+
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())

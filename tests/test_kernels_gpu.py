@@ -317,3 +317,39 @@ def test_linear_falls_back_when_rows_are_not_16_byte_multiples():
     out = torch.zeros(5, 20, dtype=torch.bfloat16, device=DEV)
     o.linear(ad, wd, None, out, 5)
     assert (out.cpu().double() - a.double() @ w.double().T).abs().max() < 0.1
+
+
+@pytest.mark.parametrize("M, n_head, n_kv_head, hd", [(1, 4, 4, 16), (8, 12, 12, 64), (37, 6, 2, 32), (128, 5, 5, 24)])
+def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd):
+    """The small-step q/k/v projection: queries to the output, keys and values into scattered pages."""
+    o = ops()
+    g = gen(M + hd)
+    C, ps = 64 + 8 * n_head, 16
+    q_dim, kv_dim = n_head * hd, n_kv_head * hd
+    N = q_dim + 2 * kv_dim
+    a = (torch.randn(M, C, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, C, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g) * 0.1
+    # each row is the next token of a request of its own, at a position of its own
+    positions = torch.randint(0, 200, (M,), generator=g).tolist()
+    n_pages = M * 13 + 2
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((M, 13), -1, dtype=torch.int32)
+    for e in range(M):
+        table[e, positions[e] // ps] = perm.pop()
+    cache = torch.zeros(n_pages, 2, n_kv_head, ps, hd, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    status = o.status_word()
+    done = o.linear_qkv(a.to(DEV), w.to(DEV), b.to(DEV), out, M, q_dim, cache, table.to(DEV),
+                        torch.arange(M, dtype=torch.int32, device=DEV),
+                        torch.tensor(positions, dtype=torch.int32, device=DEV), status)
+    assert done and int(status.item()) == 0
+    y = (a.double() @ w.double().T + b.double())
+    assert (out.cpu().double()[:, :q_dim] - y[:, :q_dim]).abs().max() < 2e-2
+    want = torch.zeros(n_pages, 2, n_kv_head, ps, hd, dtype=torch.float64)
+    for e in range(M):
+        page = int(table[e, positions[e] // ps])
+        want[page, 0, :, positions[e] % ps] = y[e, q_dim:q_dim + kv_dim].view(n_kv_head, hd)
+        want[page, 1, :, positions[e] % ps] = y[e, q_dim + kv_dim:].view(n_kv_head, hd)
+    assert (cache.cpu().double() - want).abs().max() < 2e-2
+    assert (out.cpu()[:, q_dim:] == 0).all()            # key and value columns of the buffer are not written
