@@ -56,6 +56,8 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status) {
   constexpr int VN = Piece<T>::N;
   constexpr int MAXP = HD_MAX / VN / 2;   // pieces per lane
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float smem[];
   float* qs = smem;                                  // head_dim
   float* wo = smem + head_dim;                       // DEC_WARPS * head_dim
@@ -237,11 +239,11 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
   dim3 grid(n_splits, n_head, n_rows);
   const size_t smem = (size_t)(head_dim + DEC_WARPS * head_dim + 2 * DEC_WARPS) * sizeof(float);
   if (head_dim <= 64)
-    attention_decode_kernel<T, 64><<<grid, DEC_WARPS * 32, smem, stream>>>(
+    launch_pdl(attention_decode_kernel<T, 64>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
         (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
   else
-    attention_decode_kernel<T, DEC_MAX_HD><<<grid, DEC_WARPS * 32, smem, stream>>>(
+    launch_pdl(attention_decode_kernel<T, DEC_MAX_HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
         (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
   NIB_LAUNCH_CHECK();

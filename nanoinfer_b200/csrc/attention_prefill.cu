@@ -60,6 +60,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
                          const int* __restrict__ tiles, const int* __restrict__ entry_start,
                          const int* __restrict__ entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages,
                          float scale, int window, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   constexpr int LD = HD + 8;               // padded row: ldmatrix reads without bank conflicts
   constexpr int CHUNKS = HD / 8;           // 16-byte pieces per row
   extern __shared__ __align__(16) uint8_t smem_raw[];
@@ -239,7 +241,7 @@ static int launch_prefill(const void* q, int ldq, const void* cache, void* out, 
     attr_set = true;
   }
   dim3 grid(n_tiles, n_head);
-  attention_prefill_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(
+  launch_pdl(attention_prefill_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, 
       (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, tiles, entry_start,
       entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, status);
   NIB_LAUNCH_CHECK();

@@ -22,6 +22,8 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ ca
                       int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                       const int* __restrict__ positions, int n_head, int n_kv_head, int head_dim,
                       int page_size, int n_pages, float scale, int window, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int h = blockIdx.x * ATT_WARPS + warp;
@@ -108,11 +110,11 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
   dim3 grid((n_head + ATT_WARPS - 1) / ATT_WARPS, T);
   const size_t smem = (size_t)ATT_WARPS * (head_dim + 32 + 64) * sizeof(float);
   if (dtype == DT_F32)
-    attention_simt_kernel<float><<<grid, ATT_WARPS * 32, smem, stream>>>(
+    launch_pdl(attention_simt_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const float*)q, ldq, (const float*)cache, (float*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
   else if (dtype == DT_BF16)
-    attention_simt_kernel<bf16><<<grid, ATT_WARPS * 32, smem, stream>>>(
+    launch_pdl(attention_simt_kernel<bf16>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, rows, row_entry,
         positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, status);
   else

@@ -80,6 +80,31 @@ __device__ __forceinline__ size_t kv_offset(int page, int kv, int head, int slot
   return ((((size_t)page * 2 + kv) * n_kv_head + head) * page_size + slot) * (size_t)head_dim;
 }
 
+// Programmatic dependent launch.  Every kernel of the library starts with pdl_trigger() (the next
+// kernel in the stream may be scheduled and run its prologue while this one works) and calls
+// pdl_wait() before its first access to global memory (which returns once the kernel before it has
+// finished and its writes are visible).  A step is a chain of a hundred short kernels, and this
+// hides each one's launch latency behind its predecessor.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// Launch with the programmatic-serialization attribute set.
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 }  // namespace nib
 
 #define NIB_LAUNCH_CHECK() return (int)cudaGetLastError()

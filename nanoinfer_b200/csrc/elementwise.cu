@@ -15,6 +15,8 @@ template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
                              float* __restrict__ out, int C) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const T* te = table + (size_t)tokens[t] * C;
   float* o = out + (size_t)t * C;
@@ -33,6 +35,8 @@ template <typename OutT>
 __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
                                  OutT* __restrict__ out, int C, float eps) {
+  pdl_trigger();
+  pdl_wait();
   extern __shared__ float smem[];
   float* row = smem;          // C floats
   float* scratch = smem + C;  // 32 floats
@@ -65,6 +69,8 @@ __global__ void kv_append_kernel(const T* __restrict__ src, int ld, int k_off, i
                                  int max_blocks, const int* __restrict__ row_entry,
                                  const int* __restrict__ positions, int n_kv_head, int head_dim,
                                  int page_size, int n_pages, int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int pos = positions[t];
   const int page = block_table[(size_t)row_entry[t] * max_blocks + pos / page_size];
@@ -91,10 +97,10 @@ extern "C" int nib_embed(int dtype, const int* tokens, const int* positions, con
   if (T <= 0) return 0;
   const int threads = C >= 256 ? 256 : 128;
   if (dtype == DT_F32)
-    embed_kernel<float><<<T, threads, 0, stream>>>(tokens, positions, (const float*)table,
+    launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const float*)table,
                                                    (const float*)pos_table, out, C);
   else if (dtype == DT_BF16)
-    embed_kernel<bf16><<<T, threads, 0, stream>>>(tokens, positions, (const bf16*)table,
+    launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const bf16*)table,
                                                   (const bf16*)pos_table, out, C);
   else
     return NIB_ERR_BAD_ARGUMENT;
@@ -111,11 +117,11 @@ extern "C" int nib_layernorm(int out_dtype, const float* x, const int* rows, con
   if (out_dtype == DT_F32) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    layernorm_kernel<float><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (float*)out, C, eps);
+    launch_pdl(layernorm_kernel<float>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, (float*)out, C, eps);
   } else if (out_dtype == DT_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(layernorm_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    layernorm_kernel<bf16><<<n_rows, threads, smem, stream>>>(x, rows, gamma, beta, (bf16*)out, C, eps);
+    launch_pdl(layernorm_kernel<bf16>, dim3(n_rows), dim3(threads), smem, stream, x, rows, gamma, beta, (bf16*)out, C, eps);
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
@@ -129,11 +135,11 @@ extern "C" int nib_kv_append(int dtype, const void* src, int ld, int k_off, int 
   if (T <= 0) return 0;
   const int threads = 128;
   if (dtype == DT_F32)
-    kv_append_kernel<float><<<T, threads, 0, stream>>>((const float*)src, ld, k_off, v_off, (float*)cache,
+    launch_pdl(kv_append_kernel<float>, dim3(T), dim3(threads), 0, stream, (const float*)src, ld, k_off, v_off, (float*)cache,
                                                        block_table, max_blocks, row_entry, positions,
                                                        n_kv_head, head_dim, page_size, n_pages, status);
   else if (dtype == DT_BF16)
-    kv_append_kernel<bf16><<<T, threads, 0, stream>>>((const bf16*)src, ld, k_off, v_off, (bf16*)cache,
+    launch_pdl(kv_append_kernel<bf16>, dim3(T), dim3(threads), 0, stream, (const bf16*)src, ld, k_off, v_off, (bf16*)cache,
                                                       block_table, max_blocks, row_entry, positions,
                                                       n_kv_head, head_dim, page_size, n_pages, status);
   else

@@ -19,6 +19,8 @@ __global__ void __launch_bounds__(256)
 linear_simt_kernel(const InT* __restrict__ a, int lda, const InT* __restrict__ w, int ldw,
                    const float* __restrict__ bias, OutT* __restrict__ out, int ldo, int M, int N,
                    int K, int act, int residual) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[BK][BN + 4];
   const int tid = threadIdx.x;
@@ -77,7 +79,7 @@ template <typename InT, typename OutT>
 static int launch(const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
                   int ldo, int M, int N, int K, int act, int residual, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  linear_simt_kernel<InT, OutT><<<grid, 256, 0, stream>>>((const InT*)a, lda, (const InT*)w, ldw, bias,
+  launch_pdl(linear_simt_kernel<InT, OutT>, dim3(grid), dim3(256), 0, stream, (const InT*)a, lda, (const InT*)w, ldw, bias,
                                                           (OutT*)out, ldo, M, N, K, act, residual);
   NIB_LAUNCH_CHECK();
 }

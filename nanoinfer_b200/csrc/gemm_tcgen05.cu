@@ -24,6 +24,17 @@
 #include "api.h"
 #include "common.cuh"
 
+// Development aid: with -DNIB_TC_TIMING every block writes cycle stamps of its phases to a buffer set
+// by nib_linear_tc_timing(); the normal build carries none of it.
+#ifdef NIB_TC_TIMING
+__device__ long long* g_tc_stamps = nullptr;
+#define TC_STAMP_INIT long long* tc_stamps_ = g_tc_stamps ? g_tc_stamps + 64 * (blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) : nullptr
+#define TC_STAMP(i) do { if (tc_stamps_) tc_stamps_[(i)] = clock64(); } while (0)
+#else
+#define TC_STAMP_INIT do { } while (0)
+#define TC_STAMP(i) do { } while (0)
+#endif
+
 namespace nib {
 
 constexpr int TC_BP = 128;        // rows of the P tile = MMA M
@@ -192,6 +203,9 @@ template <int ACT>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                  const __grid_constant__ CUtensorMap map_o, const TcParams prm) {
+  pdl_trigger();
+  TC_STAMP_INIT;
+  if (threadIdx.x == 0) TC_STAMP(0);
   extern __shared__ uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -233,17 +247,24 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // the set-up above touched no global memory; from here on the inputs are read
+  if (threadIdx.x == 0) TC_STAMP(1);
   const uint32_t tmem_base = tmem_base_sh;
   volatile int* abort_flag = &abort_sh;
 
   if (warp == 0) {
-    // ---------------- TMA producer: the warp walks the loop together, lane 0 waits and issues
-    int issued = 0, s = 0;
-    uint32_t parity = 1;  // a fresh barrier passes a wait on the phase before its first
-    for (int kb = 0; kb < num_kb; ++kb) {
-      if (!warp_mbar_wait(&empty_bar[s], parity, abort_flag, lane)) break;
-      if (lane == 0) {
+    // ---------------- TMA producer.  Issuing a stage costs one thread several hundred cycles (a wait,
+    // an expect and the copies, each a dependent instruction), so up to four lanes issue in
+    // parallel: lane l takes the stage steps l, l + L, ... (the same instructions on different
+    // barriers and buffers, so the lanes run in lockstep).
+    const int L = stages < 4 ? stages : 4;
+    if (lane < L) {
+      for (int kb = lane; kb < num_kb; kb += L) {
+        const int s = kb % stages;
+        const uint32_t parity = ((kb / stages) & 1) ^ 1;  // a fresh barrier passes the first round
+        if (!mbar_wait(&empty_bar[s], parity, abort_flag)) break;
         uint8_t* sp = smem + (size_t)s * stage_bytes;
+        if (kb < 12) TC_STAMP(8 + kb);
         mbar_expect_tx(&full_bar[s], stage_bytes);
         for (int sub = 0; sub < k_sub; ++sub) {
           // a block past this split's end is asked for past the end of K: it arrives as zeros
@@ -253,49 +274,56 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[s], kx, q0);
         }
       }
-      ++issued;
-      if (++s == stages) {
-        s = 0;
-        parity ^= 1;
-      }
     }
+    __syncwarp();
     if (*abort_flag && lane == 0) {
-      // let the copies that are still in flight land before the block's shared memory goes away
-      const int first = issued > stages ? issued - stages : 0;
-      for (int kb = first; kb < issued; ++kb) {
-        const long long t0 = clock64();
-        while (!mbar_try_wait(&full_bar[kb % stages], (kb / stages) & 1) && clock64() - t0 < 200000000ll) {
-        }
+      // give copies that are still in flight time to land before the block's shared memory goes away
+      const long long t0 = clock64();
+      while (clock64() - t0 < 2000000ll) {
       }
     }
     __syncwarp();
   } else if (warp == 1) {
-    // ---------------- MMA issuer: lane 0 waits and issues
+    // ---------------- MMA issuer: lane 0 waits and issues.  One thread runs a dependent
+    // instruction every few cycles, so the loop is kept to the bare minimum: the high half of the
+    // matrix descriptors is a constant, the low half is the stage's address plus a small offset.
     const uint32_t idesc = umma_idesc(TC_BP, bq);
+    const uint32_t desc_hi = (uint32_t)(umma_desc(0) >> 32);
+    const uint32_t desc_lo0 = (uint32_t)umma_desc(smem_u32(smem));   // address field: bits 0..13, in 16-byte units
+    const uint32_t stage_step = stage_bytes >> 4, p_step = p_bytes >> 4, q_step = q_bytes >> 4;
+    const uint32_t q_off = (uint32_t)k_sub * p_step;
     int s = 0;
-    uint32_t parity = 0;
+    uint32_t parity = 0, lo_stage = desc_lo0, accumulate = 0;
     for (int kb = 0; kb < num_kb; ++kb) {
       if (!warp_mbar_wait(&full_bar[s], parity, abort_flag, lane)) break;
       tc_fence_after();
       if (lane == 0) {
-        const uint32_t base = smem_u32(smem + (size_t)s * stage_bytes);
+        if (kb < 12) TC_STAMP(20 + kb);
         for (int sub = 0; sub < k_sub; ++sub) {
-          const uint32_t pa = base + sub * p_bytes;
-          const uint32_t qa = base + k_sub * p_bytes + sub * q_bytes;
+          const uint32_t pa = lo_stage + sub * p_step, qa = lo_stage + q_off + sub * q_step;
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) {
-            // 16 bf16 = 32 bytes further along K inside the swizzled row
-            umma_bf16(tmem_base, umma_desc(pa + k * 32), umma_desc(qa + k * 32), idesc, (kb | sub | k) != 0);
+            // 16 bf16 = 32 bytes = 2 address units further along K inside the swizzled row
+            uint64_t da, db;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(da) : "r"(pa + 2 * k), "r"(desc_hi));
+            asm("mov.b64 %0, {%1, %2};" : "=l"(db) : "r"(qa + 2 * k), "r"(desc_hi));
+            umma_bf16(tmem_base, da, db, idesc, accumulate);
+            accumulate = 1;
           }
         }
         umma_commit(&empty_bar[s]);  // frees the stage when these MMAs have read it
       }
+      lo_stage += stage_step;
       if (++s == stages) {
         s = 0;
         parity ^= 1;
+        lo_stage = desc_lo0;
       }
     }
-    if (lane == 0) umma_commit(&tmem_full_bar);  // arrives when every MMA above has finished
+    if (lane == 0) {
+      umma_commit(&tmem_full_bar);  // arrives when every MMA above has finished
+      TC_STAMP(2);
+    }
     __syncwarp();
   } else {
     // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +32
@@ -307,6 +335,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = (epi_ok_sh[0] & epi_ok_sh[1] & epi_ok_sh[2] & epi_ok_sh[3]) != 0;
     tc_fence_after();
+    if (threadIdx.x == 64) TC_STAMP(3);
     const bool p_ok = p < prm.p_rows;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     if (ok && prm.tma_store) {
@@ -370,6 +399,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           }
         }
       }
+      if (threadIdx.x == 64) TC_STAMP(4);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
       asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
       if (warp == 2 && lane == 0) {
@@ -386,6 +416,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         }
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
+        TC_STAMP(5);
       }
     } else if (ok) {
       for (int c0 = 0; c0 < bq; c0 += 16) {
@@ -455,6 +486,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     tmem_dealloc(tmem_base, tmem_cols);
   }
   if (threadIdx.x == 0 && abort_sh) *prm.status = NIB_STATUS_WAIT_TIMEOUT;
+  if (threadIdx.x == 0) TC_STAMP(6);
 }
 
 // ------------------------------------------------------------------ host side
@@ -630,11 +662,11 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
   dim3 grid((prm.p_rows + TC_BP - 1) / TC_BP, (prm.q_rows + prm.bq - 1) / prm.bq, splits);
   if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   if (act == ACT_GELU_TANH)
-    linear_tc_kernel<ACT_GELU_TANH><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+    launch_pdl(linear_tc_kernel<ACT_GELU_TANH>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else if (act == ACT_GELU_ERF)
-    linear_tc_kernel<ACT_GELU_ERF><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+    launch_pdl(linear_tc_kernel<ACT_GELU_ERF>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else if (act == ACT_NONE)
-    linear_tc_kernel<ACT_NONE><<<grid, TC_THREADS, smem, stream>>>(map_p, map_q, map_o, prm);
+    launch_pdl(linear_tc_kernel<ACT_NONE>, grid, dim3(TC_THREADS), smem, stream, map_p, map_q, map_o, prm);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
@@ -657,3 +689,9 @@ extern "C" int nib_linear_tc_qkv(const void* a, int lda, const void* w, int ldw,
   KvTarget kv{cache, block_table, row_entry, positions, max_blocks, q_dim, n_kv_head, head_dim, page_size, n_pages};
   return launch_tc(DT_BF16, a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE, 0, &kv, status, stream);
 }
+
+#ifdef NIB_TC_TIMING
+extern "C" int nib_linear_tc_timing(long long* buf) {
+  return (int)cudaMemcpyToSymbol(g_tc_stamps, &buf, sizeof(buf));
+}
+#endif

@@ -71,6 +71,8 @@ __device__ int block_argmax(const float* __restrict__ row, int V, BestPair* scra
 
 __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int ld, int V,
                                                      int* __restrict__ out) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ BestPair scratch[32];
   const int r = blockIdx.x;
   const int best = block_argmax(logits + (size_t)r * ld, V, scratch);
@@ -154,6 +156,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               unsigned long long* __restrict__ rng_state, int* __restrict__ out,
               unsigned long long* __restrict__ scratch) {
+  pdl_trigger();
+  pdl_wait();
   __shared__ BestPair best_scratch[32];
   __shared__ float red[32];
   __shared__ SelectShared sh;
@@ -253,7 +257,7 @@ using namespace nib;
 
 extern "C" int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  argmax_kernel<<<n_rows, 256, 0, stream>>>(logits, ld, V, out);
+  launch_pdl(argmax_kernel, dim3(n_rows), dim3(256), 0, stream, logits, ld, V, out);
   NIB_LAUNCH_CHECK();
 }
 
@@ -263,7 +267,7 @@ extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const 
   if (n_rows <= 0) return 0;
   if (n_rows > 65535 || scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
   dim3 grid(SAMPLE_CHUNKS, n_rows);
-  sample_kernel<<<grid, SAMPLE_THREADS, 0, stream>>>(logits, ld, V, row_slot, temperature, top_k, rng_state, out,
+  launch_pdl(sample_kernel, dim3(grid), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, row_slot, temperature, top_k, rng_state, out,
                                                      scratch);
   NIB_LAUNCH_CHECK();
 }
