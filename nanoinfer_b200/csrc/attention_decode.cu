@@ -287,3 +287,63 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
                                chunk, n_splits, counters, status, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }
+
+// ---------------------------------------------------------------------------------------------
+// The entry point that allocates nothing (declared and described in attention_decode_static.h).
+#include "attention_decode_static.h"
+
+// Partial results first, then the arrival counters (as ints), in one array.
+static __device__ __align__(256) float g_static_scratch[NIB_STATIC_SCRATCH_FLOATS + NIB_STATIC_COUNTERS];
+
+// In host code the array's name is only a handle; its device address differs per GPU and is looked
+// up once per device, with that device current.
+static float* static_scratch_on_current_device(int* err) {
+  constexpr int MAX_DEVICES = 64;
+  static float* addr[MAX_DEVICES] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) {
+    *err = e != cudaSuccess ? (int)e : NIB_ERR_BAD_ARGUMENT;
+    return nullptr;
+  }
+  if (addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+    if (e != cudaSuccess) {
+      *err = (int)e;
+      return nullptr;
+    }
+    addr[dev] = p;
+  }
+  *err = 0;
+  return addr[dev];
+}
+
+extern "C" void nib_attention_decode_static_limits(long long* max_floats, long long* max_counters) {
+  if (max_floats) *max_floats = NIB_STATIC_SCRATCH_FLOATS;
+  if (max_counters) *max_counters = NIB_STATIC_COUNTERS;
+}
+
+extern "C" int nib_attention_decode_static(int dtype, const void* q, int ldq, const void* cache, void* out,
+                                           int ldo, const int* block_table, int max_blocks, const int* rows,
+                                           const int* row_entry, const int* positions, int n_rows, int n_head,
+                                           int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
+                                           int window, int chunk, int n_splits, int* status,
+                                           cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_head <= 0 || n_splits <= 0 || head_dim <= 0) return NIB_ERR_BAD_ARGUMENT;
+  const long long need_floats = nib_attention_decode_scratch(n_rows, n_head, head_dim, n_splits);
+  const long long need_counters = (long long)n_rows * n_head;
+  if (need_floats > NIB_STATIC_SCRATCH_FLOATS || need_counters > NIB_STATIC_COUNTERS)
+    return NIB_ERR_STATIC_SCRATCH_TOO_SMALL;
+  int err = 0;
+  float* scratch = static_scratch_on_current_device(&err);
+  if (scratch == nullptr) return err;
+  int* counters = reinterpret_cast<int*>(scratch + NIB_STATIC_SCRATCH_FLOATS);
+  // the counters are what must start at zero; an earlier call that was cut short may have left them otherwise
+  cudaError_t e = cudaMemsetAsync(counters, 0, (size_t)need_counters * sizeof(int), stream);
+  if (e != cudaSuccess) return (int)e;
+  return nib_attention_decode(dtype, q, ldq, cache, scratch, out, ldo, block_table, max_blocks, rows, row_entry,
+                              positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
+                              chunk, n_splits, counters, status, stream);
+}
