@@ -42,12 +42,27 @@ int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw,
                   void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
                   cudaStream_t stream);
 
-// The fused query/key/value projection for steps of at most 128 rows (bfloat16): queries go to
-// out, keys and values straight into one layer of the paged cache.
-int nib_linear_tc_qkv(const void* a, int lda, const void* w, int ldw, const float* bias, void* out, int ldo,
-                      int M, int N, int K, void* cache, const int* block_table, int max_blocks,
-                      const int* row_entry, const int* positions, int q_dim, int n_kv_head, int head_dim,
-                      int page_size, int n_pages, int* status, cudaStream_t stream);
+// The general tensor-core product for steps of at most 128 rows, with three options: activations made
+// in the kernel by LayerNorm of the 32-bit residual stream (ln_x), keys and values written straight
+// into a cache layer (cache), and K split over blocks through caller-provided scratch
+// (fix_partials / fix_counters; the counters are zero before the first call and left zero).
+int nib_linear_tc_small(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                        void* out, int ldo, int M, int N, int K, int act, int residual, const float* ln_x,
+                        int ln_ldx, const float* ln_gamma, const float* ln_beta, float ln_eps,
+                        const int* ln_rows, void* cache, const int* block_table, int max_blocks,
+                        const int* row_entry, const int* positions, int q_dim, int n_kv_head, int head_dim,
+                        int page_size, int n_pages, float* fix_partials, long long fix_floats,
+                        int* fix_counters, int fix_n_counters, int* status, cudaStream_t stream);
+
+// The product for steps of at most 16 rows on the CUDA cores (bfloat16), with the same LayerNorm and
+// cache options as nib_linear_tc_small.
+int nib_linear_skinny_supported(int M, int K, int ldw, int lda, const void* w, const void* a);
+int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
+                      int ldo, int M, int N, int K, int act, int residual, const float* ln_x, int ln_ldx,
+                      const float* ln_gamma, const float* ln_beta, float ln_eps, const int* ln_rows,
+                      void* cache, const int* block_table, int max_blocks, const int* row_entry,
+                      const int* positions, int q_dim, int n_kv_head, int head_dim, int page_size, int n_pages,
+                      int* status, cudaStream_t stream);
 
 // Causal attention of T query rows over the paged cache (general SIMT kernel).  rows: the
 // step's rows to process (nullptr: rows 0..T-1).

@@ -46,6 +46,12 @@ template <> struct Piece<bf16> {
 // independent 16-byte loads.  Each lane pair keeps an online softmax of its own over its keys
 // (no exchange between lanes inside the loop but the one that completes the dot product); the
 // sixteen pairs, then the four warps, are merged once at the end, in a fixed order.
+// Units of sixteen keys whose loads a warp keeps in flight together (fewer when a lane holds many pieces).
+#ifndef NIB_DEC_UNITS
+#define NIB_DEC_UNITS 1
+#endif
+#define NIB_DEC_UNITS_FOR(pieces) ((pieces) <= 4 ? NIB_DEC_UNITS : 1)
+
 template <typename T, int HD_MAX>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* __restrict__ part_o,
@@ -57,7 +63,6 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   constexpr int VN = Piece<T>::N;
   constexpr int MAXP = HD_MAX / VN / 2;   // pieces per lane
   pdl_trigger();
-  pdl_wait();
   extern __shared__ float smem[];
   float* qs = smem;                                  // head_dim
   float* wo = smem + head_dim;                       // DEC_WARPS * head_dim
@@ -65,6 +70,9 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   float* wl = wm + DEC_WARPS;                        // DEC_WARPS
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
+  // The step's tables were written before the step began and the cache below this row's position
+  // belongs to earlier steps: both may be read before the kernel ahead (which writes this row's own
+  // key and value, and the queries) has finished.
   const int t = rows ? rows[r] : r;
   const int pos = positions[t];
   const int* table = block_table + (size_t)row_entry[t] * max_blocks;
@@ -73,9 +81,53 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   const int k_end = min(pos + 1, k_begin + chunk);  // exclusive
   const int hk = h / (n_head / n_kv_head);
   const size_t pidx = ((size_t)r * n_head + h) * n_splits + split;
-
   __shared__ int is_last_sh;
   const bool empty = k_begin >= k_end;  // nothing in this split: the merge skips l == 0
+
+  const int n_pieces = head_dim / VN;  // 16-byte pieces per row
+  const int slot_in_unit = lane >> 1, half = lane & 1;
+  // units of 16 consecutive keys that lie in one page (page_size is a multiple of 16)
+  const int first_unit = empty ? 0 : k_begin / 16, last_unit = empty ? -1 : (k_end - 1) / 16;
+  // This warp's units are first_unit + warp + i * DEC_WARPS; it works on them in groups of UNITS
+  // whose loads are all in flight together.
+  constexpr int UNITS = NIB_DEC_UNITS_FOR(MAXP);
+  const int n_mine = (first_unit + warp <= last_unit) ? (last_unit - first_unit - warp) / DEC_WARPS + 1 : 0;
+  Piece<T> kp[UNITS][MAXP], vp[UNITS][MAXP];
+  bool act[UNITS];
+  // asks for this lane pair's key and value pieces of the group that starts at the warp's unit i0
+  auto fetch = [&](int i0) {
+#pragma unroll
+    for (int uu = 0; uu < UNITS; ++uu) {
+      act[uu] = false;
+      if (i0 + uu >= n_mine) continue;
+      const int j0 = (first_unit + warp + (i0 + uu) * DEC_WARPS) * 16;
+      const int page = table[j0 / page_size];
+      if (page < 0 || page >= n_pages) {
+        if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
+        continue;
+      }
+      const int j = j0 + slot_in_unit;
+      if (j < k_begin || j >= k_end) continue;
+      act[uu] = true;
+      const int slot = j % page_size;
+      const T* kr = cache + kv_offset(page, 0, hk, slot, n_kv_head, page_size, head_dim);
+      const T* vr = cache + kv_offset(page, 1, hk, slot, n_kv_head, page_size, head_dim);
+#pragma unroll
+      for (int i = 0; i < MAXP; ++i) {
+        const int c = half + 2 * i;
+        if (c < n_pieces) {
+          kp[uu][i].load(kr + c * VN);
+          vp[uu][i].load(vr + c * VN);
+        }
+      }
+    }
+  };
+  // none of the first group's keys is the one that the kernel ahead writes
+  const int first_group_last = first_unit + warp + (min(UNITS, n_mine) - 1) * DEC_WARPS;
+  const bool early = n_mine > 0 && first_group_last * 16 + 15 < pos;
+  if (early) fetch(0);
+  pdl_wait();
+
   if (empty) {
     if (threadIdx.x == 0) {
       part_ml[2 * pidx] = -INFINITY;
@@ -85,64 +137,45 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_float(q[(size_t)t * ldq + h * head_dim + d]);
   __syncthreads();
 
-  const int n_pieces = head_dim / VN;  // 16-byte pieces per row
-  const int slot_in_unit = lane >> 1, half = lane & 1;
   float o[MAXP * VN];
 #pragma unroll
   for (int i = 0; i < MAXP * VN; ++i) o[i] = 0.0f;
   float m = -INFINITY, l = 0.0f;
 
-  // units of 16 consecutive keys that lie in one page (page_size is a multiple of 16)
-  const int first_unit = k_begin / 16, last_unit = (k_end - 1) / 16;
-  for (int u = first_unit + warp; u <= last_unit; u += DEC_WARPS) {
-    const int j0 = u * 16;
-    const int page = table[j0 / page_size];
-    if (page < 0 || page >= n_pages) {
-      if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
-      continue;
-    }
-    const int j = j0 + slot_in_unit;
-    if (j < k_begin || j >= k_end) continue;  // this lane pair's key is outside the range
-    const int slot = j % page_size;
-    const T* kr = cache + kv_offset(page, 0, hk, slot, n_kv_head, page_size, head_dim);
-    const T* vr = cache + kv_offset(page, 1, hk, slot, n_kv_head, page_size, head_dim);
-    Piece<T> kp[MAXP], vp[MAXP];
+  for (int i0 = 0; i0 < n_mine; i0 += UNITS) {
+    if (i0 > 0 || !early) fetch(i0);
 #pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const int c = half + 2 * i;
-      if (c < n_pieces) {
-        kp[i].load(kr + c * VN);
-        vp[i].load(vr + c * VN);
+    for (int uu = 0; uu < UNITS; ++uu) {
+      if (!act[uu]) continue;
+      float dot = 0.0f;
+#pragma unroll
+      for (int i = 0; i < MAXP; ++i) {
+        const int c = half + 2 * i;
+        if (c < n_pieces) {
+          float f[VN];
+          kp[uu][i].unpack(f);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) dot = fmaf(f[e], qs[c * VN + e], dot);
+        }
       }
-    }
-    float dot = 0.0f;
+      // both lanes of the pair are here together (whether a pair has a key depends on the pair only)
+      dot += __shfl_xor_sync(0x3u << (lane & ~1), dot, 1);
+      const float s = dot * scale;
+      const float m_new = fmaxf(m, s);
+      const float p = expf(s - m_new);
+      const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
+      l = l * corr + p;
+      m = m_new;
 #pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const int c = half + 2 * i;
-      if (c < n_pieces) {
-        float f[VN];
-        kp[i].unpack(f);
+      for (int i = 0; i < MAXP; ++i) {
+        const int c = half + 2 * i;
+        if (c < n_pieces) {
+          float f[VN];
+          vp[uu][i].unpack(f);
 #pragma unroll
-        for (int e = 0; e < VN; ++e) dot = fmaf(f[e], qs[c * VN + e], dot);
+          for (int e = 0; e < VN; ++e) o[i * VN + e] = fmaf(p, f[e], o[i * VN + e] * corr);
+        }
       }
-    }
-    // both lanes of the pair are here together (the range test above depends on the pair only)
-    dot += __shfl_xor_sync(0x3u << (lane & ~1), dot, 1);
-    const float s = dot * scale;
-    const float m_new = fmaxf(m, s);
-    const float p = expf(s - m_new);
-    const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
-    l = l * corr + p;
-    m = m_new;
-#pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const int c = half + 2 * i;
-      if (c < n_pieces) {
-        float f[VN];
-        vp[i].unpack(f);
-#pragma unroll
-        for (int e = 0; e < VN; ++e) o[i * VN + e] = fmaf(p, f[e], o[i * VN + e] * corr);
-      } 
     }
   }
   __syncwarp();

@@ -1,0 +1,309 @@
+// out = act(a . w^T + bias) for steps of a few rows (at most 16), in bfloat16, on the CUDA cores.
+//
+// With one to sixteen rows the product is a stream of weights with a handful of multiply-adds per
+// weight: the 128-row tcgen05 MMA takes its full 128 cycles however few columns it has, and its
+// set-up (barriers, tensor memory, descriptors) costs more than the arithmetic.  Here a block owns
+// 16 output features, its warps split K, every lane pulls weights with independent 16-byte loads
+// that are all in flight before any is used, and the small warp-level MMA (m16n8k16) multiplies them
+// with the step's rows held in shared memory.  The grid covers the output features, so every SM
+// pulls weights.
+//
+// Folded in, because each is one round trip less for a decode step:
+//   * the LayerNorm that stands before the product (the rows are normalised into shared memory while
+//     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51);
+//   * the bias, GELU and residual epilogues (crates/metal/src/shaders/batch.metal:94-97,148-165);
+//   * the write of keys and values into the paged cache for the fused q/k/v projection
+//     (batch.metal:155-164).
+// A row's result does not depend on the other rows: each (row, feature) sum has its own fixed order.
+#include "api.h"
+#include "common.cuh"
+
+namespace nib {
+
+constexpr int SK_WARPS = 8;
+constexpr int SK_MAX_ROWS = 16;
+
+struct SkinnyParams {
+  const bf16* a;        // [M, K] activations (null when ln_x is given)
+  int lda;
+  const float* ln_x;    // residual stream, normalised here
+  int ln_ldx;
+  const float* ln_gamma;
+  const float* ln_beta;
+  const int* ln_rows;
+  float ln_eps;
+  const bf16* w;        // [N, K]
+  int ldw;
+  const float* bias;
+  void* out;
+  int ldo, out_f32, residual, act;
+  int M, N, K;
+  // optional: features from kv_q_dim on go to the paged cache
+  bf16* kv_cache;
+  const int* kv_block_table;
+  const int* kv_row_entry;
+  const int* kv_positions;
+  int kv_max_blocks, kv_q_dim, kv_heads, kv_head_dim, kv_page_size, kv_n_pages;
+  int* status;
+};
+
+__device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// A block owns 16 output features at a time; its eight warps split K between them (warp w takes the
+// 32-wide steps w, w + 8, ...), so each warp's weights are a handful of independent 16-byte loads
+// that are all in flight at once, and the partial sums meet in shared memory.  The small
+// tensor-core shape m16n8k16 does the arithmetic: weights are the 16-row operand, the step's rows
+// (8 per tile, NT tiles) the 8-column one.  A lane's 16-byte piece of a weight row feeds two MMAs;
+// since a dot product does not care about the order of its terms, the piece's eight values are
+// dealt to the fragment positions as they come, and the rows' pieces are dealt the same way.
+template <int NT>
+__global__ void __launch_bounds__(SK_WARPS * 32)
+linear_skinny_kernel(const SkinnyParams prm) {
+  pdl_trigger();
+  extern __shared__ __align__(16) uint8_t sk_smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int K = prm.K, M = prm.M;
+  const int n_chunks = K >> 3;                         // 16-byte pieces per row
+  const int ldx = K + ((32 - K % 64) + 64) % 64;       // padded row: pieces of 8 rows x 4 lanes hit distinct banks
+  bf16* xs = reinterpret_cast<bf16*>(sk_smem);         // [NT * 8][ldx] the step's rows (rows >= M are zeros)
+  float* red = reinterpret_cast<float*>(sk_smem + (size_t)NT * 8 * ldx * sizeof(bf16));  // [warps][NT][32][4]
+  const int n_tiles = (prm.N + 15) / 16;
+  const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of K
+  const int fr = lane >> 2, kl = lane & 3;         // this lane's feature row (and +8) and piece within a step
+
+  // ---- Before waiting for the kernel ahead: everything that does not depend on it.  The weights of
+  // this block's first tile (and the norm's parameters) are asked for now, so that they travel
+  // while the previous kernel is still finishing.
+  uint4 wa[4], wb[4];
+  {
+    const int f0 = blockIdx.x * 16;
+    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw;
+    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int c = (warp + u * SK_WARPS) * 4 + kl;
+      const bool ok = c < n_chunks;
+      wa[u] = ok ? *reinterpret_cast<const uint4*>(w0 + c * 8) : make_uint4(0, 0, 0, 0);
+      wb[u] = ok ? *reinterpret_cast<const uint4*>(w1 + c * 8) : make_uint4(0, 0, 0, 0);
+    }
+  }
+  float4 lg[8], lb[8];   // the norm's scale and shift for this lane's part of a row (K <= 1024)
+  if (prm.ln_x != nullptr && warp < M) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int k = (j * 32 + lane) * 4;
+      if (k < K) {
+        lg[j] = *reinterpret_cast<const float4*>(prm.ln_gamma + k);
+        lb[j] = *reinterpret_cast<const float4*>(prm.ln_beta + k);
+      }
+    }
+  }
+  pdl_wait();
+
+  // ---- the step's rows into shared memory as bfloat16 (normalised on the way if asked)
+  for (int i = threadIdx.x; i < (NT * 8 - M) * (ldx / 8); i += blockDim.x)   // rows past the step: zeros
+    reinterpret_cast<uint4*>(xs + (size_t)M * ldx)[i] = make_uint4(0, 0, 0, 0);
+  if (prm.ln_x != nullptr) {
+    for (int m = warp; m < M; m += SK_WARPS) {
+      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
+      // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
+      float v[32];
+      float sum = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = (j * 32 + lane) * 4;
+        float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) t = *reinterpret_cast<const float4*>(src + k);
+        v[4 * j] = t.x; v[4 * j + 1] = t.y; v[4 * j + 2] = t.z; v[4 * j + 3] = t.w;
+        sum += (t.x + t.y) + (t.z + t.w);
+      }
+      const float mean = warp_sum(sum) / (float)K;
+      float sq = 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = (j * 32 + lane) * 4;
+        if (k < K) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float d = v[4 * j + e] - mean;
+            sq += d * d;
+          }
+        }
+      }
+      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + prm.ln_eps);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int k = (j * 32 + lane) * 4;
+        if (k < K) {
+          const float4 g = lg[j], b = lb[j];
+          __nv_bfloat162 lo = __floats2bfloat162_rn((v[4 * j] - mean) * rstd * g.x + b.x,
+                                                    (v[4 * j + 1] - mean) * rstd * g.y + b.y);
+          __nv_bfloat162 hi = __floats2bfloat162_rn((v[4 * j + 2] - mean) * rstd * g.z + b.z,
+                                                    (v[4 * j + 3] - mean) * rstd * g.w + b.w);
+          uint2 packed;
+          packed.x = *reinterpret_cast<uint32_t*>(&lo);
+          packed.y = *reinterpret_cast<uint32_t*>(&hi);
+          *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+        }
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < M * n_chunks; i += blockDim.x) {
+      const int m = i / n_chunks, c = i - m * n_chunks;
+      *reinterpret_cast<uint4*>(xs + (size_t)m * ldx + c * 8) =
+          *reinterpret_cast<const uint4*>(prm.a + (size_t)m * prm.lda + c * 8);
+    }
+  }
+  __syncthreads();
+
+  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+    const int f0 = tile * 16;
+    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw;
+    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw;
+    float acc[NT][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
+    // this warp's steps, four at a time: eight independent 16-byte loads in flight
+    for (int s0 = warp; s0 < n_steps; s0 += 4 * SK_WARPS) {
+      if (tile != blockIdx.x || s0 != warp) {   // the very first batch was asked for before the wait
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int c = (s0 + u * SK_WARPS) * 4 + kl;
+          const bool ok = c < n_chunks;
+          wa[u] = ok ? *reinterpret_cast<const uint4*>(w0 + c * 8) : make_uint4(0, 0, 0, 0);
+          wb[u] = ok ? *reinterpret_cast<const uint4*>(w1 + c * 8) : make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = (s0 + u * SK_WARPS) * 4 + kl;
+        if ((s0 + u * SK_WARPS) < n_steps) {   // uniform over the warp
+#pragma unroll
+          for (int t = 0; t < NT; ++t) {
+            uint4 xb = make_uint4(0, 0, 0, 0);
+            if (c < n_chunks) xb = *reinterpret_cast<const uint4*>(xs + (size_t)(t * 8 + fr) * ldx + c * 8);
+            mma_16x8x16(acc[t], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xb.x, xb.y);
+            mma_16x8x16(acc[t], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xb.z, xb.w);
+          }
+        }
+      }
+    }
+    // ---- the warps' partial sums meet in shared memory and are added in warp order
+    __syncthreads();   // the previous tile's sums have been read
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+      *reinterpret_cast<float4*>(red + ((size_t)(warp * NT + t) * 32 + lane) * 4) =
+          make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
+    __syncthreads();
+    for (int o = threadIdx.x; o < NT * 128; o += blockDim.x) {
+      const int t = o / 128, l = (o % 128) / 4, i = o % 4;
+      float total = 0.0f;
+#pragma unroll
+      for (int w = 0; w < SK_WARPS; ++w) total += red[((size_t)(w * NT + t) * 32 + l) * 4 + i];
+      const int n = f0 + (l >> 2) + 8 * (i >> 1);          // feature
+      const int m = t * 8 + (l & 3) * 2 + (i & 1);          // row of the step
+      if (n >= prm.N || m >= M) continue;
+      float x = total + (prm.bias ? prm.bias[n] : 0.0f);
+      if (prm.act == ACT_GELU_TANH) {
+        float th;
+        asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
+        x = 0.5f * x * (1.0f + th);
+      } else if (prm.act == ACT_GELU_ERF) {
+        x = gelu_erf(x);
+      }
+      if (prm.kv_cache != nullptr && n >= prm.kv_q_dim) {
+        const int kv_dim = prm.kv_heads * prm.kv_head_dim;
+        const int rem = n - prm.kv_q_dim;
+        const int which = rem / kv_dim, head = (rem % kv_dim) / prm.kv_head_dim, d = rem % prm.kv_head_dim;
+        const int pos = prm.kv_positions[m];
+        const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
+        if (page < 0 || page >= prm.kv_n_pages) {
+          *prm.status = NIB_STATUS_BAD_PAGE;
+        } else {
+          prm.kv_cache[kv_offset(page, which, head, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
+                                 prm.kv_head_dim) + d] = __float2bfloat16_rn(x);
+        }
+      } else if (prm.out_f32) {
+        float* dst = (float*)prm.out + (size_t)m * prm.ldo + n;
+        *dst = prm.residual ? *dst + x : x;
+      } else {
+        ((bf16*)prm.out)[(size_t)m * prm.ldo + n] = __float2bfloat16_rn(x);
+      }
+    }
+  }
+}
+
+static size_t skinny_smem(int NT, int K) {
+  const int ldx = K + ((32 - K % 64) + 64) % 64;
+  return (size_t)NT * 8 * ldx * sizeof(bf16) + (size_t)SK_WARPS * NT * 32 * 4 * sizeof(float);
+}
+
+template <int NT>
+static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
+  const size_t smem = skinny_smem(NT, prm.K);
+  static bool attr_set = false;
+  if (!attr_set) {
+    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         200 * 1024);
+    if (e != cudaSuccess) return (int)e;
+    attr_set = true;
+  }
+  int blocks = (prm.N + 15) / 16;
+  if (blocks > 4 * 148) blocks = 4 * 148;   // then each block walks several tiles with the rows in place
+  launch_pdl(linear_skinny_kernel<NT>, dim3(blocks), dim3(SK_WARPS * 32), smem, stream, prm);
+  NIB_LAUNCH_CHECK();
+}
+
+}  // namespace nib
+
+using namespace nib;
+
+// 1 if the few-rows kernel takes this problem.
+extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int lda, const void* w, const void* a) {
+  if (M < 1 || M > SK_MAX_ROWS || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)w & 15)) return 0;
+  if (skinny_smem(M <= 8 ? 1 : 2, K) > 100 * 1024) return 0;   // two blocks per SM
+  (void)lda; (void)a;
+  return 1;
+}
+
+// The product for steps of at most 16 rows (bfloat16 weights and activations; out bfloat16 or
+// float32).  Options as for nib_linear_tc_small: ln_x != null folds the LayerNorm before the product
+// in (`a` ignored); cache != null sends the features from q_dim on to the paged cache.
+extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                                 void* out, int ldo, int M, int N, int K, int act, int residual, const float* ln_x,
+                                 int ln_ldx, const float* ln_gamma, const float* ln_beta, float ln_eps,
+                                 const int* ln_rows, void* cache, const int* block_table, int max_blocks,
+                                 const int* row_entry, const int* positions, int q_dim, int n_kv_head,
+                                 int head_dim, int page_size, int n_pages, int* status, cudaStream_t stream) {
+  if (N <= 0 || M <= 0) return 0;
+  if (!nib_linear_skinny_supported(M, K, ldw, lda, w, a)) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (ln_x == nullptr && a == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  if (ln_x != nullptr && K > 1024) return NIB_ERR_UNSUPPORTED_SIZE;  // a row is held in registers while normalised
+  if (residual && out_dtype != DT_F32) return NIB_ERR_BAD_ARGUMENT;
+  if (cache != nullptr && (out_dtype != DT_BF16 || residual || N != q_dim + 2 * n_kv_head * head_dim))
+    return NIB_ERR_BAD_ARGUMENT;
+  SkinnyParams prm;
+  prm.a = (const bf16*)a; prm.lda = lda;
+  prm.ln_x = ln_x; prm.ln_ldx = ln_ldx; prm.ln_gamma = ln_gamma; prm.ln_beta = ln_beta; prm.ln_rows = ln_rows;
+  prm.ln_eps = ln_eps;
+  prm.w = (const bf16*)w; prm.ldw = ldw; prm.bias = bias; prm.out = out; prm.ldo = ldo;
+  prm.out_f32 = out_dtype == DT_F32; prm.residual = residual; prm.act = act;
+  prm.M = M; prm.N = N; prm.K = K;
+  prm.kv_cache = (bf16*)cache; prm.kv_block_table = block_table; prm.kv_row_entry = row_entry;
+  prm.kv_positions = positions; prm.kv_max_blocks = max_blocks; prm.kv_q_dim = q_dim; prm.kv_heads = n_kv_head;
+  prm.kv_head_dim = head_dim; prm.kv_page_size = page_size; prm.kv_n_pages = n_pages;
+  prm.status = status;
+  if ((lda & 7) || (a != nullptr && ((uintptr_t)a & 15))) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (ln_x != nullptr && ((ln_ldx & 3) || ((uintptr_t)ln_x & 15) || ((uintptr_t)ln_gamma & 15) ||
+                          ((uintptr_t)ln_beta & 15)))
+    return NIB_ERR_UNSUPPORTED_SIZE;
+  if (M <= 8) return launch_skinny<1>(prm, stream);
+  return launch_skinny<2>(prm, stream);
+}

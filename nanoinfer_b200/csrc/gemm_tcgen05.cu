@@ -17,6 +17,12 @@
 // to TMA: a tiled store, or for the residual sum a tiled reduce-add, so that x += tile happens in
 // the L2 without the SM reading x.  Outputs whose pitch or address TMA cannot take (rows not a
 // multiple of 16 bytes) are written with plain stores instead.
+// In the swapped orientation two more things can be folded in.  The activations may be given as the
+// 32-bit residual stream plus LayerNorm parameters: the four epilogue warps, idle until the MMAs
+// finish, normalise the rows and write them as the MMA's bfloat16 operand straight into shared
+// memory while the weights are still on their way, which saves a kernel and a round trip per norm.
+// And K may be split over several blocks whose partial tiles are summed by the last one to finish,
+// so that a product with few output tiles still pulls its weights with the whole GPU.
 // Every wait on an mbarrier is bounded: if it runs out, the kernel records
 // NIB_STATUS_WAIT_TIMEOUT, stops issuing work, frees its tensor memory and returns.
 #include <cuda.h>
@@ -66,6 +72,20 @@ struct TcParams {
   const int* kv_row_entry;
   const int* kv_positions;
   int kv_max_blocks, kv_q_dim, kv_heads, kv_head_dim, kv_page_size, kv_n_pages;
+  // Optional (swapped orientation only): the activations are LayerNorm(x[rows]) computed by the block
+  // itself from the 32-bit residual stream, instead of a bfloat16 matrix loaded by TMA
+  // (reference formula: crates/core/src/kernels/reference.rs:42-51)
+  const float* ln_x;
+  const float* ln_gamma;
+  const float* ln_beta;
+  const int* ln_rows;
+  int ln_ldx;
+  float ln_eps;
+  // Optional (swapped orientation only): K split over grid.z with the partial tiles summed, in split
+  // order, by the block of a tile that finishes last (for outputs that cannot be reduce-added)
+  float* fix_partials;
+  int* fix_counters;
+  int fix_splits;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -212,21 +232,26 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   __shared__ uint64_t full_bar[TC_MAX_STAGES];
   __shared__ uint64_t empty_bar[TC_MAX_STAGES];
   __shared__ uint64_t tmem_full_bar;
+  __shared__ uint64_t q_ready_bar;
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ int epi_ok_sh[4];
+  __shared__ int fix_last_sh;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int stages = prm.stages, bq = prm.bq;
   const int k_sub = prm.k_sub;
+  const bool ln = prm.ln_x != nullptr;            // the Q operand is made here, not loaded
   const uint32_t p_bytes = TC_BP * TC_BK * 2, q_bytes = (uint32_t)bq * TC_BK * 2;  // one 64-wide block each
-  const uint32_t stage_bytes = (uint32_t)k_sub * (p_bytes + q_bytes);  // multiples of 1024 (bq % 16 == 0)
+  // a stage holds k_sub blocks of P and, unless Q is resident, of Q; multiples of 1024 (bq % 16 == 0)
+  const uint32_t stage_bytes = (uint32_t)k_sub * (p_bytes + (ln ? 0u : q_bytes));
   const int p0 = blockIdx.x * TC_BP, q0 = blockIdx.y * bq;
   // this block's share of K, in 64-wide blocks, and in pipeline stages
   const int kb_begin = blockIdx.z * prm.kb_per_split;
   const int kb_end = min((prm.K + TC_BK - 1) / TC_BK, kb_begin + prm.kb_per_split);
   const int num_kb = (kb_end - kb_begin + k_sub - 1) / k_sub;
   const bool first_split = blockIdx.z == 0;
+  uint8_t* q_region = smem + (size_t)stages * stage_bytes;   // resident Q blocks (LayerNorm mode)
   uint32_t tmem_cols = 32;
   while ((int)tmem_cols < bq) tmem_cols <<= 1;
 
@@ -236,21 +261,24 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
       mbar_init(&empty_bar[s], 1);
     }
     mbar_init(&tmem_full_bar, 1);
+    mbar_init(&q_ready_bar, 128);
     abort_sh = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_p) : "memory");
-    asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
+    if (!ln) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_q) : "memory");
     if (prm.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)&map_o) : "memory");
   }
   if (warp == 1) tmem_alloc(&tmem_base_sh, tmem_cols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
-  pdl_wait();  // the set-up above touched no global memory; from here on the inputs are read
-  if (threadIdx.x == 0) TC_STAMP(1);
   const uint32_t tmem_base = tmem_base_sh;
   volatile int* abort_flag = &abort_sh;
+  // Only the producer goes on before the kernel ahead has finished: it asks for the WEIGHT tiles of
+  // the first stages (they do not depend on that kernel), and waits before it asks for activations.
+  if (warp != 0) pdl_wait();
+  if (threadIdx.x == 32) TC_STAMP(1);
 
   if (warp == 0) {
     // ---------------- TMA producer.  Issuing a stage costs one thread several hundred cycles (a wait,
@@ -258,10 +286,38 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     // parallel: lane l takes the stage steps l, l + L, ... (the same instructions on different
     // barriers and buffers, so the lanes run in lockstep).
     const int L = stages < 4 ? stages : 4;
+    const bool weights_are_p = prm.swap != 0;
+    // first round (the stages are all free): the weight tiles now, the activation tiles after the wait
+    const int first_round = num_kb < stages ? num_kb : stages;
     if (lane < L) {
-      for (int kb = lane; kb < num_kb; kb += L) {
+      for (int kb = lane; kb < first_round; kb += L) {
+        uint8_t* sp = smem + (size_t)kb * stage_bytes;
+        mbar_expect_tx(&full_bar[kb], stage_bytes);
+        for (int sub = 0; sub < k_sub; ++sub) {
+          const int kb64 = kb_begin + kb * k_sub + sub;
+          const int kx = (kb64 < kb_end ? kb64 : (prm.K + TC_BK - 1) / TC_BK) * TC_BK;
+          if (weights_are_p) tma_load_2d(sp + sub * p_bytes, &map_p, &full_bar[kb], kx, p0);
+          else tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[kb], kx, q0);
+        }
+      }
+    }
+    __syncwarp();
+    pdl_wait();
+    if (lane < L) {
+      for (int kb = lane; kb < first_round; kb += L) {
+        uint8_t* sp = smem + (size_t)kb * stage_bytes;
+        if (kb < 12) TC_STAMP(8 + kb);
+        for (int sub = 0; sub < k_sub; ++sub) {
+          const int kb64 = kb_begin + kb * k_sub + sub;
+          const int kx = (kb64 < kb_end ? kb64 : (prm.K + TC_BK - 1) / TC_BK) * TC_BK;
+          if (!weights_are_p) tma_load_2d(sp + sub * p_bytes, &map_p, &full_bar[kb], kx, p0);
+          else if (!ln) tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[kb], kx, q0);
+        }
+      }
+      // later rounds: a stage is refilled when the MMAs have read it
+      for (int kb = first_round + lane; kb < num_kb; kb += L) {
         const int s = kb % stages;
-        const uint32_t parity = ((kb / stages) & 1) ^ 1;  // a fresh barrier passes the first round
+        const uint32_t parity = ((kb / stages) & 1) ^ 1;
         if (!mbar_wait(&empty_bar[s], parity, abort_flag)) break;
         uint8_t* sp = smem + (size_t)s * stage_bytes;
         if (kb < 12) TC_STAMP(8 + kb);
@@ -271,7 +327,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           const int kb64 = kb_begin + kb * k_sub + sub;
           const int kx = (kb64 < kb_end ? kb64 : (prm.K + TC_BK - 1) / TC_BK) * TC_BK;
           tma_load_2d(sp + sub * p_bytes, &map_p, &full_bar[s], kx, p0);
-          tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[s], kx, q0);
+          if (!ln) tma_load_2d(sp + k_sub * p_bytes + sub * q_bytes, &map_q, &full_bar[s], kx, q0);
         }
       }
     }
@@ -292,15 +348,19 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     const uint32_t desc_lo0 = (uint32_t)umma_desc(smem_u32(smem));   // address field: bits 0..13, in 16-byte units
     const uint32_t stage_step = stage_bytes >> 4, p_step = p_bytes >> 4, q_step = q_bytes >> 4;
     const uint32_t q_off = (uint32_t)k_sub * p_step;
+    const uint32_t q_res0 = (uint32_t)umma_desc(smem_u32(q_region));
     int s = 0;
     uint32_t parity = 0, lo_stage = desc_lo0, accumulate = 0;
-    for (int kb = 0; kb < num_kb; ++kb) {
+    bool ok = true;
+    if (ln) ok = warp_mbar_wait(&q_ready_bar, 0, abort_flag, lane);  // the normalised rows are in place
+    for (int kb = 0; kb < num_kb && ok; ++kb) {
       if (!warp_mbar_wait(&full_bar[s], parity, abort_flag, lane)) break;
       tc_fence_after();
       if (lane == 0) {
         if (kb < 12) TC_STAMP(20 + kb);
         for (int sub = 0; sub < k_sub; ++sub) {
-          const uint32_t pa = lo_stage + sub * p_step, qa = lo_stage + q_off + sub * q_step;
+          const uint32_t pa = lo_stage + sub * p_step;
+          const uint32_t qa = ln ? q_res0 + (uint32_t)(kb * k_sub + sub) * q_step : lo_stage + q_off + sub * q_step;
 #pragma unroll
           for (int k = 0; k < TC_BK / 16; ++k) {
             // 16 bf16 = 32 bytes = 2 address units further along K inside the swizzled row
@@ -326,10 +386,48 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     }
     __syncwarp();
   } else {
-    // ---------------- epilogue: warp w owns TMEM lanes 32 * (w % 4) .. +32
+    // ---------------- epilogue warps: warp w owns TMEM lanes 32 * (w % 4) .. +32
     const int quarter = warp & 3;
     const int pl = quarter * 32 + lane;      // this thread's row within the P tile
     const int p = p0 + pl;
+    if (ln) {
+      // While the weights travel: normalise this tile's rows and lay them down as the resident Q
+      // operand, [local K block][row][64 bf16] in the 128-byte swizzle.  One warp per row at a time.
+      const int ew = warp - 2;
+      const int K = prm.K;
+      const int n_local = kb_end - kb_begin;
+      const int n_blocks = num_kb * k_sub;   // blocks the MMAs will read (the tail ones are zeros)
+      for (int r = ew; r < bq; r += 4) {
+        const int m = q0 + r;
+        const bool valid = m < prm.q_rows;
+        float mean = 0.0f, rstd = 0.0f;
+        const float* src = prm.ln_x;
+        if (valid) {
+          src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
+          float sum = 0.0f;
+          for (int k = lane; k < K; k += 32) sum += src[k];
+          mean = warp_sum(sum) / (float)K;
+          float sq = 0.0f;
+          for (int k = lane; k < K; k += 32) {
+            const float d = src[k] - mean;
+            sq += d * d;
+          }
+          rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + prm.ln_eps);
+        }
+        for (int i = 0; i < n_blocks; ++i) {
+          const int k = (kb_begin + i) * TC_BK + lane * 2;
+          float v0 = 0.0f, v1 = 0.0f;
+          if (valid && i < n_local) {
+            if (k < K) v0 = (src[k] - mean) * rstd * prm.ln_gamma[k] + prm.ln_beta[k];
+            if (k + 1 < K) v1 = (src[k + 1] - mean) * rstd * prm.ln_gamma[k + 1] + prm.ln_beta[k + 1];
+          }
+          uint8_t* dst = q_region + (size_t)i * q_bytes + (size_t)r * 128 + (((lane >> 2) ^ (r & 7)) << 4) + (lane & 3) * 4;
+          *reinterpret_cast<uint32_t*>(dst) = pack_bf16(v0, v1);
+        }
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMAs
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&q_ready_bar)) : "memory");
+    }
     // the four epilogue warps go on only if all of them saw the accumulator complete
     if (lane == 0) epi_ok_sh[quarter] = mbar_wait(&tmem_full_bar, 0, abort_flag) ? 1 : 0;
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -338,26 +436,27 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     if (threadIdx.x == 64) TC_STAMP(3);
     const bool p_ok = p < prm.p_rows;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
-    if (ok && prm.tma_store) {
-      // Every MMA has finished, so every pipeline buffer is idle: the tile is staged there.
-      const float bias_p = (prm.swap && prm.bias && p_ok && first_split) ? prm.bias[p] : 0.0f;
-      // 64 columns at a time: four tensor-memory loads in flight, one wait
-      for (int g0 = 0; g0 < bq; g0 += 64) {
-        uint32_t raw[4][16];
-        const int n_sub = min(4, (bq - g0) / 16);  // uniform over the block
+
+    if (ok && !prm.swap) {
+      // ======== plain orientation: this thread owns row p, the columns are output features ========
+      if (prm.tma_store) {
+        // Every MMA has finished, so every pipeline buffer is idle: the tile is staged there in blocks
+        // of [128 rows][128 bytes] in the 128-byte swizzle.  64 columns at a time: four
+        // tensor-memory loads in flight, one wait.
+        for (int g0 = 0; g0 < bq; g0 += 64) {
+          uint32_t raw[4][16];
+          const int n_sub = min(4, (bq - g0) / 16);  // uniform over the block
 #pragma unroll
-        for (int sub = 0; sub < 4; ++sub)
-          if (sub < n_sub) tmem_ld16_issue(lane_addr + (uint32_t)(g0 + sub * 16), raw[sub]);
-        tmem_ld_wait();
+          for (int sub = 0; sub < 4; ++sub)
+            if (sub < n_sub) tmem_ld16_issue(lane_addr + (uint32_t)(g0 + sub * 16), raw[sub]);
+          tmem_ld_wait();
 #pragma unroll
-        for (int sub = 0; sub < 4; ++sub) {
-          if (sub >= n_sub) continue;
-          const int c0 = g0 + sub * 16;
-          float v[16];
+          for (int sub = 0; sub < 4; ++sub) {
+            if (sub >= n_sub) continue;
+            const int c0 = g0 + sub * 16;
+            float v[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[sub][j]);
-          if (!prm.swap) {
-            // normal orientation: blocks of [128 rows][128 bytes] in the 128-byte swizzle
+            for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[sub][j]);
             if (prm.bias && first_split) {
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
@@ -386,52 +485,35 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                                pack_bf16(v[j + 4], v[j + 5]), pack_bf16(v[j + 6], v[j + 7]));
               }
             }
-          } else {
-            // swapped orientation: a dense [tokens][128 features] tile, lanes along the features
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float x = epilogue_act<ACT>(v[j] + bias_p);
-              if (prm.out_f32)
-                reinterpret_cast<float*>(smem)[(c0 + j) * TC_BP + pl] = x;
-              else
-                reinterpret_cast<bf16*>(smem)[(c0 + j) * TC_BP + pl] = __float2bfloat16_rn(x);
-            }
           }
         }
-      }
-      if (threadIdx.x == 64) TC_STAMP(4);
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
-      asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
-      if (warp == 2 && lane == 0) {
-        if (!prm.swap) {
+        if (threadIdx.x == 64) TC_STAMP(4);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
+        asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
+        if (warp == 2 && lane == 0) {
           const int cols = prm.out_f32 ? 32 : 64;
           for (int c = 0; c < bq && q0 + c < prm.q_rows; c += cols) {
             const void* src = smem + (size_t)(c / cols) * 16384;
             if (prm.residual) tma_reduce_add_2d(&map_o, src, q0 + c, p0);
             else tma_store_2d(&map_o, src, q0 + c, p0);
           }
-        } else {
-          if (prm.residual) tma_reduce_add_2d(&map_o, smem, p0, q0);
-          else tma_store_2d(&map_o, smem, p0, q0);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
+          TC_STAMP(5);
         }
-        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
-        TC_STAMP(5);
-      }
-    } else if (ok) {
-      for (int c0 = 0; c0 < bq; c0 += 16) {
-        if (q0 + c0 >= prm.q_rows) break;  // uniform over the warp
-        float v[16];
-        tmem_ld16(lane_addr + (uint32_t)c0, v);
-        if (!p_ok) continue;
-        if (!prm.swap) {
-          // out[p, q0 + c0 + j]: this thread writes 16 consecutive features of its own row
+      } else {
+        // out[p, q0 + c0 + j] with plain stores: this thread writes 16 consecutive features of its row
+        for (int c0 = 0; c0 < bq; c0 += 16) {
+          if (q0 + c0 >= prm.q_rows) break;  // uniform over the warp
+          float v[16];
+          tmem_ld16(lane_addr + (uint32_t)c0, v);
+          if (!p_ok) continue;
           const int n0 = q0 + c0;
           const int nv = min(16, prm.q_rows - n0);
 #pragma unroll
           for (int j = 0; j < 16; ++j) {  // unrolled with a guard: v[] must stay in registers
             if (j < nv) {
-              const float x = epilogue_act<ACT>(v[j] + (prm.bias ? prm.bias[n0 + j] : 0.0f));
+              const float x = epilogue_act<ACT>(v[j] + ((prm.bias && first_split) ? prm.bias[n0 + j] : 0.0f));
               if (prm.out_f32) {
                 float* o = (float*)prm.out + (size_t)p * prm.ldo + n0 + j;
                 *o = prm.residual ? *o + x : x;
@@ -440,23 +522,73 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
               }
             }
           }
-        } else {
-          // out[q0 + c0 + j, p]: the warp's lanes hold consecutive features of one token's row
-          const float b = prm.bias ? prm.bias[p] : 0.0f;
-          const bool to_cache = prm.kv_cache != nullptr && p >= prm.kv_q_dim;
-          int kv_which = 0, kv_head = 0, kv_d = 0;
-          if (to_cache) {
-            const int kv_dim = prm.kv_heads * prm.kv_head_dim;
-            const int rem = p - prm.kv_q_dim;
-            kv_which = rem / kv_dim;
-            kv_head = (rem % kv_dim) / prm.kv_head_dim;
-            kv_d = rem % prm.kv_head_dim;
+        }
+      }
+    } else if (ok) {
+      // ======== swapped orientation: this thread owns output feature p, the columns are tokens ========
+      bool is_last = true;
+      if (prm.fix_splits > 1) {
+        // K was split: park the raw partial tile, and let the block that arrives last add them up
+        const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+        float* mine = prm.fix_partials + ((tile * prm.fix_splits + blockIdx.z) * bq) * TC_BP;
+        for (int c0 = 0; c0 < bq; c0 += 16) {
+          if (q0 + c0 >= prm.q_rows) break;
+          float v[16];
+          tmem_ld16(lane_addr + (uint32_t)c0, v);
+#pragma unroll
+          for (int j = 0; j < 16; ++j) mine[(size_t)(c0 + j) * TC_BP + pl] = v[j];
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64) {
+          const int arrived = atomicAdd(&prm.fix_counters[tile], 1);
+          fix_last_sh = arrived == prm.fix_splits - 1;
+          if (fix_last_sh) prm.fix_counters[tile] = 0;  // zero again for the next launch
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        is_last = fix_last_sh != 0;
+        if (is_last) __threadfence();
+      }
+      if (is_last) {
+        const size_t tile = (size_t)blockIdx.y * gridDim.x + blockIdx.x;
+        const bool add_bias = prm.bias != nullptr && p_ok && (first_split || prm.fix_splits > 1);
+        const float bias_p = add_bias ? prm.bias[p] : 0.0f;
+        const bool to_cache = prm.kv_cache != nullptr && p >= prm.kv_q_dim;
+        int kv_which = 0, kv_head = 0, kv_d = 0;
+        if (to_cache) {
+          const int kv_dim = prm.kv_heads * prm.kv_head_dim;
+          const int rem = p - prm.kv_q_dim;
+          kv_which = rem / kv_dim;
+          kv_head = (rem % kv_dim) / prm.kv_head_dim;
+          kv_d = rem % prm.kv_head_dim;
+        }
+        for (int c0 = 0; c0 < bq; c0 += 16) {
+          if (!prm.tma_store && q0 + c0 >= prm.q_rows) break;  // uniform over the warp
+          float v[16];
+          if (prm.fix_splits > 1) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = 0.0f;
+            if (q0 + c0 < prm.q_rows) {
+              for (int z = 0; z < prm.fix_splits; ++z) {   // in split order: the sum is the same every run
+                const float* part = prm.fix_partials + ((tile * prm.fix_splits + z) * bq + c0) * TC_BP + pl;
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[j] += part[(size_t)j * TC_BP];
+              }
+            }
+          } else {
+            tmem_ld16(lane_addr + (uint32_t)c0, v);
           }
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int m = q0 + c0 + j;
-            if (m < prm.q_rows) {
-              const float x = epilogue_act<ACT>(v[j] + b);
+            const float x = epilogue_act<ACT>(v[j] + bias_p);
+            if (prm.tma_store) {
+              // a dense [tokens][128 features] tile in the idle pipeline buffers, lanes along the features
+              if (prm.out_f32)
+                reinterpret_cast<float*>(smem)[(c0 + j) * TC_BP + pl] = x;
+              else
+                reinterpret_cast<bf16*>(smem)[(c0 + j) * TC_BP + pl] = __float2bfloat16_rn(x);
+            } else if (m < prm.q_rows && p_ok) {
               if (to_cache) {
                 const int pos = prm.kv_positions[m];
                 const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks +
@@ -474,6 +606,18 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
                 ((bf16*)prm.out)[(size_t)m * prm.ldo + p] = __float2bfloat16_rn(x);
               }
             }
+          }
+        }
+        if (prm.tma_store) {
+          if (threadIdx.x == 64) TC_STAMP(4);
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (warp == 2 && lane == 0) {
+            if (prm.residual) tma_reduce_add_2d(&map_o, smem, p0, q0);
+            else tma_store_2d(&map_o, smem, p0, q0);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+            asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
+            TC_STAMP(5);
           }
         }
       }
@@ -528,9 +672,11 @@ static bool make_map(CUtensorMap* map, const void* base, bool f32, int rows, int
 using namespace nib;
 
 // 1 if the tensor-core path takes this problem, 0 if the caller must use the SIMT kernel.
+// `a` may be null (activations made in the kernel by LayerNorm): then only the weights are checked.
 extern "C" int nib_linear_tc_supported(const void* a, int lda, const void* w, int ldw, int K) {
-  if (K < 8 || (K & 7) || (lda & 7) || (ldw & 7)) return 0;  // TMA: 16-byte row strides
-  if (((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return 0;
+  if (K < 8 || (K & 7) || (ldw & 7)) return 0;  // TMA: 16-byte row strides
+  if ((uintptr_t)w & 15) return 0;
+  if (a != nullptr && ((lda & 7) || ((uintptr_t)a & 15))) return 0;
   return 1;
 }
 
@@ -541,13 +687,32 @@ struct KvTarget {
   const int* positions;
   int max_blocks, q_dim, heads, head_dim, page_size, n_pages;
 };
+struct LnSource {
+  const float* x;
+  int ldx;
+  const float* gamma;
+  const float* beta;
+  float eps;
+  const int* rows;
+};
+struct FixScratch {
+  float* partials;
+  long long n_floats;
+  int* counters;
+  int n_counters;
+};
+
+constexpr int TC_LN_MAX_Q_BYTES = 96 * 1024;  // resident normalised activations in LayerNorm mode
 
 static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
-                     int ldo, int M, int N, int K, int act, int residual, const KvTarget* kv, int* status,
-                     cudaStream_t stream) {
+                     int ldo, int M, int N, int K, int act, int residual, const LnSource* ln, const KvTarget* kv,
+                     const FixScratch* fix, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (ln != nullptr) a = nullptr;
+  if (ln == nullptr && a == nullptr) return NIB_ERR_BAD_ARGUMENT;
   if (!nib_linear_tc_supported(a, lda, w, ldw, K)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (residual && out_dtype != DT_F32) return NIB_ERR_BAD_ARGUMENT;
+  if (ln != nullptr && M > 128) return NIB_ERR_UNSUPPORTED_SIZE;
   TcParams prm;
   prm.K = K;
   prm.out = out;
@@ -570,6 +735,12 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     prm.kv_max_blocks = kv->max_blocks; prm.kv_q_dim = kv->q_dim; prm.kv_heads = kv->heads;
     prm.kv_head_dim = kv->head_dim; prm.kv_page_size = kv->page_size; prm.kv_n_pages = kv->n_pages;
   }
+  prm.ln_x = nullptr; prm.ln_gamma = prm.ln_beta = nullptr; prm.ln_rows = nullptr; prm.ln_ldx = 0; prm.ln_eps = 0.0f;
+  if (ln != nullptr) {
+    prm.ln_x = ln->x; prm.ln_ldx = ln->ldx; prm.ln_gamma = ln->gamma; prm.ln_beta = ln->beta;
+    prm.ln_eps = ln->eps; prm.ln_rows = ln->rows;
+  }
+  prm.fix_partials = nullptr; prm.fix_counters = nullptr; prm.fix_splits = 0;
   prm.swap = M <= 128;
   const int esz = prm.out_f32 ? 4 : 2;
   // TMA can store the tile if the output's rows are 16-byte multiples (it also clips a store at the
@@ -582,13 +753,23 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     prm.p_rows = N; prm.q_rows = M; p_base = w; p_ld = ldw; q_base = a; q_ld = lda;
     prm.bq = (M + 15) / 16 * 16;
     prm.tma_store = tma_ok && kv == nullptr;
-    // few tiles cannot pull the weights at full bandwidth: split K where the tiles can be summed
-    // in memory (the residual add), at least two 64-wide blocks per split
+    // Few tiles cannot pull the weights at full bandwidth: split K over more blocks, at least two
+    // 64-wide blocks each.  The residual add sums the splits in memory (TMA reduce-add); other
+    // outputs need the caller's scratch, where the last block of a tile adds the partial tiles up.
     const int tiles = (N + TC_BP - 1) / TC_BP;
-    if (residual && tma_ok && tiles < 148) {
-      splits = (148 + tiles - 1) / tiles;
-      if (splits > num_kb64 / 2) splits = num_kb64 / 2;
-      if (splits < 1) splits = 1;
+    if (tiles < 148 && num_kb64 >= 4) {
+      int want = (148 + tiles - 1) / tiles;
+      if (want > num_kb64 / 2) want = num_kb64 / 2;
+      if (want >= 2) {
+        if (residual && prm.tma_store) {
+          splits = want;
+        } else if (fix != nullptr && fix->partials != nullptr && fix->counters != nullptr &&
+                   (long long)tiles * want * prm.bq * TC_BP <= fix->n_floats && tiles <= fix->n_counters) {
+          splits = want;
+          prm.fix_partials = fix->partials;
+          prm.fix_counters = fix->counters;
+        }
+      }
     }
   } else {
     prm.p_rows = M; prm.q_rows = N; p_base = a; p_ld = lda; q_base = w; q_ld = ldw;
@@ -617,27 +798,42 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
   }
   prm.kb_per_split = (num_kb64 + splits - 1) / splits;
   splits = (num_kb64 + prm.kb_per_split - 1) / prm.kb_per_split;
+  if (prm.fix_partials != nullptr) prm.fix_splits = splits;
+  if (prm.fix_splits <= 1) { prm.fix_partials = nullptr; prm.fix_counters = nullptr; prm.fix_splits = 0; }
   prm.k_sub = (prm.bq <= 128 && prm.kb_per_split >= 4) ? 2 : 1;
-  const int stage_bytes = prm.k_sub * (TC_BP * TC_BK * 2 + prm.bq * TC_BK * 2);
   const int num_stage_steps = (prm.kb_per_split + prm.k_sub - 1) / prm.k_sub;
+  const int q_block = prm.bq * TC_BK * 2;
+  size_t q_resident = 0;
+  if (ln != nullptr) {
+    q_resident = (size_t)num_stage_steps * prm.k_sub * q_block;
+    if (q_resident > (size_t)TC_LN_MAX_Q_BYTES) return NIB_ERR_UNSUPPORTED_SIZE;
+  }
+  const int stage_bytes = prm.k_sub * (TC_BP * TC_BK * 2 + (ln != nullptr ? 0 : q_block));
   // A deep pipeline (one block per SM) unless the grid is several waves of bandwidth-bound blocks
   // (the head's 393 tiles of a decode step): then about 72 KB per block, so that three blocks share
   // an SM and one's prologue and epilogue hide behind the others' loads.
   const long n_ctas = (long)((prm.p_rows + TC_BP - 1) / TC_BP) * ((prm.q_rows + prm.bq - 1) / prm.bq) * splits;
-  int stages = ((prm.swap && n_ctas > 2 * 148 ? 72 : 200) * 1024) / stage_bytes;
+  long budget = (prm.swap && n_ctas > 2 * 148 ? 72 : 200) * 1024 - (long)q_resident;
+  if (budget < 2 * stage_bytes) budget = 2 * stage_bytes;
+  int stages = (int)(budget / stage_bytes);
   if (stages < 2) stages = 2;
   if (stages > TC_MAX_STAGES) stages = TC_MAX_STAGES;
   if (stages > num_stage_steps) stages = num_stage_steps;
   if (stages < 1) stages = 1;
   prm.stages = stages;
-  size_t tile_bytes = (size_t)stages * stage_bytes;
+  size_t tile_bytes = (size_t)stages * stage_bytes + q_resident;
   const size_t staging = (size_t)TC_BP * prm.bq * esz;
   if (prm.tma_store && staging > tile_bytes) tile_bytes = staging;
   const size_t smem = tile_bytes + 1024;
+  if (smem > 225 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
 
   CUtensorMap map_p, map_q, map_o;
   if (!make_map(&map_p, p_base, false, prm.p_rows, K, p_ld, TC_BP, TC_BK, true)) return NIB_ERR_DRIVER;
-  if (!make_map(&map_q, q_base, false, prm.q_rows, K, q_ld, prm.bq, TC_BK, true)) return NIB_ERR_DRIVER;
+  if (ln == nullptr) {
+    if (!make_map(&map_q, q_base, false, prm.q_rows, K, q_ld, prm.bq, TC_BK, true)) return NIB_ERR_DRIVER;
+  } else {
+    map_q = map_p;  // unused
+  }
   if (prm.tma_store) {
     const bool ok = prm.swap ? make_map(&map_o, out, prm.out_f32, M, N, ldo, prm.bq, TC_BP, false)
                              : make_map(&map_o, out, prm.out_f32, M, N, ldo, TC_BP, prm.out_f32 ? 32 : 64, true);
@@ -675,19 +871,33 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
 extern "C" int nib_linear_tc(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
                              void* out, int ldo, int M, int N, int K, int act, int residual, int* status,
                              cudaStream_t stream) {
-  return launch_tc(out_dtype, a, lda, w, ldw, bias, out, ldo, M, N, K, act, residual, nullptr, status, stream);
+  return launch_tc(out_dtype, a, lda, w, ldw, bias, out, ldo, M, N, K, act, residual, nullptr, nullptr, nullptr,
+                   status, stream);
 }
 
-// The fused query/key/value projection of a step of at most 128 rows: out[m, n] for the first q_dim
-// features (the queries, bfloat16), the rest written to the rows' slots in one cache layer
-// [n_pages, 2, n_kv_head, page_size, head_dim] through the block tables.
-extern "C" int nib_linear_tc_qkv(const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
-                                 int ldo, int M, int N, int K, void* cache, const int* block_table,
-                                 int max_blocks, const int* row_entry, const int* positions, int q_dim,
-                                 int n_kv_head, int head_dim, int page_size, int n_pages, int* status,
-                                 cudaStream_t stream) {
+// The general form for steps of at most 128 rows.  Any of three options may be on:
+//   * ln_x != null: the activations are LayerNorm(ln_x[ln_rows[m] or m]) (gamma, beta, eps), made in
+//     the kernel from the 32-bit residual stream (`a` is ignored);
+//   * cache != null: the fused query/key/value projection: the first q_dim features go to out, the
+//     rest to the rows' slots in one cache layer [n_pages, 2, n_kv_head, page_size, head_dim];
+//   * fix_partials != null: scratch (floats, and zeroed int counters that the kernel leaves zero)
+//     that lets K be split over blocks for outputs that are not a residual add.
+// Returns NIB_ERR_UNSUPPORTED_SIZE where the shape is not taken (more than 128 rows with ln_x, or
+// too much K for the resident activations); the caller then runs the plain kernels.
+extern "C" int nib_linear_tc_small(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
+                                   void* out, int ldo, int M, int N, int K, int act, int residual,
+                                   const float* ln_x, int ln_ldx, const float* ln_gamma, const float* ln_beta,
+                                   float ln_eps, const int* ln_rows, void* cache, const int* block_table,
+                                   int max_blocks, const int* row_entry, const int* positions, int q_dim,
+                                   int n_kv_head, int head_dim, int page_size, int n_pages, float* fix_partials,
+                                   long long fix_floats, int* fix_counters, int fix_n_counters, int* status,
+                                   cudaStream_t stream) {
+  if (M > 128) return NIB_ERR_UNSUPPORTED_SIZE;
+  LnSource ln{ln_x, ln_ldx, ln_gamma, ln_beta, ln_eps, ln_rows};
   KvTarget kv{cache, block_table, row_entry, positions, max_blocks, q_dim, n_kv_head, head_dim, page_size, n_pages};
-  return launch_tc(DT_BF16, a, lda, w, ldw, bias, out, ldo, M, N, K, ACT_NONE, 0, &kv, status, stream);
+  FixScratch fix{fix_partials, fix_floats, fix_counters, fix_n_counters};
+  return launch_tc(out_dtype, a, lda, w, ldw, bias, out, ldo, M, N, K, act, residual, ln_x ? &ln : nullptr,
+                   cache ? &kv : nullptr, fix_partials ? &fix : nullptr, status, stream);
 }
 
 #ifdef NIB_TC_TIMING

@@ -39,7 +39,13 @@ _SIGNATURES = {
     "nib_linear_tc_supported": [_c_ptr, _c_int, _c_ptr, _c_int, _c_int],
     "nib_linear_tc": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                       _c_int, _c_int, _c_ptr, _c_ptr],
-    "nib_linear_tc_qkv": [_c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+    "nib_linear_tc_small": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
+                            _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                            ctypes.c_longlong, _c_ptr, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_skinny_supported": [_c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_skinny": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
+                          _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
                           _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
@@ -237,16 +243,147 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
 
 
 def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
-    return bool(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and library().nib_linear_tc_supported(
-        _ptr(a), a.stride(0), _ptr(w), w.stride(0), w.shape[1]))
+    return bool(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
+                and library().nib_linear_tc_supported(_ptr(a), a.stride(0), _ptr(w), w.stride(0), w.shape[1]))
 
 
-def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
-           act: int = ACT_NONE, residual: bool = False) -> None:
+class NormInput:
+    """Activations given as the 32-bit residual stream plus the parameters of the LayerNorm that
+    stands before the product: ``linear`` normalises ``x[rows[m]]`` (or ``x[m]``) itself, inside the
+    tensor-core kernel where the step is small enough, else with the LayerNorm kernel into scratch
+    taken from ``workspace``."""
+
+    def __init__(self, x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, workspace,
+                 dtype: torch.dtype, rows: Optional[torch.Tensor] = None, max_rows: int = 0):
+        self.x, self.gamma, self.beta, self.eps = x, gamma, beta, float(eps)
+        self.workspace, self.dtype, self.rows, self.max_rows = workspace, dtype, rows, max_rows
+
+    def materialise(self, M: int) -> torch.Tensor:
+        out = self.workspace.get("norm.fallback", (max(M, self.max_rows), self.x.shape[1]), self.dtype)
+        layernorm(self.x, self.gamma, self.beta, self.eps, out, M, self.rows)
+        return out
+
+
+SMALL_STEP_MAX_ROWS = 128
+_split_scratch: Optional[torch.Tensor] = None
+_split_counters: Optional[torch.Tensor] = None
+
+
+def _split_buffers(device):
+    """Scratch for the K splits of small steps: 4 M floats of partial tiles and 4096 tile counters
+    (found zero and left zero by the kernel), allocated once."""
+    global _split_scratch, _split_counters
+    if _split_scratch is None:
+        _split_scratch = torch.empty(4 << 20, dtype=torch.float32, device=device)
+        _split_counters = torch.zeros(4096, dtype=torch.int32, device=device)
+    return _split_scratch, _split_counters
+
+
+def _option_args(norm, kv):
+    if kv is not None:
+        cache, block_table, row_entry, positions, q_dim = kv
+        n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+        kv_args = (_ptr(cache), _ptr(block_table), block_table.shape[1], _ptr(row_entry), _ptr(positions), q_dim,
+                   n_kv_head, head_dim, page_size, n_pages)
+    else:
+        kv_args = (None, None, 0, None, None, 0, 0, 0, 0, 0)
+    if norm is not None:
+        ln_args = (_ptr(norm.x), norm.x.stride(0), _ptr(norm.gamma), _ptr(norm.beta), norm.eps, _ptr(norm.rows))
+    else:
+        ln_args = (None, 0, None, None, 0.0, None)
+    return ln_args, kv_args
+
+
+def _small_inputs_ok(a, norm, w, out) -> bool:
+    if w.dtype != torch.bfloat16 or w.stride(1) != 1 or out.stride(1) != 1:
+        return False
+    if a is not None and (a.dtype != torch.bfloat16 or a.stride(1) != 1):
+        return False
+    if norm is not None and (norm.x.dtype != torch.float32 or norm.x.stride(1) != 1):
+        return False
+    return a is not None or norm is not None
+
+
+SKINNY_MAX_ROWS = 16
+
+
+def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None) -> bool:
+    """The CUDA-core kernel for steps of at most 16 rows (bfloat16): every SM streams weight rows, a
+    few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in; ``kv``:
+    (cache layer, block table, row_entry, positions, q_dim) sends keys and values straight to the
+    cache.  False if the kernel does not apply."""
+    if M > SKINNY_MAX_ROWS or not _small_inputs_ok(a, norm, w, out):
+        return False
+    N, K = w.shape
+    lib = library()
+    if not lib.nib_linear_skinny_supported(M, K, w.stride(0), 0, _ptr(w), None):
+        return False
+    ln_args, kv_args = _option_args(norm, kv)
+    if _profiler is not None:
+        _profiler.label = f"M={M} N={N} K={K}" + (" ln" if norm is not None else "") + (" kv" if kv else "")
+    code = lib.nib_linear_skinny(_dt(out), _ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0),
+                                 _ptr(bias), _ptr(out), out.stride(0), M, N, K, act, int(residual), *ln_args,
+                                 *kv_args, _ptr(status_word()), _stream())
+    if code == -2:   # alignment or size not taken
+        return False
+    _check(code, "linear_skinny")
+    return True
+
+
+def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=True) -> bool:
+    """The tensor-core kernel for steps of at most 128 rows with its options: ``norm`` folds the
+    LayerNorm before the product into the kernel, ``kv`` sends keys and values straight to the
+    cache, ``split`` lets K be split over blocks through scratch.  False if it does not apply."""
+    if M > SMALL_STEP_MAX_ROWS or not _small_inputs_ok(a, norm, w, out):
+        return False
+    N, K = w.shape
+    lib = library()
+    if not lib.nib_linear_tc_supported(_ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0), K):
+        return False
+    parts, counters = _split_buffers(w.device) if split else (None, None)
+    ln_args, kv_args = _option_args(norm, kv)
+    if _profiler is not None:
+        _profiler.label = f"M={M} N={N} K={K}" + (" ln" if norm is not None else "") + (" kv" if kv else "")
+    code = lib.nib_linear_tc_small(_dt(out), _ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0),
+                                   _ptr(bias), _ptr(out), out.stride(0), M, N, K, act, int(residual), *ln_args,
+                                   *kv_args, _ptr(parts), parts.numel() if split else 0, _ptr(counters),
+                                   counters.numel() if split else 0, _ptr(status_word()), _stream())
+    if code == -2:   # the shape is not taken by the small-step kernel
+        return False
+    _check(code, "linear_tc_small")
+    return True
+
+
+def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
+    """Steps of at most 128 rows: up to 16 rows the CUDA-core kernel (with the LayerNorm folded in),
+    beyond that the tensor cores.  Folding the norm into the tensor-core kernel, or splitting K
+    through scratch, costs more round trips than it saves at these sizes, so the tensor-core kernel
+    is given normed rows and is not split here."""
+    if M <= SKINNY_MAX_ROWS:
+        if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
+            return True
+        if norm is not None:   # too wide to be normalised inside the kernel: normalise first
+            a, norm = norm.materialise(M), None
+            if linear_skinny(a, None, w, bias, out, M, act, residual, kv):
+                return True
+    if M > SMALL_STEP_MAX_ROWS or kv is None:
+        return False          # the plain tensor-core call does as well
+    if norm is not None:
+        a, norm = norm.materialise(M), None
+    return linear_small_tc(a, norm, w, bias, out, M, act, residual, kv, split=False)
+
+
+def linear(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+           act: int = ACT_NONE, residual: bool = False, norm: Optional[NormInput] = None) -> None:
     """The matrix product of the model: out[:M] = act(a[:M] . w^T + bias), added to the 32-bit
-    ``out`` with ``residual``.  bfloat16 runs on the tensor cores where shape and alignment allow
-    (rows of 16-byte multiples), else on the CUDA cores; float32 always runs on the CUDA cores in
-    true 32-bit arithmetic."""
+    ``out`` with ``residual``.  With ``norm`` the activations are LayerNorm of the residual stream
+    (``a`` is then None).  bfloat16 runs on the tensor cores where shape and alignment allow (rows
+    of 16-byte multiples), else on the CUDA cores; float32 always runs on the CUDA cores in true
+    32-bit arithmetic."""
+    if _linear_small(a, norm, w, bias, out, M, act, residual):
+        return
+    if norm is not None:
+        a = norm.materialise(M)   # (scratch: a second call for the same rows rewrites the same values)
     if _profiler is not None:
         _profiler.label = f"M={M} N={w.shape[0]} K={w.shape[1]}"
     if linear_tc_supported(a, w):
@@ -255,27 +392,16 @@ def linear(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: 
         linear_simt(a, w, bias, out, M, act, residual)
 
 
-QKV_FUSED_MAX_ROWS = 128
-
-
-def linear_qkv(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+def linear_qkv(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
                q_dim: int, cache: torch.Tensor, block_table: torch.Tensor, row_entry: torch.Tensor,
-               positions: torch.Tensor, status: torch.Tensor) -> bool:
+               positions: torch.Tensor, status: torch.Tensor, norm: Optional[NormInput] = None) -> bool:
     """The fused q/k/v projection with the cache append in its epilogue: queries to out[:M, :q_dim],
     keys and values to their slots of ``cache``.  Returns False (and does nothing) where the fused
     kernel does not apply: more than 128 rows, float32, or a shape the tensor cores refuse."""
-    if M > QKV_FUSED_MAX_ROWS or not linear_tc_supported(a, w) or cache.dtype != torch.bfloat16 \
-            or out.dtype != torch.bfloat16:
+    if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         return False
-    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
-    N, K = w.shape
-    if _profiler is not None:
-        _profiler.label = f"M={M} N={N} K={K} qkv"
-    _check(library().nib_linear_tc_qkv(_ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
-                                       out.stride(0), M, N, K, _ptr(cache), _ptr(block_table),
-                                       block_table.shape[1], _ptr(row_entry), _ptr(positions), q_dim, n_kv_head,
-                                       head_dim, page_size, n_pages, _ptr(status), _stream()), "linear_tc_qkv")
-    return True
+    return _linear_small(a, norm, w, bias, out, M, ACT_NONE, False,
+                         kv=(cache, block_table, row_entry, positions, q_dim))
 
 
 def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, block_table: torch.Tensor,

@@ -155,8 +155,12 @@ class Model:
             self.layers[e.layer].forward(x, ctx, caches.get(owner), states.get(i), e.cache_of is None, self.dtype)
         if n_logits <= 0:
             return None
-        h = ws.get("model.final", (n_logits, self.width), self.dtype)
-        self.final_norm.forward(x, h, n_logits, rows=logit_rows)
+        # the final norm runs on the wanted rows only; the head folds it into its product where it can
+        h = self.final_norm.as_input(x, ctx, self.dtype, rows=logit_rows) if getattr(
+            self.head, "takes_norm_input", False) else None
+        if h is None:
+            h = ws.get("model.final", (n_logits, self.width), self.dtype)
+            self.final_norm.forward(x, h, n_logits, rows=logit_rows)
         pitch = _round_up(self.vocab_size, 16)
         logits = ws.get("model.logits", (n_logits, pitch), torch.float32)
         self.head.forward(h, logits[:, :self.vocab_size], n_logits, ctx)

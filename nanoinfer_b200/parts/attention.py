@@ -20,8 +20,15 @@ from .base import (MATRIX, VECTOR, KVCacheSpec, KVCacheView, Mixer, ParamSpec, P
                    register_mixer)
 
 
+def _split(xn):
+    """(tensor, norm input): a part's input is either the normed rows or a foldable norm input."""
+    return (None, xn) if isinstance(xn, ops.NormInput) else (xn, None)
+
+
 @register_mixer("causal_attention")
 class CausalSelfAttention(Mixer):
+    takes_norm_input = True
+
     def __init__(self, width: int, n_head: int, n_kv_head: int, head_dim: int, scale: float,
                  window: int = 0, bias: bool = True, position: Optional[PositionEncoding] = None):
         if n_head <= 0 or n_kv_head <= 0 or n_head % n_kv_head != 0:
@@ -52,14 +59,15 @@ class CausalSelfAttention(Mixer):
             raise ValueError("causal_attention needs a paged cache")
         T, p = ctx.n_rows, self.params
         ws = ctx.workspace
+        xn, norm = _split(xn)
         if writes_cache:
             qkv = ws.get("attention.qkv", (ctx.max_rows, self.q_dim + 2 * self.kv_dim), self.dtype)
             # small steps: keys and values go to the cache from the projection's epilogue
             fused = self.position is None and ops.linear_qkv(
                 xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T, self.q_dim, cache.layer, cache.block_table,
-                ctx.row_entry, ctx.positions, ctx.status)
+                ctx.row_entry, ctx.positions, ctx.status, norm=norm)
             if not fused:
-                ops.linear(xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T)
+                ops.linear(xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T, norm=norm)
                 if self.position is not None:
                     self.position.on_qk(qkv[:T, :self.q_dim], qkv[:T, self.q_dim:self.q_dim + self.kv_dim], ctx)
                 ops.kv_append(qkv, self.q_dim, self.q_dim + self.kv_dim, cache.layer, cache.block_table,
@@ -69,7 +77,7 @@ class CausalSelfAttention(Mixer):
             # this layer reads another layer's keys and values: only the queries are projected
             q = ws.get("attention.q", (ctx.max_rows, self.q_dim), self.dtype)
             qb = p.get("qkv_bias")
-            ops.linear(xn, p["qkv_weight"][:self.q_dim], None if qb is None else qb[:self.q_dim], q, T)
+            ops.linear(xn, p["qkv_weight"][:self.q_dim], None if qb is None else qb[:self.q_dim], q, T, norm=norm)
             if self.position is not None:
                 self.position.on_qk(q[:T], None, ctx)
         att = ws.get("attention.out", (ctx.max_rows, self.q_dim), self.dtype)

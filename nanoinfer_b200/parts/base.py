@@ -84,6 +84,13 @@ class Norm(Part):
         """out[:n_rows] = norm(x[rows] or x[:n_rows]); x is the 32-bit residual stream."""
         raise NotImplementedError
 
+    def as_input(self, x: torch.Tensor, ctx: "StepContext", dtype: torch.dtype,
+                 rows: Optional[torch.Tensor] = None):
+        """Optional: this norm of ``x`` in a form that a following matrix product accepts as its
+        activations and may fold into its own kernel (``kernels.ops.NormInput``).  None: the norm
+        cannot be folded, and is run by ``forward``."""
+        return None
+
 
 class PositionEncoding(Part):
     """Either adds to the embeddings (``additive_table``/``on_embedding``) or transforms
@@ -105,7 +112,12 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     """Mixes information across positions (attention here).  ``forward`` reads the normed
-    rows ``xn`` and ADDS its output to the 32-bit residual stream ``x`` in place."""
+    rows ``xn`` and ADDS its output to the 32-bit residual stream ``x`` in place.
+
+    A part that sets ``takes_norm_input = True`` may be given ``xn`` as a foldable norm input
+    (``Norm.as_input``) instead of a tensor, and passes it on to its first matrix product."""
+
+    takes_norm_input = False
 
     def kv_spec(self) -> Optional[KVCacheSpec]:
         return None
@@ -119,7 +131,10 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
-    """Per-row transformation; ``forward`` ADDS its output to the residual stream ``x``."""
+    """Per-row transformation; ``forward`` ADDS its output to the residual stream ``x``.
+    ``takes_norm_input`` as for mixers."""
+
+    takes_norm_input = False
 
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: "StepContext") -> None:
         raise NotImplementedError

@@ -36,10 +36,17 @@ class Block:
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
-    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
-        T = ctx.n_rows
+    def _normed(self, norm, part, x, ctx, dtype):
+        """The part's input: a foldable norm input where both the norm and the part can do that,
+        else the norm's output in scratch."""
+        if part.takes_norm_input:
+            folded = norm.as_input(x, ctx, dtype)
+            if folded is not None:
+                return folded
         xn = ctx.workspace.get("block.normed", (ctx.max_rows, self.width), dtype)
-        self.norm_1.forward(x, xn, T)
-        self.mixer.forward(xn, x, ctx, cache, state, writes_cache)
-        self.norm_2.forward(x, xn, T)
-        self.feed_forward.forward(xn, x, ctx)
+        norm.forward(x, xn, ctx.n_rows)
+        return xn
+
+    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
+        self.mixer.forward(self._normed(self.norm_1, self.mixer, x, ctx, dtype), x, ctx, cache, state, writes_cache)
+        self.feed_forward.forward(self._normed(self.norm_2, self.feed_forward, x, ctx, dtype), x, ctx)

@@ -13,6 +13,8 @@ from .base import TABLE, Head, ParamSpec, StepContext, register_head
 
 @register_head("linear_head")
 class LinearHead(Head):
+    takes_norm_input = True
+
     def __init__(self, vocab_size: int, width: int):
         self._vocab, self.width = int(vocab_size), int(width)
 
@@ -23,5 +25,9 @@ class LinearHead(Head):
     def param_specs(self) -> List[ParamSpec]:
         return [ParamSpec("weight", (self._vocab, self.width), TABLE)]
 
-    def forward(self, h: torch.Tensor, out: torch.Tensor, n_rows: int, ctx: StepContext) -> None:
-        ops.linear(h, self.params["weight"], None, out, n_rows)
+    def forward(self, h, out: torch.Tensor, n_rows: int, ctx: StepContext) -> None:
+        """``h``: the normed rows, or a foldable norm input (``Norm.as_input``) of the rows wanted."""
+        if isinstance(h, ops.NormInput):
+            ops.linear(None, self.params["weight"], None, out, n_rows, norm=h)
+        else:
+            ops.linear(h, self.params["weight"], None, out, n_rows)

@@ -15,6 +15,8 @@ from .base import MATRIX, VECTOR, FeedForward, ParamSpec, StepContext, register_
 
 @register_feed_forward("dense_mlp")
 class DenseMLP(FeedForward):
+    takes_norm_input = True
+
     def __init__(self, width: int, inner: int, activation: str, bias: bool = True):
         if activation not in ("tanh", "erf"):
             raise ValueError(f"activation {activation!r} is not one of 'tanh', 'erf' (the two GELU forms)")
@@ -30,5 +32,6 @@ class DenseMLP(FeedForward):
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
         T, p = ctx.n_rows, self.params
         fc = ctx.workspace.get("mlp.fc", (ctx.max_rows, self.inner), self.dtype)
-        ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, act=ops.ACT_CODES[self.activation])
+        xn, norm = (None, xn) if isinstance(xn, ops.NormInput) else (xn, None)
+        ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, act=ops.ACT_CODES[self.activation], norm=norm)
         ops.linear(fc, p["proj_weight"], p.get("proj_bias"), x, T, residual=True)

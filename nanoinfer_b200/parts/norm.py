@@ -22,6 +22,12 @@ class LayerNorm(Norm):
             ParamSpec("bias", (self.width,), VECTOR, INIT_NORMAL),
         ]
 
+    def as_input(self, x: torch.Tensor, ctx, dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
+        """This norm applied to the residual stream, in the form a matrix product can take as its
+        activations (the product then normalises the rows itself where it can)."""
+        return ops.NormInput(x, self.params["weight"], self.params["bias"], self.eps, ctx.workspace, dtype,
+                             rows=rows, max_rows=0 if rows is not None else ctx.max_rows)
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> None:
         ops.layernorm(x, self.params["weight"], self.params["bias"], self.eps, out, n_rows, rows)

@@ -353,3 +353,71 @@ def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd)
         want[page, 1, :, positions[e] % ps] = y[e, q_dim + kv_dim:].view(n_kv_head, hd)
     assert (cache.cpu().double() - want).abs().max() < 2e-2
     assert (out.cpu()[:, q_dim:] == 0).all()            # key and value columns of the buffer are not written
+
+
+SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (64, 1000, 120), (128, 257, 64),
+                (16, 768, 3072), (5, 50257, 64)]
+
+
+@pytest.mark.parametrize("M, N, K", SMALL_SHAPES)
+@pytest.mark.parametrize("folded", [False, True])
+@pytest.mark.parametrize("kernel", ["dispatch", "tensor_core"])
+def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, kernel):
+    """Steps of at most 128 rows, through the dispatcher (CUDA-core kernel up to 16 rows) and through
+    the tensor-core kernel with all its options: K split over blocks (partial tiles summed by the last
+    block, or reduce-added for the residual) and the LayerNorm before the product folded in."""
+    o = ops()
+
+    def product(a, wd, bd, out, M, act=0, residual=False, norm=None):
+        if kernel == "dispatch":
+            o.linear(a, wd, bd, out, M, act=act, residual=residual, norm=norm)
+        else:
+            assert o.linear_small_tc(a, norm, wd, bd, out, M, act, residual, split=True)
+
+    from nanoinfer_b200.parts.base import Workspace
+    g = gen(M * 3 + N + K)
+    x = torch.randn(M + 5, K, generator=g) * 2.0 + 0.5
+    gamma, beta = 1 + 0.1 * torch.randn(K, generator=g), 0.1 * torch.randn(K, generator=g)
+    rows = torch.randperm(M + 5, generator=g)[:M].to(torch.int32)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    xn = P.layernorm(x.double(), gamma.double(), beta.double(), 1e-5)[rows.long()]
+    xn16 = xn.to(torch.bfloat16)
+    y = xn16.double() @ w.double().T + b.double()
+    scale = max(1.0, float(y.abs().max()))
+    ws = Workspace(torch.device(DEV))
+    wd, bd = w.to(DEV), b.to(DEV)
+
+    def activations():
+        if folded:
+            return None, o.NormInput(x.to(DEV), gamma.to(DEV), beta.to(DEV), 1e-5, ws, torch.bfloat16,
+                                     rows=rows.to(DEV))
+        return xn16.to(DEV), None
+
+    for act, fn in (("none", lambda u: u), ("tanh", P.gelu_tanh)):
+        a, norm = activations()
+        out = torch.full((M + 2, N), 3.0, dtype=torch.bfloat16, device=DEV)
+        product(a, wd, bd, out, M, act=o.ACT_CODES[act], norm=norm)
+        assert (out.cpu().double()[:M] - fn(y)).abs().max() < 1.5e-2 * scale, act
+        assert (out.cpu()[M:] == 3.0).all()
+    a, norm = activations()
+    res = torch.randn(M + 2, N, generator=g)
+    rd = res.to(DEV)
+    product(a, wd, bd, rd, M, residual=True, norm=norm)
+    assert (rd.cpu().double()[:M] - (res.double()[:M] + y)).abs().max() < 4e-3 * scale
+    assert torch.equal(rd.cpu()[M:], res[M:])
+    a, norm = activations()
+    pitch = (N + 15) // 16 * 16
+    buf = torch.full((M, pitch), -7.0, device=DEV)
+    product(a, wd, None, buf[:, :N], M, norm=norm)
+    assert (buf.cpu().double()[:, :N] - (y - b.double())).abs().max() < 4e-3 * scale
+    assert (buf.cpu()[:, N:] == -7.0).all()
+    assert int(o.status_word().item()) == 0
+    # the same call twice gives the same bits: the splits are summed in a fixed order
+    a, norm = activations()
+    out1 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    product(a, wd, bd, out1, M, norm=norm)
+    a, norm = activations()
+    out2 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    product(a, wd, bd, out2, M, norm=norm)
+    assert torch.equal(out1, out2)
