@@ -54,15 +54,16 @@ int nib_linear_tc_small(int out_dtype, const void* a, int lda, const void* w, in
                         int page_size, int n_pages, float* fix_partials, long long fix_floats,
                         int* fix_counters, int fix_n_counters, int* status, cudaStream_t stream);
 
-// The product for steps of at most 16 rows on the CUDA cores (bfloat16), with the same LayerNorm and
-// cache options as nib_linear_tc_small.
-int nib_linear_skinny_supported(int M, int K, int ldw, int lda, const void* w, const void* a);
+// The product for steps of at most 64 rows with warp-level MMAs (bfloat16), with the same LayerNorm
+// (at most 16 rows) and cache options as nib_linear_tc_small.  split: blocks of a cluster that split
+// K (0: chosen by the library; else 1, 2, 4 or 8).
+int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const void* w);
 int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
                       int ldo, int M, int N, int K, int act, int residual, const float* ln_x, int ln_ldx,
                       const float* ln_gamma, const float* ln_beta, float ln_eps, const int* ln_rows,
                       void* cache, const int* block_table, int max_blocks, const int* row_entry,
                       const int* positions, int q_dim, int n_kv_head, int head_dim, int page_size, int n_pages,
-                      int* status, cudaStream_t stream);
+                      int split, int* status, cudaStream_t stream);
 
 // Causal attention of T query rows over the paged cache (general SIMT kernel).  rows: the
 // step's rows to process (nullptr: rows 0..T-1).

@@ -21,13 +21,13 @@ template <typename T> struct Piece;  // one 16-byte piece of a key or value row
 template <> struct Piece<float> {
   static constexpr int N = 4;
   float4 raw;
-  __device__ __forceinline__ void load(const float* p) { raw = *reinterpret_cast<const float4*>(p); }
+  __device__ __forceinline__ void load(const void* p) { raw = *reinterpret_cast<const float4*>(p); }
   __device__ __forceinline__ void unpack(float* f) const { f[0] = raw.x; f[1] = raw.y; f[2] = raw.z; f[3] = raw.w; }
 };
 template <> struct Piece<bf16> {
   static constexpr int N = 8;
   uint4 raw;
-  __device__ __forceinline__ void load(const bf16* p) { raw = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void load(const void* p) { raw = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void unpack(float* f) const {
     const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
@@ -39,21 +39,26 @@ template <> struct Piece<bf16> {
   }
 };
 
+// 2^x by the hardware's approximation (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float pow2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 // partial layout: o [row][head][split][head_dim], ml [row][head][split][2]
 //
-// Inside a warp, lanes 2s and 2s+1 own key slot s of every 16-key unit: they split the 16-byte
-// pieces of the key row (and of the value row) between them, so a unit is 32 lanes x several
-// independent 16-byte loads.  Each lane pair keeps an online softmax of its own over its keys
-// (no exchange between lanes inside the loop but the one that completes the dot product); the
-// sixteen pairs, then the four warps, are merged once at the end, in a fixed order.
-// Units of sixteen keys whose loads a warp keeps in flight together (fewer when a lane holds many pieces).
-#ifndef NIB_DEC_UNITS
-#define NIB_DEC_UNITS 1
-#endif
-#define NIB_DEC_UNITS_FOR(pieces) ((pieces) <= 4 ? NIB_DEC_UNITS : 1)
-
-template <typename T, int HD_MAX>
-__global__ void __launch_bounds__(DEC_WARPS * 32)
+// A (page, K|V, head) of the cache is a contiguous run of rows, so a warp reads it as a plain
+// stream: LPR lanes stand side by side on one key row (a 16-byte piece each; LPR is the power of
+// two that covers the row), the 32 / LPR lane groups of the warp on consecutive rows, and one load
+// instruction of the warp covers whole 128-byte lines.  (Lanes spread over many rows with a piece
+// of each ask for a 32-byte sector per line and instruction, which halves what the memory system
+// delivers.)  A lane keeps the score products of its piece, the group completes them with
+// shuffles; every group runs an online softmax of its own over its keys, BATCH keys at a time, and
+// keeps the output for its lanes' pieces.  The groups, then the warps, are merged once at the end,
+// in a fixed order.
+template <typename T, int LPR>
+__global__ void __launch_bounds__(DEC_WARPS * 32, 6)   // six blocks an SM: what the host's choice of splits counts on
 attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* __restrict__ part_o,
                         float* __restrict__ part_ml, T* __restrict__ out, int ldo,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
@@ -61,13 +66,15 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
                         int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status) {
   constexpr int VN = Piece<T>::N;
-  constexpr int MAXP = HD_MAX / VN / 2;   // pieces per lane
+  constexpr int BATCH = LPR / 2 < 4 ? LPR / 2 : 4;   // keys per lane group and batch
+  constexpr int GROUPS = 32 / LPR;                   // lane groups of a warp: rows per load instruction
+  constexpr int BK = BATCH * GROUPS;                 // keys per batch of a warp: 16, 8 or 4
+  constexpr int ALL_GROUPS = DEC_WARPS * GROUPS;
   pdl_trigger();
-  extern __shared__ float smem[];
-  float* qs = smem;                                  // head_dim
-  float* wo = smem + head_dim;                       // DEC_WARPS * head_dim
-  float* wm = wo + DEC_WARPS * head_dim;             // DEC_WARPS
-  float* wl = wm + DEC_WARPS;                        // DEC_WARPS
+  extern __shared__ __align__(16) float smem[];
+  float* go = smem;                                  // ALL_GROUPS * head_dim
+  float* gm = go + ALL_GROUPS * head_dim;            // ALL_GROUPS
+  float* gl = gm + ALL_GROUPS;                       // ALL_GROUPS
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
   // The step's tables were written before the step began and the cache below this row's position
@@ -84,47 +91,42 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   __shared__ int is_last_sh;
   const bool empty = k_begin >= k_end;  // nothing in this split: the merge skips l == 0
 
-  const int n_pieces = head_dim / VN;  // 16-byte pieces per row
-  const int slot_in_unit = lane >> 1, half = lane & 1;
-  // units of 16 consecutive keys that lie in one page (page_size is a multiple of 16)
-  const int first_unit = empty ? 0 : k_begin / 16, last_unit = empty ? -1 : (k_end - 1) / 16;
-  // This warp's units are first_unit + warp + i * DEC_WARPS; it works on them in groups of UNITS
-  // whose loads are all in flight together.
-  constexpr int UNITS = NIB_DEC_UNITS_FOR(MAXP);
-  const int n_mine = (first_unit + warp <= last_unit) ? (last_unit - first_unit - warp) / DEC_WARPS + 1 : 0;
-  Piece<T> kp[UNITS][MAXP], vp[UNITS][MAXP];
-  bool act[UNITS];
-  // asks for this lane pair's key and value pieces of the group that starts at the warp's unit i0
-  auto fetch = [&](int i0) {
+  const int group = lane / LPR, c = lane % LPR;
+  const bool has_piece = c * VN < head_dim;
+  // batches of BK consecutive keys (BK divides 16, so a batch lies in one page); this warp's batches
+  // are first_batch + warp + i * DEC_WARPS
+  const int first_batch = empty ? 0 : k_begin / BK, last_batch = empty ? -1 : (k_end - 1) / BK;
+  const int n_mine = (first_batch + warp <= last_batch) ? (last_batch - first_batch - warp) / DEC_WARPS + 1 : 0;
+  Piece<T> kp[BATCH], vp[BATCH];
+  uint32_t live = 0;   // bit i: key i of the batch in kp/vp is one of this split's
+  // where this lane's piece of a row lies: ((page * 2 + K|V) * n_kv_head + head) * page_size + slot) * head_dim + piece
+  const size_t kv_stride = (size_t)n_kv_head * page_size * head_dim;
+  const T* lane_base = cache + ((size_t)hk * page_size + group) * head_dim + c * VN;
+  // asks for this lane's pieces of the warp's batch i
+  auto fetch = [&](int i) {
+    const int j0 = (first_batch + warp + i * DEC_WARPS) * BK;
+    const int page = table[page_size == 16 ? (j0 >> 4) : j0 / page_size];
+    live = 0;
+    if (page < 0 || page >= n_pages) {
+      if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
+      return;
+    }
+    const int slot0 = page_size == 16 ? (j0 & 15) : j0 % page_size;
+    const T* kr = lane_base + (size_t)page * 2 * kv_stride + (size_t)slot0 * head_dim;
 #pragma unroll
-    for (int uu = 0; uu < UNITS; ++uu) {
-      act[uu] = false;
-      if (i0 + uu >= n_mine) continue;
-      const int j0 = (first_unit + warp + (i0 + uu) * DEC_WARPS) * 16;
-      const int page = table[j0 / page_size];
-      if (page < 0 || page >= n_pages) {
-        if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
-        continue;
-      }
-      const int j = j0 + slot_in_unit;
-      if (j < k_begin || j >= k_end) continue;
-      act[uu] = true;
-      const int slot = j % page_size;
-      const T* kr = cache + kv_offset(page, 0, hk, slot, n_kv_head, page_size, head_dim);
-      const T* vr = cache + kv_offset(page, 1, hk, slot, n_kv_head, page_size, head_dim);
-#pragma unroll
-      for (int i = 0; i < MAXP; ++i) {
-        const int c = half + 2 * i;
-        if (c < n_pieces) {
-          kp[uu][i].load(kr + c * VN);
-          vp[uu][i].load(vr + c * VN);
+    for (int b = 0; b < BATCH; ++b) {
+      const int j = j0 + b * GROUPS + group;
+      if (j >= k_begin && j < k_end) {
+        live |= 1u << b;
+        if (has_piece) {
+          kp[b].load(kr + b * GROUPS * head_dim);
+          vp[b].load(kr + b * GROUPS * head_dim + kv_stride);
         }
       }
     }
   };
-  // none of the first group's keys is the one that the kernel ahead writes
-  const int first_group_last = first_unit + warp + (min(UNITS, n_mine) - 1) * DEC_WARPS;
-  const bool early = n_mine > 0 && first_group_last * 16 + 15 < pos;
+  // none of the first batch's keys is the one that the kernel ahead writes
+  const bool early = n_mine > 0 && (first_batch + warp) * BK + BK - 1 < pos;
   if (early) fetch(0);
   pdl_wait();
 
@@ -134,102 +136,86 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
       part_ml[2 * pidx + 1] = 0.0f;
     }
   } else {
-  for (int d = threadIdx.x; d < head_dim; d += blockDim.x) qs[d] = to_float(q[(size_t)t * ldq + h * head_dim + d]);
-  __syncthreads();
-
-  float o[MAXP * VN];
+  float qf[VN];   // this lane's piece of the query
+  {
+    Piece<T> qp;
+    if (has_piece) {
+      qp.load(q + (size_t)t * ldq + h * head_dim + c * VN);
+      qp.unpack(qf);
+    } else {
 #pragma unroll
-  for (int i = 0; i < MAXP * VN; ++i) o[i] = 0.0f;
+      for (int e = 0; e < VN; ++e) qf[e] = 0.0f;
+    }
+  }
+  float o[VN];
+#pragma unroll
+  for (int e = 0; e < VN; ++e) o[e] = 0.0f;
+  // scores are kept times log2(e), so that the exponentials are plain powers of two
+  const float scale2 = scale * 1.4426950408889634f;
   float m = -INFINITY, l = 0.0f;
 
-  for (int i0 = 0; i0 < n_mine; i0 += UNITS) {
-    if (i0 > 0 || !early) fetch(i0);
+  for (int i = 0; i < n_mine; ++i) {
+    if (i > 0 || !early) fetch(i);
+    float sc[BATCH];
 #pragma unroll
-    for (int uu = 0; uu < UNITS; ++uu) {
-      if (!act[uu]) continue;
+    for (int b = 0; b < BATCH; ++b) {
       float dot = 0.0f;
+      if (((live >> b) & 1u) && has_piece) {
+        float f[VN];
+        kp[b].unpack(f);
 #pragma unroll
-      for (int i = 0; i < MAXP; ++i) {
-        const int c = half + 2 * i;
-        if (c < n_pieces) {
-          float f[VN];
-          kp[uu][i].unpack(f);
-#pragma unroll
-          for (int e = 0; e < VN; ++e) dot = fmaf(f[e], qs[c * VN + e], dot);
-        }
+        for (int e = 0; e < VN; ++e) dot = fmaf(f[e], qf[e], dot);
       }
-      // both lanes of the pair are here together (whether a pair has a key depends on the pair only)
-      dot += __shfl_xor_sync(0x3u << (lane & ~1), dot, 1);
-      const float s = dot * scale;
-      const float m_new = fmaxf(m, s);
-      const float p = expf(s - m_new);
-      const float corr = (m == -INFINITY) ? 0.0f : expf(m - m_new);
-      l = l * corr + p;
-      m = m_new;
 #pragma unroll
-      for (int i = 0; i < MAXP; ++i) {
-        const int c = half + 2 * i;
-        if (c < n_pieces) {
-          float f[VN];
-          vp[uu][i].unpack(f);
+      for (int d = 1; d < LPR; d <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);   // the group's lanes, in a fixed order
+      sc[b] = ((live >> b) & 1u) ? dot * scale2 : -INFINITY;
+    }
+    float m_new = m;
 #pragma unroll
-          for (int e = 0; e < VN; ++e) o[i * VN + e] = fmaf(p, f[e], o[i * VN + e] * corr);
-        }
+    for (int b = 0; b < BATCH; ++b) m_new = fmaxf(m_new, sc[b]);
+    if (m_new == -INFINITY) continue;   // the group has had no key yet
+    const float corr = pow2(m - m_new);  // (2^-inf = 0 for the first keys)
+    m = m_new;
+    l *= corr;
+#pragma unroll
+    for (int e = 0; e < VN; ++e) o[e] *= corr;
+#pragma unroll
+    for (int b = 0; b < BATCH; ++b) {
+      const float p = pow2(sc[b] - m);   // 0 for a key that is not there
+      l += p;
+      if (has_piece && ((live >> b) & 1u)) {
+        float f[VN];
+        vp[b].unpack(f);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) o[e] = fmaf(p, f[e], o[e]);
       }
     }
   }
-  __syncwarp();
-  // ---- merge the sixteen lane pairs of the warp
-  const float mw = warp_max(m);
-  const float f_lane = (m == -INFINITY) ? 0.0f : expf(m - mw);
-  float lw = (half == 0) ? l * f_lane : 0.0f;
-  lw = warp_sum(lw);
-#pragma unroll
-  for (int i = 0; i < MAXP * VN; ++i) {
-    float v = o[i] * f_lane;
-    v += __shfl_xor_sync(0xffffffffu, v, 2);
-    v += __shfl_xor_sync(0xffffffffu, v, 4);
-    v += __shfl_xor_sync(0xffffffffu, v, 8);
-    v += __shfl_xor_sync(0xffffffffu, v, 16);
-    o[i] = v;
+  // ---- the lane groups' results meet in shared memory and are merged in group order
+  const int g = warp * GROUPS + group;
+  if (c == 0) {
+    gm[g] = m;
+    gl[g] = l;
   }
-  if (lane == 0) {
-    wm[warp] = mw;
-    wl[warp] = lw;
-  }
-  if (slot_in_unit == 0) {
+  if (has_piece) {
 #pragma unroll
-    for (int i = 0; i < MAXP; ++i) {
-      const int c = half + 2 * i;
-      if (c < n_pieces) {
-#pragma unroll
-        for (int e = 0; e < VN; ++e) wo[warp * head_dim + c * VN + e] = o[i * VN + e];
-      }
-    }
+    for (int e = 0; e < VN; ++e) go[g * head_dim + c * VN + e] = o[e];
   }
   __syncthreads();
-  // ---- merge the warps of the block, in warp order
   float M = -INFINITY;
-#pragma unroll
-  for (int w = 0; w < DEC_WARPS; ++w) M = fmaxf(M, wm[w]);
+  for (int w = 0; w < ALL_GROUPS; ++w) M = fmaxf(M, gm[w]);
   float L = 0.0f;
-  float f[DEC_WARPS];
-#pragma unroll
-  for (int w = 0; w < DEC_WARPS; ++w) {
-    f[w] = (wm[w] == -INFINITY) ? 0.0f : expf(wm[w] - M);
-    L += wl[w] * f[w];
-  }
+  for (int w = 0; w < ALL_GROUPS; ++w) L += (gm[w] == -INFINITY) ? 0.0f : gl[w] * pow2(gm[w] - M);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
-#pragma unroll
-    for (int w = 0; w < DEC_WARPS; ++w) acc += wo[w * head_dim + d] * f[w];
+    for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2(gm[w] - M);
     if (n_splits == 1)
       out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L);
     else
       part_o[pidx * head_dim + d] = acc;
   }
   if (n_splits > 1 && threadIdx.x == 0) {
-    part_ml[2 * pidx] = M;
+    part_ml[2 * pidx] = M;      // (in the power-of-two scale)
     part_ml[2 * pidx + 1] = L;
   }
   }  // !empty
@@ -251,13 +237,13 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   float Lx = 0.0f;
   for (int sp = 0; sp < n_splits; ++sp) {
     const float ls = part_ml[2 * (base + sp) + 1];
-    if (ls > 0.0f) Lx += ls * expf(part_ml[2 * (base + sp)] - Mx);
+    if (ls > 0.0f) Lx += ls * pow2(part_ml[2 * (base + sp)] - Mx);
   }
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
       const float ls = part_ml[2 * (base + sp) + 1];
-      if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * expf(part_ml[2 * (base + sp)] - Mx);
+      if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * pow2(part_ml[2 * (base + sp)] - Mx);
     }
     out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / Lx);
   }
@@ -270,15 +256,18 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
                          int page_size, int n_pages, float scale, int window, int chunk, int n_splits,
                          int* counters, int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
-  const size_t smem = (size_t)(head_dim + DEC_WARPS * head_dim + 2 * DEC_WARPS) * sizeof(float);
-  if (head_dim <= 64)
-    launch_pdl(attention_decode_kernel<T, 64>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
-        (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
-  else
-    launch_pdl(attention_decode_kernel<T, DEC_MAX_HD>, dim3(grid), dim3(DEC_WARPS * 32), smem, stream, 
-        (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status);
+  const int n_pieces = head_dim / Piece<T>::N;
+#define NIB_DECODE_LAUNCH(LPR)                                                                                     \
+  launch_pdl(attention_decode_kernel<T, LPR>, dim3(grid), dim3(DEC_WARPS * 32),                                    \
+             (size_t)(DEC_WARPS * (32 / LPR) * (head_dim + 2)) * sizeof(float), stream, (const T*)q, ldq,           \
+             (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry, positions,   \
+             n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status)
+  if (n_pieces <= 2) NIB_DECODE_LAUNCH(2);
+  else if (n_pieces <= 4) NIB_DECODE_LAUNCH(4);
+  else if (n_pieces <= 8) NIB_DECODE_LAUNCH(8);
+  else if (n_pieces <= 16) NIB_DECODE_LAUNCH(16);
+  else NIB_DECODE_LAUNCH(32);
+#undef NIB_DECODE_LAUNCH
   NIB_LAUNCH_CHECK();
 }
 

@@ -1,16 +1,19 @@
-// out = act(a . w^T + bias) for steps of a few rows (at most 16), in bfloat16, on the CUDA cores.
+// out = act(a . w^T + bias) for steps of a few rows (at most 64), in bfloat16, with warp-level MMAs.
 //
-// With one to sixteen rows the product is a stream of weights with a handful of multiply-adds per
-// weight: the 128-row tcgen05 MMA takes its full 128 cycles however few columns it has, and its
-// set-up (barriers, tensor memory, descriptors) costs more than the arithmetic.  Here a block owns
-// 16 output features, its warps split K, every lane pulls weights with independent 16-byte loads
-// that are all in flight before any is used, and the small warp-level MMA (m16n8k16) multiplies them
-// with the step's rows held in shared memory.  The grid covers the output features, so every SM
-// pulls weights.
+// With a few rows the product is a stream of weights with a handful of multiply-adds per weight:
+// the 128-row tcgen05 MMA takes its full 128 cycles however few columns it has, its set-up
+// (barriers, tensor memory, descriptors) costs more than the arithmetic, and its 128-feature tiles
+// leave most SMs without work.  Here a block owns 16 output features, its warps split K, every lane
+// pulls weights with independent 16-byte loads that are all in flight before any is used, and the
+// small warp-level MMA (m16n8k16) multiplies them with the step's rows held in shared memory.  Where
+// 16-feature tiles alone would leave SMs idle (a narrow output, a long K), the blocks of a cluster
+// split K between them and exchange their partial sums through distributed shared memory, each
+// block finishing a share of the rows: every sum still has one fixed order.
 //
 // Folded in, because each is one round trip less for a decode step:
-//   * the LayerNorm that stands before the product (the rows are normalised into shared memory while
-//     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51);
+//   * the LayerNorm that stands before the product, for steps of at most 16 rows (the rows are
+//     normalised into shared memory while the first weights are on their way; formula of
+//     crates/core/src/kernels/reference.rs:42-51);
 //   * the bias, GELU and residual epilogues (crates/metal/src/shaders/batch.metal:94-97,148-165);
 //   * the write of keys and values into the paged cache for the fused q/k/v projection
 //     (batch.metal:155-164).
@@ -21,7 +24,9 @@
 namespace nib {
 
 constexpr int SK_WARPS = 8;
-constexpr int SK_MAX_ROWS = 16;
+constexpr int SK_MAX_ROWS = 64;
+constexpr int SK_MAX_LN_ROWS = 16;   // the norm is folded in for steps of at most this many rows
+constexpr int SK_MAX_SPLIT = 8;      // blocks of a cluster that split K
 
 struct SkinnyParams {
   const bf16* a;        // [M, K] activations (null when ln_x is given)
@@ -38,6 +43,7 @@ struct SkinnyParams {
   void* out;
   int ldo, out_f32, residual, act;
   int M, N, K;
+  int split, k_per;     // blocks of a cluster and the slice of K that each takes (a multiple of 32)
   // optional: features from kv_q_dim on go to the paged cache
   bf16* kv_cache;
   const int* kv_block_table;
@@ -56,26 +62,57 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// A block owns 16 output features at a time; its eight warps split K between them (warp w takes the
-// 32-wide steps w, w + 8, ...), so each warp's weights are a handful of independent 16-byte loads
-// that are all in flight at once, and the partial sums meet in shared memory.  The small
-// tensor-core shape m16n8k16 does the arithmetic: weights are the 16-row operand, the step's rows
-// (8 per tile, NT tiles) the 8-column one.  A lane's 16-byte piece of a weight row feeds two MMAs;
-// since a dot product does not care about the order of its terms, the piece's eight values are
-// dealt to the fragment positions as they come, and the rows' pieces are dealt the same way.
+__device__ __forceinline__ int cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return (int)r;
+}
+__device__ __forceinline__ void cluster_arrive() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// stores v at the place of `local` in the shared memory of block `rank` of the cluster
+__device__ __forceinline__ void store_to_rank(float* local, int rank, float v) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
+}
+
+__host__ __device__ inline int skinny_ldx(int k_per) { return k_per + ((32 - k_per % 64) + 64) % 64; }
+
+// A cluster of `split` blocks owns 16 output features at a time; block r of it takes the slice
+// [r * k_per, (r + 1) * k_per) of K, and its eight warps split the slice between them (warp w takes
+// the 32-wide steps w, w + 8, ...), so each warp's weights are a handful of independent 16-byte
+// loads that are all in flight at once.  The warps' partial sums meet in shared memory; the
+// blocks' sums are then dealt out by row (row m goes to block m % split), added there in block
+// order and finished by that block.  The small tensor-core shape m16n8k16 does the arithmetic:
+// weights are the 16-row operand, the step's rows (8 per tile, NT tiles) the 8-column one.  A lane's
+// 16-byte piece of a weight row feeds two MMAs; since a dot product does not care about the order of
+// its terms, the piece's eight values are dealt to the fragment positions as they come, and the
+// rows' pieces are dealt the same way.
 template <int NT>
-__global__ void __launch_bounds__(SK_WARPS * 32)
+__global__ void __launch_bounds__(SK_WARPS * 32, 2)
 linear_skinny_kernel(const SkinnyParams prm) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t sk_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int K = prm.K, M = prm.M;
-  const int n_chunks = K >> 3;                         // 16-byte pieces per row
-  const int ldx = K + ((32 - K % 64) + 64) % 64;       // padded row: pieces of 8 rows x 4 lanes hit distinct banks
+  const int M = prm.M, S = prm.split;
+  const int rank = S > 1 ? cluster_rank() : 0;
+  const int walker = blockIdx.x / S, n_walkers = gridDim.x / S;
+  const int k0 = rank * prm.k_per;                     // this block's slice of K
+  const int Ks = min(prm.K - k0, prm.k_per);
+  const int n_chunks = Ks >> 3;                        // 16-byte pieces per row of the slice
+  const int ldx = skinny_ldx(prm.k_per);               // padded row: pieces of 8 rows x 4 lanes hit distinct banks
   bf16* xs = reinterpret_cast<bf16*>(sk_smem);         // [NT * 8][ldx] the step's rows (rows >= M are zeros)
   float* red = reinterpret_cast<float*>(sk_smem + (size_t)NT * 8 * ldx * sizeof(bf16));  // [warps][NT][32][4]
+  float* xch = red + SK_WARPS * NT * 128;              // [2][split][rows of a block][16] sums of the other blocks
+  float* ln_gb = xch + 2 * NT * 128;                   // [2][K] the norm's scale and shift
   const int n_tiles = (prm.N + 15) / 16;
-  const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of K
+  const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of the slice
   const int fr = lane >> 2, kl = lane & 3;         // this lane's feature row (and +8) and piece within a step
 
   // ---- Before waiting for the kernel ahead: everything that does not depend on it.  The weights of
@@ -83,9 +120,9 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // while the previous kernel is still finishing.
   uint4 wa[4], wb[4];
   {
-    const int f0 = blockIdx.x * 16;
-    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw;
-    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw;
+    const int f0 = walker * 16;
+    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw + k0;
+    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw + k0;
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int c = (warp + u * SK_WARPS) * 4 + kl;
@@ -94,23 +131,21 @@ linear_skinny_kernel(const SkinnyParams prm) {
       wb[u] = ok ? *reinterpret_cast<const uint4*>(w1 + c * 8) : make_uint4(0, 0, 0, 0);
     }
   }
-  float4 lg[8], lb[8];   // the norm's scale and shift for this lane's part of a row (K <= 1024)
-  if (prm.ln_x != nullptr && warp < M) {
-#pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int k = (j * 32 + lane) * 4;
-      if (k < K) {
-        lg[j] = *reinterpret_cast<const float4*>(prm.ln_gamma + k);
-        lb[j] = *reinterpret_cast<const float4*>(prm.ln_beta + k);
-      }
+  if (prm.ln_x != nullptr) {
+    for (int i = threadIdx.x; i < prm.K / 4; i += blockDim.x) {
+      reinterpret_cast<float4*>(ln_gb)[i] = reinterpret_cast<const float4*>(prm.ln_gamma)[i];
+      reinterpret_cast<float4*>(ln_gb + prm.K)[i] = reinterpret_cast<const float4*>(prm.ln_beta)[i];
     }
   }
+  if (S > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
   pdl_wait();
 
   // ---- the step's rows into shared memory as bfloat16 (normalised on the way if asked)
   for (int i = threadIdx.x; i < (NT * 8 - M) * (ldx / 8); i += blockDim.x)   // rows past the step: zeros
     reinterpret_cast<uint4*>(xs + (size_t)M * ldx)[i] = make_uint4(0, 0, 0, 0);
   if (prm.ln_x != nullptr) {
+    __syncthreads();   // the norm's parameters are in place
+    const int K = prm.K;
     for (int m = warp; m < M; m += SK_WARPS) {
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
       // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
@@ -142,7 +177,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
       for (int j = 0; j < 8; ++j) {
         const int k = (j * 32 + lane) * 4;
         if (k < K) {
-          const float4 g = lg[j], b = lb[j];
+          const float4 g = *reinterpret_cast<const float4*>(ln_gb + k);
+          const float4 b = *reinterpret_cast<const float4*>(ln_gb + K + k);
           __nv_bfloat162 lo = __floats2bfloat162_rn((v[4 * j] - mean) * rstd * g.x + b.x,
                                                     (v[4 * j + 1] - mean) * rstd * g.y + b.y);
           __nv_bfloat162 hi = __floats2bfloat162_rn((v[4 * j + 2] - mean) * rstd * g.z + b.z,
@@ -158,21 +194,24 @@ linear_skinny_kernel(const SkinnyParams prm) {
     for (int i = threadIdx.x; i < M * n_chunks; i += blockDim.x) {
       const int m = i / n_chunks, c = i - m * n_chunks;
       *reinterpret_cast<uint4*>(xs + (size_t)m * ldx + c * 8) =
-          *reinterpret_cast<const uint4*>(prm.a + (size_t)m * prm.lda + c * 8);
+          *reinterpret_cast<const uint4*>(prm.a + (size_t)m * prm.lda + k0 + c * 8);
     }
   }
   __syncthreads();
 
-  for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x) {
+  constexpr int OUTS = (NT * 128 + SK_WARPS * 32 - 1) / (SK_WARPS * 32);   // sums per thread
+  const int rows_per_rank = NT * 8 / S;
+  int round = 0;
+  for (int tile = walker; tile < n_tiles; tile += n_walkers, ++round) {
     const int f0 = tile * 16;
-    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw;
-    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw;
+    const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw + k0;
+    const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw + k0;
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
     // this warp's steps, four at a time: eight independent 16-byte loads in flight
     for (int s0 = warp; s0 < n_steps; s0 += 4 * SK_WARPS) {
-      if (tile != blockIdx.x || s0 != warp) {   // the very first batch was asked for before the wait
+      if (s0 != warp) {   // a tile's first batch was asked for ahead: before the wait, or during the tile before
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
           const int c = (s0 + u * SK_WARPS) * 4 + kl;
@@ -195,6 +234,18 @@ linear_skinny_kernel(const SkinnyParams prm) {
         }
       }
     }
+    if (tile + n_walkers < n_tiles) {   // the next tile's first batch travels while this one is finished
+      const int g0 = (tile + n_walkers) * 16;
+      const bf16* v0 = prm.w + (size_t)min(g0 + fr, prm.N - 1) * prm.ldw + k0;
+      const bf16* v1 = prm.w + (size_t)min(g0 + fr + 8, prm.N - 1) * prm.ldw + k0;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int c = (warp + u * SK_WARPS) * 4 + kl;
+        const bool ok = c < n_chunks;
+        wa[u] = ok ? *reinterpret_cast<const uint4*>(v0 + c * 8) : make_uint4(0, 0, 0, 0);
+        wb[u] = ok ? *reinterpret_cast<const uint4*>(v1 + c * 8) : make_uint4(0, 0, 0, 0);
+      }
+    }
     // ---- the warps' partial sums meet in shared memory and are added in warp order
     __syncthreads();   // the previous tile's sums have been read
 #pragma unroll
@@ -202,15 +253,52 @@ linear_skinny_kernel(const SkinnyParams prm) {
       *reinterpret_cast<float4*>(red + ((size_t)(warp * NT + t) * 32 + lane) * 4) =
           make_float4(acc[t][0], acc[t][1], acc[t][2], acc[t][3]);
     __syncthreads();
-    for (int o = threadIdx.x; o < NT * 128; o += blockDim.x) {
-      const int t = o / 128, l = (o % 128) / 4, i = o % 4;
-      float total = 0.0f;
+    // sum o belongs to row o / 16 of the step and feature f0 + o % 16 (consecutive threads: consecutive features)
+    float total[OUTS];
 #pragma unroll
-      for (int w = 0; w < SK_WARPS; ++w) total += red[((size_t)(w * NT + t) * 32 + l) * 4 + i];
-      const int n = f0 + (l >> 2) + 8 * (i >> 1);          // feature
-      const int m = t * 8 + (l & 3) * 2 + (i & 1);          // row of the step
+    for (int q = 0; q < OUTS; ++q) {
+      const int o = threadIdx.x + q * SK_WARPS * 32;
+      total[q] = 0.0f;
+      if (o < NT * 128) {
+        const int m = o >> 4, nl = o & 15;
+        const int t = m >> 3, l = (nl & 7) * 4 + ((m & 7) >> 1), i = (nl >> 3) * 2 + (m & 1);
+#pragma unroll
+        for (int w = 0; w < SK_WARPS; ++w) total[q] += red[((size_t)(w * NT + t) * 32 + l) * 4 + i];
+      }
+    }
+    float* xb = xch + (round & 1) * NT * 128;
+    if (S > 1) {
+      // Row m is finished by block m % S: the others send their sums there.  Two buffers by turns:
+      // a block writes into a buffer again only after the barrier of the round between, which its
+      // owner reaches after reading it.
+      if (round == 0) cluster_wait();
+#pragma unroll
+      for (int q = 0; q < OUTS; ++q) {
+        const int o = threadIdx.x + q * SK_WARPS * 32;
+        if (o < NT * 128) {
+          const int m = o >> 4, nl = o & 15;
+          const int owner = m % S;
+          if (owner != rank) store_to_rank(xb + ((size_t)rank * rows_per_rank + m / S) * 16 + nl, owner, total[q]);
+        }
+      }
+      cluster_arrive();
+      cluster_wait();
+    }
+#pragma unroll
+    for (int q = 0; q < OUTS; ++q) {
+      const int o = threadIdx.x + q * SK_WARPS * 32;
+      if (o >= NT * 128) continue;
+      const int m = o >> 4, nl = o & 15;
+      const int n = f0 + nl;
       if (n >= prm.N || m >= M) continue;
-      float x = total + (prm.bias ? prm.bias[n] : 0.0f);
+      float x = total[q];
+      if (S > 1) {
+        if (m % S != rank) continue;
+        x = 0.0f;
+        for (int r = 0; r < S; ++r)   // in block order, this block's own sum at its place
+          x += (r == rank) ? total[q] : xb[((size_t)r * rows_per_rank + m / S) * 16 + nl];
+      }
+      x += prm.bias ? prm.bias[n] : 0.0f;
       if (prm.act == ACT_GELU_TANH) {
         float th;
         asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
@@ -238,26 +326,70 @@ linear_skinny_kernel(const SkinnyParams prm) {
       }
     }
   }
+  if (S > 1 && round == 0) cluster_wait();   // (a block without a tile still completes the opening barrier)
 }
 
-static size_t skinny_smem(int NT, int K) {
-  const int ldx = K + ((32 - K % 64) + 64) % 64;
-  return (size_t)NT * 8 * ldx * sizeof(bf16) + (size_t)SK_WARPS * NT * 32 * 4 * sizeof(float);
+static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)); }
+
+static size_t skinny_smem(int NT, int k_per, int K, bool ln) {
+  return (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16) + (size_t)SK_WARPS * NT * 128 * sizeof(float) +
+         (size_t)2 * NT * 128 * sizeof(float) + (ln ? (size_t)2 * K * sizeof(float) : 0);
+}
+
+constexpr size_t SK_SMEM_LIMIT = 200 * 1024;
+constexpr size_t SK_SMEM_TWO_PER_SM = 110 * 1024;
+
+static int skinny_k_per(int K, int split) { return (((K + split - 1) / split) + 31) / 32 * 32; }
+
+// How many blocks split K.  An exchange through the cluster costs about a microsecond, so K is split
+// only while every block keeps at least 512 of it and no SM gets more than two blocks; and where the
+// rows would not fit in shared memory otherwise.
+static int skinny_split(int M, int N, int K, bool ln) {
+  if (ln) return 1;   // the norm needs whole rows
+  const int NT = skinny_tiles(M), n_tiles = (N + 15) / 16;
+  int split = 1;
+  while (split < SK_MAX_SPLIT) {
+    const int s2 = split * 2, kp = skinny_k_per(K, s2);
+    if ((s2 - 1) * kp >= K) break;
+    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_TWO_PER_SM;
+    if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 512)) break;
+    split = s2;
+  }
+  return split;
 }
 
 template <int NT>
 static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
-  const size_t smem = skinny_smem(NT, prm.K);
+  const size_t smem = skinny_smem(NT, prm.k_per, prm.K, prm.ln_x != nullptr);
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         200 * 1024);
+                                         (int)SK_SMEM_LIMIT);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  int blocks = (prm.N + 15) / 16;
-  if (blocks > 4 * 148) blocks = 4 * 148;   // then each block walks several tiles with the rows in place
-  launch_pdl(linear_skinny_kernel<NT>, dim3(blocks), dim3(SK_WARPS * 32), smem, stream, prm);
+  // one wave: at most two blocks per SM (one when the rows take much shared memory), each cluster
+  // then walks several tiles with the rows in place
+  const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
+  int walkers = (prm.N + 15) / 16;
+  const int cap = per_sm * 148 / prm.split;
+  if (walkers > cap) walkers = cap;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(walkers * prm.split);
+  cfg.blockDim = dim3(SK_WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  attr[1].id = cudaLaunchAttributeClusterDimension;
+  attr[1].val.clusterDim.x = prm.split;
+  attr[1].val.clusterDim.y = 1;
+  attr[1].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = prm.split > 1 ? 2 : 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
+  if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();
 }
 
@@ -265,45 +397,57 @@ static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
 
 using namespace nib;
 
-// 1 if the few-rows kernel takes this problem.
-extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int lda, const void* w, const void* a) {
+// 1 if the few-rows kernel takes this problem (ln: with the LayerNorm folded in).
+extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const void* w) {
   if (M < 1 || M > SK_MAX_ROWS || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)w & 15)) return 0;
-  if (skinny_smem(M <= 8 ? 1 : 2, K) > 100 * 1024) return 0;   // two blocks per SM
-  (void)lda; (void)a;
+  if (ln && (M > SK_MAX_LN_ROWS || K > 1024 || (K & 3))) return 0;  // a row is held in registers while normalised
+  const int split = skinny_split(M, 16, K, ln != 0);   // (the split that smem alone asks for)
+  if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0) > SK_SMEM_LIMIT) return 0;
   return 1;
 }
 
-// The product for steps of at most 16 rows (bfloat16 weights and activations; out bfloat16 or
+// The product for steps of at most 64 rows (bfloat16 weights and activations; out bfloat16 or
 // float32).  Options as for nib_linear_tc_small: ln_x != null folds the LayerNorm before the product
-// in (`a` ignored); cache != null sends the features from q_dim on to the paged cache.
+// in (`a` ignored; at most 16 rows); cache != null sends the features from q_dim on to the paged
+// cache.  split: blocks of a cluster that split K (0: chosen here; 1, 2, 4 or 8).
 extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
                                  void* out, int ldo, int M, int N, int K, int act, int residual, const float* ln_x,
                                  int ln_ldx, const float* ln_gamma, const float* ln_beta, float ln_eps,
                                  const int* ln_rows, void* cache, const int* block_table, int max_blocks,
                                  const int* row_entry, const int* positions, int q_dim, int n_kv_head,
-                                 int head_dim, int page_size, int n_pages, int* status, cudaStream_t stream) {
+                                 int head_dim, int page_size, int n_pages, int split, int* status,
+                                 cudaStream_t stream) {
   if (N <= 0 || M <= 0) return 0;
-  if (!nib_linear_skinny_supported(M, K, ldw, lda, w, a)) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (ln_x == nullptr && a == nullptr) return NIB_ERR_BAD_ARGUMENT;
-  if (ln_x != nullptr && K > 1024) return NIB_ERR_UNSUPPORTED_SIZE;  // a row is held in registers while normalised
+  const bool ln = ln_x != nullptr;
+  if (!nib_linear_skinny_supported(M, K, ldw, ln, w)) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (!ln && a == nullptr) return NIB_ERR_BAD_ARGUMENT;
   if (residual && out_dtype != DT_F32) return NIB_ERR_BAD_ARGUMENT;
   if (cache != nullptr && (out_dtype != DT_BF16 || residual || N != q_dim + 2 * n_kv_head * head_dim))
     return NIB_ERR_BAD_ARGUMENT;
+  if (split == 0) split = skinny_split(M, N, K, ln);
+  if (split != 1 && split != 2 && split != 4 && split != 8) return NIB_ERR_BAD_ARGUMENT;
+  if (ln && split != 1) return NIB_ERR_BAD_ARGUMENT;
+  const int k_per = skinny_k_per(K, split);
+  if ((split - 1) * k_per >= K) return NIB_ERR_BAD_ARGUMENT;   // a block would have nothing
+  if (skinny_smem(skinny_tiles(M), k_per, K, ln) > SK_SMEM_LIMIT) return NIB_ERR_UNSUPPORTED_SIZE;
   SkinnyParams prm;
   prm.a = (const bf16*)a; prm.lda = lda;
   prm.ln_x = ln_x; prm.ln_ldx = ln_ldx; prm.ln_gamma = ln_gamma; prm.ln_beta = ln_beta; prm.ln_rows = ln_rows;
   prm.ln_eps = ln_eps;
   prm.w = (const bf16*)w; prm.ldw = ldw; prm.bias = bias; prm.out = out; prm.ldo = ldo;
   prm.out_f32 = out_dtype == DT_F32; prm.residual = residual; prm.act = act;
-  prm.M = M; prm.N = N; prm.K = K;
+  prm.M = M; prm.N = N; prm.K = K; prm.split = split; prm.k_per = k_per;
   prm.kv_cache = (bf16*)cache; prm.kv_block_table = block_table; prm.kv_row_entry = row_entry;
   prm.kv_positions = positions; prm.kv_max_blocks = max_blocks; prm.kv_q_dim = q_dim; prm.kv_heads = n_kv_head;
   prm.kv_head_dim = head_dim; prm.kv_page_size = page_size; prm.kv_n_pages = n_pages;
   prm.status = status;
   if ((lda & 7) || (a != nullptr && ((uintptr_t)a & 15))) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (ln_x != nullptr && ((ln_ldx & 3) || ((uintptr_t)ln_x & 15) || ((uintptr_t)ln_gamma & 15) ||
-                          ((uintptr_t)ln_beta & 15)))
+  if (ln && ((ln_ldx & 3) || ((uintptr_t)ln_x & 15) || ((uintptr_t)ln_gamma & 15) || ((uintptr_t)ln_beta & 15)))
     return NIB_ERR_UNSUPPORTED_SIZE;
-  if (M <= 8) return launch_skinny<1>(prm, stream);
-  return launch_skinny<2>(prm, stream);
+  switch (skinny_tiles(M)) {
+    case 1: return launch_skinny<1>(prm, stream);
+    case 2: return launch_skinny<2>(prm, stream);
+    case 4: return launch_skinny<4>(prm, stream);
+    default: return launch_skinny<8>(prm, stream);
+  }
 }

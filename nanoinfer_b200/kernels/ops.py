@@ -43,10 +43,10 @@ _SIGNATURES = {
                             _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
                             _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                             ctypes.c_longlong, _c_ptr, _c_int, _c_ptr, _c_ptr],
-    "nib_linear_skinny_supported": [_c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_skinny_supported": [_c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_linear_skinny": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
-                          _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                          _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
@@ -304,26 +304,27 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
     return a is not None or norm is not None
 
 
-SKINNY_MAX_ROWS = 16
+SKINNY_MAX_ROWS = 64
 
 
-def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None) -> bool:
-    """The CUDA-core kernel for steps of at most 16 rows (bfloat16): every SM streams weight rows, a
-    few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in; ``kv``:
-    (cache layer, block table, row_entry, positions, q_dim) sends keys and values straight to the
-    cache.  False if the kernel does not apply."""
+def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=0) -> bool:
+    """The warp-level MMA kernel for steps of at most 64 rows (bfloat16): every SM streams weight
+    rows, a few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in (at
+    most 16 rows); ``kv``: (cache layer, block table, row_entry, positions, q_dim) sends keys and
+    values straight to the cache; ``split``: blocks of a cluster that split K (0: chosen by the
+    library).  False if the kernel does not apply."""
     if M > SKINNY_MAX_ROWS or not _small_inputs_ok(a, norm, w, out):
         return False
     N, K = w.shape
     lib = library()
-    if not lib.nib_linear_skinny_supported(M, K, w.stride(0), 0, _ptr(w), None):
+    if not lib.nib_linear_skinny_supported(M, K, w.stride(0), int(norm is not None), _ptr(w)):
         return False
     ln_args, kv_args = _option_args(norm, kv)
     if _profiler is not None:
         _profiler.label = f"M={M} N={N} K={K}" + (" ln" if norm is not None else "") + (" kv" if kv else "")
     code = lib.nib_linear_skinny(_dt(out), _ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0),
                                  _ptr(bias), _ptr(out), out.stride(0), M, N, K, act, int(residual), *ln_args,
-                                 *kv_args, _ptr(status_word()), _stream())
+                                 *kv_args, int(split), _ptr(status_word()), _stream())
     if code == -2:   # alignment or size not taken
         return False
     _check(code, "linear_skinny")
@@ -355,14 +356,18 @@ def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=N
 
 
 def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
-    """Steps of at most 128 rows: up to 16 rows the CUDA-core kernel (with the LayerNorm folded in),
-    beyond that the tensor cores.  Folding the norm into the tensor-core kernel, or splitting K
-    through scratch, costs more round trips than it saves at these sizes, so the tensor-core kernel
-    is given normed rows and is not split here."""
-    if M <= SKINNY_MAX_ROWS:
+    """Steps of at most 128 rows: up to 64 rows the warp-level MMA kernel (up to 16 with the
+    LayerNorm folded in), beyond that tcgen05.  Folding the norm into the tcgen05 kernel, or splitting
+    K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
+    normed rows and is not split here."""
+    N, K = w.shape
+    # measured: up to 16 rows the MMA kernel wins everywhere; up to 32 everywhere but the widest
+    # outputs; up to 64 for small weights and for the projection that writes the cache
+    mma = M <= 16 or (M <= 32 and N <= 8192) or (M <= SKINNY_MAX_ROWS and (kv is not None or N * K <= (1 << 20)))
+    if mma:
         if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
             return True
-        if norm is not None:   # too wide to be normalised inside the kernel: normalise first
+        if norm is not None:   # too wide or too many rows to be normalised inside the kernel: normalise first
             a, norm = norm.materialise(M), None
             if linear_skinny(a, None, w, bias, out, M, act, residual, kv):
                 return True
@@ -434,8 +439,9 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
 
 
 def decode_split(n_rows: int, n_head: int, max_keys: int) -> tuple:
-    """(chunk, n_splits): keys per split (a multiple of 64) so that about four blocks per SM are in flight."""
-    want = max(1, -(-592 // max(1, n_rows * n_head)))
+    """(chunk, n_splits): keys per split (a multiple of 64) so that the blocks fill the GPU once: six
+    blocks an SM are resident, and a block that comes after the first wave runs nearly alone."""
+    want = max(1, 888 // max(1, n_rows * n_head))
     chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
     return chunk, max(1, -(-max_keys // chunk))
 

@@ -319,7 +319,7 @@ def test_linear_falls_back_when_rows_are_not_16_byte_multiples():
     assert (out.cpu().double() - a.double() @ w.double().T).abs().max() < 0.1
 
 
-@pytest.mark.parametrize("M, n_head, n_kv_head, hd", [(1, 4, 4, 16), (8, 12, 12, 64), (37, 6, 2, 32), (128, 5, 5, 24)])
+@pytest.mark.parametrize("M, n_head, n_kv_head, hd", [(1, 4, 4, 16), (8, 12, 12, 64), (20, 3, 1, 48), (37, 6, 2, 32), (64, 12, 12, 64), (128, 5, 5, 24)])
 def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd):
     """The small-step q/k/v projection: queries to the output, keys and values into scattered pages."""
     o = ops()
@@ -363,8 +363,8 @@ SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (6
 @pytest.mark.parametrize("folded", [False, True])
 @pytest.mark.parametrize("kernel", ["dispatch", "tensor_core"])
 def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, kernel):
-    """Steps of at most 128 rows, through the dispatcher (CUDA-core kernel up to 16 rows) and through
-    the tensor-core kernel with all its options: K split over blocks (partial tiles summed by the last
+    """Steps of at most 128 rows, through the dispatcher (warp-level MMA kernel up to 64 rows) and through
+    the tcgen05 kernel with all its options: K split over blocks (partial tiles summed by the last
     block, or reduce-added for the residual) and the LayerNorm before the product folded in."""
     o = ops()
 
@@ -421,3 +421,64 @@ def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, k
     out2 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
     product(a, wd, bd, out2, M, norm=norm)
     assert torch.equal(out1, out2)
+
+
+SPLIT_SHAPES = [(1, 96, 768), (8, 768, 3072), (16, 768, 768), (20, 100, 1000), (33, 70, 3072), (64, 1000, 264),
+                (64, 768, 3072), (48, 2304, 768)]
+
+
+@pytest.mark.parametrize("M, N, K", SPLIT_SHAPES)
+@pytest.mark.parametrize("split", [0, 1, 2, 4, 8])
+def test_few_row_product_with_k_split_over_a_cluster(M, N, K, split):
+    """The warp-level MMA kernel for steps of at most 64 rows, with K split over the blocks of a
+    cluster (their sums exchanged through distributed shared memory): every epilogue, rows and
+    columns beside the result untouched, the same bits twice, and a split that would leave a block
+    without work refused."""
+    o = ops()
+    g = gen(M * 7 + N + K + split)
+    a = (torch.randn(M, K, generator=g) * 0.7).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    y = a.double() @ w.double().T + b.double()
+    scale = max(1.0, float(y.abs().max()))
+    ad, wd, bd = a.to(DEV), w.to(DEV), b.to(DEV)
+    k_per = (-(-K // max(split, 1)) + 31) // 32 * 32
+    if split > 1 and (split - 1) * k_per >= K:
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        with pytest.raises(o.KernelError):
+            o.linear_skinny(ad, None, wd, bd, out, M, split=split)
+        return
+    # the step's rows of a block's slice of K must fit in shared memory: else the kernel declines
+    row_tiles = 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
+    pitch = k_per + ((32 - k_per % 64) + 64) % 64
+    if split and row_tiles * 8 * pitch * 2 + 10 * row_tiles * 128 * 4 > 200 * 1024:
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+        assert not o.linear_skinny(ad, None, wd, bd, out, M, split=split)
+        assert (out == 0).all()
+        return
+    for act, fn in (("none", lambda u: u), ("tanh", P.gelu_tanh), ("erf", P.gelu_erf)):
+        out = torch.full((M + 2, N), 3.0, dtype=torch.bfloat16, device=DEV)
+        assert o.linear_skinny(ad, None, wd, bd, out, M, act=o.ACT_CODES[act], split=split)
+        assert (out.cpu().double()[:M] - fn(y)).abs().max() < 1.5e-2 * scale, act
+        assert (out.cpu()[M:] == 3.0).all()
+    res = torch.randn(M + 2, N, generator=g)
+    rd = res.to(DEV)
+    assert o.linear_skinny(ad, None, wd, bd, rd, M, residual=True, split=split)
+    assert (rd.cpu().double()[:M] - (res.double()[:M] + y)).abs().max() < 4e-3 * scale
+    assert torch.equal(rd.cpu()[M:], res[M:])
+    pitch = (N + 15) // 16 * 16
+    buf = torch.full((M, pitch), -7.0, device=DEV)
+    assert o.linear_skinny(ad, None, wd, None, buf[:, :N], M, split=split)
+    assert (buf.cpu().double()[:, :N] - (y - b.double())).abs().max() < 4e-3 * scale
+    assert (buf.cpu()[:, N:] == -7.0).all()
+    out1 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    out2 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    assert o.linear_skinny(ad, None, wd, bd, out1, M, split=split)
+    assert o.linear_skinny(ad, None, wd, bd, out2, M, split=split)
+    assert torch.equal(out1, out2)
+    # a row's result does not depend on the rows beside it
+    if M > 1:
+        alone = torch.zeros(1, N, dtype=torch.bfloat16, device=DEV)
+        assert o.linear_skinny(ad[M - 1:], None, wd, bd, alone, 1, split=split or 1)
+        assert (alone.cpu().double() - out1.cpu().double()[M - 1:]).abs().max() < 1.5e-2 * scale
+    assert int(o.status_word().item()) == 0
