@@ -11,8 +11,8 @@
 // and fixes the head size at 64).  Several requests share a launch: the host lists the tiles as
 // (entry, first row within the entry).
 //
-// TODO(perf): S and O could live in tensor memory with tcgen05.mma; this kernel is the legacy
-// tensor-core path and is kept simple.
+// The warp-level MMA keeps S and P in registers, which the softmax between the two products wants;
+// the head size 64 of this architecture gives the 128-row tcgen05 shapes little to work on.
 #include "api.h"
 #include "common.cuh"
 
@@ -47,6 +47,12 @@ __device__ __forceinline__ void mma_bf16(float* c, const uint32_t* a, uint32_t b
       "{%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// 2^x by the hardware's approximation (relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float pow2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
 }
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
@@ -87,25 +93,28 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     const bf16* src = q + (size_t)(row0 + (valid ? r : 0)) * ldq + h * HD + piece * 8;
     cp_async16(qs + r * LD + piece * 8, src, valid);
   }
+  // a row's place in the cache: (((page * 2 + K|V) * n_kv_head + head) * page_size + slot) * HD
+  const size_t kv_stride = (size_t)n_kv_head * page_size * HD;
+  const bf16* head_base = cache + (size_t)hk * page_size * HD;
   auto load_kv = [&](int tile, int buf) {
     const int j0 = tile * PF_BN;
     for (int c = tid; c < PF_BN * CHUNKS; c += PF_THREADS) {
       const int r = c / CHUNKS, piece = c % CHUNKS;
       const int j = j0 + r;
       bool valid = j <= pos_last;
-      size_t koff = 0, voff = 0;
+      const bf16* src = cache;
       if (valid) {
-        const int page = table[j / page_size];
+        const int page = table[page_size == 16 ? (j >> 4) : j / page_size];
         if (page < 0 || page >= n_pages) {
           valid = false;
           if (j >= key_lo) *status = NIB_STATUS_BAD_PAGE;  // pages behind a window may be gone, and are not read
         } else {
-          koff = kv_offset(page, 0, hk, j % page_size, n_kv_head, page_size, HD) + piece * 8;
-          voff = kv_offset(page, 1, hk, j % page_size, n_kv_head, page_size, HD) + piece * 8;
+          const int slot = page_size == 16 ? (j & 15) : j % page_size;
+          src = head_base + (size_t)page * 2 * kv_stride + (size_t)slot * HD + piece * 8;
         }
       }
-      cp_async16(ks + (buf * PF_BN + r) * LD + piece * 8, cache + koff, valid);
-      cp_async16(vs + (buf * PF_BN + r) * LD + piece * 8, cache + voff, valid);
+      cp_async16(ks + (buf * PF_BN + r) * LD + piece * 8, src, valid);
+      cp_async16(vs + (buf * PF_BN + r) * LD + piece * 8, src + kv_stride, valid);
     }
   };
   load_kv(tile_first, 0);
@@ -121,6 +130,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
   const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
   uint32_t qf[HD / 16][4];
+  const float scale2 = scale * 1.4426950408889634f;
 
   for (int tile = tile_first; tile <= tile_last; ++tile) {
     const int buf = (tile - tile_first) & 1;
@@ -150,35 +160,43 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
         mma_bf16(s[2 * nn + 1], qf[kk], b[2], b[3]);
       }
     }
-    // ---- scale, mask, online softmax
-    const int j_base = tile * PF_BN + (lane & 3) * 2;
+    // ---- mask, online softmax.  Scores are kept times log2(e), so that the exponentials are plain
+    // powers of two; only the tiles on the causal edge (or a window's edge) need the mask.
+    const int wp0 = pos_first + warp * 16, wp1 = wp0 + 15;   // positions of the warp's rows
+    const bool edge = tile * PF_BN + PF_BN - 1 > wp0 || (window > 0 && tile * PF_BN < wp1 - window + 1);
+    if (edge) {
+      const int j_base = tile * PF_BN + (lane & 3) * 2;
+#pragma unroll
+      for (int i = 0; i < PF_BN / 8; ++i) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int j = j_base + i * 8 + c;
+          if (!(j <= p0 && j >= lo0)) s[i][c] = -INFINITY;
+          if (!(j <= p1 && j >= lo1)) s[i][2 + c] = -INFINITY;
+        }
+      }
+    }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int i = 0; i < PF_BN / 8; ++i) {
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const int j = j_base + i * 8 + c;
-        s[i][c] = (j <= p0 && j >= lo0) ? s[i][c] * scale : -INFINITY;
-        s[i][2 + c] = (j <= p1 && j >= lo1) ? s[i][2 + c] * scale : -INFINITY;
-        mx0 = fmaxf(mx0, s[i][c]);
-        mx1 = fmaxf(mx1, s[i][2 + c]);
-      }
+      mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
+      mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
     }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
-    // a row with no key yet (all masked so far) keeps m = -inf; exp(-inf - -inf) is avoided
-    const float c0 = (m0 == -INFINITY) ? 0.0f : expf(m0 - mn0);
-    const float c1 = (m1 == -INFINITY) ? 0.0f : expf(m1 - mn1);
+    const float mn0 = fmaxf(m0, mx0 * scale2), mn1 = fmaxf(m1, mx1 * scale2);   // (scale2 > 0)
+    // a row with no key yet (all masked so far) keeps m = -inf; 2^(-inf - -inf) is avoided
+    const float ms0 = (mn0 == -INFINITY) ? 0.0f : mn0, ms1 = (mn1 == -INFINITY) ? 0.0f : mn1;
+    const float c0 = pow2(m0 - ms0), c1 = pow2(m1 - ms1);
     float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
     for (int i = 0; i < PF_BN / 8; ++i) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
-        s[i][c] = (s[i][c] == -INFINITY) ? 0.0f : expf(s[i][c] - mn0);
-        s[i][2 + c] = (s[i][2 + c] == -INFINITY) ? 0.0f : expf(s[i][2 + c] - mn1);
+        s[i][c] = pow2(fmaf(s[i][c], scale2, -ms0));
+        s[i][2 + c] = pow2(fmaf(s[i][2 + c], scale2, -ms1));
         sum0 += s[i][c];
         sum1 += s[i][2 + c];
       }
@@ -265,7 +283,7 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
                                      int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
+  if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 1) || ((uintptr_t)out & 3)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
 #define NIB_PF_CASE(D)                                                                                         \

@@ -800,7 +800,14 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
   splits = (num_kb64 + prm.kb_per_split - 1) / prm.kb_per_split;
   if (prm.fix_partials != nullptr) prm.fix_splits = splits;
   if (prm.fix_splits <= 1) { prm.fix_partials = nullptr; prm.fix_counters = nullptr; prm.fix_splits = 0; }
-  prm.k_sub = (prm.bq <= 128 && prm.kb_per_split >= 4) ? 2 : 1;
+  // A deep pipeline (one block per SM) unless the grid is several waves of blocks: then a block gets
+  // about half (a third, for the many bandwidth-bound tiles of a decode step's head) of an SM's
+  // shared memory, so that two or three blocks share an SM and one's prologue and epilogue hide
+  // behind the others' loads and MMAs.
+  const long n_ctas = (long)((prm.p_rows + TC_BP - 1) / TC_BP) * ((prm.q_rows + prm.bq - 1) / prm.bq) * splits;
+  const size_t staging = prm.tma_store ? (size_t)TC_BP * prm.bq * esz : 0;
+  const bool pair = !prm.swap && ln == nullptr && n_ctas > 148 && staging <= 100 * 1024;
+  prm.k_sub = (!pair && prm.bq <= 128 && prm.kb_per_split >= 4) ? 2 : 1;
   const int num_stage_steps = (prm.kb_per_split + prm.k_sub - 1) / prm.k_sub;
   const int q_block = prm.bq * TC_BK * 2;
   size_t q_resident = 0;
@@ -809,11 +816,7 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     if (q_resident > (size_t)TC_LN_MAX_Q_BYTES) return NIB_ERR_UNSUPPORTED_SIZE;
   }
   const int stage_bytes = prm.k_sub * (TC_BP * TC_BK * 2 + (ln != nullptr ? 0 : q_block));
-  // A deep pipeline (one block per SM) unless the grid is several waves of bandwidth-bound blocks
-  // (the head's 393 tiles of a decode step): then about 72 KB per block, so that three blocks share
-  // an SM and one's prologue and epilogue hide behind the others' loads.
-  const long n_ctas = (long)((prm.p_rows + TC_BP - 1) / TC_BP) * ((prm.q_rows + prm.bq - 1) / prm.bq) * splits;
-  long budget = (prm.swap && n_ctas > 2 * 148 ? 72 : 200) * 1024 - (long)q_resident;
+  long budget = (pair ? 100 : (prm.swap && n_ctas > 2 * 148 ? 72 : 200)) * 1024 - (long)q_resident;
   if (budget < 2 * stage_bytes) budget = 2 * stage_bytes;
   int stages = (int)(budget / stage_bytes);
   if (stages < 2) stages = 2;
@@ -822,8 +825,7 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
   if (stages < 1) stages = 1;
   prm.stages = stages;
   size_t tile_bytes = (size_t)stages * stage_bytes + q_resident;
-  const size_t staging = (size_t)TC_BP * prm.bq * esz;
-  if (prm.tma_store && staging > tile_bytes) tile_bytes = staging;
+  if (staging > tile_bytes) tile_bytes = staging;
   const size_t smem = tile_bytes + 1024;
   if (smem > 225 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
 
