@@ -18,8 +18,10 @@
 extern "C" {
 #endif
 
+// A negative token -(s + 1) stands for feedback[s]: the token that the step before sampled for
+// slot s and left on the device (feedback may be null when no token is negative).
 int nib_embed(int dtype, const int* tokens, const int* positions, const void* table,
-              const void* pos_table, float* out, int T, int C, cudaStream_t stream);
+              const void* pos_table, const int* feedback, float* out, int T, int C, cudaStream_t stream);
 
 int nib_layernorm(int out_dtype, const float* x, const int* rows, const float* gamma,
                   const float* beta, void* out, int n_rows, int C, float eps, cudaStream_t stream);
@@ -95,10 +97,12 @@ int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStr
 // One token per logits row.  temperature, top_k and rng_state are per-slot arrays indexed by
 // row_slot[r]: argmax where temperature <= 0, else temperature / top-k sampling with the
 // request's own xorshift64* state (advanced by one draw).
+// last_token (may be null): per-slot array that also receives each row's token, for the next step's
+// embedding to read.
 // scratch: 2 * n_rows 64-bit words that are zero before the first call (the kernel leaves them zero).
 int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
-               unsigned long long* scratch, cudaStream_t stream);
+               int* last_token, unsigned long long* scratch, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

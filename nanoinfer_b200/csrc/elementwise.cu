@@ -14,11 +14,13 @@ namespace nib {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
-                             float* __restrict__ out, int C) {
+                             const int* __restrict__ feedback, float* __restrict__ out, int C) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
-  const T* te = table + (size_t)tokens[t] * C;
+  int tok = tokens[t];
+  if (tok < 0) tok = feedback[-tok - 1];   // the token that the step before sampled for slot -tok - 1
+  const T* te = table + (size_t)tok * C;
   float* o = out + (size_t)t * C;
   if (pos_table != nullptr) {
     const T* pe = pos_table + (size_t)positions[t] * C;
@@ -173,15 +175,16 @@ kv_append_pieces_kernel(const T* __restrict__ src, int ld, int k_off, int v_off,
 using namespace nib;
 
 extern "C" int nib_embed(int dtype, const int* tokens, const int* positions, const void* table,
-                         const void* pos_table, float* out, int T, int C, cudaStream_t stream) {
+                         const void* pos_table, const int* feedback, float* out, int T, int C,
+                         cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = C >= 256 ? 256 : 128;
   if (dtype == DT_F32)
     launch_pdl(embed_kernel<float>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const float*)table,
-                                                   (const float*)pos_table, out, C);
+                                                   (const float*)pos_table, feedback, out, C);
   else if (dtype == DT_BF16)
     launch_pdl(embed_kernel<bf16>, dim3(T), dim3(threads), 0, stream, tokens, positions, (const bf16*)table,
-                                                  (const bf16*)pos_table, out, C);
+                                                  (const bf16*)pos_table, feedback, out, C);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

@@ -155,7 +155,7 @@ __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               unsigned long long* __restrict__ rng_state, int* __restrict__ out,
-              unsigned long long* __restrict__ scratch) {
+              int* __restrict__ last_token, unsigned long long* __restrict__ scratch) {
   pdl_trigger();
   pdl_wait();
   __shared__ BestPair best_scratch[32];
@@ -183,7 +183,9 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
         __threadfence();
         const unsigned long long word = atomicExch(&scratch[2 * r], 0ull);
         scratch[2 * r + 1] = 0ull;
-        out[r] = (int)(0xffffffffu - (uint32_t)(word & 0xffffffffull));
+        const int tok = (int)(0xffffffffu - (uint32_t)(word & 0xffffffffull));
+        out[r] = tok;
+        if (last_token != nullptr) last_token[row_slot[r]] = tok;
       }
     }
     return;
@@ -247,7 +249,9 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
         }
       }
     }
-    out[r] = (tok == 0x7fffffff) ? 0 : tok;
+    tok = (tok == 0x7fffffff) ? 0 : tok;
+    out[r] = tok;
+    if (last_token != nullptr) last_token[row_slot[r]] = tok;
   }
 }
 
@@ -263,11 +267,11 @@ extern "C" int nib_argmax(const float* logits, int ld, int n_rows, int V, int* o
 
 extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                           const float* temperature, const int* top_k, unsigned long long* rng_state,
-                          int* out, unsigned long long* scratch, cudaStream_t stream) {
+                          int* out, int* last_token, unsigned long long* scratch, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_rows > 65535 || scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
   dim3 grid(SAMPLE_CHUNKS, n_rows);
   launch_pdl(sample_kernel, dim3(grid), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, row_slot, temperature, top_k, rng_state, out,
-                                                     scratch);
+                                                     last_token, scratch);
   NIB_LAUNCH_CHECK();
 }

@@ -23,6 +23,7 @@ rewritten before every replay.
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -129,7 +130,7 @@ class ModelRunner:
         self.launches_last_step = 0
 
     # ------------------------------------------------------------------ checks
-    def _validate(self, items: Sequence[StepItem]) -> int:
+    def _validate(self, items: Sequence[StepItem], feedback: bool = False) -> int:
         if not items:
             raise StepError("a step needs at least one item")
         if len(items) > self.max_entries:
@@ -149,6 +150,10 @@ class ModelRunner:
                 raise StepError("empty work item")
             for t in it.tokens:
                 if not 0 <= int(t) < vocab:
+                    # the one exception: a lone token -(slot + 1) stands for the token that the step
+                    # before sampled for this request and that is still on the device
+                    if feedback and n == 1 and int(t) == -(r.slot + 1):
+                        continue
                     raise BadToken(f"token id {t} is out of vocabulary")
             if limit is not None and r.n_tokens + n > limit:
                 raise ContextFull(f"context full: {r.n_tokens + n} tokens exceeds max {limit}")
@@ -181,7 +186,7 @@ class ModelRunner:
         lay.tabs, lay.total = tuple(tabs), o
         return lay
 
-    def _context(self, lay: _Layout, plan, starts, pos0s, slots, max_q: int, max_kv: int):
+    def _context(self, lay: _Layout, plan, starts, pos0s, slots, max_q: int, max_kv: int, sampler=None):
         dev = self._meta_dev
         T, E, M = lay.T, lay.E, lay.M
         ctx = StepContext(
@@ -190,7 +195,7 @@ class ModelRunner:
             entry_start=dev[lay.start:lay.start + E + 1], entry_pos0=dev[lay.pos0:lay.pos0 + E],
             entry_slot=dev[lay.slot:lay.slot + E], status=self.status, workspace=self.workspace,
             host_entry_start=starts, host_entry_pos0=pos0s, host_entry_slot=slots,
-            max_q_len=max_q, max_kv_len=max_kv,
+            max_q_len=max_q, max_kv_len=max_kv, token_feedback=getattr(sampler, "last_token", None),
         )
         plan.bind(dev[lay.plan:lay.plan + lay.n_plan])
         ctx.attention_plan = plan
@@ -210,7 +215,7 @@ class ModelRunner:
         """Run one step.  Returns float32 logits [wanted, vocab] (None if nothing is wanted), or with
         ``sampler`` the sampled tokens, int32 [wanted].  Either lives in the engine's scratch memory
         and is valid until the next step."""
-        T = self._validate(items)
+        T = self._validate(items, feedback=sampler is not None and hasattr(sampler, "last_token"))
         self.cache.append([(it.request, len(it.tokens)) for it in items])  # all pages of the step, or none
         E = len(items)
         decode_only = T == E
@@ -287,14 +292,23 @@ class ModelRunner:
             logits, tokens = cap.logits, cap.tokens
             self.launches_last_step = cap.launches
         else:
-            args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv)
+            args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv, sampler)
             n_seen = self._seen.get(key, 0) if key is not None else 0
             if key is not None and n_seen >= 1 and len(self._graphs) < self.max_graphs:
                 # the shape was run once already (scratch is sized, attributes are set): capture it
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
-                with torch.cuda.graph(graph):
-                    logits, tokens = self._run(*args, M, sampler)
+                # Nothing but kernel launches happens while capturing, but the garbage collector may
+                # wake up at any allocation and release pinned memory or events of an engine that
+                # is no longer used, which a strict capture does not survive: it stays off meanwhile.
+                gc_was_on = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.graph(graph, capture_error_mode="relaxed"):
+                        logits, tokens = self._run(*args, M, sampler)
+                finally:
+                    if gc_was_on:
+                        gc.enable()
                 cap = _Captured(graph, logits, tokens, ops.launch_count() - before)
                 self._graphs[key] = cap
                 graph.replay()

@@ -63,6 +63,13 @@ class Request:
     def n_pending(self) -> int:
         return len(self.prompt) + len(self.output) - self.n_computed
 
+    def next_tokens(self, n: int) -> List[int]:
+        """The next ``n`` tokens that are not in the cache yet (without building the whole list)."""
+        a, p = self.n_computed, len(self.prompt)
+        if a >= p:
+            return self.output[a - p:a - p + n]
+        return (self.prompt[a:a + n] + self.output[:max(0, a + n - p)])[:n]
+
 
 @dataclass
 class ScheduledItem:
@@ -70,6 +77,8 @@ class ScheduledItem:
     n_tokens: int
     #: the portion reaches the request's last token, so its last logits give the next token
     samples: bool = False
+    #: where in the request's output the step's token was put (set when the step is recorded)
+    output_index: int = -1
 
     def __post_init__(self):
         self.samples = self.n_tokens == self.request.n_pending
@@ -226,7 +235,11 @@ class Scheduler:
     # ------------------------------------------------------------------ after the step
     def on_step_done(self, items: Sequence[ScheduledItem], sampled: Sequence[int]) -> List[Request]:
         """Record what a step produced.  ``sampled`` holds one token for every item whose
-        ``samples`` is true, in order.  Returns the requests that ended."""
+        ``samples`` is true, in order.  Returns the requests that ended.
+
+        A token may be a negative stand-in for a value that the host has not read yet (the engine
+        runs one step ahead of its reads): it counts as a token for the length and context rules,
+        and ``on_tokens_read`` puts the value in later and applies the end-token rule then."""
         ended: List[Request] = []
         it = iter(sampled)
         for item in items:
@@ -237,6 +250,7 @@ class Scheduler:
                 continue  # mid-prompt portion: its prediction is not a token
             tok = int(next(it))
             req.output.append(tok)
+            item.output_index = len(req.output) - 1
             p = req.params
             if p.eos_token_id is not None and tok == p.eos_token_id:
                 reason = "eos"
@@ -247,5 +261,28 @@ class Scheduler:
             else:
                 continue
             self._finish(req, reason)
+            ended.append(req)
+        return ended
+
+    def on_tokens_read(self, items: Sequence[ScheduledItem], values: Sequence[int]) -> List[Request]:
+        """The values of a step's tokens that were recorded as stand-ins.  Returns the requests that
+        end at their end token now (their later tokens, computed ahead, are dropped)."""
+        ended: List[Request] = []
+        it = iter(values)
+        for item in items:
+            if not item.samples:
+                continue
+            tok, req, idx = int(next(it)), item.request, item.output_index
+            if idx < 0 or idx >= len(req.output) or req.output[idx] >= 0:
+                continue  # the request ended at an earlier token, or the value is known already
+            req.output[idx] = tok
+            eos = req.params.eos_token_id
+            if eos is None or tok != eos:
+                continue
+            del req.output[idx + 1:]       # what was computed ahead of the end token is dropped
+            if req.state == FINISHED:
+                req.finish_reason = "eos"  # it had ended meanwhile for another reason, at this token or a later one
+                continue
+            self._finish(req, "eos")
             ended.append(req)
         return ended

@@ -30,7 +30,7 @@ _lib = None
 _c_int, _c_float, _c_ptr = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
 _SIGNATURES = {
-    "nib_embed": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_embed": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     "nib_layernorm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_float, _c_ptr],
     "nib_kv_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
                       _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
@@ -56,7 +56,7 @@ _SIGNATURES = {
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
 }
 
 
@@ -170,8 +170,11 @@ def _i32(t: torch.Tensor, name: str) -> None:
 
 # ------------------------------------------------------------------------------ ops
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
-          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None) -> None:
-    """out[t] = table[tokens[t]] (+ pos_table[positions[t]]), written as 32-bit floats."""
+          pos_table: Optional[torch.Tensor] = None, positions: Optional[torch.Tensor] = None,
+          feedback: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] (+ pos_table[positions[t]]), written as 32-bit floats.  A negative
+    token -(s + 1) stands for ``feedback[s]``, the token that the step before left on the device for
+    slot s."""
     T, C = tokens.shape[0], table.shape[1]
     _i32(tokens, "tokens")
     if out.dtype != torch.float32 or out.shape[0] < T or out.shape[1] != C or not out.is_contiguous():
@@ -180,8 +183,10 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
         if positions is None or pos_table.dtype != table.dtype or pos_table.shape[1] != C:
             raise KernelError("embed: pos_table needs positions, the table's dtype and its width")
         _i32(positions, "positions")
+    if feedback is not None:
+        _i32(feedback, "feedback")
     _check(library().nib_embed(_dt(table), _ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table),
-                               _ptr(out), T, C, _stream()), "embed")
+                               _ptr(feedback), _ptr(out), T, C, _stream()), "embed")
 
 
 def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: float, out: torch.Tensor,
@@ -554,10 +559,12 @@ _sample_scratch: Optional[torch.Tensor] = None
 
 
 def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
-           top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor) -> None:
+           top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor,
+           last_token: Optional[torch.Tensor] = None) -> None:
     """One token per row.  ``temperature``, ``top_k`` and ``rng_state`` are per-slot arrays and
     ``row_slot`` names each row's slot: greedy where the slot's temperature <= 0, else
-    temperature / top-k sampling that advances the slot's xorshift64* word."""
+    temperature / top-k sampling that advances the slot's xorshift64* word.  ``last_token``: a
+    per-slot array that also receives the tokens (for the next step's embedding)."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with contiguous rows")
     if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:
@@ -569,4 +576,4 @@ def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperatur
         _sample_scratch = torch.zeros(2 * max(n_rows, 256), dtype=torch.int64, device=logits.device)
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
                                 _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
-                                _ptr(_sample_scratch), _stream()), "sample")
+                                _ptr(last_token), _ptr(_sample_scratch), _stream()), "sample")

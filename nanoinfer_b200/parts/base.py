@@ -226,6 +226,9 @@ class StepContext:
     #: which rows are single decoded tokens and which are prompt portions (set by the step function;
     #: the attention kernels build it themselves when it is absent)
     attention_plan: Optional[object] = None
+    #: int32 [slots]: the token last sampled for each slot, left on the device by the sampler; a
+    #: negative entry -(s + 1) of ``tokens`` stands for ``token_feedback[s]``
+    token_feedback: Optional[torch.Tensor] = None
 
 
 class Workspace:

@@ -22,6 +22,6 @@ class TokenEmbedding(Embedding):
     def forward(self, ctx: StepContext, x: torch.Tensor, position: Optional[PositionEncoding]) -> None:
         table = position.additive_table() if position is not None else None
         ops.embed(ctx.tokens[:ctx.n_rows], self.params["table"], x, table,
-                  ctx.positions if table is not None else None)
+                  ctx.positions if table is not None else None, feedback=ctx.token_feedback)
         if position is not None and table is None:
             position.on_embedding(x, ctx)

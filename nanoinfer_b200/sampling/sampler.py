@@ -51,6 +51,9 @@ class Sampler:
         self.rng = slots.register(("sampler", "rng"), (), torch.int64)
         self.temperature = slots.register(("sampler", "temperature"), (), torch.float32)
         self.top_k = slots.register(("sampler", "top_k"), (), torch.int32)
+        #: the token last sampled for each slot: the next step's embedding can read it from here
+        #: before the host has seen it
+        self.last_token = slots.register(("sampler", "last_token"), (), torch.int32)
         self._out = torch.zeros(max(1, slots.n_slots), dtype=torch.int32, device=slots.device)
 
     def set_request(self, slot: int, params: SamplingParams, n_draws_done: int = 0) -> None:
@@ -66,5 +69,5 @@ class Sampler:
         n = logits.shape[0]
         if n > self._out.numel():
             self._out = torch.zeros(n, dtype=torch.int32, device=logits.device)
-        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out)
+        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out, self.last_token)
         return self._out[:n]

@@ -137,3 +137,35 @@ def test_few_pages_preemption_gives_the_same_tokens(model_dirs):
     assert got == ample
     assert tight.scheduler.stats.preemptions >= 1
     assert tight.cache.pages_used() == [0]
+
+
+def test_running_a_step_ahead_of_the_reads_gives_the_same_tokens(model_dirs):
+    """With ``run_ahead`` a step is launched before the host has read the tokens of the step before
+    (they go from sampler to embedding on the device).  Tokens, end reasons and what comes back to
+    the pool must be those of the engine that reads every step: greedy and sampled, with end tokens
+    that cut requests short, and with so few pages that requests are preempted meanwhile."""
+    import nanoinfer_b200 as nb
+    d = model_dirs("A", torch.float32, sharpen=0.0)
+    prompts = [random_tokens(512, n, 90 + i) for i, n in enumerate([14, 14, 14, 30, 3, 22])]
+    base = engine(d, "float32", max_batch=4, max_rows=64, run_ahead=False)
+    greedy = base.generate(prompts, nb.SamplingParams(max_new_tokens=40, temperature=0.0))
+    # end tokens taken from what is generated: one early, one late, one never
+    eos = [greedy[0][3], greedy[1][30], None, None, greedy[4][11], None]
+    params = [nb.SamplingParams(max_new_tokens=40, temperature=0.0 if i % 2 == 0 else 0.8, top_k=30, seed=7 + i,
+                                eos_token_id=e) for i, e in enumerate(eos)]
+    for kw in (dict(), dict(max_tokens=128, prefill_budget=16)):
+        outs = {}
+        for ahead in (False, True):
+            eng = engine(d, "float32", max_batch=4, max_rows=64, run_ahead=ahead, **kw)
+            reqs = [eng.add_request(p, sp) for p, sp in zip(prompts, params)]
+            ended = []
+            while eng.has_work():
+                ended += eng.step()
+            assert sorted(r.id for r in ended) == sorted(r.id for r in reqs)
+            assert all(t >= 0 for r in reqs for t in r.output)
+            assert eng.cache.pages_used() == [0] and eng.cache.slots.n_free == 4
+            outs[ahead] = [(r.output, r.finish_reason) for r in reqs]
+            if kw:
+                assert eng.scheduler.stats.preemptions >= 1
+        assert outs[True] == outs[False]
+        assert outs[True][0][1] == "eos" and len(outs[True][0][0]) <= 4

@@ -151,3 +151,55 @@ def test_random_traffic_always_finishes_everything():
         for r in reqs:
             assert r.state == FINISHED and r.finish_reason == "length" and len(r.output) == r.params.max_new_tokens
         assert cache.pages_used() == [0]
+
+
+def test_tokens_recorded_as_stand_ins_get_their_values_one_step_later():
+    """The engine runs one step ahead of its reads: a step's tokens are recorded as negative
+    stand-ins (they count for lengths at once) and their values follow.  An end token that turns up
+    then ends the request there and drops what was computed ahead; the pages all come back."""
+    cache, s = setup(max_tokens=512, max_positions=64)
+    a = s.add([1] * 4, SamplingParams(max_new_tokens=50, eos_token_id=9))
+    b = s.add([1] * 6, SamplingParams(max_new_tokens=3, eos_token_id=9))
+    values = {0: [5, 5], 1: [9, 9], 2: [5, 5]}    # step -> token of every sampling item; a and b end at step 1
+    in_flight, step, reported = None, 0, []
+    while s.has_work() or in_flight:
+        items = s.schedule()
+        if items:
+            cache.append([(i.request.cache, i.n_tokens) for i in items])
+            for i in items:
+                cache.commit(i.request.cache, i.n_tokens)
+                toks = i.request.next_tokens(i.n_tokens)
+                # a stand-in is only ever the lone token of a decoding request, in its own slot
+                assert all(t >= 0 for t in toks) or (i.n_tokens == 1 and toks[0] == -(i.request.cache.slot + 1))
+            stand_ins = [-(i.request.cache.slot + 1) for i in items if i.samples]
+            ended_now = s.on_step_done(items, stand_ins)
+        else:
+            ended_now = []
+        if in_flight:
+            reported += in_flight[2] + s.on_tokens_read(in_flight[0], in_flight[1])
+        in_flight = (items, values.get(step, [5] * 8)[:sum(1 for i in items if i.samples)], ended_now) if items else None
+        step += 1
+        cache.check()
+    assert a.output == [5, 9] and a.finish_reason == "eos"
+    assert b.output == [5, 9] and b.finish_reason == "eos"      # not "length": the end token came first
+    assert set(id(r) for r in reported) == {id(a), id(b)}
+    assert all(t >= 0 for r in (a, b) for t in r.output)
+    assert cache.pages_used() == [0]
+    # the third token of b would have ended it by length with the same token: the reason is the end token's
+    cache, s = setup(max_tokens=512, max_positions=64)
+    c = s.add([1] * 3, SamplingParams(max_new_tokens=1, eos_token_id=9))
+    items = s.schedule()
+    cache.append([(i.request.cache, i.n_tokens) for i in items])
+    cache.commit(items[0].request.cache, 3)
+    assert s.on_step_done(items, [-1]) == [c] and c.finish_reason == "length" and c.output == [-1]
+    assert s.on_tokens_read(items, [9]) == [] and c.finish_reason == "eos" and c.output == [9]
+
+
+def test_next_tokens_is_a_slice_of_prompt_and_output():
+    _, s = setup(max_tokens=512)
+    r = s.add([1, 2, 3, 4], SamplingParams())
+    r.output = [5, 6, 7]
+    for done in range(7):
+        r.n_computed = done
+        for n in range(1, 8 - done):
+            assert r.next_tokens(n) == r.tokens[done:done + n]
