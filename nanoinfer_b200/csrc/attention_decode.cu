@@ -199,7 +199,8 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   }
   if (has_piece) {
 #pragma unroll
-    for (int e = 0; e < VN; ++e) go[g * head_dim + c * VN + e] = o[e];
+    for (int e = 0; e < VN; e += 4)
+      *reinterpret_cast<float4*>(go + g * head_dim + c * VN + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
   }
   __syncthreads();
   float M = -INFINITY;

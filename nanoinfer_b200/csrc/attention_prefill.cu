@@ -1,8 +1,10 @@
 // Causal attention for prompt portions in bfloat16: a tiled flash kernel over the paged cache.
 //
-// One block takes 64 consecutive query rows of one request and one head; its four warps own 16
-// rows each.  Keys and values are gathered page by page into shared memory with cp.async (two
-// buffers, the next tile loads while this one is computed); scores S = Q K^T and the weighted
+// One block takes 64 consecutive query rows of one request and one head; two warps share each 16
+// rows, one for each half of a tile's 64 keys (a block's time is its longest chain of tiles, so the
+// chain is made of half-size links), and their two softmax states are merged at the end.  Keys and
+// values are gathered page by page into shared memory with cp.async (two buffers, the next tile
+// loads while this one is computed); scores S = Q K^T and the weighted
 // sum O += P V run on the tensor cores (mma.sync m16n8k16, bf16 in, 32-bit accumulate); the
 // softmax is online over tiles of 64 keys, in 32-bit, with the scale applied after the dot
 // product and the causal bound as a loop bound plus a mask on the tiles that straddle it
@@ -20,7 +22,9 @@ namespace nib {
 
 constexpr int PF_BM = 64;   // query rows per block
 constexpr int PF_BN = 64;   // keys per tile
-constexpr int PF_THREADS = 128;
+constexpr int PF_KSPLIT = 2;  // warps that share a row group, each with a part of a tile's keys
+constexpr int PF_THREADS = 128 * PF_KSPLIT;
+constexpr int PF_WN = PF_BN / PF_KSPLIT;   // keys per warp and tile
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -76,8 +80,9 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
   bf16* vs = ks + 2 * PF_BN * LD;                        // [2][PF_BN][LD]
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int e = tiles[2 * blockIdx.x], q_off = tiles[2 * blockIdx.x + 1];
-  const int h = blockIdx.y, hk = h / (n_head / n_kv_head);
+  // (heads are the fast index of the grid: blocks start in the order of the tile list, longest first)
+  const int e = tiles[2 * blockIdx.y], q_off = tiles[2 * blockIdx.y + 1];
+  const int h = blockIdx.x, hk = h / (n_head / n_kv_head);
   const int row0 = entry_start[e] + q_off;               // first row of the tile in the step
   const int n_rows = min(PF_BM, entry_start[e + 1] - row0);
   const int pos_first = entry_pos0[e] + q_off;           // position of the tile's first row
@@ -125,7 +130,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;
-  const int r0 = warp * 16 + (lane >> 2), r1 = r0 + 8;     // rows within the tile
+  const int rg = warp & 3, kh = warp >> 2;                  // row group and part of the keys
+  const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;        // rows within the tile
   const int p0 = pos_first + r0, p1 = pos_first + r1;       // their positions
   const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
@@ -141,19 +147,19 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     if (tile == tile_first) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
-        ldmatrix_x4(qf[kk], qs + (warp * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
+        ldmatrix_x4(qf[kk], qs + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
     }
-    const bf16* kt = ks + buf * PF_BN * LD;
-    const bf16* vt = vs + buf * PF_BN * LD;
+    const bf16* kt = ks + (buf * PF_BN + kh * PF_WN) * LD;   // this warp's keys of the tile
+    const bf16* vt = vs + (buf * PF_BN + kh * PF_WN) * LD;
 
-    // ---- S = Q K^T : 16 rows x 64 keys per warp
-    float s[PF_BN / 8][4];
+    // ---- S = Q K^T : 16 rows x PF_WN keys per warp
+    float s[PF_WN / 8][4];
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
+    for (int i = 0; i < PF_WN / 8; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.0f;
 #pragma unroll
     for (int kk = 0; kk < HD / 16; ++kk) {
 #pragma unroll
-      for (int nn = 0; nn < PF_BN / 16; ++nn) {
+      for (int nn = 0; nn < PF_WN / 16; ++nn) {
         uint32_t b[4];
         ldmatrix_x4(b, kt + (nn * 16 + (lane & 7) + 8 * (lane >> 4)) * LD + kk * 16 + 8 * ((lane >> 3) & 1));
         mma_bf16(s[2 * nn], qf[kk], b[0], b[1]);
@@ -162,12 +168,13 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     }
     // ---- mask, online softmax.  Scores are kept times log2(e), so that the exponentials are plain
     // powers of two; only the tiles on the causal edge (or a window's edge) need the mask.
-    const int wp0 = pos_first + warp * 16, wp1 = wp0 + 15;   // positions of the warp's rows
-    const bool edge = tile * PF_BN + PF_BN - 1 > wp0 || (window > 0 && tile * PF_BN < wp1 - window + 1);
+    const int wp0 = pos_first + rg * 16, wp1 = wp0 + 15;     // positions of the warp's rows
+    const int wj0 = tile * PF_BN + kh * PF_WN;               // the warp's first key of the tile
+    const bool edge = wj0 + PF_WN - 1 > wp0 || (window > 0 && wj0 < wp1 - window + 1);
     if (edge) {
-      const int j_base = tile * PF_BN + (lane & 3) * 2;
+      const int j_base = wj0 + (lane & 3) * 2;
 #pragma unroll
-      for (int i = 0; i < PF_BN / 8; ++i) {
+      for (int i = 0; i < PF_WN / 8; ++i) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int j = j_base + i * 8 + c;
@@ -178,7 +185,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     }
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) {
+    for (int i = 0; i < PF_WN / 8; ++i) {
       mx0 = fmaxf(mx0, fmaxf(s[i][0], s[i][1]));
       mx1 = fmaxf(mx1, fmaxf(s[i][2], s[i][3]));
     }
@@ -192,7 +199,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     const float c0 = pow2(m0 - ms0), c1 = pow2(m1 - ms1);
     float sum0 = 0.0f, sum1 = 0.0f;
 #pragma unroll
-    for (int i = 0; i < PF_BN / 8; ++i) {
+    for (int i = 0; i < PF_WN / 8; ++i) {
 #pragma unroll
       for (int c = 0; c < 2; ++c) {
         s[i][c] = pow2(fmaf(s[i][c], scale2, -ms0));
@@ -215,7 +222,7 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     }
     // ---- O += P V
 #pragma unroll
-    for (int kk = 0; kk < PF_BN / 16; ++kk) {
+    for (int kk = 0; kk < PF_WN / 16; ++kk) {
       uint32_t a[4];
       a[0] = pack2(s[2 * kk][0], s[2 * kk][1]);
       a[1] = pack2(s[2 * kk][2], s[2 * kk][3]);
@@ -232,6 +239,36 @@ attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __rest
     __syncthreads();   // everyone is done with this buffer before the next load overwrites it
   }
   cp_async_wait<0>();
+
+  // ---- the warps of a row group merge their halves (through the idle key buffers), in a fixed order
+  static_assert(PF_KSPLIT == 2, "the merge below is written for two warps per row group");
+  float* mo = reinterpret_cast<float*>(ks);                 // [4 row groups][32 lanes][HD / 2 + 4]
+  constexpr int MO = HD / 2 + 4;
+  float* mine = mo + (size_t)(rg * 32 + lane) * MO;
+  if (kh == 1) {
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i)
+      *reinterpret_cast<float4*>(mine + 4 * i) = make_float4(o[i][0], o[i][1], o[i][2], o[i][3]);
+    *reinterpret_cast<float4*>(mine + HD / 2) = make_float4(m0, m1, l0, l1);
+  }
+  __syncthreads();
+  if (kh == 1) return;
+  {
+    const float4 other = *reinterpret_cast<const float4*>(mine + HD / 2);
+    const float mn0 = fmaxf(m0, other.x), mn1 = fmaxf(m1, other.y);
+    const float ms0 = (mn0 == -INFINITY) ? 0.0f : mn0, ms1 = (mn1 == -INFINITY) ? 0.0f : mn1;
+    const float a0 = pow2(m0 - ms0), a1 = pow2(m1 - ms1), b0 = pow2(other.x - ms0), b1 = pow2(other.y - ms1);
+    l0 = l0 * a0 + other.z * b0;
+    l1 = l1 * a1 + other.w * b1;
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+      const float4 t = *reinterpret_cast<const float4*>(mine + 4 * i);
+      o[i][0] = o[i][0] * a0 + t.x * b0;
+      o[i][1] = o[i][1] * a0 + t.y * b0;
+      o[i][2] = o[i][2] * a1 + t.z * b1;
+      o[i][3] = o[i][3] * a1 + t.w * b1;
+    }
+  }
 
   // ---- normalise and store
   const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
@@ -258,7 +295,7 @@ static int launch_prefill(const void* q, int ldq, const void* cache, void* out, 
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid(n_tiles, n_head);
+  dim3 grid(n_head, n_tiles);
   launch_pdl(attention_prefill_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, 
       (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, tiles, entry_start,
       entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, status);
@@ -285,7 +322,7 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 1) || ((uintptr_t)out & 3)) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (n_tiles > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
 #define NIB_PF_CASE(D)                                                                                         \
   case D:                                                                                                      \
     return launch_prefill<D>(q, ldq, cache, out, ldo, block_table, max_blocks, tiles, n_tiles, entry_start,    \

@@ -236,6 +236,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   __shared__ int epi_ok_sh[4];
+  __shared__ __align__(16) float bias_sh[256];   // the bias of the tile's columns (plain orientation)
   __shared__ int fix_last_sh;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -428,6 +429,13 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMAs
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&q_ready_bar)) : "memory");
     }
+    // While the MMAs run: the bias of this tile's columns into shared memory.  (Read from global
+    // memory in the epilogue, every 16 columns would stall for a round trip to L2 of their own: the
+    // four epilogue warps have nothing to hide it behind.)
+    if (!prm.swap) {
+      for (int c = (int)threadIdx.x - 64; c < bq; c += 128)
+        bias_sh[c] = (prm.bias && first_split && q0 + c < prm.q_rows) ? prm.bias[q0 + c] : 0.0f;
+    }
     // the four epilogue warps go on only if all of them saw the accumulator complete
     if (lane == 0) epi_ok_sh[quarter] = mbar_wait(&tmem_full_bar, 0, abort_flag) ? 1 : 0;
     asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -457,12 +465,10 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             float v[16];
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(raw[sub][j]);
-            if (prm.bias && first_split) {
 #pragma unroll
-              for (int j = 0; j < 16; ++j) {
-                const int n = q0 + c0 + j;
-                v[j] += (n < prm.q_rows) ? prm.bias[n] : 0.0f;
-              }
+            for (int j = 0; j < 16; j += 4) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bias_sh + c0 + j);
+              v[j] += b4.x; v[j + 1] += b4.y; v[j + 2] += b4.z; v[j + 3] += b4.w;
             }
             if (ACT != ACT_NONE) {
 #pragma unroll
@@ -513,7 +519,7 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 16; ++j) {  // unrolled with a guard: v[] must stay in registers
             if (j < nv) {
-              const float x = epilogue_act<ACT>(v[j] + ((prm.bias && first_split) ? prm.bias[n0 + j] : 0.0f));
+              const float x = epilogue_act<ACT>(v[j] + bias_sh[c0 + j]);
               if (prm.out_f32) {
                 float* o = (float*)prm.out + (size_t)p * prm.ldo + n0 + j;
                 *o = prm.residual ? *o + x : x;

@@ -502,6 +502,9 @@ class AttentionPlan:
             else:
                 pre.extend(range(a, b))
                 tiles.extend((e, off) for off in range(0, b - a, 64))
+        # the tiles that reach furthest back have the most keys to go through: they are launched first,
+        # so that the short ones fill the gaps at the end
+        tiles.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
         self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
         flat = dec + pre + [v for t in tiles for v in t]
         self.host = flat
