@@ -779,20 +779,35 @@ static int launch_tc(int out_dtype, const void* a, int lda, const void* w, int l
     }
   } else {
     prm.p_rows = M; prm.q_rows = N; p_base = a; p_ld = lda; q_base = w; q_ld = ldw;
-    // pick the Q tile (and a split of K for residual outputs) that fills the 148 SMs best
+    // Pick the Q tile (and a split of K for residual outputs) by a model of the block's time, in
+    // cycles, from measurements of this kernel: a 64-wide K block costs what its operands take to
+    // arrive at about 53 bytes a cycle and SM (the MMAs are faster), and a block has fixed costs
+    // (set-up, the first load's latency, epilogue, store).  Up to 148 blocks run one per SM; more
+    // than that run two per SM where the staged tile allows: the two share the SM's load bandwidth,
+    // and one's fixed costs hide behind the other's loads.
     const int p_tiles = (M + TC_BP - 1) / TC_BP;
     double best = 1e30;
     int best_bq = 64, best_splits = 1;
-    for (int bq = 256; bq >= 64; bq >>= 1) {
+    for (int bq = 256; bq >= 64; bq -= 64) {
       if (bq > 64 && N < bq) continue;
       const int tiles = p_tiles * ((N + bq - 1) / bq);
       const int max_splits = (residual && tma_ok) ? (num_kb64 >= 8 ? num_kb64 / 4 : 1) : 1;
       for (int sp = 1; sp <= max_splits && sp <= 8; ++sp) {
         const long ctas = (long)tiles * sp;
-        const long waves = (ctas + 147) / 148;
         const double kb = (double)((num_kb64 + sp - 1) / sp);
-        const double per_kb = 2.0 * bq > 300.0 ? 2.0 * bq : 300.0;   // MMA cycles vs issue cycles
-        const double cost = waves * (kb * per_kb + 2500.0 + 14.0 * bq);
+        const double load = 2.4 * (TC_BP + bq), mma = (double)bq;
+        const double per_kb = load > mma ? load : mma;
+        const double fixed = 3500.0 + (act != ACT_NONE ? 32.0 : 20.0) * bq;
+        const bool two = ctas > 148 && (size_t)TC_BP * bq * esz <= 100 * 1024;
+        double cost;
+        if (!two) {
+          cost = (double)((ctas + 147) / 148) * (kb * per_kb + fixed);
+        } else {
+          const long rounds = (ctas + 295) / 296;                  // rounds of two blocks per SM
+          const bool last_single = ctas - (rounds - 1) * 296 <= 148;   // the last round has one block per SM
+          cost = (double)(rounds - 1) * (2.0 * kb * per_kb + fixed) +
+                 (last_single ? kb * per_kb + fixed : 2.0 * kb * per_kb + fixed);
+        }
         if (cost < best) { best = cost; best_bq = bq; best_splits = sp; }
       }
     }
