@@ -59,12 +59,13 @@ __device__ __forceinline__ float pow2(float x) {
 // in a fixed order.
 template <typename T, int LPR>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 6)   // six blocks an SM: what the host's choice of splits counts on
-attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, T* __restrict__ out, int ldo,
+attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* part_o,
+                        float* part_ml, T* __restrict__ out, int ldo,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
-                        int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status) {
+                        int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status,
+                        int cluster_merge) {
   constexpr int VN = Piece<T>::N;
   constexpr int BATCH = LPR / 2 < 4 ? LPR / 2 : 4;   // keys per lane group and batch
   constexpr int GROUPS = 32 / LPR;                   // lane groups of a warp: rows per load instruction
@@ -75,6 +76,11 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   float* go = smem;                                  // ALL_GROUPS * head_dim
   float* gm = go + ALL_GROUPS * head_dim;            // ALL_GROUPS
   float* gl = gm + ALL_GROUPS;                       // ALL_GROUPS
+  // When the splits of a (row, head) are the blocks of one cluster, they hand their results to the
+  // first of them through distributed shared memory instead of through global scratch and a counter.
+  float* xo = gl + ALL_GROUPS;                       // n_splits * head_dim (used in block 0 of the cluster)
+  float* xml = xo + n_splits * head_dim;             // n_splits * 2
+  if (cluster_merge) cluster_arrive();               // met below, before the first store into another block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
   // The step's tables were written before the step began and the cache below this row's position
@@ -129,11 +135,17 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   const bool early = n_mine > 0 && (first_batch + warp) * BK + BK - 1 < pos;
   if (early) fetch(0);
   pdl_wait();
+  if (cluster_merge) cluster_wait();   // every block of the cluster runs by now
 
   if (empty) {
     if (threadIdx.x == 0) {
-      part_ml[2 * pidx] = -INFINITY;
-      part_ml[2 * pidx + 1] = 0.0f;
+      if (cluster_merge) {
+        store_to_rank(xml + 2 * split, 0, -INFINITY);
+        store_to_rank(xml + 2 * split + 1, 0, 0.0f);
+      } else {
+        part_ml[2 * pidx] = -INFINITY;
+        part_ml[2 * pidx + 1] = 0.0f;
+      }
     }
   } else {
   float qf[VN];   // this lane's piece of the query
@@ -212,27 +224,44 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
     for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2(gm[w] - M);
     if (n_splits == 1)
       out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L);
+    else if (cluster_merge)
+      store_to_rank(xo + split * head_dim + d, 0, acc);
     else
       part_o[pidx * head_dim + d] = acc;
   }
   if (n_splits > 1 && threadIdx.x == 0) {
-    part_ml[2 * pidx] = M;      // (in the power-of-two scale)
-    part_ml[2 * pidx + 1] = L;
+    if (cluster_merge) {
+      store_to_rank(xml + 2 * split, 0, M);
+      store_to_rank(xml + 2 * split + 1, 0, L);
+    } else {
+      part_ml[2 * pidx] = M;      // (in the power-of-two scale)
+      part_ml[2 * pidx + 1] = L;
+    }
   }
   }  // !empty
   if (n_splits == 1) return;
-  // ---- the block that finishes last merges the splits of its (row, head), in split order
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int arrived = atomicAdd(&counters[r * n_head + h], 1);
-    is_last_sh = arrived == n_splits - 1;
-    if (is_last_sh) counters[r * n_head + h] = 0;  // zero again for the next launch
+  size_t base = ((size_t)r * n_head + h) * n_splits;
+  if (cluster_merge) {
+    // ---- the first block of the cluster merges the splits, in split order
+    cluster_arrive();
+    cluster_wait();
+    if (split != 0) return;
+    part_o = xo;
+    part_ml = xml;
+    base = 0;
+  } else {
+    // ---- the block that finishes last merges the splits of its (row, head), in split order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int arrived = atomicAdd(&counters[r * n_head + h], 1);
+      is_last_sh = arrived == n_splits - 1;
+      if (is_last_sh) counters[r * n_head + h] = 0;  // zero again for the next launch
+    }
+    __syncthreads();
+    if (!is_last_sh) return;
+    __threadfence();
   }
-  __syncthreads();
-  if (!is_last_sh) return;
-  __threadfence();
-  const size_t base = ((size_t)r * n_head + h) * n_splits;
   float Mx = -INFINITY;
   for (int sp = 0; sp < n_splits; ++sp) Mx = fmaxf(Mx, part_ml[2 * (base + sp)]);
   float Lx = 0.0f;
@@ -258,11 +287,15 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
                          int* counters, int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
   const int n_pieces = head_dim / Piece<T>::N;
+  // two or four splits run as one cluster and merge through distributed shared memory (clusters of
+  // eight measured slower than the merge through global scratch: they are harder to place)
+  const int cluster = (n_splits == 2 || n_splits == 4) ? n_splits : 1;
 #define NIB_DECODE_LAUNCH(LPR)                                                                                     \
-  launch_pdl(attention_decode_kernel<T, LPR>, dim3(grid), dim3(DEC_WARPS * 32),                                    \
-             (size_t)(DEC_WARPS * (32 / LPR) * (head_dim + 2)) * sizeof(float), stream, (const T*)q, ldq,           \
-             (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks, rows, row_entry, positions,   \
-             n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk, n_splits, counters, status)
+  launch_pdl_cluster(attention_decode_kernel<T, LPR>, dim3(grid), dim3(DEC_WARPS * 32),                            \
+             (size_t)(DEC_WARPS * (32 / LPR) * (head_dim + 2) + n_splits * (head_dim + 2)) * sizeof(float), stream, \
+             cluster, (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks,   \
+             rows, row_entry, positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, chunk,    \
+             n_splits, counters, status, cluster > 1 ? 1 : 0)
   if (n_pieces <= 2) NIB_DECODE_LAUNCH(2);
   else if (n_pieces <= 4) NIB_DECODE_LAUNCH(4);
   else if (n_pieces <= 8) NIB_DECODE_LAUNCH(8);

@@ -62,26 +62,6 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ int cluster_rank() {
-  uint32_t r;
-  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-  return (int)r;
-}
-__device__ __forceinline__ void cluster_arrive() {
-  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void cluster_wait() {
-  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-// stores v at the place of `local` in the shared memory of block `rank` of the cluster
-__device__ __forceinline__ void store_to_rank(float* local, int rank, float v) {
-  uint32_t remote;
-  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
-               : "=r"(remote)
-               : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
-  asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(v) : "memory");
-}
-
 __host__ __device__ inline int skinny_ldx(int k_per) { return k_per + ((32 - k_per % 64) + 64) % 64; }
 
 // A cluster of `split` blocks owns 16 output features at a time; block r of it takes the slice
@@ -137,8 +117,49 @@ linear_skinny_kernel(const SkinnyParams prm) {
       reinterpret_cast<float4*>(ln_gb + prm.K)[i] = reinterpret_cast<const float4*>(prm.ln_beta)[i];
     }
   }
+  // What the epilogue needs and the kernel ahead does not write: the first tile's bias, and for the
+  // cache-writing projection the place of each row's slot (two dependent lookups in the step's
+  // tables).  Asked for now, they are there when the sums are; asked for then, each would be a round
+  // trip to L2 at the very end of the chain.  (Kept to the steps of at most 16 rows: registers.)
+  constexpr int OUTS = (NT * 128 + SK_WARPS * 32 - 1) / (SK_WARPS * 32);   // sums per thread
+  constexpr bool AHEAD = NT <= 2;
+  float bias_r[OUTS];
+  float res_r[OUTS];
+  long long kv_base[OUTS];   // element offset of (page, K, head 0, slot, 0) in the cache layer; -1: bad page
+#pragma unroll
+  for (int q = 0; q < OUTS; ++q) {
+    bias_r[q] = 0.0f; res_r[q] = 0.0f; kv_base[q] = 0;
+    if (AHEAD) {
+      const int o = threadIdx.x + q * SK_WARPS * 32;
+      const int m = o >> 4, n = walker * 16 + (o & 15);
+      if (o < NT * 128 && m < M) {
+        if (prm.bias != nullptr && n < prm.N) bias_r[q] = prm.bias[n];
+        if (prm.kv_cache != nullptr) {
+          const int pos = prm.kv_positions[m];
+          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
+          kv_base[q] = (page < 0 || page >= prm.kv_n_pages)
+                           ? -1
+                           : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
+                                                  prm.kv_head_dim);
+        }
+      }
+    }
+  }
   if (S > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
   pdl_wait();
+  // the residual stream's old values, asked for as early as the kernel ahead allows
+  auto fetch_residual = [&](int f0) {
+    if (AHEAD && prm.residual) {
+#pragma unroll
+      for (int q = 0; q < OUTS; ++q) {
+        const int o = threadIdx.x + q * SK_WARPS * 32;
+        const int m = o >> 4, n = f0 + (o & 15);
+        if (o < NT * 128 && m < M && n < prm.N && (S == 1 || m % S == rank))
+          res_r[q] = ((const float*)prm.out)[(size_t)m * prm.ldo + n];
+      }
+    }
+  };
+  fetch_residual(walker * 16);
 
   // ---- the step's rows into shared memory as bfloat16 (normalised on the way if asked)
   for (int i = threadIdx.x; i < (NT * 8 - M) * (ldx / 8); i += blockDim.x)   // rows past the step: zeros
@@ -199,13 +220,21 @@ linear_skinny_kernel(const SkinnyParams prm) {
   }
   __syncthreads();
 
-  constexpr int OUTS = (NT * 128 + SK_WARPS * 32 - 1) / (SK_WARPS * 32);   // sums per thread
   const int rows_per_rank = NT * 8 / S;
   int round = 0;
   for (int tile = walker; tile < n_tiles; tile += n_walkers, ++round) {
     const int f0 = tile * 16;
     const bf16* w0 = prm.w + (size_t)min(f0 + fr, prm.N - 1) * prm.ldw + k0;
     const bf16* w1 = prm.w + (size_t)min(f0 + fr + 8, prm.N - 1) * prm.ldw + k0;
+    if (AHEAD && round > 0) {   // (the first tile's were asked for above)
+#pragma unroll
+      for (int q = 0; q < OUTS; ++q) {
+        const int o = threadIdx.x + q * SK_WARPS * 32;
+        const int n = f0 + (o & 15);
+        if (o < NT * 128 && (o >> 4) < M && prm.bias != nullptr && n < prm.N) bias_r[q] = prm.bias[n];
+      }
+      fetch_residual(f0);
+    }
     float acc[NT][4];
 #pragma unroll
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f;
@@ -298,7 +327,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
         for (int r = 0; r < S; ++r)   // in block order, this block's own sum at its place
           x += (r == rank) ? total[q] : xb[((size_t)r * rows_per_rank + m / S) * 16 + nl];
       }
-      x += prm.bias ? prm.bias[n] : 0.0f;
+      x += AHEAD ? bias_r[q] : (prm.bias ? prm.bias[n] : 0.0f);
       if (prm.act == ACT_GELU_TANH) {
         float th;
         asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(0.7978845608028654f * (x + 0.044715f * x * x * x)));
@@ -310,17 +339,26 @@ linear_skinny_kernel(const SkinnyParams prm) {
         const int kv_dim = prm.kv_heads * prm.kv_head_dim;
         const int rem = n - prm.kv_q_dim;
         const int which = rem / kv_dim, head = (rem % kv_dim) / prm.kv_head_dim, d = rem % prm.kv_head_dim;
-        const int pos = prm.kv_positions[m];
-        const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
-        if (page < 0 || page >= prm.kv_n_pages) {
-          *prm.status = NIB_STATUS_BAD_PAGE;
+        long long base;
+        if (AHEAD) {
+          base = kv_base[q];
         } else {
-          prm.kv_cache[kv_offset(page, which, head, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
-                                 prm.kv_head_dim) + d] = __float2bfloat16_rn(x);
+          const int pos = prm.kv_positions[m];
+          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
+          base = (page < 0 || page >= prm.kv_n_pages)
+                     ? -1
+                     : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
+                                            prm.kv_head_dim);
+        }
+        if (base < 0) {
+          *prm.status = NIB_STATUS_BAD_PAGE;
+        } else {   // from (page, K, head 0, slot): K|V and the head are whole strides further
+          prm.kv_cache[base + ((long long)which * prm.kv_heads + head) * prm.kv_page_size * prm.kv_head_dim + d] =
+              __float2bfloat16_rn(x);
         }
       } else if (prm.out_f32) {
         float* dst = (float*)prm.out + (size_t)m * prm.ldo + n;
-        *dst = prm.residual ? *dst + x : x;
+        *dst = prm.residual ? (AHEAD ? res_r[q] : *dst) + x : x;
       } else {
         ((bf16*)prm.out)[(size_t)m * prm.ldo + n] = __float2bfloat16_rn(x);
       }
