@@ -75,6 +75,14 @@ int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, voi
                        int page_size, int n_pages, float scale, int window, int* status,
                        cudaStream_t stream);
 
+// tcgen05 attention for prompt portions (bfloat16, head size 64, page size a multiple of 16): tiles of
+// 128 query rows, S and O in tensor memory, keys and values by TMA page by page.  q holds T rows.
+int nib_attention_prefill_tc_supported(int head_dim, int page_size);
+int nib_attention_prefill_tc(const void* q, int ldq, int T, const void* cache, void* out, int ldo,
+                             const int* block_table, int max_blocks, const int* tiles, int n_tiles,
+                             const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head, int head_dim,
+                             int page_size, int n_pages, float scale, int window, int* status, cudaStream_t stream);
+
 // Split-KV attention for single decoded tokens (float32 or bfloat16, head sizes up to 128 in steps
 // of 8, pages of a multiple of 16 positions) and its scratch need.
 long long nib_attention_decode_scratch(int n_rows, int n_head, int head_dim, int n_splits);

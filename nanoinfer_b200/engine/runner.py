@@ -284,7 +284,8 @@ class ModelRunner:
         # split into single tokens and 64-row prompt tiles, and the split of the decode keys
         key = None
         if self.use_graphs:
-            key = (T, E, M, plan.n_decode, plan.n_prefill_rows, plan.n_tiles, plan.max_decode_keys, id(sampler))
+            key = (T, E, M, plan.n_decode, plan.n_prefill_rows, plan.n_tiles, plan.n_wide_tiles,
+                   plan.max_decode_keys, id(sampler))
         cap = self._graphs.get(key) if key is not None else None
         if cap is not None:
             cap.graph.replay()

@@ -47,6 +47,9 @@ _SIGNATURES = {
     "nib_linear_skinny": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
                           _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_attention_prefill_tc_supported": [_c_int, _c_int],
+    "nib_attention_prefill_tc": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
+                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
@@ -472,6 +475,23 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                                           _ptr(counters), _ptr(status), _stream()), "attention_decode")
 
 
+def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
+                         tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
+                         n_rows: int, n_head: int, scale: float, window: int, status: torch.Tensor) -> None:
+    """tcgen05 attention for prompt portions (bfloat16, head size 64): ``tiles`` holds (entry, first
+    row within the entry) pairs of 128 rows each; ``q`` holds the step's ``n_rows`` rows."""
+    n_pages, _, n_kv_head, page_size, head_dim = cache.shape
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention_prefill_tc: bfloat16 only")
+    if not cache.is_contiguous() or q.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("attention_prefill_tc: contiguous cache layer and rows")
+    _check(library().nib_attention_prefill_tc(_ptr(q), q.stride(0), n_rows, _ptr(cache), _ptr(out), out.stride(0),
+                                              _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
+                                              _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
+                                              page_size, n_pages, float(scale), int(window), _ptr(status),
+                                              _stream()), "attention_prefill_tc")
+
+
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                       tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
                       n_head: int, scale: float, window: int, status: torch.Tensor) -> None:
@@ -502,11 +522,16 @@ class AttentionPlan:
             else:
                 pre.extend(range(a, b))
                 tiles.extend((e, off) for off in range(0, b - a, 64))
+        # the same portions in tiles of 128 rows, for the tcgen05 kernel
+        wide = [(e, off) for e in range(len(entry_start) - 1) if entry_start[e + 1] - entry_start[e] > 1
+                for off in range(0, entry_start[e + 1] - entry_start[e], 128)]
         # the tiles that reach furthest back have the most keys to go through: they are launched first,
         # so that the short ones fill the gaps at the end
         tiles.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
+        wide.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
         self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
-        flat = dec + pre + [v for t in tiles for v in t]
+        self.n_wide_tiles = len(wide)
+        flat = dec + pre + [v for t in tiles for v in t] + [v for t in wide for v in t]
         self.host = flat
         if bind:
             self.bind(torch.tensor(flat, dtype=torch.int32, device=device) if flat else None)
@@ -519,6 +544,8 @@ class AttentionPlan:
         self.decode_rows = None if all_decode or nd == 0 else buf[:nd]
         self.prefill_rows = None if nd == 0 or npre == 0 else buf[nd:nd + npre]
         self.tiles = buf[nd + npre:nd + npre + 2 * self.n_tiles] if self.n_tiles else None
+        at = nd + npre + 2 * self.n_tiles
+        self.wide_tiles = buf[at:at + 2 * self.n_wide_tiles] if self.n_wide_tiles else None
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
@@ -541,7 +568,12 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
                          window, ctx.status, keys, ctx.workspace, plan.decode_rows)
     if plan.n_prefill_rows:
-        if q.dtype == torch.bfloat16 and library().nib_attention_prefill_supported(head_dim) \
+        if q.dtype == torch.bfloat16 and library().nib_attention_prefill_tc_supported(head_dim, page_size) \
+                and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
+                and out.data_ptr() % 16 == 0:
+            attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
+                                 ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status)
+        elif q.dtype == torch.bfloat16 and library().nib_attention_prefill_supported(head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status)

@@ -153,6 +153,12 @@ ATT_CASES = [
     (4, 1, 32, 32, [260, 90], [200, 90], 50),
     (2, 2, 128, 16, [150, 64, 65], [150, 64, 2], 0),
     (3, 3, 48, 16, [100, 31], [37, 1], 0),
+    # head size 64 in bfloat16 goes to the tcgen05 kernel: tiles of 128 rows, a window, pages of 32,
+    # grouped heads, portions that begin in the middle of a page and of a tile
+    (12, 12, 64, 16, [1024, 300], [1024, 200], 0),
+    (4, 2, 64, 32, [400, 150], [333, 150], 90),
+    (2, 1, 64, 16, [515, 2], [257, 2], 0),
+    (3, 3, 64, 48, [200, 129, 128], [100, 129, 128], 130),
 ]
 
 
@@ -173,6 +179,38 @@ def test_attention_over_scattered_pages(dtype, case):
     assert int(ctx.status.item()) == 0
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert (out.cpu().double() - want).abs().max() < tol
+
+
+@pytest.mark.parametrize("case", [c for c in ATT_CASES if c[2] == 64 and max(c[5]) > 1])
+def test_both_prefill_attention_kernels_at_head_size_64(case):
+    """Head size 64 is taken by the tcgen05 kernel; the warp-level MMA kernel (which serves the other
+    head sizes) and the tcgen05 kernel are each called directly here and must both agree with the
+    plain attention on the rows of the prompt portions."""
+    o = ops()
+    n_head, n_kv_head, hd, ps, lengths, q_lens, window = case
+    c = paged_case(torch.bfloat16, n_head, n_kv_head, hd, ps, lengths, q_lens, seed=hd + len(lengths))
+    scale = 0.7 / math.sqrt(hd)
+    want = torch.cat([
+        P.causal_attention(q.double(), k.double(), v.double(), n_head, n_kv_head, scale=scale, window=window,
+                           q_pos0=len(k) - len(q))
+        for q, k, v in zip(c["qs"], c["ks"], c["vs"])])
+    q = torch.cat(c["qs"]).to(torch.bfloat16).to(DEV)
+    ctx = Ctx(c["row_entry"], c["positions"])
+    plan = o.AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, torch.device(DEV))
+    rows = [t for e in range(len(lengths)) if q_lens[e] > 1
+            for t in range(ctx.host_entry_start[e], ctx.host_entry_start[e + 1])]
+    cache, table = c["cache"].to(DEV), c["table"].to(DEV)
+    assert o.library().nib_attention_prefill_tc_supported(hd, ps) and o.library().nib_attention_prefill_supported(hd)
+    for kernel in ("tcgen05", "mma"):
+        out = torch.zeros_like(q)
+        if kernel == "tcgen05":
+            o.attention_prefill_tc(q, cache, out, table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
+                                   ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status)
+        else:
+            o.attention_prefill(q, cache, out, table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
+                                n_head, scale, window, ctx.status)
+        assert int(ctx.status.item()) == 0, kernel
+        assert (out.cpu().double()[rows] - want[rows]).abs().max() < 2e-2, kernel
 
 
 def test_attention_finds_one_far_key_among_hundreds():
