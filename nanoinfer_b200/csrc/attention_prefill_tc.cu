@@ -2,11 +2,11 @@
 // by tcgen05.mma with S and O in tensor memory, keys and values brought page by page by TMA.
 //
 // One block takes 128 consecutive query rows of one request and one head (head size 64) and walks
-// the keys in tiles of 128.  Warp 0 is the TMA producer: its lanes look the tile's pages up in the
-// request's block table and load their keys and values (16 rows x 128 bytes a load) into a ring of
-// three stages of 128-byte-swizzled shared memory.  Warp 1 issues the MMAs: S = Q K^T (128 x 128 x 64) into
-// one of two score buffers in tensor memory, two tiles ahead of the softmax; and, once the softmax
-// warps have laid P down in shared memory as bfloat16 (two buffers), O += P V (128 x 64 x 128; V is
+// the keys in tiles of 128.  Warps 0 and 6 are the TMA producers of keys and of values: their lanes
+// look the tile's pages up in the request's block table and load them (16 rows x 128 bytes a load)
+// into rings of three stages of 128-byte-swizzled shared memory.  Warp 1 issues the MMAs: S = Q K^T (128 x 128 x 64) into
+// one of three score buffers in tensor memory, three tiles ahead of the softmax; and, once the softmax
+// warps have laid P down in shared memory as bfloat16 (three buffers), O += P V (128 x 64 x 128; V is
 // read as it lies, keys down the rows, as an MN-major operand), accumulated in tensor memory over
 // all tiles.  Warps 2..5 are the softmax: a thread owns a row, so the row maximum and sum need no
 // exchange between threads.  The running maximum is only raised when a tile exceeds it by more than
@@ -45,7 +45,7 @@ namespace nib {
 
 constexpr int AT_BM = 128;      // query rows per block = MMA M
 constexpr int AT_HD = 64;       // head size: one 128-byte swizzle row
-constexpr int AT_THREADS = 192;
+constexpr int AT_THREADS = 224;   // keys' producer, MMA issue, four softmax warps, values' producer
 constexpr int AT_UNIT = 16;     // rows of one TMA load of keys or values (divides the page size)
 
 struct AtParams {
@@ -103,6 +103,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const float* v) {
 }
 
 constexpr int AT_STAGES = 3;     // stages of keys and values
+constexpr int AT_NBUF = 3;       // score buffers in tensor memory and P buffers in shared memory
 constexpr float AT_RAISE = 8.0f; // the running maximum is raised when a tile exceeds it by more than 2^8
 
 // AT_BN: keys per tile.  64: two blocks an SM (256 columns of tensor memory and 97 KB each); 128: one
@@ -112,9 +113,9 @@ template <int AT_BN>
 struct AtShape {
   static constexpr int KV_STAGE = AT_BN * 128;            // bytes of a stage of keys (or values): [BN keys][64]
   static constexpr int P_BYTES = (AT_BN / 64) * 16384;    // one P buffer: [BN / 64 key blocks][128 rows][64 keys]
-  static constexpr uint32_t O_COL = 2 * AT_BN;            // tensor memory: S0 at 0, S1 at BN, O at 2 BN
+  static constexpr uint32_t O_COL = AT_NBUF * AT_BN;      // tensor memory: the score buffers, then O
   static constexpr uint32_t TMEM_COLS = AT_BN == 64 ? 256 : 512;
-  static constexpr size_t SMEM = 16384 + 2 * AT_STAGES * KV_STAGE + 2 * P_BYTES + 1024;
+  static constexpr size_t SMEM = 16384 + 2 * AT_STAGES * KV_STAGE + AT_NBUF * P_BYTES + 1024;
 };
 
 template <int AT_BN>
@@ -132,7 +133,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   uint8_t* v_s = k_s + AT_STAGES * AT_KV_STAGE;         // [stages][BN keys][64]
   uint8_t* p_s = v_s + AT_STAGES * AT_KV_STAGE;         // [2][BN / 64][128 rows][64 keys]
   __shared__ __align__(8) uint64_t q_full, k_full[AT_STAGES], k_empty[AT_STAGES], v_full[AT_STAGES], v_empty[AT_STAGES],
-      s_full[2], p_full[2], o_full[2];
+      s_full[AT_NBUF], p_full[AT_NBUF], o_full[AT_NBUF];
   __shared__ uint32_t tmem_base_sh;
   __shared__ int abort_sh;
   volatile int* abort_flag = &abort_sh;
@@ -160,14 +161,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_init(&v_full[i], 1);
       mbar_init(&v_empty[i], 1);
     }
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < AT_NBUF; ++i) {
       mbar_init(&s_full[i], 1);
       mbar_init(&p_full[i], 128);
       mbar_init(&o_full[i], 1);
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  // tensor memory: scores S0 and S1 (BN columns each), then the output O (64 columns)
+  // tensor memory: the score buffers (BN columns each), then the output O (64 columns)
   if (warp == 1) tmem_alloc(&tmem_base_sh, TMEM_COLS);
   tc_fence_before();
   __syncthreads();
@@ -175,47 +176,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const uint32_t tmem_base = tmem_base_sh;
   pdl_wait();   // the queries, and this step's keys and values, come from the kernels ahead
 
-  if (warp == 0) {
-    // ---------------- producer: Q once, then a stage of keys and values per tile.  A load brings one
-    // unit of 16 rows; lanes 0.. issue the units of the keys and lanes 16.. those of the values, each
-    // with its own look-up in the block table, so a tile's loads leave together.
-    if (lane == 0) {
+  if (warp == 0 || warp == 6) {
+    // ---------------- producers: Q once, then a stage of keys (warp 0) and of values (warp 6) per
+    // tile.  A load brings one unit of 16 rows; lane u issues unit u of its tile, with its own look-up
+    // in the block table, so a tile's loads leave together.
+    const bool is_v = warp == 6;
+    if (!is_v && lane == 0) {
       mbar_expect_tx(&q_full, 16384);
       tma_load_2d(q_s, &map_q, &q_full, h * AT_HD, row0);
     }
-    const int u = lane & 15;
-    const bool is_v = lane >= 16, active = u < AT_BN / AT_UNIT;
+    const int u = lane;
+    const bool active = u < AT_BN / AT_UNIT;
     bool ok = true;
-    for (int it = 0; ok && it < n_it; ++it) {
-      const int st = it % AT_STAGES, round = it / AT_STAGES;
-      // keys outside [key_lo, pos_last] are masked; their rows are read from the nearest unit of the
-      // request that is there (finite values, weight zero)
-      int row = -1;
-      if (active) {
-        int j = (tile_first + it) * AT_BN + u * AT_UNIT;
-        j = max(min(j, pos_last), key_lo) / AT_UNIT * AT_UNIT;
-        const int page = table[j / prm.page_size];
-        if (page < 0 || page >= prm.n_pages) {
-          *prm.status = NIB_STATUS_BAD_PAGE;
-          row = hk * prm.page_size;   // (page 0: in the pool)
-        } else {
-          row = ((page * 2) * prm.n_kv_head + hk) * prm.page_size + j % prm.page_size;
-        }
+    // keys outside [key_lo, pos_last] are masked; their rows are read from the nearest unit of the
+    // request that is there (finite values, weight zero)
+    auto unit_row = [&](int it) -> int {
+      if (!active || it >= n_it) return -1;
+      int j = (tile_first + it) * AT_BN + u * AT_UNIT;
+      j = max(min(j, pos_last), key_lo) / AT_UNIT * AT_UNIT;
+      const int page = table[j / prm.page_size];
+      if (page < 0 || page >= prm.n_pages) {
+        *prm.status = NIB_STATUS_BAD_PAGE;
+        return hk * prm.page_size;   // (page 0: in the pool)
       }
-      // Keys and values have barriers of their own: a stage's keys are free as soon as the scores
-      // are made from them, long before its values are, so the next keys (which the scores two
-      // tiles ahead wait for) are on their way early.
-      if (round > 0) ok = warp_mbar_wait(&k_empty[st], (round + 1) & 1, abort_flag, lane);
+      return ((page * 2) * prm.n_kv_head + hk) * prm.page_size + j % prm.page_size;
+    };
+    // The two warps run loops of their own: the keys' warp is held back only by the scores (a stage's
+    // keys are free as soon as the scores are made from them), the values' warp by the P V products,
+    // so the keys that the scores three tiles ahead wait for leave early.
+    uint8_t* dst_base = (is_v ? v_s : k_s) + u * 2048;
+    const int row_off = is_v ? prm.n_kv_head * prm.page_size : 0;
+    int row_next = unit_row(0);
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % AT_STAGES, round = it / AT_STAGES;
+      const int row = row_next;
+      row_next = unit_row(it + 1);   // the next tile's look-up travels while this tile's stage is waited for
+      uint64_t* empty = is_v ? &v_empty[st] : &k_empty[st];
+      uint64_t* full = is_v ? &v_full[st] : &k_full[st];
+      if (round > 0) ok = warp_mbar_wait(empty, (round + 1) & 1, abort_flag, lane);
       if (!ok) break;
-      if (lane == 0) mbar_expect_tx(&k_full[st], AT_KV_STAGE);
+      if (lane == 0) mbar_expect_tx(full, AT_KV_STAGE);
       __syncwarp();
-      if (active && !is_v) tma_load_2d(k_s + st * AT_KV_STAGE + u * 2048, &map_kv, &k_full[st], 0, row);
-      if (round > 0) ok = warp_mbar_wait(&v_empty[st], (round + 1) & 1, abort_flag, lane);
-      if (!ok) break;
-      if (lane == 0) mbar_expect_tx(&v_full[st], AT_KV_STAGE);
-      __syncwarp();
-      if (active && is_v)
-        tma_load_2d(v_s + st * AT_KV_STAGE + u * 2048, &map_kv, &v_full[st], 0, row + prm.n_kv_head * prm.page_size);
+      if (active) tma_load_2d(dst_base + st * AT_KV_STAGE, &map_kv, full, 0, row + row_off);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -224,7 +226,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const uint32_t idesc_s = umma_idesc(AT_BM, AT_BN);
       const uint32_t idesc_o = umma_idesc(AT_BM, AT_HD) | (1u << 16);   // B (= V) is MN-major: keys down the rows
       const uint32_t o_tmem = tmem_base + O_COL;
-      // scores of tile `it` into buffer it & 1 (free: P of tile it - 2 was made from it)
+      // scores of tile `it` into buffer it % AT_NBUF (free: P of tile it - AT_NBUF was made from it)
       AT_T0;
       auto issue_s = [&](int it) -> bool {
         const int st = it % AT_STAGES;
@@ -235,21 +237,21 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t qa = smem_u32(q_s), kb = smem_u32(k_s + st * AT_KV_STAGE);
 #pragma unroll
         for (int k = 0; k < AT_HD / 16; ++k)   // 16 of the head's 64 values per instruction: 32 bytes along the row
-          umma_bf16(tmem_base + (uint32_t)((it & 1) * AT_BN), umma_desc(qa + k * 32), umma_desc(kb + k * 32), idesc_s,
-                    k > 0);
-        umma_commit(&s_full[it & 1]);
+          umma_bf16(tmem_base + (uint32_t)((it % AT_NBUF) * AT_BN), umma_desc(qa + k * 32), umma_desc(kb + k * 32),
+                    idesc_s, k > 0);
+        umma_commit(&s_full[it % AT_NBUF]);
         umma_commit(&k_empty[st]);
         return true;
       };
       bool ok = mbar_wait(&q_full, 0, abort_flag);
       if (ok) ok = issue_s(0);
-      if (ok && n_it > 1) ok = issue_s(1);
+      for (int a = 1; ok && a < AT_NBUF && a < n_it; ++a) ok = issue_s(a);
       for (int it = 0; ok && it < n_it; ++it) {
-        const int st = it % AT_STAGES, b = it & 1;
+        const int st = it % AT_STAGES, b = it % AT_NBUF;
         AT_LAP(3);
         if (!mbar_wait(&v_full[st], (it / AT_STAGES) & 1, abort_flag)) break;
         AT_LAP(1);
-        if (!mbar_wait(&p_full[b], (it >> 1) & 1, abort_flag)) break;
+        if (!mbar_wait(&p_full[b], (it / AT_NBUF) & 1, abort_flag)) break;
         AT_LAP(2);
         tc_fence_after();
         const uint32_t vb = smem_u32(v_s + st * AT_KV_STAGE);
@@ -260,7 +262,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     (it > 0 || k > 0) ? 1u : 0u);
         umma_commit(&o_full[b]);
         umma_commit(&v_empty[st]);
-        if (it + 2 < n_it) ok = issue_s(it + 2);
+        if (it + AT_NBUF < n_it) ok = issue_s(it + AT_NBUF);
       }
       AT_LAP(3);
       AT_FLUSH_MMA();
@@ -279,8 +281,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     bool ok = true;
     AT_T0;
     for (int it = 0; it < n_it; ++it) {
-      const int b = it & 1;
-      ok = warp_mbar_wait(&s_full[b], (it >> 1) & 1, abort_flag, lane);
+      const int b = it % AT_NBUF;
+      ok = warp_mbar_wait(&s_full[b], (it / AT_NBUF) & 1, abort_flag, lane);
       if (!ok) break;
       tc_fence_after();
       AT_LAP(0);
@@ -315,7 +317,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           const float corr = (m_new == -INFINITY) ? 1.0f : at_pow2(m - m_new);
           l *= corr;
           // O holds the tiles up to it - 1 once their MMAs are done
-          ok = warp_mbar_wait(&o_full[(it - 1) & 1], ((it - 1) >> 1) & 1, abort_flag, lane);
+          ok = warp_mbar_wait(&o_full[(it - 1) % AT_NBUF], ((it - 1) / AT_NBUF) & 1, abort_flag, lane);
           if (!ok) break;
           tc_fence_after();
 #pragma unroll 1
@@ -332,9 +334,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // a row with no key yet (all masked so far) keeps m = -inf; 2^(-inf - -inf) is avoided
       const float ms = (m == -INFINITY) ? 0.0f : m;
       AT_LAP(3);
-      // P of tile it - 2 (the last user of this buffer) has been read by its MMA
-      if (it >= 2) {
-        ok = warp_mbar_wait(&o_full[b], ((it - 2) >> 1) & 1, abort_flag, lane);
+      // P of tile it - AT_NBUF (the last user of this buffer) has been read by its MMA
+      if (it >= AT_NBUF) {
+        ok = warp_mbar_wait(&o_full[b], ((it - AT_NBUF) / AT_NBUF) & 1, abort_flag, lane);
         if (!ok) break;
       }
       AT_LAP(4);
@@ -360,7 +362,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       AT_LAP(6);
     }
     // the last MMA into O
-    if (ok) ok = warp_mbar_wait(&o_full[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag, lane);
+    if (ok) ok = warp_mbar_wait(&o_full[(n_it - 1) % AT_NBUF], ((n_it - 1) / AT_NBUF) & 1, abort_flag, lane);
     AT_LAP(7);
     AT_FLUSH(n_it);
     if (ok) {
