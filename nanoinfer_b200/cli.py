@@ -2,6 +2,7 @@
 
     python -m nanoinfer_b200 --weights DIR generate --prompt-ids 464,3616 --tokens 40
     python -m nanoinfer_b200 --weights DIR bench --tokens 64 --prompt-len 64 --batch 1,8,64
+    python -m nanoinfer_b200 --weights DIR serve-bench --requests 128 --max-batch 32
     python -m nanoinfer_b200 random-weights --config gpt2-small --seed 1 --out DIR
 
 ``--weights`` is the reference's global option (main.rs:30-32): the folder with
@@ -10,7 +11,9 @@ and defaults (main.rs:48-72): ``--tokens 40 --temperature 0.0 --top-k 40 --seed 
 --profile``; the prompt is given as token ids.  ``bench`` keeps ``--tokens 64 --prompt-len 64
 --runs 5 --warmup 1 --bandwidth-gbs`` (crates/cli/src/bench.rs:24-58) and ``--batch``/``--dtype``
 of the batch sweep (crates/cli/src/metal_batch.rs:20-58).  The reference chooses a strategy
-with ``--stage``; here the one choice left is ``--dtype``.
+with ``--stage``; here the one choice left is ``--dtype``.  ``serve-bench`` keeps the options of the
+reference's ``metal-serve`` (crates/cli/src/metal_serve.rs:33-79): ``--requests --max-batch
+--prompt-min/max --out-min/max --rate --prefill-budget --kv-blocks --seed --gantt --out --summary``.
 """
 from __future__ import annotations
 
@@ -94,6 +97,12 @@ def cmd_bench(args) -> int:
     return run_cli_bench(args)
 
 
+def cmd_serve_bench(args) -> int:
+    from .serve_bench import run_cli
+
+    return run_cli(args)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="nanoinfer_b200", description="A small LLM inference engine for one B200")
     ap.add_argument("--weights", default="weights/gpt2",
@@ -122,6 +131,25 @@ def main(argv=None) -> int:
     b.add_argument("--out", default=None, help="append the result line to this file")
     b.add_argument("--note", default="")
     b.set_defaults(fn=cmd_bench)
+
+    s = sub.add_parser("serve-bench", help="many requests of random lengths: continuous against static batching")
+    s.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    s.add_argument("--requests", type=int, default=128, help="number of requests")
+    s.add_argument("--max-batch", type=int, default=32, help="most requests in flight")
+    s.add_argument("--prompt-min", type=int, default=16)
+    s.add_argument("--prompt-max", type=int, default=256, help="prompt lengths are uniform in [min, max]")
+    s.add_argument("--out-min", type=int, default=16)
+    s.add_argument("--out-max", type=int, default=256, help="output lengths are uniform in [min, max] (no end token)")
+    s.add_argument("--rate", type=float, default=0.0, help="mean arrivals per second (0: everything at t = 0)")
+    s.add_argument("--prefill-budget", type=int, default=256, help="most prompt tokens per step")
+    s.add_argument("--kv-blocks", type=int, default=None,
+                   help="pages of 16 positions in the pool (default: max_batch full requests and 8 more)")
+    s.add_argument("--seed", type=int, default=7)
+    s.add_argument("--gantt", type=int, default=32, help="requests in the summary's timeline")
+    s.add_argument("--out", default=None, help="append one result line per policy to this file")
+    s.add_argument("--summary", default=None, help="write the full summary (JSON) to this file")
+    s.add_argument("--note", default="")
+    s.set_defaults(fn=cmd_serve_bench)
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     r.add_argument("--config", required=True, help="a preset name (gpt2-small, gpt2-medium, gpt2-xl, "

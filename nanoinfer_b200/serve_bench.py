@@ -1,0 +1,258 @@
+"""The serving benchmark: many requests of random lengths through the continuous-batching
+scheduler, beside a static-batching baseline, in the manner of the reference's ``metal-serve``
+(crates/cli/src/metal_serve.rs).
+
+The workload is the reference's (metal_serve.rs:97-131): request ``i`` arrives after an
+exponential gap of mean ``1 / rate`` (``rate`` 0: everything at t = 0), with a prompt length uniform in
+``[prompt_min, prompt_max]`` and a fixed output length uniform in ``[out_min, out_max]`` (no end
+token), all from one xorshift generator seeded with ``seed``.  The reference cuts its prompts out of an
+English text; here they are seeded random token ids of the same lengths.
+
+Two policies run the same requests (metal_serve.rs:163-363):
+  * ``static``: batches of ``max_batch`` in arrival order; a batch runs until its longest request is
+    done, and a slot whose request ended early stays empty until then;
+  * ``continuous``: the engine's scheduler (admission while a slot and pages are free, decode rows
+    first, prompt portions under ``prefill_budget``).
+For each the summary gives what the reference's does (metal_serve.rs:373-469): generated tokens per
+second over the makespan, time to first token, time per output token and end-to-end latency at p50
+and p99, iterations, rows computed, peak and mean pages in use, and a down-sampled iteration trace.
+Times are the host's wall clock; the engine runs one step ahead of its reads, so a token's time is
+when the host has read it.
+"""
+from __future__ import annotations
+
+import json
+import sys
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+_MASK64 = (1 << 64) - 1
+
+
+class XorShift:
+    """The workload generator of the reference (metal_serve.rs:82-95): xorshift64 (13, 7, 17)."""
+
+    def __init__(self, seed: int):
+        self.s = ((int(seed) * 0x9E3779B97F4A7C15) & _MASK64) | 1
+
+    def next(self) -> int:
+        s = self.s
+        s ^= (s << 13) & _MASK64
+        s ^= s >> 7
+        s ^= (s << 17) & _MASK64
+        self.s = s
+        return s
+
+    def unif(self) -> float:
+        return (self.next() >> 11) / float(1 << 53)
+
+    def range(self, lo: int, hi: int) -> int:
+        return lo + self.next() % (hi - lo + 1)
+
+
+@dataclass
+class ServeRequest:
+    id: int
+    arrival: float
+    prompt: List[int]
+    out_len: int
+
+
+@dataclass
+class RequestLog:
+    admitted: float = 0.0
+    first_token: float = 0.0
+    finished: float = 0.0
+    generated: int = 0
+
+
+@dataclass
+class Iteration:
+    t0: float
+    dt: float
+    decode_rows: int
+    prefill_rows: int
+    occupied: int
+    kv_pages: int
+
+
+@dataclass
+class Outcome:
+    logs: List[RequestLog]
+    iters: List[Iteration] = field(default_factory=list)
+    makespan: float = 0.0
+    pages_peak: int = 0
+    preemptions: int = 0
+
+
+def workload(n_requests: int, prompt_min: int, prompt_max: int, out_min: int, out_max: int, rate: float, seed: int,
+             vocab_size: int) -> List[ServeRequest]:
+    import math
+
+    rng = XorShift(seed)
+    t, reqs = 0.0, []
+    for i in range(n_requests):
+        if rate > 0.0:
+            t += -math.log(max(rng.unif(), 1e-12)) / rate
+        n_prompt = rng.range(prompt_min, prompt_max)
+        prompt = [rng.next() % vocab_size for _ in range(n_prompt)]
+        reqs.append(ServeRequest(i, t, prompt, rng.range(out_min, out_max)))
+    return reqs
+
+
+def _run(engine, reqs: List[ServeRequest], static: bool) -> Outcome:
+    """Feeds the requests to the engine as they arrive and steps it until all are done."""
+    from .sampling.sampler import SamplingParams
+
+    sched, cache = engine.scheduler, engine.cache
+    logs = [RequestLog() for _ in reqs]
+    out = Outcome(logs)
+    handle: Dict[int, object] = {}        # request id -> the engine's request
+    rid_of: Dict[int, int] = {}           # id(engine's request) -> request id
+    first_seen: Dict[int, bool] = {}
+    nxt, done = 0, 0
+    last_decode, last_prefill = sched.stats.decode_rows, sched.stats.prefill_rows
+    pre0 = sched.stats.preemptions
+    t_start = time.perf_counter()
+    now = lambda: time.perf_counter() - t_start
+    while done < len(reqs):
+        t = now()
+        # static batching takes the next batch only when the engine is empty
+        may_add = not static or not engine.has_work()
+        room = engine.scheduler.max_batch if static else len(reqs)
+        while may_add and nxt < len(reqs) and reqs[nxt].arrival <= t and room > 0:
+            r = reqs[nxt]
+            handle[r.id] = engine.add_request(r.prompt, SamplingParams(max_new_tokens=r.out_len, temperature=0.0))
+            rid_of[id(handle[r.id])] = r.id
+            nxt += 1
+            room -= 1
+        if not engine.has_work():
+            if nxt < len(reqs):
+                time.sleep(max(0.0, min(reqs[nxt].arrival - now(), 0.01)))
+            continue
+        t0 = now()
+        ended = engine.step()
+        t1 = now()
+        st = sched.stats
+        used = cache.pages_used()
+        pages = max(used) if used else 0
+        out.iters.append(Iteration(t0, t1 - t0, st.decode_rows - last_decode, st.prefill_rows - last_prefill,
+                                   len(sched.running), pages))
+        last_decode, last_prefill = st.decode_rows, st.prefill_rows
+        out.pages_peak = max(out.pages_peak, pages)
+        for rid, h in handle.items():
+            if rid not in first_seen:
+                if h.admitted_order >= 0 and logs[rid].admitted == 0.0:
+                    logs[rid].admitted = t0
+                if h.output and h.output[0] >= 0:
+                    first_seen[rid] = True
+                    logs[rid].first_token = t1
+        for h in ended:
+            rid = rid_of.pop(id(h))
+            logs[rid].finished = t1
+            logs[rid].generated = len(h.output)
+            if rid not in first_seen:
+                first_seen[rid] = True
+                logs[rid].first_token = t1
+            del handle[rid]
+            done += 1
+    out.makespan = now()
+    out.preemptions = sched.stats.preemptions - pre0
+    return out
+
+
+def run_continuous(engine, reqs: List[ServeRequest]) -> Outcome:
+    return _run(engine, reqs, static=False)
+
+
+def run_static(engine, reqs: List[ServeRequest]) -> Outcome:
+    return _run(engine, reqs, static=True)
+
+
+def _pct(xs: List[float], p: float) -> float:
+    xs = sorted(xs)
+    return xs[int(round((len(xs) - 1) * p))] if xs else 0.0
+
+
+def summarise(name: str, reqs: List[ServeRequest], o: Outcome, page_size: int, gantt: int = 32) -> dict:
+    gen = sum(l.generated for l in o.logs)
+    ttft = [l.first_token - r.arrival for r, l in zip(reqs, o.logs)]
+    tpot = [(l.finished - l.first_token) / (r.out_len - 1) for r, l in zip(reqs, o.logs) if r.out_len > 1]
+    e2e = [l.finished - r.arrival for r, l in zip(reqs, o.logs)]
+    rows = sum(i.decode_rows + i.prefill_rows for i in o.iters)
+    wasted = sum(max(0, i.occupied - i.decode_rows) for i in o.iters) if name == "static" else 0
+    busy = sum(i.dt for i in o.iters)
+    kv_avg = sum(i.kv_pages * i.dt for i in o.iters) / max(busy, 1e-12)
+    stride = max(1, -(-len(o.iters) // 120))
+    print(f"{name:<11} {gen / o.makespan:>8.0f} tok/s  makespan {o.makespan:>6.2f} s  iters {len(o.iters):>5}  "
+          f"TTFT p50 {1e3 * _pct(ttft, 0.5):>7.1f} ms p99 {1e3 * _pct(ttft, 0.99):>7.1f} ms  "
+          f"TPOT p50 {1e3 * _pct(tpot, 0.5):>6.2f} ms p99 {1e3 * _pct(tpot, 0.99):>6.2f} ms  "
+          f"e2e p50 {_pct(e2e, 0.5):>6.2f} s  KV peak {o.pages_peak} pages")
+    return {
+        "policy": name,
+        "throughput_tok_s": gen / o.makespan,
+        "generated_tokens": gen,
+        "makespan_s": o.makespan,
+        "engine_busy_s": busy,
+        "iterations": len(o.iters),
+        "rows_computed": rows,
+        "wasted_decode_rows": wasted,
+        "preemptions": o.preemptions,
+        "ttft_ms": {"p50": 1e3 * _pct(ttft, 0.5), "p99": 1e3 * _pct(ttft, 0.99)},
+        "tpot_ms": {"p50": 1e3 * _pct(tpot, 0.5), "p99": 1e3 * _pct(tpot, 0.99)},
+        "e2e_s": {"p50": _pct(e2e, 0.5), "p99": _pct(e2e, 0.99)},
+        "kv_pages_peak": o.pages_peak,
+        "kv_pages_avg_used": kv_avg,
+        "kv_page_tokens": page_size,
+        "gantt": [{"id": r.id, "arrival": r.arrival, "admitted": l.admitted, "first_token": l.first_token,
+                   "finished": l.finished, "prompt_len": len(r.prompt), "out_len": r.out_len}
+                  for r, l in list(zip(reqs, o.logs))[:gantt]],
+        "iters": [{"t": i.t0, "dt": i.dt, "decode_rows": i.decode_rows, "prefill_rows": i.prefill_rows,
+                   "occupied": i.occupied, "kv_pages": i.kv_pages} for i in o.iters[::stride]],
+    }
+
+
+def run_cli(args) -> int:
+    from .engine.engine import Engine
+    from .registry import load_config
+
+    cfg = load_config(args.weights)
+    limit = getattr(cfg, "n_positions", None)
+    if limit is not None and args.prompt_max + args.out_max > limit:
+        print(f"prompt_max + out_max > {limit}", file=sys.stderr)
+        return 2
+    page = 16
+    pages_per_request = -(-(args.prompt_max + args.out_max) // page)
+    kv_blocks = args.kv_blocks or args.max_batch * pages_per_request + 8
+    reqs = workload(args.requests, args.prompt_min, args.prompt_max, args.out_min, args.out_max, args.rate, args.seed,
+                    cfg.vocab_size)
+    total_in, total_out = sum(len(r.prompt) for r in reqs), sum(r.out_len for r in reqs)
+    print(f"serve-bench: {args.requests} requests (prompt {args.prompt_min}-{args.prompt_max}, output "
+          f"{args.out_min}-{args.out_max}; {total_in} prompt + {total_out} output tokens), rate {args.rate} req/s, "
+          f"max batch {args.max_batch}, {kv_blocks} KV pages, {args.dtype}", file=sys.stderr)
+
+    def engine():
+        return Engine(args.weights, dtype=args.dtype, max_tokens=kv_blocks * page, max_batch=args.max_batch,
+                      max_rows=max(512, args.prefill_budget + args.max_batch), prefill_budget=args.prefill_budget,
+                      page_size=page)
+
+    eng = engine()
+    run_continuous(eng, reqs[:min(len(reqs), 4)])           # warm up: kernels built, first graphs captured
+    s_static = summarise("static", reqs, run_static(eng, reqs), page, args.gantt)
+    s_cont = summarise("continuous", reqs, run_continuous(eng, reqs), page, args.gantt)
+    print(f"continuous / static throughput: {s_cont['throughput_tok_s'] / s_static['throughput_tok_s']:.2f}x")
+    summary = {"requests": args.requests, "max_batch": args.max_batch, "prefill_budget": args.prefill_budget,
+               "kv_blocks": kv_blocks, "dtype": args.dtype, "seed": args.seed, "rate": args.rate, "note": args.note,
+               "policies": [s_static, s_cont]}
+    if args.summary:
+        with open(args.summary, "w") as fh:
+            json.dump(summary, fh)
+    if args.out:
+        with open(args.out, "a") as fh:
+            for s in (s_static, s_cont):
+                fh.write(json.dumps({"stage": f"serve-{s['policy']}", "dtype": args.dtype,
+                                     "throughput_tok_s": s["throughput_tok_s"], "ttft_ms": s["ttft_ms"],
+                                     "tpot_ms": s["tpot_ms"], "e2e_s": s["e2e_s"], "requests": args.requests,
+                                     "max_batch": args.max_batch, "note": args.note}) + "\n")
+    return 0

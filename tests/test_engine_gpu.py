@@ -169,3 +169,23 @@ def test_running_a_step_ahead_of_the_reads_gives_the_same_tokens(model_dirs):
                 assert eng.scheduler.stats.preemptions >= 1
         assert outs[True] == outs[False]
         assert outs[True][0][1] == "eos" and len(outs[True][0][0]) <= 4
+
+
+def test_serving_benchmark_runs_both_policies_to_the_end(model_dirs):
+    """The serving workload through the continuous scheduler and through static batching: every request
+    generates exactly its output length under both, and continuous batching needs fewer iterations."""
+    from nanoinfer_b200 import serve_bench as sb
+    d = model_dirs("A", torch.bfloat16)
+    reqs = sb.workload(24, 2, 40, 2, 30, 0.0, 3, 512)
+    eng = engine(d, "bfloat16", max_batch=4, max_rows=64, prefill_budget=32, max_tokens=4 * 80 + 128)
+    stat = sb.run_static(eng, reqs)
+    cont = sb.run_continuous(eng, reqs)
+    for o in (stat, cont):
+        assert [l.generated for l in o.logs] == [r.out_len for r in reqs]
+        assert all(0.0 <= l.admitted <= l.first_token <= l.finished <= o.makespan for l in o.logs)
+    assert len(cont.iters) < len(stat.iters)
+    s = sb.summarise("continuous", reqs, cont, 16)
+    assert s["generated_tokens"] == sum(r.out_len for r in reqs) and s["throughput_tok_s"] > 0
+    if s["preemptions"] == 0:   # every token but a request's last goes through the model once
+        assert s["rows_computed"] == sum(len(r.prompt) + r.out_len - 1 for r in reqs)
+    assert eng.cache.pages_used() == [0] and eng.cache.slots.n_free == 4

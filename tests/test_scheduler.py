@@ -203,3 +203,21 @@ def test_next_tokens_is_a_slice_of_prompt_and_output():
         r.n_computed = done
         for n in range(1, 8 - done):
             assert r.next_tokens(n) == r.tokens[done:done + n]
+
+
+def test_serving_workload_is_seeded_and_within_its_bounds():
+    from nanoinfer_b200.serve_bench import XorShift, workload
+    a = workload(50, 3, 40, 2, 9, 25.0, 7, 1000)
+    b = workload(50, 3, 40, 2, 9, 25.0, 7, 1000)
+    c = workload(50, 3, 40, 2, 9, 25.0, 8, 1000)
+    assert [(r.arrival, r.prompt, r.out_len) for r in a] == [(r.arrival, r.prompt, r.out_len) for r in b]
+    assert [r.prompt for r in a] != [r.prompt for r in c]
+    assert all(3 <= len(r.prompt) <= 40 and 2 <= r.out_len <= 9 and all(0 <= t < 1000 for t in r.prompt) for r in a)
+    assert all(x.arrival < y.arrival for x, y in zip(a, a[1:]))
+    assert 50 / a[-1].arrival == __import__("pytest").approx(25.0, rel=0.5)      # about `rate` arrivals a second
+    assert all(r.arrival == 0.0 for r in workload(5, 3, 4, 2, 3, 0.0, 1, 10))
+    # the generator is the reference's xorshift64 (13, 7, 17) on seed * 0x9e3779b97f4a7c15 | 1
+    g = XorShift(7)
+    s = ((7 * 0x9E3779B97F4A7C15) & (2 ** 64 - 1)) | 1
+    s ^= (s << 13) & (2 ** 64 - 1); s ^= s >> 7; s ^= (s << 17) & (2 ** 64 - 1)
+    assert g.next() == s
