@@ -23,6 +23,7 @@ rewritten before every replay.
 """
 from __future__ import annotations
 
+import contextlib
 import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
@@ -206,8 +207,9 @@ class ModelRunner:
         return ctx, caches, logit_rows, logit_slot
 
     def _run(self, ctx, caches, logit_rows, logit_slot, M: int, sampler):
-        logits = self.model.forward(ctx, caches, self.cache.state_tensors, logit_rows, M)
-        tokens = sampler.sample(logits, logit_slot) if (sampler is not None and logits is not None) else None
+        with ops.bound_stream() if self.device.type == "cuda" else contextlib.nullcontext():
+            logits = self.model.forward(ctx, caches, self.cache.state_tensors, logit_rows, M)
+            tokens = sampler.sample(logits, logit_slot) if (sampler is not None and logits is not None) else None
         return logits, tokens
 
     # ------------------------------------------------------------------ the step

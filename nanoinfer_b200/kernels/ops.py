@@ -132,8 +132,28 @@ def library() -> _Library:
     return _lib
 
 
+_bound_stream: Optional[int] = None
+
+
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """The stream that kernels are enqueued on: torch's current stream, looked up once per step when
+    the step function has bound it (the look-up costs more than a launch does)."""
+    return _bound_stream if _bound_stream is not None else torch.cuda.current_stream().cuda_stream
+
+
+class bound_stream:
+    """``with bound_stream():`` every launch inside goes to the stream that is current on entry."""
+
+    def __enter__(self):
+        global _bound_stream
+        self._before = _bound_stream
+        _bound_stream = torch.cuda.current_stream().cuda_stream
+        return self
+
+    def __exit__(self, *exc):
+        global _bound_stream
+        _bound_stream = self._before
+        return False
 
 
 _launches = 0
@@ -250,9 +270,23 @@ def linear_tc(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], ou
            "linear_tc")
 
 
+_capability: dict = {}
+
+
+def _can(name: str, *args) -> bool:
+    """A capability query of the library, remembered: the answers depend on sizes and alignments
+    only, and a foreign-function call costs about as much as a launch."""
+    key = (name,) + args
+    got = _capability.get(key)
+    if got is None:
+        got = _capability[key] = bool(getattr(library(), name)(*args))
+    return got
+
+
 def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
     return bool(a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and a.stride(1) == 1 and w.stride(1) == 1
-                and library().nib_linear_tc_supported(_ptr(a), a.stride(0), _ptr(w), w.stride(0), w.shape[1]))
+                and _can("nib_linear_tc_supported", 16 + (_ptr(a) & 15), a.stride(0), 16 + (_ptr(w) & 15), w.stride(0),
+                         w.shape[1]))   # (only the alignment of the pointers matters: 16 + the low bits)
 
 
 class NormInput:
@@ -325,7 +359,7 @@ def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=Non
         return False
     N, K = w.shape
     lib = library()
-    if not lib.nib_linear_skinny_supported(M, K, w.stride(0), int(norm is not None), _ptr(w)):
+    if not _can("nib_linear_skinny_supported", M, K, w.stride(0), int(norm is not None), 16 + (_ptr(w) & 15)):
         return False
     ln_args, kv_args = _option_args(norm, kv)
     if _profiler is not None:
@@ -568,12 +602,12 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
                          window, ctx.status, keys, ctx.workspace, plan.decode_rows)
     if plan.n_prefill_rows:
-        if q.dtype == torch.bfloat16 and library().nib_attention_prefill_tc_supported(head_dim, page_size) \
+        if q.dtype == torch.bfloat16 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
                                  ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status)
-        elif q.dtype == torch.bfloat16 and library().nib_attention_prefill_supported(head_dim) \
+        elif q.dtype == torch.bfloat16 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status)
