@@ -56,6 +56,16 @@ int nib_linear_tc_small(int out_dtype, const void* a, int lda, const void* w, in
                         int page_size, int n_pages, float* fix_partials, long long fix_floats,
                         int* fix_counters, int fix_n_counters, int* status, cudaStream_t stream);
 
+// The product for many rows by pairs of blocks that share one 256-row MMA (cta_group::2): each block
+// loads its own 128 rows of the activations and half of the weight tile.  bq: columns of a tile (0:
+// chosen by the library; else a multiple of 32 up to 256); splits: splits of K for residual outputs
+// (0: chosen by the library).
+int nib_linear_tc_pair_supported(int out_dtype, const void* a, int lda, const void* w, int ldw, const void* out,
+                                 int ldo, int M, int N, int K, int residual);
+int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
+                       int ldo, int M, int N, int K, int act, int residual, int bq, int splits, int* status,
+                       cudaStream_t stream);
+
 // The product for steps of at most 64 rows with warp-level MMAs (bfloat16), with the same LayerNorm
 // (at most 16 rows) and cache options as nib_linear_tc_small.  split: blocks of a cluster that split
 // K (0: chosen by the library; else 1, 2, 4 or 8).

@@ -43,6 +43,9 @@ _SIGNATURES = {
                             _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
                             _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
                             ctypes.c_longlong, _c_ptr, _c_int, _c_ptr, _c_ptr],
+    "nib_linear_tc_pair_supported": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int],
+    "nib_linear_tc_pair": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_linear_skinny_supported": [_c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_linear_skinny": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
@@ -289,6 +292,25 @@ def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
                          w.shape[1]))   # (only the alignment of the pointers matters: 16 + the low bits)
 
 
+def linear_tc_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
+                   act: int = ACT_NONE, residual: bool = False, bq: int = 0, splits: int = 0) -> bool:
+    """The tcgen05 product for many rows by pairs of blocks (one 256-row MMA over two SMs, each block
+    loading half of the weight tile).  False if the shape or an alignment is not taken."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or w.stride(1) != 1 \
+            or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        return False
+    N, K = w.shape
+    if not _can("nib_linear_tc_pair_supported", _dt(out), 16 + (_ptr(a) & 15), a.stride(0), 16 + (_ptr(w) & 15),
+                w.stride(0), 16 + (_ptr(out) & 15), out.stride(0), M, N, K, int(residual)):
+        return False
+    if _profiler is not None:
+        _profiler.label = f"M={M} N={N} K={K}"
+    _check(library().nib_linear_tc_pair(_dt(out), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
+                                        out.stride(0), M, N, K, act, int(residual), int(bq), int(splits),
+                                        _ptr(status_word()), _stream()), "linear_tc_pair")
+    return True
+
+
 class NormInput:
     """Activations given as the 32-bit residual stream plus the parameters of the LayerNorm that
     stands before the product: ``linear`` normalises ``x[rows[m]]`` (or ``x[m]``) itself, inside the
@@ -347,6 +369,7 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
 
 
 SKINNY_MAX_ROWS = 64
+PAIR_MIN_ROWS = 1536
 
 
 def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=0) -> bool:
@@ -433,6 +456,10 @@ def linear(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tens
         a = norm.materialise(M)   # (scratch: a second call for the same rows rewrites the same values)
     if _profiler is not None:
         _profiler.label = f"M={M} N={w.shape[0]} K={w.shape[1]}"
+    # measured: from about two thousand rows on, pairs of blocks on one 256-row MMA (half of the weight
+    # tile per SM) beat the single-block kernel, by 5 to 40 per cent
+    if M >= PAIR_MIN_ROWS and linear_tc_pair(a, w, bias, out, M, act, residual):
+        return
     if linear_tc_supported(a, w):
         linear_tc(a, w, bias, out, M, act, residual)
     else:

@@ -520,3 +520,54 @@ def test_few_row_product_with_k_split_over_a_cluster(M, N, K, split):
         assert o.linear_skinny(ad[M - 1:], None, wd, bd, alone, 1, split=split or 1)
         assert (alone.cpu().double() - out1.cpu().double()[M - 1:]).abs().max() < 1.5e-2 * scale
     assert int(o.status_word().item()) == 0
+
+
+PAIR_SHAPES = [(256, 256, 64), (2048, 2304, 768), (2000, 3072, 768), (513, 1000, 264), (1024, 768, 3072), (300, 200, 72)]
+
+
+@pytest.mark.parametrize("M, N, K", PAIR_SHAPES)
+@pytest.mark.parametrize("bq", [0, 128, 192, 256])
+def test_product_by_pairs_of_blocks(M, N, K, bq):
+    """The tcgen05 product for many rows by pairs of blocks that share one 256-row MMA: every epilogue,
+    ragged edges in rows and columns, K split over blocks for the residual sum, rows and columns beside
+    the result untouched."""
+    o = ops()
+    g = gen(M + N + K + bq)
+    a = (torch.randn(M, K, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    y = a.double() @ w.double().T + b.double()
+    scale = max(1.0, float(y.abs().max()))
+    ad, wd, bd = a.to(DEV), w.to(DEV), b.to(DEV)
+    if bq > N and bq > 128:
+        bq = 128
+    for act, fn in (("none", lambda u: u), ("tanh", P.gelu_tanh), ("erf", P.gelu_erf)):
+        out = torch.full((M + 2, N), 3.0, dtype=torch.bfloat16, device=DEV)
+        assert o.linear_tc_pair(ad, wd, bd, out, M, act=o.ACT_CODES[act], bq=bq)
+        assert (out.cpu().double()[:M] - fn(y)).abs().max() < 1.5e-2 * scale, act
+        assert (out.cpu()[M:] == 3.0).all()
+    for splits in (0, 1, 2):
+        res = torch.randn(M + 2, N, generator=g)
+        rd = res.to(DEV)
+        assert o.linear_tc_pair(ad, wd, bd, rd, M, residual=True, bq=bq, splits=splits)
+        assert (rd.cpu().double()[:M] - (res.double()[:M] + y)).abs().max() < 4e-3 * scale, splits
+        assert torch.equal(rd.cpu()[M:], res[M:])
+    pitch = (N + 15) // 16 * 16 + 16
+    buf = torch.full((M, pitch), -7.0, device=DEV)
+    if (N * 4) % 16 == 0:
+        assert o.linear_tc_pair(ad, wd, None, buf[:, :N], M, bq=bq)
+        assert (buf.cpu().double()[:, :N] - (y - b.double())).abs().max() < 4e-3 * scale
+        assert (buf.cpu()[:, N:] == -7.0).all()
+    assert int(o.status_word().item()) == 0
+
+
+def test_product_by_pairs_declines_what_it_cannot_take():
+    o = ops()
+    a = torch.zeros(100, 64, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 64, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(100, 128, dtype=torch.bfloat16, device=DEV)
+    assert not o.linear_tc_pair(a, w, None, out, 100)                    # fewer than 256 rows
+    a = torch.zeros(256, 36, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(128, 36, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(256, 128, dtype=torch.bfloat16, device=DEV)
+    assert not o.linear_tc_pair(a, w, None, out, 256)                    # 72-byte rows
