@@ -59,11 +59,14 @@ int nib_linear_tc_small(int out_dtype, const void* a, int lda, const void* w, in
 // The product for many rows by pairs of blocks that share one 256-row MMA (cta_group::2): each block
 // loads its own 128 rows of the activations and half of the weight tile.  bq: columns of a tile (0:
 // chosen by the library; else a multiple of 32 up to 256); splits: splits of K for residual outputs
-// (0: chosen by the library).
+// (0: chosen by the library).  cache != null: the fused q/k/v projection, keys and values straight
+// into the rows' slots of one cache layer (q_dim a multiple of 64, head_dim of 16).
 int nib_linear_tc_pair_supported(int out_dtype, const void* a, int lda, const void* w, int ldw, const void* out,
                                  int ldo, int M, int N, int K, int residual);
 int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,
-                       int ldo, int M, int N, int K, int act, int residual, int bq, int splits, int* status,
+                       int ldo, int M, int N, int K, int act, int residual, int bq, int splits, void* cache,
+                       const int* block_table, int max_blocks, const int* row_entry, const int* positions,
+                       int q_dim, int n_kv_head, int head_dim, int page_size, int n_pages, int* status,
                        cudaStream_t stream);
 
 // The product for steps of at most 64 rows with warp-level MMAs (bfloat16), with the same LayerNorm

@@ -35,6 +35,14 @@ struct PairParams {
   const float* bias;
   int residual;
   int* status;
+  // Optional: output columns from kv_q_dim on are keys and values, which go straight to the rows' slots
+  // in the paged cache instead of to `out` (the reference's QKV epilogue,
+  // crates/metal/src/shaders/batch.metal:155-164); q_dim and head_dim are multiples of 16
+  bf16* kv_cache;
+  const int* kv_block_table;
+  const int* kv_row_entry;
+  const int* kv_positions;
+  int kv_max_blocks, kv_q_dim, kv_heads, kv_head_dim, kv_page_size, kv_n_pages;
 };
 
 // ------------------------------------------------------------------ PTX wrappers of the pair forms
@@ -210,6 +218,15 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const int pl = quarter * 32 + lane;
     for (int c = (int)threadIdx.x - 64; c < bq; c += 128)   // while the MMAs run: the bias of the tile's columns
       bias_sh[c] = (prm.bias && first_split && q0 + c < prm.N) ? prm.bias[q0 + c] : 0.0f;
+    // the cache slot of this thread's row (two dependent look-ups in the step's tables), while the MMAs run
+    long long kv_base = -1;   // element offset of (page, K, head 0, slot, 0) in the cache layer
+    const bool kv_tile = prm.kv_cache != nullptr && q0 + bq > prm.kv_q_dim;
+    if (kv_tile && p0 + pl < prm.M) {
+      const int pos = prm.kv_positions[p0 + pl];
+      const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[p0 + pl] * prm.kv_max_blocks + pos / prm.kv_page_size];
+      if (page < 0 || page >= prm.kv_n_pages) *prm.status = NIB_STATUS_BAD_PAGE;
+      else kv_base = (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size, prm.kv_head_dim);
+    }
     if (lane == 0) epi_ok_sh[quarter] = mbar_wait(&tmem_full_bar, 0, abort_flag) ? 1 : 0;
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = (epi_ok_sh[0] & epi_ok_sh[1] & epi_ok_sh[2] & epi_ok_sh[3]) != 0;
@@ -241,7 +258,19 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
 #pragma unroll
             for (int j = 0; j < 16; ++j) v[j] = pair_act<ACT>(v[j]);
           }
-          if (prm.out_f32) {
+          if (kv_tile && q0 + c0 >= prm.kv_q_dim) {
+            // 16 consecutive values of one head of this row's key or value: 32 bytes into its cache slot
+            if (kv_base >= 0 && q0 + c0 < prm.N) {
+              const int kv_dim = prm.kv_heads * prm.kv_head_dim, rem = q0 + c0 - prm.kv_q_dim;
+              const int which = rem / kv_dim, head = (rem % kv_dim) / prm.kv_head_dim, d = rem % prm.kv_head_dim;
+              bf16* dst = prm.kv_cache + kv_base +
+                          ((long long)which * prm.kv_heads + head) * prm.kv_page_size * prm.kv_head_dim + d;
+              *reinterpret_cast<uint4*>(dst) = make_uint4(pack_bf16(v[0], v[1]), pack_bf16(v[2], v[3]),
+                                                          pack_bf16(v[4], v[5]), pack_bf16(v[6], v[7]));
+              *reinterpret_cast<uint4*>(dst + 8) = make_uint4(pack_bf16(v[8], v[9]), pack_bf16(v[10], v[11]),
+                                                              pack_bf16(v[12], v[13]), pack_bf16(v[14], v[15]));
+            }
+          } else if (prm.out_f32) {
             uint8_t* blk = smem + (size_t)(c0 / 32) * 16384 + (size_t)pl * 128;
 #pragma unroll
             for (int j = 0; j < 16; j += 4) {
@@ -264,7 +293,8 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
       asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
       if (warp == 2 && lane == 0) {
         const int cols = prm.out_f32 ? 32 : 64;
-        for (int c = 0; c < bq && q0 + c < prm.N; c += cols) {
+        const int n_out = prm.kv_cache != nullptr ? prm.kv_q_dim : prm.N;   // columns that go to `out`
+        for (int c = 0; c < bq && q0 + c < n_out; c += cols) {
           const void* src = smem + (size_t)(c / cols) * 16384;
           if (prm.residual) tma_reduce_add_2d(&map_o, src, q0 + c, p0);
           else tma_store_2d(&map_o, src, q0 + c, p0);
@@ -321,10 +351,20 @@ static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, const
 }
 
 // bq: columns of a tile (0: chosen here); splits: splits of K for residual outputs (0: chosen here).
+// cache != null: the fused query/key/value projection: the first q_dim columns go to out, the rest to the
+// rows' slots in one cache layer [n_pages, 2, n_kv_head, page_size, head_dim].
 extern "C" int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
                                   void* out, int ldo, int M, int N, int K, int act, int residual, int bq, int splits,
-                                  int* status, cudaStream_t stream) {
+                                  void* cache, const int* block_table, int max_blocks, const int* row_entry,
+                                  const int* positions, int q_dim, int n_kv_head, int head_dim, int page_size,
+                                  int n_pages, int* status, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
+  if (cache != nullptr) {
+    // the fused q/k/v projection: bfloat16, no residual, whole 16-value pieces of a head per thread, and a
+    // tile's columns that go to `out` a multiple of what one TMA store moves
+    if (out_dtype != DT_BF16 || residual || n_kv_head <= 0 || N != q_dim + 2 * n_kv_head * head_dim) return NIB_ERR_BAD_ARGUMENT;
+    if ((q_dim & 63) || (head_dim & 15) || ((uintptr_t)cache & 15)) return NIB_ERR_UNSUPPORTED_SIZE;
+  }
   if (!nib_linear_tc_pair_supported(out_dtype, a, lda, w, ldw, out, ldo, M, N, K, residual)) return NIB_ERR_UNSUPPORTED_SIZE;
   const int esz = out_dtype == DT_F32 ? 4 : 2;
   const int num_kb = (K + PR_BK - 1) / PR_BK;
@@ -371,6 +411,9 @@ extern "C" int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const v
   prm.kb_per_split = (num_kb + splits - 1) / splits;
   splits = (num_kb + prm.kb_per_split - 1) / prm.kb_per_split;
   prm.out_f32 = out_dtype == DT_F32; prm.bias = bias; prm.residual = residual; prm.status = status;
+  prm.kv_cache = (bf16*)cache; prm.kv_block_table = block_table; prm.kv_row_entry = row_entry;
+  prm.kv_positions = positions; prm.kv_max_blocks = max_blocks; prm.kv_q_dim = q_dim; prm.kv_heads = n_kv_head;
+  prm.kv_head_dim = head_dim; prm.kv_page_size = page_size; prm.kv_n_pages = n_pages;
   const int stage_bytes = PR_BP * PR_BK * 2 + (bq / 2) * PR_BK * 2;
   // grids of more than one wave of pairs: about half of an SM's shared memory a block, so that two
   // pairs share two SMs and one's epilogue hides behind the other's loads and MMAs

@@ -45,7 +45,8 @@ _SIGNATURES = {
                             ctypes.c_longlong, _c_ptr, _c_int, _c_ptr, _c_ptr],
     "nib_linear_tc_pair_supported": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int],
     "nib_linear_tc_pair": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+                           _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_linear_skinny_supported": [_c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_linear_skinny": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int,
                           _c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr, _c_ptr,
@@ -293,9 +294,10 @@ def linear_tc_supported(a: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def linear_tc_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor, M: int,
-                   act: int = ACT_NONE, residual: bool = False, bq: int = 0, splits: int = 0) -> bool:
+                   act: int = ACT_NONE, residual: bool = False, bq: int = 0, splits: int = 0, kv=None) -> bool:
     """The tcgen05 product for many rows by pairs of blocks (one 256-row MMA over two SMs, each block
-    loading half of the weight tile).  False if the shape or an alignment is not taken."""
+    loading half of the weight tile).  ``kv``: (cache layer, block table, row_entry, positions, q_dim)
+    sends keys and values straight to the cache.  False if the shape or an alignment is not taken."""
     if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or w.stride(1) != 1 \
             or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
         return False
@@ -303,10 +305,13 @@ def linear_tc_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     if not _can("nib_linear_tc_pair_supported", _dt(out), 16 + (_ptr(a) & 15), a.stride(0), 16 + (_ptr(w) & 15),
                 w.stride(0), 16 + (_ptr(out) & 15), out.stride(0), M, N, K, int(residual)):
         return False
+    _, kv_args = _option_args(None, kv)
+    if kv is not None and (kv[4] % 64 or kv[0].shape[4] % 16 or out.dtype != torch.bfloat16 or residual):
+        return False
     if _profiler is not None:
-        _profiler.label = f"M={M} N={N} K={K}"
+        _profiler.label = f"M={M} N={N} K={K}" + (" kv" if kv else "")
     _check(library().nib_linear_tc_pair(_dt(out), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
-                                        out.stride(0), M, N, K, act, int(residual), int(bq), int(splits),
+                                        out.stride(0), M, N, K, act, int(residual), int(bq), int(splits), *kv_args,
                                         _ptr(status_word()), _stream()), "linear_tc_pair")
     return True
 
@@ -470,12 +475,17 @@ def linear_qkv(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.
                q_dim: int, cache: torch.Tensor, block_table: torch.Tensor, row_entry: torch.Tensor,
                positions: torch.Tensor, status: torch.Tensor, norm: Optional[NormInput] = None) -> bool:
     """The fused q/k/v projection with the cache append in its epilogue: queries to out[:M, :q_dim],
-    keys and values to their slots of ``cache``.  Returns False (and does nothing) where the fused
-    kernel does not apply: more than 128 rows, float32, or a shape the tensor cores refuse."""
+    keys and values to their slots of ``cache``.  Returns False (and does nothing) where no fused
+    kernel applies: between 129 rows and the pair kernel's minimum, float32, or a shape the tensor
+    cores refuse."""
     if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         return False
-    return _linear_small(a, norm, w, bias, out, M, ACT_NONE, False,
-                         kv=(cache, block_table, row_entry, positions, q_dim))
+    kv = (cache, block_table, row_entry, positions, q_dim)
+    if M >= PAIR_MIN_ROWS:   # many rows: the pair kernel writes the cache from its epilogue too
+        if norm is not None:
+            a, norm = norm.materialise(M), None
+        return linear_tc_pair(a, w, bias, out, M, kv=kv)
+    return _linear_small(a, norm, w, bias, out, M, ACT_NONE, False, kv=kv)
 
 
 def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, block_table: torch.Tensor,

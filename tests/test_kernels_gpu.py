@@ -571,3 +571,49 @@ def test_product_by_pairs_declines_what_it_cannot_take():
     w = torch.zeros(128, 36, dtype=torch.bfloat16, device=DEV)
     out = torch.zeros(256, 128, dtype=torch.bfloat16, device=DEV)
     assert not o.linear_tc_pair(a, w, None, out, 256)                    # 72-byte rows
+
+
+@pytest.mark.parametrize("n_head, n_kv_head, hd, lens", [(12, 12, 64, [1024, 700, 324]), (6, 2, 32, [1600]),
+                                                         (4, 4, 16, [513, 500, 600])])
+def test_fused_qkv_projection_for_many_rows(n_head, n_kv_head, hd, lens):
+    """The q/k/v projection of prompt portions by the pair kernel: queries to the output, keys and values
+    from the epilogue into the rows' slots of scattered pages (portions that start in mid-page)."""
+    o = ops()
+    g = gen(sum(lens) + hd)
+    M, ps = sum(lens), 16
+    C = 64 + 8 * n_head
+    q_dim, kv_dim = n_head * hd, n_kv_head * hd
+    N = q_dim + 2 * kv_dim
+    a = (torch.randn(M, C, generator=g) * 0.5).to(torch.bfloat16)
+    w = (torch.randn(N, C, generator=g) * 0.1).to(torch.bfloat16)
+    b = torch.randn(N, generator=g) * 0.1
+    pos0 = [5 + 11 * e for e in range(len(lens))]                      # each portion continues a request
+    max_blocks = max(-(-(p0 + n) // ps) for p0, n in zip(pos0, lens)) + 1
+    n_pages = sum(-(-(p0 + n) // ps) for p0, n in zip(pos0, lens)) + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    table = torch.full((len(lens), max_blocks), -1, dtype=torch.int32)
+    row_entry, positions = [], []
+    for e, (p0, n) in enumerate(zip(pos0, lens)):
+        for blk in range(-(-(p0 + n) // ps)):
+            table[e, blk] = perm.pop()
+        row_entry += [e] * n
+        positions += list(range(p0, p0 + n))
+    cache = torch.zeros(n_pages, 2, n_kv_head, ps, hd, dtype=torch.bfloat16, device=DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    status = o.status_word()
+    done = o.linear_qkv(a.to(DEV), w.to(DEV), b.to(DEV), out, M, q_dim, cache, table.to(DEV),
+                        torch.tensor(row_entry, dtype=torch.int32, device=DEV),
+                        torch.tensor(positions, dtype=torch.int32, device=DEV), status)
+    if q_dim % 64:
+        assert not done and (out == 0).all() and (cache == 0).all()    # declined: nothing was written
+        return
+    assert done and int(status.item()) == 0
+    y = (a.double() @ w.double().T + b.double())
+    assert (out.cpu().double()[:, :q_dim] - y[:, :q_dim]).abs().max() < 3e-2
+    want = torch.zeros(n_pages, 2, n_kv_head, ps, hd, dtype=torch.float64)
+    for t in range(M):
+        page = int(table[row_entry[t], positions[t] // ps])
+        want[page, 0, :, positions[t] % ps] = y[t, q_dim:q_dim + kv_dim].view(n_kv_head, hd)
+        want[page, 1, :, positions[t] % ps] = y[t, q_dim + kv_dim:].view(n_kv_head, hd)
+    assert (cache.cpu().double() - want).abs().max() < 3e-2
+    assert (out.cpu()[:, q_dim:] == 0).all()            # key and value columns of the buffer are not written
