@@ -16,7 +16,7 @@ def engine(model_dir, dtype, **kw):
 
 @pytest.mark.parametrize("name", ["A", "B"])
 def test_greedy_generation_matches_the_plain_implementation(name, model_dirs):
-    """BASELINE's tiny workloads: A: prompts of 1, 7 and 33 tokens, 16 new tokens each;
+    """The tiny workloads: A: prompts of 1, 7 and 33 tokens, 16 new tokens each;
     B: prompts of 2, 5, 17 and 40, 20 new tokens, prompts cut into portions of 8 beside decodes."""
     import nanoinfer_b200 as nb
     from plain_gpt2 import PlainGPT2
