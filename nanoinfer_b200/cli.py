@@ -73,11 +73,12 @@ def cmd_generate(args) -> int:
     printed = 0
     while eng.has_work():
         eng.step()
-        if t_first is None and req.output:
-            t_first = time.perf_counter() - t0
-        for tok in req.output[printed:]:
-            print(tok, end=" ", flush=True)
-        printed = len(req.output)
+        # (the engine runs a step ahead of its reads: the newest entry may still be a negative stand-in)
+        while printed < len(req.output) and req.output[printed] >= 0:
+            if t_first is None:
+                t_first = time.perf_counter() - t0
+            print(req.output[printed], end=" ", flush=True)
+            printed += 1
     total = time.perf_counter() - t0
     print()
     n = len(req.output)

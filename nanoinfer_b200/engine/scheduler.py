@@ -46,6 +46,8 @@ class Request:
     id: int
     prompt: List[int]
     params: SamplingParams
+    #: generated tokens; while the engine runs a step ahead of its reads the newest may be a negative
+    #: stand-in (its value follows one step later); a finished request that was reported holds values only
     output: List[int] = field(default_factory=list)
     state: str = WAITING
     finish_reason: Optional[str] = None

@@ -189,3 +189,31 @@ def test_serving_benchmark_runs_both_policies_to_the_end(model_dirs):
     if s["preemptions"] == 0:   # every token but a request's last goes through the model once
         assert s["rows_computed"] == sum(len(r.prompt) + r.out_len - 1 for r in reqs)
     assert eng.cache.pages_used() == [0] and eng.cache.slots.n_free == 4
+
+
+def test_command_line_generate_prints_the_tokens_of_the_entry_point(model_dirs, capsys):
+    """``generate`` streams token ids as the host reads them; they are those of ``Engine.generate``,
+    greedy and sampled with the reference's option names."""
+    import nanoinfer_b200 as nb
+    from nanoinfer_b200 import cli
+    d = model_dirs("A", torch.float32)
+    prompt = random_tokens(512, 9, 123)
+    ids = ",".join(str(t) for t in prompt)
+    for extra, params in ((["--temperature", "0.0"], nb.SamplingParams(max_new_tokens=14, temperature=0.0)),
+                          (["--temperature", "0.9", "--top-k", "25", "--seed", "5"],
+                           nb.SamplingParams(max_new_tokens=14, temperature=0.9, top_k=25, seed=5))):
+        assert cli.main(["--weights", d, "generate", "--dtype", "float32", "--prompt-ids", ids, "--tokens", "14"]
+                        + extra) == 0
+        printed = [int(t) for t in capsys.readouterr().out.split()]
+        want = engine(d, "float32", max_batch=1, max_rows=64).generate([prompt], params)[0]
+        assert printed == want and len(printed) == 14 and all(t >= 0 for t in printed)
+
+
+def test_command_line_random_weights_writes_a_loadable_folder(tmp_path):
+    import nanoinfer_b200 as nb
+    from nanoinfer_b200 import cli
+    out = str(tmp_path / "m")
+    assert cli.main(["random-weights", "--config", "gpt2-tiny-b", "--seed", "3", "--out", out, "--dtype", "float32"]) == 0
+    eng = engine(out, "float32", max_batch=2, max_rows=32)
+    got = eng.generate([[1, 2, 3]], nb.SamplingParams(max_new_tokens=4, temperature=0.0))
+    assert len(got[0]) == 4
