@@ -361,6 +361,118 @@ def test_norm_embedding_mlp_and_head_parts_alone(dtype):
     assert (logits.cpu().double() - xn.cpu().double() @ wte.double().T).abs().max() < tol * 4
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_head, n_kv_head, hd, window", [(5, 5, 16, 0), (6, 2, 48, 0), (4, 1, 32, 20)])
+def test_attention_mixer_and_block_alone(dtype, n_head, n_kv_head, hd, window):
+    """The attention mixer alone, built through its registry with sizes of its own (grouped key/value
+    heads, a window): two steps over a hand-made cache, a prompt portion beside another request's single
+    token, then single tokens; and the pre-norm block around it and a feed-forward.  Against the plain
+    formulas on whole sequences."""
+    import plain_gpt2 as P
+    from nanoinfer_b200 import parts as NP
+    from nanoinfer_b200.parts.base import KVCacheView, StepContext, Workspace
+    dev = torch.device("cuda")
+    g = torch.Generator().manual_seed(n_head + hd)
+    C, ps, scale = 56, 16, 0.9 / math.sqrt(hd)
+    q_dim, kv_dim = n_head * hd, n_kv_head * hd
+    w_qkv = (torch.randn(q_dim + 2 * kv_dim, C, generator=g) * 0.2).to(dtype)
+    b_qkv = torch.randn(q_dim + 2 * kv_dim, generator=g) * 0.1
+    w_out = (torch.randn(C, q_dim, generator=g) * 0.2).to(dtype)
+    b_out = torch.randn(C, generator=g) * 0.1
+    mixer = NP.MIXERS.build("causal_attention", width=C, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd, scale=scale,
+                            window=window)
+    mixer.bind({"qkv_weight": w_qkv.to(dev), "qkv_bias": b_qkv.to(dev), "out_weight": w_out.to(dev),
+                "out_bias": b_out.to(dev)})
+    mixer.prepare(dtype, dev)
+    lens = [37, 9]                                       # two requests
+    xn_all = [(torch.randn(n, C, generator=g)).to(dtype) for n in lens]
+    x0_all = [torch.randn(n, C, generator=g) for n in lens]
+    # the plain result on whole sequences
+    want = []
+    for xn, x0 in zip(xn_all, x0_all):
+        qkv = xn.double() @ w_qkv.double().T + b_qkv.double()
+        att = P.causal_attention(qkv[:, :q_dim], qkv[:, q_dim:q_dim + kv_dim], qkv[:, q_dim + kv_dim:], n_head, n_kv_head,
+                                 scale=scale, window=window)
+        want.append(x0.double() + att @ w_out.double().T + b_out.double())
+    # the pre-norm block around the same mixer and a feed-forward: x += mixer(norm_1(x)); x += mlp(norm_2(x))
+    I = 88
+    g1, be1 = 1 + 0.1 * torch.randn(C, generator=g), 0.1 * torch.randn(C, generator=g)
+    g2, be2 = 1 + 0.1 * torch.randn(C, generator=g), 0.1 * torch.randn(C, generator=g)
+    w1, b1 = (torch.randn(I, C, generator=g) * 0.1).to(dtype), torch.randn(I, generator=g) * 0.1
+    w2, b2 = (torch.randn(C, I, generator=g) * 0.1).to(dtype), torch.randn(C, generator=g) * 0.1
+
+    def bind(part, **tensors):
+        part.bind({k: v.to(dev) for k, v in tensors.items()})
+        part.prepare(dtype, dev)
+        return part
+
+    def attention_part():
+        return bind(NP.MIXERS.build("causal_attention", width=C, n_head=n_head, n_kv_head=n_kv_head, head_dim=hd,
+                                    scale=scale, window=window),
+                    qkv_weight=w_qkv, qkv_bias=b_qkv, out_weight=w_out, out_bias=b_out)
+
+    block = NP.BLOCKS["pre_norm"](
+        C, bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g1, bias=be1), attention_part(),
+        bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g2, bias=be2),
+        bind(NP.FEED_FORWARDS.build("dense_mlp", width=C, inner=I, activation="tanh"),
+             fc_weight=w1, fc_bias=b1, proj_weight=w2, proj_bias=b2))
+    want_block = []
+    for x0 in x0_all:
+        x = x0.double()
+        xn = P.layernorm(x, g1.double(), be1.double(), 2e-5)
+        qkv = xn @ w_qkv.double().T + b_qkv.double()
+        att = P.causal_attention(qkv[:, :q_dim], qkv[:, q_dim:q_dim + kv_dim], qkv[:, q_dim + kv_dim:], n_head, n_kv_head,
+                                 scale=scale, window=window)
+        x = x + att @ w_out.double().T + b_out.double()
+        h = P.layernorm(x, g2.double(), be2.double(), 2e-5)
+        want_block.append(x + P.gelu_tanh(h @ w1.double().T + b1.double()) @ w2.double().T + b2.double())
+
+    ws = Workspace(dev)
+    table = torch.tensor([[5, 2, 7, -1], [3, 0, -1, -1]], dtype=torch.int32, device=dev)
+
+    def run(apply, want, tol, cuts):
+        layer = torch.zeros(8, 2, n_kv_head, ps, hd, dtype=dtype, device=dev)
+        for entries in cuts:                        # entries: (request, first row, rows)
+            rows = sum(n for _, _, n in entries)
+            starts = [0]
+            for _, _, n in entries:
+                starts.append(starts[-1] + n)
+            pos0 = [a for _, a, _ in entries]
+            ctx = StepContext(
+                n_rows=rows, n_entries=len(entries), max_rows=64,
+                tokens=torch.zeros(rows, dtype=torch.int32, device=dev),
+                positions=torch.tensor([a + i for _, a, n in entries for i in range(n)], dtype=torch.int32, device=dev),
+                row_entry=torch.tensor([e for e, (_, _, n) in enumerate(entries) for _ in range(n)], dtype=torch.int32,
+                                       device=dev),
+                entry_start=torch.tensor(starts, dtype=torch.int32, device=dev),
+                entry_pos0=torch.tensor(pos0, dtype=torch.int32, device=dev),
+                entry_slot=torch.arange(len(entries), dtype=torch.int32, device=dev),
+                status=torch.zeros(1, dtype=torch.int32, device=dev), workspace=ws,
+                host_entry_start=starts, host_entry_pos0=pos0, host_entry_slot=list(range(len(entries))),
+                max_q_len=max(n for _, _, n in entries), max_kv_len=max(a + n for _, a, n in entries))
+            x = torch.zeros(64, C, device=dev)
+            x[:rows] = torch.cat([x0_all[r][a:a + n] for r, a, n in entries]).to(dev)
+            view = KVCacheView(layer, torch.stack([table[r] for r, _, _ in entries]).contiguous(), ps, window)
+            apply(x, ctx, view, entries)
+            assert int(ctx.status.item()) == 0
+            at = 0
+            for r, a, n in entries:
+                assert (x[at:at + n].cpu().double() - want[r][a:a + n]).abs().max() < tol, (r, a, n)
+                at += n
+
+    # a prompt portion beside another request's single token; the other way round; then single tokens
+    cuts = [[(0, 0, 30), (1, 0, 1)], [(1, 1, 7), (0, 30, 1)], [(0, 31, 1), (1, 8, 1)]] + [[(0, i, 1)] for i in range(32, 37)]
+
+    def apply_mixer(x, ctx, view, entries):
+        xn = torch.zeros(64, C, dtype=dtype, device=dev)
+        xn[:ctx.n_rows] = torch.cat([xn_all[r][a:a + n] for r, a, n in entries]).to(dev)
+        mixer.forward(xn, x, ctx, view, None)
+
+    run(apply_mixer, want, 5e-5 if dtype == torch.float32 else 6e-2, cuts)
+    run(lambda x, ctx, view, entries: block.forward(x, ctx, view, None, True, dtype), want_block,
+        1e-4 if dtype == torch.float32 else 1e-1, cuts)
+
+
 def test_unsupported_sizes_are_refused_with_a_clear_error():
     from nanoinfer_b200 import parts as NP
     with pytest.raises(ValueError, match="head_dim"):
