@@ -26,15 +26,6 @@ constexpr int PF_KSPLIT = 2;  // warps that share a row group, each with a part 
 constexpr int PF_THREADS = 128 * PF_KSPLIT;
 constexpr int PF_WN = PF_BN / PF_KSPLIT;   // keys per warp and tile
 
-__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, bool valid) {
-  const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
-  const int n = valid ? 16 : 0;  // 0 bytes read: the 16 bytes are filled with zeros
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(gmem_src), "r"(n) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N> __device__ __forceinline__ void cp_async_wait() {
-  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
-}
 __device__ __forceinline__ void ldmatrix_x4(uint32_t* r, const void* p) {
   const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"

@@ -18,6 +18,10 @@
 //   * the write of keys and values into the paged cache for the fused q/k/v projection
 //     (batch.metal:155-164).
 // A row's result does not depend on the other rows: each (row, feature) sum has its own fixed order.
+#include <map>
+#include <mutex>
+#include <utility>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -212,11 +216,13 @@ linear_skinny_kernel(const SkinnyParams prm) {
       }
     }
   } else {
-    for (int i = threadIdx.x; i < M * n_chunks; i += blockDim.x) {
-      const int m = i / n_chunks, c = i - m * n_chunks;
-      *reinterpret_cast<uint4*>(xs + (size_t)m * ldx + c * 8) =
-          *reinterpret_cast<const uint4*>(prm.a + (size_t)m * prm.lda + k0 + c * 8);
-    }
+    // asynchronous copies: all of a thread's pieces are in flight at once (with 64 rows the rows are
+    // four times the block's weights, and a loop of loads and stores was a chain of round trips)
+    for (int m = warp; m < M; m += SK_WARPS)
+      for (int c = lane; c < n_chunks; c += 32)
+        cp_async16(xs + (size_t)m * ldx + c * 8, prm.a + (size_t)m * prm.lda + k0 + c * 8, true);
+    cp_async_commit();
+    cp_async_wait<0>();
   }
   __syncthreads();
 
@@ -389,7 +395,8 @@ static int skinny_split(int M, int N, int K, bool ln) {
   while (split < SK_MAX_SPLIT) {
     const int s2 = split * 2, kp = skinny_k_per(K, s2);
     if ((s2 - 1) * kp >= K) break;
-    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_TWO_PER_SM;
+    // (rows that leave room for one block per SM only are still better unsplit: measured at 64 rows)
+    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_LIMIT;
     if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 512)) break;
     split = s2;
   }
@@ -406,14 +413,7 @@ static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  // one wave: at most two blocks per SM (one when the rows take much shared memory), each cluster
-  // then walks several tiles with the rows in place
-  const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
-  int walkers = (prm.N + 15) / 16;
-  const int cap = per_sm * 148 / prm.split;
-  if (walkers > cap) walkers = cap;
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(walkers * prm.split);
   cfg.blockDim = dim3(SK_WARPS * 32);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -426,6 +426,36 @@ static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = prm.split > 1 ? 2 : 1;
+  // One wave: at most two blocks per SM (one when the rows take much shared memory), each cluster
+  // then walks several tiles with the rows in place.  How many clusters the device holds at once is
+  // asked of the runtime (a cluster's blocks share a GPC, so it is fewer than SMs / blocks): a
+  // cluster too many would wait for a whole wave to end.
+  const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
+  int cap = per_sm * 148;
+  if (prm.split > 1) {
+    static std::mutex mu;
+    static std::map<std::pair<int, size_t>, int> held;   // (blocks of a cluster, shared memory) -> clusters at once
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = held.find({prm.split, smem});
+    if (it == held.end()) {
+      int n = 0;
+      cfg.gridDim = dim3(prm.split * 148);
+      cudaLaunchConfig_t q = cfg;
+      q.attrs = attr + 1;      // the query takes the cluster shape only
+      q.numAttrs = 1;
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT>, &q);
+      if (e != cudaSuccess) return (int)e;
+      if (n < 1) return NIB_ERR_UNSUPPORTED_SIZE;
+      it = held.emplace(std::make_pair(prm.split, smem), n).first;
+    }
+    cap = it->second;
+    if (cap > per_sm * 148 / prm.split) cap = per_sm * 148 / prm.split;
+  }
+  // as few walkers as finish in the same number of rounds
+  const int n_tiles = (prm.N + 15) / 16;
+  const int rounds = (n_tiles + cap - 1) / cap;
+  const int walkers = (n_tiles + rounds - 1) / rounds;
+  cfg.gridDim = dim3(walkers * prm.split);
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
   if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();

@@ -431,9 +431,9 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
     K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
     normed rows and is not split here."""
     N, K = w.shape
-    # measured: up to 16 rows the MMA kernel wins everywhere; up to 32 everywhere but the widest
-    # outputs; up to 64 for small weights and for the projection that writes the cache
-    mma = M <= 16 or (M <= 32 and N <= 8192) or (M <= SKINNY_MAX_ROWS and (kv is not None or N * K <= (1 << 20)))
+    # measured: up to 16 rows the MMA kernel wins everywhere; up to 64 everywhere but the widest
+    # outputs (the head), where its 16-feature tiles read the rows too often
+    mma = M <= 16 or (M <= SKINNY_MAX_ROWS and N <= 8192)
     if mma:
         if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
             return True
