@@ -28,7 +28,12 @@ TINY_B = dict(architectures=["GPT2LMHeadModel"], vocab_size=1000, n_positions=64
 TINY_LONG = dict(architectures=["GPT2LMHeadModel"], vocab_size=320, n_positions=640, n_embd=96, n_layer=2, n_head=3,
                  n_inner=160, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
                  scale_attn_by_inverse_layer_idx=False)
-TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG}
+# GPT-2 small's layer sizes (width 768, 12 heads of 64, inner 3072, 1024 positions) with two layers and a
+# small vocabulary: the sizes at which the engine picks its tensor-memory kernels.
+WIDE = dict(architectures=["GPT2LMHeadModel"], vocab_size=2003, n_positions=1024, n_embd=768, n_layer=2, n_head=12,
+            n_inner=3072, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+            scale_attn_by_inverse_layer_idx=False)
+TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE}
 
 
 def sharpen_attention(tensors, factor):

@@ -122,3 +122,43 @@ def test_mixed_requests_with_few_pages(name, dtype, model_dirs, plain_logits, tm
     assert any(len(e) >= 3 and min(len(t) for _, t, _ in e) == 1 and max(len(t) for _, t, _ in e) > 1
                for e, _ in steps), "the plan must mix portions with single tokens"
     check(s, reqs, model_dir, plain_logits, TOL[dtype])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_small_layer_sizes_long_prompts_in_one_step(dtype, model_dirs, plain_logits, tmp_path):
+    """GPT-2 small's layer sizes: two long prompts in ONE step of 1700 rows (in bfloat16 that is the
+    step that runs the paired tensor-memory products, whose q/k/v epilogue writes the cache, and the
+    tensor-memory attention over several requests), a third request's prompt in portions beside
+    their decoded tokens, then single tokens up to the last position of the context.  Attention is
+    sharpened less than in the tiny models: 64-wide heads of a 768-wide model give larger scores."""
+    model_dir = model_dirs("WIDE", TORCH_DTYPE[dtype], sharpen=2.5)
+    vocab = TINY["WIDE"]["vocab_size"]
+    reqs = {"r0": random_tokens(vocab, 1024, 300), "r1": random_tokens(vocab, 733, 301),
+            "r2": random_tokens(vocab, 200, 302)}
+    s = TraceSession(model_dir, dtype, tmp_path / "wide", 1024 + 768 + 256, vocab)
+    want0 = [0, 1, 127, 128, 129, 500, 998, 999]
+    want1 = [0, 15, 16, 255, 256, 698, 699]
+    s.step([("r0", reqs["r0"][:1000], want0), ("r1", reqs["r1"][:700], want1)])
+    # a third prompt in portions (130, then 70) beside single tokens of the two
+    s.step([("r0", reqs["r0"][1000:1001], [0]), ("r2", reqs["r2"][:130], [0, 127, 129]),
+            ("r1", reqs["r1"][700:701], [0])])
+    s.step([("r2", reqs["r2"][130:], [0, 69]), ("r1", reqs["r1"][701:702], [0]), ("r0", reqs["r0"][1001:1002], [0])],
+           end=["r2"])
+    # a portion of 20 beside single tokens, then single tokens to the end (r0 ends at position 1023)
+    s.step([("r1", reqs["r1"][702:722], range(20)), ("r0", reqs["r0"][1002:1003], [0])])
+    for p in range(1003, 1024):
+        entries = [("r0", reqs["r0"][p:p + 1], [0])]
+        q = 722 + (p - 1003)
+        if q < 733:
+            entries.append(("r1", reqs["r1"][q:q + 1], [0]))
+        s.step(entries, end=(["r0"] if p == 1023 else []) + (["r1"] if q == 732 else []))
+    s.close()
+    worst = 0.0
+    for rid, toks in reqs.items():
+        ref = plain_logits(model_dir, toks)
+        for pos, row in s.logits[rid].items():
+            d = max_diff(row, ref[pos])
+            worst = max(worst, d)
+            assert d <= TOL[dtype], f"request {rid} position {pos}: max |logit difference| {d:.3e} > {TOL[dtype]}"
+    assert set(s.logits["r0"]) == set(want0) | set(range(1000, 1024))
+    assert set(s.logits["r1"]) == set(want1) | set(range(700, 733))
