@@ -33,7 +33,12 @@ TINY_LONG = dict(architectures=["GPT2LMHeadModel"], vocab_size=320, n_positions=
 WIDE = dict(architectures=["GPT2LMHeadModel"], vocab_size=2003, n_positions=1024, n_embd=768, n_layer=2, n_head=12,
             n_inner=3072, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
             scale_attn_by_inverse_layer_idx=False)
-TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE}
+# GPT-2 XL's layer sizes (width 1600, 25 heads of 64, inner 6400) with one layer: a width that is no
+# multiple of 128 or 256, an odd number of heads, rows too wide for the norm folded into the few-row product.
+XLW = dict(architectures=["GPT2LMHeadModel"], vocab_size=1501, n_positions=512, n_embd=1600, n_layer=1, n_head=25,
+           n_inner=6400, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+           scale_attn_by_inverse_layer_idx=False)
+TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE, "XLW": XLW}
 
 
 def sharpen_attention(tensors, factor):

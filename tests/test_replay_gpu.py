@@ -162,3 +162,29 @@ def test_small_layer_sizes_long_prompts_in_one_step(dtype, model_dirs, plain_log
             assert d <= TOL[dtype], f"request {rid} position {pos}: max |logit difference| {d:.3e} > {TOL[dtype]}"
     assert set(s.logits["r0"]) == set(want0) | set(range(1000, 1024))
     assert set(s.logits["r1"]) == set(want1) | set(range(700, 733))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_xl_layer_sizes(dtype, model_dirs, plain_logits, tmp_path):
+    """GPT-2 XL's layer sizes, one layer: four prompts of about 400 tokens in one step of 1600 rows,
+    then the four decode side by side."""
+    model_dir = model_dirs("XLW", TORCH_DTYPE[dtype], sharpen=2.0)
+    vocab = TINY["XLW"]["vocab_size"]
+    lens = [420, 407, 399, 412]
+    reqs = {f"r{i}": random_tokens(vocab, n, 400 + i) for i, n in enumerate(lens)}
+    first = [393, 400, 381, 396]                      # rows of the first step: 1570 in all
+    s = TraceSession(model_dir, dtype, tmp_path / "xl", 4 * 448, vocab)
+    s.step([(r, reqs[r][:n], [0, 1, 63, 64, n - 1]) for r, n in zip(reqs, first)])
+    at = dict(zip(reqs, first))
+    while at:
+        entries = [(r, reqs[r][p:p + 1], [0]) for r, p in at.items()]
+        ended = [r for r, p in at.items() if p + 1 == len(reqs[r])]
+        s.step(entries, end=ended)
+        at = {r: p + 1 for r, p in at.items() if r not in ended}
+    s.close()
+    for rid, toks in reqs.items():
+        ref = plain_logits(model_dir, toks)
+        for pos, row in s.logits[rid].items():
+            d = max_diff(row, ref[pos])
+            assert d <= TOL[dtype], f"request {rid} position {pos}: max |logit difference| {d:.3e} > {TOL[dtype]}"
+        assert len(s.logits[rid]) == 5 + len(toks) - first[int(rid[1:])]
