@@ -48,6 +48,7 @@ struct SkinnyParams {
   int ldo, out_f32, residual, act;
   int M, N, K;
   int split, k_per;     // blocks of a cluster and the slice of K that each takes (a multiple of 32)
+  int alias;            // 1: every block has one tile, and the warps' sums take the place of the rows
   // optional: features from kv_q_dim on go to the paged cache
   bf16* kv_cache;
   const int* kv_block_table;
@@ -92,8 +93,13 @@ linear_skinny_kernel(const SkinnyParams prm) {
   const int n_chunks = Ks >> 3;                        // 16-byte pieces per row of the slice
   const int ldx = skinny_ldx(prm.k_per);               // padded row: pieces of 8 rows x 4 lanes hit distinct banks
   bf16* xs = reinterpret_cast<bf16*>(sk_smem);         // [NT * 8][ldx] the step's rows (rows >= M are zeros)
-  float* red = reinterpret_cast<float*>(sk_smem + (size_t)NT * 8 * ldx * sizeof(bf16));  // [warps][NT][32][4]
-  float* xch = red + SK_WARPS * NT * 128;              // [2][split][rows of a block][16] sums of the other blocks
+  // [warps][NT][32][4] the warps' partial sums: behind the rows, or (prm.alias: a block with one tile
+  // only, whose rows are used up by then) in their place
+  const size_t xs_bytes = (size_t)NT * 8 * ldx * sizeof(bf16), red_bytes = (size_t)SK_WARPS * NT * 128 * sizeof(float);
+  float* red = reinterpret_cast<float*>(sk_smem + (prm.alias ? 0 : xs_bytes));
+  // [2][split][rows of a block][16] sums of the other blocks
+  float* xch = reinterpret_cast<float*>(sk_smem + (prm.alias ? (xs_bytes > red_bytes ? xs_bytes : red_bytes)
+                                                             : xs_bytes + red_bytes));
   float* ln_gb = xch + 2 * NT * 128;                   // [2][K] the norm's scale and shift
   const int n_tiles = (prm.N + 15) / 16;
   const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of the slice
@@ -375,9 +381,10 @@ linear_skinny_kernel(const SkinnyParams prm) {
 
 static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)); }
 
-static size_t skinny_smem(int NT, int k_per, int K, bool ln) {
-  return (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16) + (size_t)SK_WARPS * NT * 128 * sizeof(float) +
-         (size_t)2 * NT * 128 * sizeof(float) + (ln ? (size_t)2 * K * sizeof(float) : 0);
+static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool alias = false) {
+  const size_t xs = (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16), red = (size_t)SK_WARPS * NT * 128 * sizeof(float);
+  return (alias ? (xs > red ? xs : red) : xs + red) + (size_t)2 * NT * 128 * sizeof(float) +
+         (ln ? (size_t)2 * K * sizeof(float) : 0);
 }
 
 constexpr size_t SK_SMEM_LIMIT = 200 * 1024;
@@ -404,8 +411,7 @@ static int skinny_split(int M, int N, int K, bool ln) {
 }
 
 template <int NT>
-static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
-  const size_t smem = skinny_smem(NT, prm.k_per, prm.K, prm.ln_x != nullptr);
+static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -415,7 +421,6 @@ static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg = {};
   cfg.blockDim = dim3(SK_WARPS * 32);
-  cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -430,31 +435,47 @@ static int launch_skinny(const SkinnyParams& prm, cudaStream_t stream) {
   // then walks several tiles with the rows in place.  How many clusters the device holds at once is
   // asked of the runtime (a cluster's blocks share a GPC, so it is fewer than SMs / blocks): a
   // cluster too many would wait for a whole wave to end.
-  const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
-  int cap = per_sm * 148;
-  if (prm.split > 1) {
+  int err = 0;
+  auto clusters_at_once = [&](size_t smem) {
+    const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
+    if (prm.split == 1) return per_sm * 148;
     static std::mutex mu;
     static std::map<std::pair<int, size_t>, int> held;   // (blocks of a cluster, shared memory) -> clusters at once
     std::lock_guard<std::mutex> lock(mu);
     auto it = held.find({prm.split, smem});
     if (it == held.end()) {
       int n = 0;
-      cfg.gridDim = dim3(prm.split * 148);
       cudaLaunchConfig_t q = cfg;
+      q.gridDim = dim3(prm.split * 148);
+      q.dynamicSmemBytes = smem;
       q.attrs = attr + 1;      // the query takes the cluster shape only
       q.numAttrs = 1;
       cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT>, &q);
-      if (e != cudaSuccess) return (int)e;
-      if (n < 1) return NIB_ERR_UNSUPPORTED_SIZE;
+      if (e != cudaSuccess) { err = (int)e; return 0; }
+      if (n < 1) { err = NIB_ERR_UNSUPPORTED_SIZE; return 0; }
       it = held.emplace(std::make_pair(prm.split, smem), n).first;
     }
-    cap = it->second;
-    if (cap > per_sm * 148 / prm.split) cap = per_sm * 148 / prm.split;
+    const int cap = it->second;
+    return cap < per_sm * 148 / prm.split ? cap : per_sm * 148 / prm.split;
+  };
+  const int n_tiles = (prm.N + 15) / 16;
+  const bool ln = prm.ln_x != nullptr;
+  size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln);
+  int cap = clusters_at_once(smem);
+  if (err) return err;
+  prm.alias = 0;
+  if (n_tiles > cap) {
+    // More tiles than one wave of blocks: if a block has one tile only, its warps' sums can lie where
+    // the rows were, and the smaller blocks may all fit at once.
+    const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, true);
+    const int cap_one = smem_one < smem ? clusters_at_once(smem_one) : 0;
+    if (err) return err;
+    if (n_tiles <= cap_one) { prm.alias = 1; smem = smem_one; cap = cap_one; }
   }
   // as few walkers as finish in the same number of rounds
-  const int n_tiles = (prm.N + 15) / 16;
   const int rounds = (n_tiles + cap - 1) / cap;
   const int walkers = (n_tiles + rounds - 1) / rounds;
+  cfg.dynamicSmemBytes = smem;
   cfg.gridDim = dim3(walkers * prm.split);
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
   if (e != cudaSuccess) return (int)e;
