@@ -290,6 +290,7 @@ class ModelRunner:
                    plan.max_decode_keys, id(sampler))
         cap = self._graphs.get(key) if key is not None else None
         if cap is not None:
+            self._graphs[key] = self._graphs.pop(key)   # most recently used last
             cap.graph.replay()
             self.graph_replays += 1
             logits, tokens = cap.logits, cap.tokens
@@ -297,8 +298,11 @@ class ModelRunner:
         else:
             args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv, sampler)
             n_seen = self._seen.get(key, 0) if key is not None else 0
-            if key is not None and n_seen >= 1 and len(self._graphs) < self.max_graphs:
-                # the shape was run once already (scratch is sized, attributes are set): capture it
+            if key is not None and n_seen >= 1:
+                # the shape was run once already (scratch is sized, attributes are set): capture it,
+                # in place of the graph that has not been used for the longest time if the table is full
+                while len(self._graphs) >= self.max_graphs:
+                    del self._graphs[next(iter(self._graphs))]
                 graph = torch.cuda.CUDAGraph()
                 before = ops.launch_count()
                 # Nothing but kernel launches happens while capturing, but the garbage collector may
@@ -322,6 +326,8 @@ class ModelRunner:
                 logits, tokens = self._run(*args, M, sampler)
                 self.launches_last_step = ops.launch_count() - before
                 if key is not None:
+                    if len(self._seen) >= 64 * self.max_graphs:   # shapes that never came back
+                        self._seen.clear()
                     self._seen[key] = n_seen + 1
 
         for it in items:

@@ -101,6 +101,34 @@ def test_step_refuses_bad_input_and_changes_nothing(model_dirs):
         r2.step([StepItem(c, [1] * 129, [])])
 
 
+def test_graph_table_keeps_the_most_recently_used_shapes(model_dirs):
+    """A table of two graphs under steps of three shapes by turns: old graphs make room, every step
+    gives the logits that the step function gives without graphs."""
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    m = load_model(model_dirs("A", torch.float32), torch.float32, "cuda")
+
+    def run(use_graphs):
+        cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=3 * 64, max_requests=3, page_size=16,
+                             dtype=torch.float32, device=torch.device("cuda"), max_positions=m.max_positions)
+        runner = ModelRunner(m, cache, max_rows=64, max_entries=3, use_graphs=use_graphs, max_graphs=2)
+        reqs = [cache.open_request() for _ in range(3)]
+        for i, r in enumerate(reqs):
+            runner.step([StepItem(r, random_tokens(512, 5 + 3 * i, 60 + i), [])])
+        out = []
+        for turn in range(18):
+            live = reqs[:turn % 3 + 1]               # one, two, three rows, and again
+            out.append(runner.step([StepItem(r, [(7 * turn + 3 * i) % 512], [0]) for i, r in enumerate(live)]).cpu().clone())
+        return out, runner
+
+    plain, _ = run(False)
+    got, runner = run(True)
+    assert len(runner._graphs) == 2 and runner.graph_replays >= 6
+    for a, b in zip(plain, got):
+        assert torch.equal(a, b)
+
+
 def test_sampling_with_seeds_is_reproducible_and_independent_of_the_batch(model_dirs):
     import nanoinfer_b200 as nb
     d = model_dirs("A", torch.float32, sharpen=0.0)
