@@ -116,8 +116,11 @@ class RequestCache:
 class StateSlots:
     """Per-request state of fixed size: ``n_slots`` rows in every registered tensor."""
 
-    def __init__(self, n_slots: int, device: Optional[torch.device]):
+    def __init__(self, n_slots: int, device: Optional[torch.device], spare: int = 0):
+        """``spare``: rows beyond the slots in every tensor, never handed out (rows that pad a step
+        to the shape of a captured graph point there)."""
         self.n_slots = int(n_slots)
+        self.spare = int(spare)
         self.device = device
         self._free: List[int] = list(range(self.n_slots - 1, -1, -1))
         self._held = [False] * self.n_slots
@@ -127,7 +130,7 @@ class StateSlots:
         """A zeroed tensor [n_slots, *shape] addressed by slot; None when there is no device."""
         if self.device is None:
             return None
-        t = torch.zeros((self.n_slots, *shape), dtype=dtype, device=self.device)
+        t = torch.zeros((self.n_slots + self.spare, *shape), dtype=dtype, device=self.device)
         self.tensors[key] = t
         return t
 
@@ -165,10 +168,14 @@ class CacheManager:
     def __init__(self, kv_needs: Sequence[Tuple[int, KVCacheSpec]], state_needs: Sequence[Tuple[int, StateSpec]],
                  max_tokens: int, max_requests: int, page_size: int = 16,
                  dtype: torch.dtype = torch.float32, device: Optional[torch.device] = None,
-                 max_positions: Optional[int] = None, pages_per_group: Optional[Sequence[int]] = None):
+                 max_positions: Optional[int] = None, pages_per_group: Optional[Sequence[int]] = None,
+                 padding: bool = False):
         """``max_tokens``: how many tokens live requests may hold together, each request's count
         rounded up to whole pages; every group's pool gets ``ceil(max_tokens / page_size)`` pages
-        unless ``pages_per_group`` says otherwise.  ``device`` None: bookkeeping only."""
+        unless ``pages_per_group`` says otherwise.  ``device`` None: bookkeeping only.
+        ``padding``: one page per group and one state slot more than the pools hand out
+        (``pad_page``, ``pad_slot``): the step function points the rows there with which it pads a
+        batch of single tokens to the shape of a captured graph.  No request ever holds them."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = int(page_size)
@@ -184,11 +191,13 @@ class CacheManager:
             group = CacheGroup(spec, owners, self.page_size, PagePool(n_pages))
             if device is not None:
                 group.tensor = torch.zeros(
-                    (len(owners), n_pages, 2, spec.n_kv_head, self.page_size, spec.head_dim),
+                    (len(owners), n_pages + (1 if padding else 0), 2, spec.n_kv_head, self.page_size, spec.head_dim),
                     dtype=dtype, device=device)
             self.groups.append(group)
         self._group_of: Dict[int, int] = {idx: gi for gi, g in enumerate(self.groups) for idx in g.owners}
-        self.slots = StateSlots(max_requests, device)
+        self.pad_page: Optional[List[int]] = [g.pool.n_pages for g in self.groups] if padding else None
+        self.pad_slot: Optional[int] = int(max_requests) if padding else None
+        self.slots = StateSlots(max_requests, device, spare=1 if padding else 0)
         self.state_tensors: Dict[int, torch.Tensor] = {}
         for idx, spec in state_needs:
             t = self.slots.register(("state", idx), tuple(spec.shape), spec.dtype)

@@ -42,7 +42,7 @@ class Engine:
             max_tokens = max_batch * (limit if limit is not None else 2048)
         self.cache = CacheManager(self.model.kv_needs(), self.model.state_needs(), max_tokens=max_tokens,
                                   max_requests=max_batch, page_size=page_size, dtype=dtype, device=self.device,
-                                  max_positions=limit)
+                                  max_positions=limit, padding=True)
         self.runner = ModelRunner(self.model, self.cache, max_rows=max_rows, max_entries=max_batch,
                                   check_status=check_status, use_graphs=use_graphs)
         self.sampler = Sampler(self.cache.slots)

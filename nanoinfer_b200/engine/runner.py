@@ -91,6 +91,8 @@ class _Captured:
 
 #: decode graphs are shaped by the longest key range rounded up to this many positions
 GRAPH_KEY_BUCKET = 256
+#: batches of more than PAD_FROM single tokens are padded to a multiple of PAD_TO rows
+PAD_FROM, PAD_TO = 8, 8
 
 
 class ModelRunner:
@@ -125,6 +127,7 @@ class ModelRunner:
         self._seen: Dict[tuple, int] = {}
         self.steps_run = 0
         self.graph_replays = 0
+        self.padded_steps = 0
         self.last_meta_bytes = 0
         self.last_logit_slot = None
         #: kernel launches of the last step (counted by the kernel interface)
@@ -227,18 +230,32 @@ class ModelRunner:
             copied.synchronize()  # returns at once unless the GPU is four steps behind
 
         want_rows: List[int] = []
+        n_pad = 0
         if decode_only:
             pos0s = [it.request.n_tokens for it in items]
-            starts = self._arange[:E + 1].tolist()
             slots = [it.request.slot for it in items]
             want_rows = [e for e, it in enumerate(items) if len(it.want)]
+            tokens_in = [it.tokens[0] for it in items]
+            # A batch of more than PAD_FROM single tokens, all wanted, is filled up to the next multiple
+            # of PAD_TO with rows of a request that is none: token 0 at position 0, key and value
+            # into the cache's spare page, state in its spare slot.  Batches that shrink and grow by
+            # a request then share a graph instead of each running uncaptured, then being captured.
+            if (self.use_graphs and self.cache.pad_slot is not None and E > PAD_FROM and len(want_rows) == E):
+                n_pad = min(-(-E // PAD_TO) * PAD_TO, self.max_entries) - E
+                tokens_in += [0] * n_pad
+                pos0s += [0] * n_pad
+                slots += [self.cache.pad_slot] * n_pad
+                want_rows += range(E, E + n_pad)
+                E = T = E + n_pad
+                self.padded_steps += 1 if n_pad else 0
+            starts = self._arange[:E + 1].tolist()
             M = len(want_rows)
             max_q, max_kv = 1, max(pos0s) + 1
             plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
             if self.use_graphs:  # the split of the keys must not change from step to step of a graph
                 plan.max_decode_keys = -(-plan.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
             lay = self._layout(T, E, M, len(plan.host))
-            buf[lay.tok:lay.tok + T] = [it.tokens[0] for it in items]
+            buf[lay.tok:lay.tok + T] = tokens_in
             buf[lay.pos:lay.pos + T] = pos0s
             buf[lay.ent:lay.ent + T] = self._arange[:E]
             buf[lay.lrow:lay.lrow + M] = want_rows
@@ -276,6 +293,9 @@ class ModelRunner:
             tab = buf[off:off + E * mb].reshape(E, mb)
             for e, it in enumerate(items):
                 tab[e] = it.request.table_rows[gi]
+            if n_pad:
+                tab[E - n_pad:] = -1
+                tab[E - n_pad:, 0] = self.cache.pad_page[gi]
         self.last_meta_bytes = 4 * lay.total
         self._meta_dev[:lay.total].copy_(host[:lay.total], non_blocking=True)
         if copied is not None:
@@ -298,9 +318,12 @@ class ModelRunner:
         else:
             args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv, sampler)
             n_seen = self._seen.get(key, 0) if key is not None else 0
-            if key is not None and n_seen >= 1:
-                # the shape was run once already (scratch is sized, attributes are set): capture it,
-                # in place of the graph that has not been used for the longest time if the table is full
+            # A shape that was run already (scratch is sized, attributes are set) is captured: a batch
+            # of single tokens the second time it comes, since it will come again step after step; a
+            # step with prompt portions the fourth time only (most such shapes of a serving mix come
+            # once or twice, and a capture costs about two uncaptured steps).  The new graph takes the
+            # place of the one that has not been used for the longest time if the table is full.
+            if key is not None and n_seen >= (1 if decode_only else 3):
                 while len(self._graphs) >= self.max_graphs:
                     del self._graphs[next(iter(self._graphs))]
                 graph = torch.cuda.CUDAGraph()
@@ -335,7 +358,8 @@ class ModelRunner:
         self.steps_run += 1
         if self.check_status:
             self.raise_on_status()
-        return tokens if sampler is not None else logits
+        out = tokens if sampler is not None else logits
+        return out[:M - n_pad] if n_pad and out is not None else out
 
     def raise_on_status(self) -> None:
         """Read the device status word (this waits for the step) and raise if a kernel flagged a fault."""

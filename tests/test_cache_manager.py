@@ -167,3 +167,26 @@ def test_random_orders_keep_every_page_accounted_for(seed):
         m.close_request(r)
     assert all(g.pool.n_free == g.pool.n_pages for g in m.groups) and m.slots.n_free == 4
     assert total == m.groups[0].pool.n_pages
+
+
+def test_padding_page_and_slot_lie_outside_the_pools():
+    """With ``padding`` the cache has one page per group and one state slot that no request can get."""
+    import torch
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.parts.base import KVCacheSpec
+    needs = [(0, KVCacheSpec(2, 16, 0)), (1, KVCacheSpec(2, 16, 8))]
+    c = CacheManager(needs, [], max_tokens=64, max_requests=3, page_size=16, dtype=torch.float32,
+                     device=torch.device("cpu"), padding=True)
+    assert c.pad_slot == 3 and c.pad_page == [4, 4]
+    assert [g.tensor.shape[1] for g in c.groups] == [5, 5]
+    reqs = [c.open_request() for _ in range(3)]
+    assert sorted(r.slot for r in reqs) == [0, 1, 2]
+    c.append([(reqs[0], 33), (reqs[1], 16)])
+    for r in reqs[:2]:
+        c.commit(r, 33 if r is reqs[0] else 16)
+    held = {p for r in reqs for blocks in r.blocks for p in blocks}
+    assert 4 not in held and c.pages_free()[0] == 0
+    c.check()
+    plain = CacheManager(needs, [], max_tokens=64, max_requests=3, page_size=16, dtype=torch.float32,
+                         device=torch.device("cpu"))
+    assert plain.pad_slot is None and plain.pad_page is None and plain.groups[0].tensor.shape[1] == 4

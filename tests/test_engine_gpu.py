@@ -129,6 +129,48 @@ def test_graph_table_keeps_the_most_recently_used_shapes(model_dirs):
         assert torch.equal(a, b)
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_batches_padded_to_a_graph_shape_give_the_same_logits(dtype, model_dirs, plain_logits):
+    """Eleven, then ten, then nine requests decode side by side: the step function fills the batch
+    up to sixteen rows with rows of no request (so that the three sizes share one graph); the real
+    rows' logits are those of the plain implementation, and of a step function that does not pad."""
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    d = model_dirs("B", dtype)
+    m = load_model(d, dtype, "cuda")
+    prompts = [random_tokens(1000, 3 + 2 * i, 80 + i) for i in range(11)]
+    more = [random_tokens(1000, 12, 95 + i) for i in range(11)]
+
+    def run(padding):
+        cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=11 * 48, max_requests=11, page_size=16,
+                             dtype=dtype, device=torch.device("cuda"), max_positions=m.max_positions, padding=padding)
+        runner = ModelRunner(m, cache, max_rows=64, max_entries=16)
+        reqs = [cache.open_request() for _ in range(11)]
+        for r, p in zip(reqs, prompts):
+            runner.step([StepItem(r, p, [])])
+        rows = {i: [] for i in range(11)}
+        for t in range(12):
+            live = range(11 - t // 4)                         # 11, 10, then 9 rows
+            out = runner.step([StepItem(reqs[i], [more[i][t]], [0]) for i in live])
+            assert out.shape[0] == len(live)
+            for k, i in enumerate(live):
+                rows[i].append(out[k].float().cpu().clone())
+        cache.check()
+        return rows, runner
+
+    padded, runner = run(True)
+    exact, runner_exact = run(False)
+    assert runner.padded_steps == 12 and runner_exact.padded_steps == 0
+    assert runner.graph_replays >= 10 and len(runner._graphs) == 1
+    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    for i in range(11):
+        ref = plain_logits(d, prompts[i] + more[i])
+        for t, (a, b) in enumerate(zip(padded[i], exact[i])):
+            assert (a - ref[len(prompts[i]) + t]).abs().max() <= tol
+            assert (a - b).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
 def test_sampling_with_seeds_is_reproducible_and_independent_of_the_batch(model_dirs):
     import nanoinfer_b200 as nb
     d = model_dirs("A", torch.float32, sharpen=0.0)
