@@ -79,61 +79,167 @@ __global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ l
   if (threadIdx.x == 0) out[r] = best;
 }
 
+constexpr int SEL_BINS = 1024;        // coarse bins of the first pass
+constexpr float SEL_SPAN = 24.0f;     // e^-24 * 2^32 < 1: a token that far below the maximum has no mass
+constexpr int SEL_LIST = 2048;        // tokens of the chosen bin that are listed in shared memory
+
 struct SelectShared {
   unsigned long long hist[256];
+  uint32_t lo[SEL_BINS], hi[SEL_BINS];   // the coarse histogram, 64-bit sums in two halves
+  uint32_t list_key[SEL_LIST];           // the chosen bin's tokens: their keys ...
+  int list_idx[SEL_LIST];                // ... and indices (in no particular order)
+  int n_list;                            // how many the bin has (the lists hold the first SEL_LIST)
   unsigned long long target;
   unsigned long long total;
   uint32_t digit;
+  int bin;
   int count;
   int first;
 };
 
-// One radix select.  MASS = false: weights are 1 and `target` is a rank (1-based, from the
-// top).  MASS = true: weights are probability masses; elements with key <= thresh are left
-// out except that `tie_mass` is added for the key `thresh` itself, and the target is
-// u24 * total >> 24 (at least 1), computed from the first histogram.
+// The coarse bin of a scaled logit: bin 0 holds the maximum, the bins go down in steps of
+// SEL_SPAN / (SEL_BINS - 1), the last bin holds everything further down (and NaNs).  Every step of
+// the mapping is monotone, so all of a bin's tokens are larger than all of the next bin's.
+__device__ __forceinline__ int coarse_bin(float s, float mx) {
+  const float t = (mx - s) * ((float)(SEL_BINS - 1) / SEL_SPAN);
+  return t < (float)(SEL_BINS - 1) ? (int)t : SEL_BINS - 1;
+}
+
+// One select.  MASS = false: weights are 1 and `target` is a rank (1-based, from the top).
+// MASS = true: weights are probability masses; elements with key <= thresh are left out except that
+// `tie_mass` is added for the key `thresh` itself, and the target is u24 * total >> 24 (at least 1).
+//
+// A radix select over the keys' bytes alone would start with the byte that holds the sign and most
+// of the exponent, where logits crowd into a handful of values: fifty thousand atomic adds on a few
+// shared words (64-bit ones are compare-and-swap loops) took most of a millisecond.  So the first
+// pass sorts the tokens into SEL_BINS bins that are linear in the distance from the maximum, where
+// they spread out, with native 32-bit atomic adds (a 64-bit sum is kept as two halves with a carry;
+// integer sums do not depend on the order of the additions).  A warp finds the bin in which the
+// target falls; one more pass lists that bin's tokens (a few dozen to a few hundred) in shared
+// memory, and the four byte passes settle the exact key among the listed ones.  A bin with more
+// than SEL_LIST tokens (logits that are nearly all alike) is not listed: the byte passes then walk
+// the whole row as the first pass does.
 template <bool MASS>
 __device__ void radix_select(const float* __restrict__ row, int V, float temperature, float mx,
                              bool use_thresh, uint32_t thresh, unsigned long long tie_mass,
                              unsigned long long target, uint32_t u24, SelectShared& sh,
                              uint32_t& key_out, unsigned long long& resid_out) {
+  const int thresh_bin = (MASS && use_thresh) ? coarse_bin(key_float(thresh), mx) : -1;
+  for (int i = threadIdx.x; i < SEL_BINS; i += blockDim.x) sh.lo[i] = sh.hi[i] = 0u;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = row[i] / temperature;
+    if (MASS) {
+      if (use_thresh && float_key(s) <= thresh) continue;
+      const unsigned long long w = mass_of(s, mx);
+      const uint32_t wl = (uint32_t)w, wh = (uint32_t)(w >> 32);
+      const int b = coarse_bin(s, mx);
+      if (wl) {
+        const uint32_t old = atomicAdd(&sh.lo[b], wl);
+        if (old + wl < old) atomicAdd(&sh.hi[b], 1u);
+      }
+      if (wh) atomicAdd(&sh.hi[b], wh);
+    } else {
+      atomicAdd(&sh.lo[coarse_bin(s, mx)], 1u);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    constexpr int PER = SEL_BINS / 32;
+    if (MASS && use_thresh && thresh_bin / PER == lane) {   // the kept ties of the threshold key
+      const unsigned long long v = (((unsigned long long)sh.hi[thresh_bin] << 32) | sh.lo[thresh_bin]) + tie_mass;
+      sh.lo[thresh_bin] = (uint32_t)v;
+      sh.hi[thresh_bin] = (uint32_t)(v >> 32);
+    }
+    unsigned long long mine = 0ull;
+    for (int b = lane * PER; b < (lane + 1) * PER; ++b) mine += ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
+    unsigned long long incl = mine;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+      if (lane >= o) incl += up;
+    }
+    const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
+    unsigned long long tgt = target;
+    if (MASS) {
+      // (u24 * total) >> 24 without overflow: total < 2^49
+      const unsigned long long hi = __umul64hi((unsigned long long)u24, total);
+      const unsigned long long lo = (unsigned long long)u24 * total;
+      tgt = (hi << 40) | (lo >> 24);
+      if (tgt < 1ull) tgt = 1ull;
+    }
+    const uint32_t reached = __ballot_sync(0xffffffffu, incl >= tgt);
+    const int owner = reached ? __ffs(reached) - 1 : 31;
+    if (lane == owner) {
+      unsigned long long cum = incl - mine;
+      int b = lane * PER;
+      for (; b < (lane + 1) * PER - 1; ++b) {
+        const unsigned long long h = ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
+        if (cum + h >= tgt) break;
+        cum += h;
+      }
+      sh.bin = b;
+      sh.target = tgt - cum;
+      sh.total = total;
+    }
+  }
+  __syncthreads();
+  const int bin = sh.bin;
+  target = sh.target;
+  if (threadIdx.x == 0) sh.n_list = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    const float s = row[i] / temperature;
+    if (coarse_bin(s, mx) != bin) continue;
+    const uint32_t key = float_key(s);
+    if (MASS && use_thresh && key <= thresh) continue;
+    const int at = atomicAdd(&sh.n_list, 1);
+    if (at < SEL_LIST) {
+      sh.list_key[at] = key;
+      sh.list_idx[at] = i;
+    }
+  }
+  __syncthreads();
+  const int n_list = sh.n_list;
+  const bool listed = n_list <= SEL_LIST;
+
   uint32_t prefix = 0, mask = 0;
   for (int shift = 24; shift >= 0; shift -= 8) {
     for (int i = threadIdx.x; i < 256; i += blockDim.x) sh.hist[i] = 0ull;
     __syncthreads();
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
-      const float s = row[i] / temperature;
-      const uint32_t key = float_key(s);
-      if ((key & mask) != prefix) continue;
-      unsigned long long w = 1ull;
-      if (MASS) {
-        if (use_thresh && key <= thresh) continue;
-        w = mass_of(s, mx);
+    if (listed) {
+      for (int j = threadIdx.x; j < n_list; j += blockDim.x) {
+        const uint32_t key = sh.list_key[j];
+        if ((key & mask) != prefix) continue;
+        atomicAdd(&sh.hist[(key >> shift) & 255u], MASS ? mass_of(key_float(key), mx) : 1ull);
       }
-      atomicAdd(&sh.hist[(key >> shift) & 255u], w);
+    } else {
+      for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float s = row[i] / temperature;
+        if (coarse_bin(s, mx) != bin) continue;
+        const uint32_t key = float_key(s);
+        if ((key & mask) != prefix) continue;
+        unsigned long long w = 1ull;
+        if (MASS) {
+          if (use_thresh && key <= thresh) continue;
+          w = mass_of(s, mx);
+        }
+        atomicAdd(&sh.hist[(key >> shift) & 255u], w);
+      }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-      if (MASS && use_thresh && (thresh & mask) == prefix) sh.hist[(thresh >> shift) & 255u] += tie_mass;
-      unsigned long long tgt = target;
-      if (MASS && shift == 24) {
-        unsigned long long total = 0ull;
-        for (int d = 0; d < 256; ++d) total += sh.hist[d];
-        // (u24 * total) >> 24 without overflow: total < 2^49
-        const unsigned long long hi = __umul64hi((unsigned long long)u24, total);
-        const unsigned long long lo = (unsigned long long)u24 * total;
-        tgt = (hi << 40) | (lo >> 24);
-        if (tgt < 1ull) tgt = 1ull;
-        sh.total = total;
-      }
+      if (MASS && use_thresh && thresh_bin == bin && (thresh & mask) == prefix)
+        sh.hist[(thresh >> shift) & 255u] += tie_mass;
       unsigned long long cum = 0ull;
       int d = 255;
       for (; d > 0; --d) {
-        if (cum + sh.hist[d] >= tgt) break;
+        if (cum + sh.hist[d] >= target) break;
         cum += sh.hist[d];
       }
       sh.digit = (uint32_t)d;
-      sh.target = tgt - cum;
+      sh.target = target - cum;
     }
     __syncthreads();
     prefix |= sh.digit << shift;
@@ -151,7 +257,7 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
 // to the lowest index), and the block that arrives last writes the token and clears the words.
 // A sampled row is the work of block 0 of its row alone.  `scratch` holds 2 words per row
 // (the folded maximum and the arrival count), zero between launches.
-__global__ void __launch_bounds__(SAMPLE_THREADS)
+__global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               unsigned long long* __restrict__ rng_state, int* __restrict__ out,
@@ -225,10 +331,22 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
     sh.first = 0x7fffffff;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    if (float_key(row[i] / temp) == key) {
-      atomicAdd(&sh.count, 1);
-      atomicMin(&sh.first, i);
+  // (the last select's list holds every token of the chosen key's bin, unless it was too long;
+  // a threshold key's own tokens are not in it: they are left out of the masses and re-enter as ties)
+  const bool from_list = sh.n_list <= SEL_LIST && !(use_thresh && key == thresh);
+  if (from_list) {
+    for (int j = threadIdx.x; j < sh.n_list; j += blockDim.x) {
+      if (sh.list_key[j] == key) {
+        atomicAdd(&sh.count, 1);
+        atomicMin(&sh.first, sh.list_idx[j]);
+      }
+    }
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+      if (float_key(row[i] / temp) == key) {
+        atomicAdd(&sh.count, 1);
+        atomicMin(&sh.first, i);
+      }
     }
   }
   __syncthreads();
@@ -240,7 +358,14 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
     if (n < 1) n = 1;
     if (n > c) n = c;
     int tok = sh.first;
-    if (n > 1) {
+    if (n > 1 && from_list) {        // the n-th lowest index among the listed tokens of the key
+      for (long long seen = 1; seen < n; ++seen) {
+        int next = 0x7fffffff;
+        for (int j = 0; j < sh.n_list; ++j)
+          if (sh.list_key[j] == key && sh.list_idx[j] > tok && sh.list_idx[j] < next) next = sh.list_idx[j];
+        tok = next;
+      }
+    } else if (n > 1) {
       long long seen = 0;
       for (int i = 0; i < V; ++i) {
         if (float_key(row[i] / temp) == key && ++seen == n) {
