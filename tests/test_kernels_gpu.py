@@ -275,27 +275,30 @@ def test_argmax_ties_and_odd_vocabulary():
 @pytest.mark.parametrize("V", [1000, 50257])
 def test_sampling_follows_the_reference_walk(V):
     o = ops()
-    lg = torch.randn(6, V, generator=gen(6)) * 2.5
+    R = 8
+    lg = torch.randn(R, V, generator=gen(6)) * 2.5
     lg[4, :] = lg[4, 0]                                             # all equal: every walk is a tie
-    temps = [0.8, 1.0, 0.0, 1.3, 1.0, 0.6]
-    topk = [40, 0, 5, 7, 3, V + 5]
-    seeds = [42, 7, 1, 99, 5, 2 ** 40 + 3]
-    slots = torch.tensor([3, 0, 5, 1, 2, 4], dtype=torch.int32, device=DEV)
-    t_dev = torch.zeros(6, device=DEV); k_dev = torch.zeros(6, dtype=torch.int32, device=DEV)
-    rng = torch.zeros(6, dtype=torch.int64, device=DEV)
+    # rows 6 and 7: a low temperature spreads the scaled logits far beyond the span in which tokens
+    # have mass; row 6 keeps so many that the k-th largest lies among the massless ones
+    temps = [0.8, 1.0, 0.0, 1.3, 1.0, 0.6, 0.3, 0.05]
+    topk = [40, 0, 5, 7, 3, V + 5, 2 * V // 5, 0]
+    seeds = [42, 7, 1, 99, 5, 2 ** 40 + 3, 11, 12]
+    slots = torch.tensor([3, 0, 5, 1, 2, 4, 7, 6], dtype=torch.int32, device=DEV)
+    t_dev = torch.zeros(R, device=DEV); k_dev = torch.zeros(R, dtype=torch.int32, device=DEV)
+    rng = torch.zeros(R, dtype=torch.int64, device=DEV)
     for r, sl in enumerate(slots.tolist()):
         t_dev[sl], k_dev[sl], rng[sl] = temps[r], topk[r], seeds[r]
-    plain = [P.XorShiftSampler(temps[r], topk[r], seeds[r]) for r in range(6)]
-    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    plain = [P.XorShiftSampler(temps[r], topk[r], seeds[r]) for r in range(R)]
+    out = torch.zeros(R, dtype=torch.int32, device=DEV)
     dev = lg.to(DEV)
     agree = total = 0
     for _ in range(12):
-        o.sample(dev, 6, slots, t_dev, k_dev, rng, out)
+        o.sample(dev, R, slots, t_dev, k_dev, rng, out)
         got = out.tolist()
-        want = [plain[r].sample(lg[r]) for r in range(6)]
+        want = [plain[r].sample(lg[r]) for r in range(R)]
         assert got[2] == want[2]                                    # greedy row
         assert 0 <= got[4] < 3                                      # ties: the three lowest indices are kept
-        for r in (0, 1, 3, 5):
+        for r in (0, 1, 3, 5, 6, 7):
             total += 1
             agree += int(got[r] == want[r])
     # the walks agree except where r falls within rounding of a boundary between two tokens
