@@ -121,9 +121,11 @@ int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStr
 // last_token (may be null): per-slot array that also receives each row's token, for the next step's
 // embedding to read.
 // scratch: 2 * n_rows 64-bit words that are zero before the first call (the kernel leaves them zero).
+// teams != 0: the launch is made of clusters whose blocks share a sampled row's passes (for steps in
+// which some row may be sampled; the tokens are the same either way).
 int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                const float* temperature, const int* top_k, unsigned long long* rng_state, int* out,
-               int* last_token, unsigned long long* scratch, cudaStream_t stream);
+               int* last_token, unsigned long long* scratch, int teams, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -100,6 +100,27 @@ __device__ __forceinline__ void cluster_arrive() {
 __device__ __forceinline__ void cluster_wait() {
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// the address of `local` in the shared memory of block `rank` of the cluster, and 32-bit accesses there
+__device__ __forceinline__ uint32_t cluster_addr(const void* local, int rank) {
+  uint32_t remote;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;"
+               : "=r"(remote)
+               : "r"((uint32_t)__cvta_generic_to_shared(local)), "r"(rank));
+  return remote;
+}
+__device__ __forceinline__ uint32_t cluster_load(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void cluster_store(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t cluster_atomic_add(uint32_t addr, uint32_t v) {
+  uint32_t old;
+  asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");
+  return old;
+}
 // stores v at the place of `local` in the shared memory of block `rank` of the cluster
 __device__ __forceinline__ void store_to_rank(float* local, int rank, float v) {
   uint32_t remote;

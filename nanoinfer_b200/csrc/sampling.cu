@@ -22,6 +22,22 @@ namespace nib {
 
 constexpr int SAMPLE_THREADS = 1024;
 constexpr int SAMPLE_CHUNKS = 16;   // blocks that share a greedy row
+constexpr int SAMPLE_TEAM = 8;      // blocks (one cluster) that share a sampled row
+
+// The blocks that work on one sampled row: this block alone (n = 1), or the n blocks of its cluster.
+// Every block of a team passes the same sync() calls in the same order: none stands inside a
+// branch that differs between the blocks of a team.
+struct Team {
+  int rank, n;
+  __device__ __forceinline__ void sync() const {
+    if (n > 1) {
+      cluster_arrive();
+      cluster_wait();
+    } else {
+      __syncthreads();
+    }
+  }
+};
 
 __device__ __forceinline__ uint32_t float_key(float f) {
   const uint32_t b = __float_as_uint(f);
@@ -89,6 +105,8 @@ struct SelectShared {
   uint32_t list_key[SEL_LIST];           // the chosen bin's tokens: their keys ...
   int list_idx[SEL_LIST];                // ... and indices (in no particular order)
   int n_list;                            // how many the bin has (the lists hold the first SEL_LIST)
+  float peer_max[SAMPLE_TEAM];           // the maxima of the team's blocks
+  uint32_t pub_thresh;                   // the first select's key, for the other blocks of the team
   unsigned long long target;
   unsigned long long total;
   uint32_t digit;
@@ -122,12 +140,17 @@ __device__ __forceinline__ int coarse_bin(float s, float mx) {
 template <bool MASS>
 __device__ void radix_select(const float* __restrict__ row, int V, float temperature, float mx,
                              bool use_thresh, uint32_t thresh, unsigned long long tie_mass,
-                             unsigned long long target, uint32_t u24, SelectShared& sh,
+                             unsigned long long target, uint32_t u24, SelectShared& sh, const Team team,
                              uint32_t& key_out, unsigned long long& resid_out) {
+  // With a team, every block takes a slice of the row for the passes over all tokens; the first
+  // block adds the histograms up, picks the bin, owns the list (the others append to it through
+  // distributed shared memory) and does the byte passes alone.
+  const int per = (V + team.n - 1) / team.n;
+  const int v0 = min(V, team.rank * per), v1 = min(V, v0 + per);
   const int thresh_bin = (MASS && use_thresh) ? coarse_bin(key_float(thresh), mx) : -1;
   for (int i = threadIdx.x; i < SEL_BINS; i += blockDim.x) sh.lo[i] = sh.hi[i] = 0u;
   __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     const float s = row[i] / temperature;
     if (MASS) {
       if (use_thresh && float_key(s) <= thresh) continue;
@@ -143,64 +166,84 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
       atomicAdd(&sh.lo[coarse_bin(s, mx)], 1u);
     }
   }
-  __syncthreads();
-  if (threadIdx.x < 32) {
-    const int lane = threadIdx.x;
-    constexpr int PER = SEL_BINS / 32;
-    if (MASS && use_thresh && thresh_bin / PER == lane) {   // the kept ties of the threshold key
-      const unsigned long long v = (((unsigned long long)sh.hi[thresh_bin] << 32) | sh.lo[thresh_bin]) + tie_mass;
-      sh.lo[thresh_bin] = (uint32_t)v;
-      sh.hi[thresh_bin] = (uint32_t)(v >> 32);
-    }
-    unsigned long long mine = 0ull;
-    for (int b = lane * PER; b < (lane + 1) * PER; ++b) mine += ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
-    unsigned long long incl = mine;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += up;
-    }
-    const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
-    unsigned long long tgt = target;
-    if (MASS) {
-      // (u24 * total) >> 24 without overflow: total < 2^49
-      const unsigned long long hi = __umul64hi((unsigned long long)u24, total);
-      const unsigned long long lo = (unsigned long long)u24 * total;
-      tgt = (hi << 40) | (lo >> 24);
-      if (tgt < 1ull) tgt = 1ull;
-    }
-    const uint32_t reached = __ballot_sync(0xffffffffu, incl >= tgt);
-    const int owner = reached ? __ffs(reached) - 1 : 31;
-    if (lane == owner) {
-      unsigned long long cum = incl - mine;
-      int b = lane * PER;
-      for (; b < (lane + 1) * PER - 1; ++b) {
-        const unsigned long long h = ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
-        if (cum + h >= tgt) break;
-        cum += h;
+  team.sync();   // every block's histogram is complete
+  if (team.rank == 0) {
+    if (team.n > 1) {
+      for (int b = threadIdx.x; b < SEL_BINS; b += blockDim.x) {
+        unsigned long long v = ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
+        for (int r = 1; r < team.n; ++r)
+          v += ((unsigned long long)cluster_load(cluster_addr(&sh.hi[b], r)) << 32) | cluster_load(cluster_addr(&sh.lo[b], r));
+        sh.lo[b] = (uint32_t)v;
+        sh.hi[b] = (uint32_t)(v >> 32);
       }
-      sh.bin = b;
-      sh.target = tgt - cum;
-      sh.total = total;
+      __syncthreads();
+    }
+    if (threadIdx.x < 32) {
+      const int lane = threadIdx.x;
+      constexpr int PER = SEL_BINS / 32;
+      if (MASS && use_thresh && thresh_bin / PER == lane) {   // the kept ties of the threshold key
+        const unsigned long long v = (((unsigned long long)sh.hi[thresh_bin] << 32) | sh.lo[thresh_bin]) + tie_mass;
+        sh.lo[thresh_bin] = (uint32_t)v;
+        sh.hi[thresh_bin] = (uint32_t)(v >> 32);
+      }
+      unsigned long long mine = 0ull;
+      for (int b = lane * PER; b < (lane + 1) * PER; ++b) mine += ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
+      unsigned long long incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+      }
+      const unsigned long long total = __shfl_sync(0xffffffffu, incl, 31);
+      unsigned long long tgt = target;
+      if (MASS) {
+        // (u24 * total) >> 24 without overflow: total < 2^49
+        const unsigned long long hi = __umul64hi((unsigned long long)u24, total);
+        const unsigned long long lo = (unsigned long long)u24 * total;
+        tgt = (hi << 40) | (lo >> 24);
+        if (tgt < 1ull) tgt = 1ull;
+      }
+      const uint32_t reached = __ballot_sync(0xffffffffu, incl >= tgt);
+      const int owner = reached ? __ffs(reached) - 1 : 31;
+      if (lane == owner) {
+        unsigned long long cum = incl - mine;
+        int b = lane * PER;
+        for (; b < (lane + 1) * PER - 1; ++b) {
+          const unsigned long long h = ((unsigned long long)sh.hi[b] << 32) | sh.lo[b];
+          if (cum + h >= tgt) break;
+          cum += h;
+        }
+        sh.bin = b;
+        sh.target = tgt - cum;
+        sh.total = total;
+        sh.n_list = 0;
+      }
     }
   }
-  __syncthreads();
-  const int bin = sh.bin;
-  target = sh.target;
-  if (threadIdx.x == 0) sh.n_list = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
+  team.sync();   // the bin is chosen (and the first block has read the others' histograms)
+  const int bin = team.rank == 0 ? sh.bin : (int)cluster_load(cluster_addr(&sh.bin, 0));
+  for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) {
     const float s = row[i] / temperature;
     if (coarse_bin(s, mx) != bin) continue;
     const uint32_t key = float_key(s);
     if (MASS && use_thresh && key <= thresh) continue;
-    const int at = atomicAdd(&sh.n_list, 1);
-    if (at < SEL_LIST) {
-      sh.list_key[at] = key;
-      sh.list_idx[at] = i;
+    if (team.rank == 0) {
+      const int at = atomicAdd(&sh.n_list, 1);
+      if (at < SEL_LIST) {
+        sh.list_key[at] = key;
+        sh.list_idx[at] = i;
+      }
+    } else {
+      const int at = (int)cluster_atomic_add(cluster_addr(&sh.n_list, 0), 1u);
+      if (at < SEL_LIST) {
+        cluster_store(cluster_addr(&sh.list_key[at], 0), key);
+        cluster_store(cluster_addr(&sh.list_idx[at], 0), (uint32_t)i);
+      }
     }
   }
-  __syncthreads();
+  team.sync();   // the list is complete
+  if (team.rank != 0) return;   // (the caller's next sync() is the next one for every block)
+  target = sh.target;
   const int n_list = sh.n_list;
   const bool listed = n_list <= SEL_LIST;
 
@@ -229,17 +272,35 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
       }
     }
     __syncthreads();
-    if (threadIdx.x == 0) {
-      if (MASS && use_thresh && thresh_bin == bin && (thresh & mask) == prefix)
+    if (threadIdx.x < 32) {
+      // the digit in which the target falls, from the top: a lane per eight digits, a scan over the
+      // lanes, then the owning lane walks its eight (one thread walking all 256 cost 5 us a pass)
+      const int lane = threadIdx.x;
+      const int top = 255 - 8 * lane;
+      if (MASS && use_thresh && thresh_bin == bin && (thresh & mask) == prefix &&
+          (255 - (int)((thresh >> shift) & 255u)) / 8 == lane)
         sh.hist[(thresh >> shift) & 255u] += tie_mass;
-      unsigned long long cum = 0ull;
-      int d = 255;
-      for (; d > 0; --d) {
-        if (cum + sh.hist[d] >= target) break;
-        cum += sh.hist[d];
+      unsigned long long mine = 0ull;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) mine += sh.hist[top - j];
+      unsigned long long incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
       }
-      sh.digit = (uint32_t)d;
-      sh.target = target - cum;
+      const uint32_t reached = __ballot_sync(0xffffffffu, incl >= target);
+      const int owner = reached ? __ffs(reached) - 1 : 31;
+      if (lane == owner) {
+        unsigned long long cum = incl - mine;
+        int d = top;
+        for (; d > top - 7; --d) {
+          if (cum + sh.hist[d] >= target) break;
+          cum += sh.hist[d];
+        }
+        sh.digit = (uint32_t)d;
+        sh.target = target - cum;
+      }
     }
     __syncthreads();
     prefix |= sh.digit << shift;
@@ -255,13 +316,14 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
 // the vocabulary, folds (value, index) into one 64-bit word per row with atomicMax (the value's
 // order-preserving key in the high half, ~index in the low half: the largest value wins, ties go
 // to the lowest index), and the block that arrives last writes the token and clears the words.
-// A sampled row is the work of block 0 of its row alone.  `scratch` holds 2 words per row
-// (the folded maximum and the arrival count), zero between launches.
+// A sampled row is the work of the first `team_size` blocks of its row: block 0 alone, or (launched
+// as clusters of SAMPLE_TEAM blocks) one cluster, whose blocks share the passes over all tokens.
+// `scratch` holds 2 words per row (the folded maximum and the arrival count), zero between launches.
 __global__ void __launch_bounds__(SAMPLE_THREADS, 1)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
               unsigned long long* __restrict__ rng_state, int* __restrict__ out,
-              int* __restrict__ last_token, unsigned long long* __restrict__ scratch) {
+              int* __restrict__ last_token, unsigned long long* __restrict__ scratch, int team_size) {
   pdl_trigger();
   pdl_wait();
   __shared__ BestPair best_scratch[32];
@@ -296,10 +358,13 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
     }
     return;
   }
-  if (blockIdx.x != 0) return;
+  // ---- a sampled row: the first `team` blocks of the row's grid line (one cluster, or block 0 alone)
+  if ((int)blockIdx.x >= team_size) return;
+  const Team team{team_size > 1 ? cluster_rank() : 0, team_size};
+  team.sync();   // every block of the team runs: its shared memory may be written from now on
   // one draw of xorshift64*, kept per request
   __shared__ uint32_t u24_sh;
-  if (threadIdx.x == 0) {
+  if (team.rank == 0 && threadIdx.x == 0) {
     unsigned long long s = rng_state[slot];
     s ^= s >> 12;
     s ^= s << 25;
@@ -308,22 +373,38 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __rest
     u24_sh = (uint32_t)((s * 0x2545F4914F6CDD1Dull) >> 40);
   }
   float mxl = -INFINITY;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) mxl = fmaxf(mxl, row[i] / temp);
-  const float mx = block_max(mxl, red);  // also orders the write of u24_sh
+  {
+    const int per = (V + team.n - 1) / team.n;
+    const int v0 = min(V, team.rank * per), v1 = min(V, v0 + per);
+    for (int i = v0 + threadIdx.x; i < v1; i += blockDim.x) mxl = fmaxf(mxl, row[i] / temp);
+  }
+  float mx = block_max(mxl, red);  // also orders the write of u24_sh
+  if (team.n > 1) {   // every block tells every block its maximum
+    if ((int)threadIdx.x < team.n)
+      cluster_store(cluster_addr(&sh.peer_max[team.rank], threadIdx.x), __float_as_uint(mx));
+    team.sync();
+    for (int r = 0; r < team.n; ++r) mx = fmaxf(mx, sh.peer_max[r]);
+  }
   const uint32_t u24 = u24_sh;
 
   int k = top_k[slot];
   bool use_thresh = false;
   uint32_t thresh = 0;
   unsigned long long tie_keep = 0ull, tie_mass = 0ull;
-  if (k > 0 && k < V) {
-    radix_select<false>(row, V, temp, mx, false, 0u, 0ull, (unsigned long long)k, 0u, sh, thresh, tie_keep);
+  if (k > 0 && k < V) {   // (the same for every block of the team)
+    radix_select<false>(row, V, temp, mx, false, 0u, 0ull, (unsigned long long)k, 0u, sh, team, thresh, tie_keep);
     use_thresh = true;
-    tie_mass = tie_keep * mass_of(key_float(thresh), mx);
+    if (team.n > 1) {   // the first block found the k-th key: the others need it for their slices
+      if (team.rank == 0 && threadIdx.x == 0) sh.pub_thresh = thresh;
+      team.sync();
+      if (team.rank != 0) thresh = cluster_load(cluster_addr(&sh.pub_thresh, 0));
+    }
+    tie_mass = tie_keep * mass_of(key_float(thresh), mx);   // (used by the first block only)
   }
   uint32_t key;
   unsigned long long resid;
-  radix_select<true>(row, V, temp, mx, use_thresh, thresh, tie_mass, 0ull, u24, sh, key, resid);
+  radix_select<true>(row, V, temp, mx, use_thresh, thresh, tie_mass, 0ull, u24, sh, team, key, resid);
+  if (team.rank != 0) return;   // (after the last sync(): nothing reads this block's shared memory any more)
 
   // the tokens that carry `key`, lowest index first; the walk stops at the n-th of them
   if (threadIdx.x == 0) {
@@ -392,11 +473,17 @@ extern "C" int nib_argmax(const float* logits, int ld, int n_rows, int V, int* o
 
 extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const int* row_slot,
                           const float* temperature, const int* top_k, unsigned long long* rng_state,
-                          int* out, int* last_token, unsigned long long* scratch, cudaStream_t stream) {
+                          int* out, int* last_token, unsigned long long* scratch, int teams,
+                          cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_rows > 65535 || scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
   dim3 grid(SAMPLE_CHUNKS, n_rows);
-  launch_pdl(sample_kernel, dim3(grid), dim3(SAMPLE_THREADS), 0, stream, logits, ld, V, row_slot, temperature, top_k, rng_state, out,
-                                                     last_token, scratch);
+  // teams != 0: some rows may be sampled, and the launch is made of clusters of SAMPLE_TEAM blocks
+  // (a greedy row does not care); a launch of greedy rows only needs no clusters
+  static_assert(SAMPLE_CHUNKS % SAMPLE_TEAM == 0, "a row's grid line is whole clusters");
+  // (only while all of them fit on the device at once: more rows are better off one block each)
+  const int team = (teams && n_rows * SAMPLE_TEAM <= 128) ? SAMPLE_TEAM : 1;
+  launch_pdl_cluster(sample_kernel, dim3(grid), dim3(SAMPLE_THREADS), 0, stream, team, logits, ld, V, row_slot,
+                     temperature, top_k, rng_state, out, last_token, scratch, team);
   NIB_LAUNCH_CHECK();
 }

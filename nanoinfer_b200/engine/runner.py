@@ -307,7 +307,7 @@ class ModelRunner:
         key = None
         if self.use_graphs:
             key = (T, E, M, plan.n_decode, plan.n_prefill_rows, plan.n_tiles, plan.n_wide_tiles,
-                   plan.max_decode_keys, id(sampler))
+                   plan.max_decode_keys, id(sampler), getattr(sampler, "any_sampled", None))
         cap = self._graphs.get(key) if key is not None else None
         if cap is not None:
             self._graphs[key] = self._graphs.pop(key)   # most recently used last

@@ -63,7 +63,8 @@ _SIGNATURES = {
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
-    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
+                   _c_ptr],
 }
 
 
@@ -666,11 +667,13 @@ _sample_scratch: Optional[torch.Tensor] = None
 
 def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
            top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor,
-           last_token: Optional[torch.Tensor] = None) -> None:
+           last_token: Optional[torch.Tensor] = None, teams: bool = True) -> None:
     """One token per row.  ``temperature``, ``top_k`` and ``rng_state`` are per-slot arrays and
     ``row_slot`` names each row's slot: greedy where the slot's temperature <= 0, else
     temperature / top-k sampling that advances the slot's xorshift64* word.  ``last_token``: a
-    per-slot array that also receives the tokens (for the next step's embedding)."""
+    per-slot array that also receives the tokens (for the next step's embedding).  ``teams``: launch
+    clusters of blocks that share a sampled row's passes over the vocabulary (False when every row
+    is known to be greedy; the tokens are the same either way)."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with contiguous rows")
     if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:
@@ -682,4 +685,4 @@ def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperatur
         _sample_scratch = torch.zeros(2 * max(n_rows, 256), dtype=torch.int64, device=logits.device)
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
                                 _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
-                                _ptr(last_token), _ptr(_sample_scratch), _stream()), "sample")
+                                _ptr(last_token), _ptr(_sample_scratch), int(bool(teams)), _stream()), "sample")

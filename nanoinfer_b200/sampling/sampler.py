@@ -55,6 +55,8 @@ class Sampler:
         #: before the host has seen it
         self.last_token = slots.register(("sampler", "last_token"), (), torch.int32)
         self._out = torch.zeros(max(1, slots.n_slots), dtype=torch.int32, device=slots.device)
+        #: slots whose request samples with a temperature (a slot stays here until its next request)
+        self._sampled_slots = set()
 
     def set_request(self, slot: int, params: SamplingParams, n_draws_done: int = 0) -> None:
         """Write a request's options into its slot; ``n_draws_done`` restores the generator of a
@@ -63,11 +65,22 @@ class Sampler:
         self.rng[slot] = _as_signed(xorshift64star_state(params.seed, draws))
         self.temperature[slot] = float(params.temperature)
         self.top_k[slot] = int(params.top_k)
+        if params.temperature > 0.0:
+            self._sampled_slots.add(slot)
+        else:
+            self._sampled_slots.discard(slot)
+
+    @property
+    def any_sampled(self) -> bool:
+        """Whether some slot may hold a request that samples with a temperature: the kernel is then
+        launched as clusters of blocks that share a sampled row."""
+        return bool(self._sampled_slots)
 
     def sample(self, logits: torch.Tensor, row_slot: torch.Tensor) -> torch.Tensor:
         """One token per logits row (int32, on the device; valid until the next call)."""
         n = logits.shape[0]
         if n > self._out.numel():
             self._out = torch.zeros(n, dtype=torch.int32, device=logits.device)
-        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out, self.last_token)
+        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out, self.last_token,
+                   teams=self.any_sampled)
         return self._out[:n]

@@ -272,8 +272,10 @@ def test_argmax_ties_and_odd_vocabulary():
     assert out.tolist() == [P.argmax(lg[i]) for i in range(5)] and out.tolist()[1:4] == [123, V - 1, 0]
 
 
+@pytest.mark.parametrize("teams", [False, True])
 @pytest.mark.parametrize("V", [1000, 50257])
-def test_sampling_follows_the_reference_walk(V):
+def test_sampling_follows_the_reference_walk(V, teams):
+    """``teams``: a sampled row is the work of one block, or of the eight blocks of a cluster."""
     o = ops()
     R = 8
     lg = torch.randn(R, V, generator=gen(6)) * 2.5
@@ -293,7 +295,7 @@ def test_sampling_follows_the_reference_walk(V):
     dev = lg.to(DEV)
     agree = total = 0
     for _ in range(12):
-        o.sample(dev, R, slots, t_dev, k_dev, rng, out)
+        o.sample(dev, R, slots, t_dev, k_dev, rng, out, teams=teams)
         got = out.tolist()
         want = [plain[r].sample(lg[r]) for r in range(R)]
         assert got[2] == want[2]                                    # greedy row
