@@ -43,6 +43,27 @@ def test_greedy_generation_matches_the_plain_implementation(name, model_dirs):
         assert first_diff >= 1
 
 
+def test_greedy_generation_of_a_dozen_requests_with_padded_batches(model_dirs):
+    """Twelve requests of different output lengths through the entry point (one step ahead of its
+    reads): batches of 12, 11, 10 and 9 single tokens are padded to 16 rows and share graphs; the
+    tokens are the plain implementation's."""
+    import nanoinfer_b200 as nb
+    from plain_gpt2 import PlainGPT2
+    d = model_dirs("A", torch.float32)
+    prompts = [random_tokens(512, 2 + (5 * i) % 9, 140 + i) for i in range(12)]
+    n_new = [6 + i for i in range(12)]
+    plain = PlainGPT2(d)
+    eng = engine(d, "float32", max_batch=16, max_rows=64)
+    reqs = [eng.add_request(p, nb.SamplingParams(max_new_tokens=n, temperature=0.0)) for p, n in zip(prompts, n_new)]
+    while eng.has_work():
+        eng.step()
+    assert eng.runner.padded_steps >= 5
+    for r, p, n in zip(reqs, prompts, n_new):
+        assert r.output == plain.greedy(p, n)
+    assert eng.cache.pages_used() == [0] and eng.cache.slots.n_free == 16
+    eng.cache.check()
+
+
 def test_long_decoding_and_the_first_tokens(model_dirs, plain_logits):
     """One token at a time from position 0 to the end of a 640-position context: the first tokens
     (one key, one page) and the last (hundreds of keys, forty pages)."""
