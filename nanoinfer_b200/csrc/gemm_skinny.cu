@@ -30,6 +30,8 @@ namespace nib {
 constexpr int SK_WARPS = 8;
 constexpr int SK_MAX_ROWS = 64;
 constexpr int SK_MAX_LN_ROWS = 16;   // the norm is folded in for steps of at most this many rows
+constexpr int SK_LN_REG_WIDTH = 1024;   // rows up to this wide are normalised in registers ...
+constexpr int SK_LN_MAX_WIDTH = 4096;   // ... wider ones, up to this, in shared memory
 constexpr int SK_MAX_SPLIT = 8;      // blocks of a cluster that split K
 
 struct SkinnyParams {
@@ -65,6 +67,11 @@ __device__ __forceinline__ void mma_16x8x16(float* c, uint32_t a0, uint32_t a1, 
       "{%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
 }
 
 __host__ __device__ inline int skinny_ldx(int k_per) { return k_per + ((32 - k_per % 64) + 64) % 64; }
@@ -174,7 +181,39 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // ---- the step's rows into shared memory as bfloat16 (normalised on the way if asked)
   for (int i = threadIdx.x; i < (NT * 8 - M) * (ldx / 8); i += blockDim.x)   // rows past the step: zeros
     reinterpret_cast<uint4*>(xs + (size_t)M * ldx)[i] = make_uint4(0, 0, 0, 0);
-  if (prm.ln_x != nullptr) {
+  if (prm.ln_x != nullptr && prm.K > SK_LN_REG_WIDTH) {
+    // Rows too wide for a lane's registers: a warp brings its row into a buffer of its own in shared
+    // memory (summing on the way) and makes the other two passes there.
+    __syncthreads();   // the norm's parameters are in place
+    const int K = prm.K;
+    float* mine = ln_gb + 2 * K + (size_t)warp * K;
+    for (int m = warp; m < M; m += SK_WARPS) {
+      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
+      float sum = 0.0f;
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 t = *reinterpret_cast<const float4*>(src + k);
+        *reinterpret_cast<float4*>(mine + k) = t;
+        sum += (t.x + t.y) + (t.z + t.w);
+      }
+      const float mean = warp_sum(sum) / (float)K;
+      float sq = 0.0f;
+      for (int k = lane * 4; k < K; k += 128) {   // (a lane reads back what it wrote)
+        const float4 t = *reinterpret_cast<const float4*>(mine + k);
+        const float d0 = t.x - mean, d1 = t.y - mean, d2 = t.z - mean, d3 = t.w - mean;
+        sq += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
+      }
+      const float rstd = 1.0f / sqrtf(warp_sum(sq) / (float)K + prm.ln_eps);
+      for (int k = lane * 4; k < K; k += 128) {
+        const float4 t = *reinterpret_cast<const float4*>(mine + k);
+        const float4 g = *reinterpret_cast<const float4*>(ln_gb + k);
+        const float4 b = *reinterpret_cast<const float4*>(ln_gb + K + k);
+        uint2 packed;
+        packed.x = pack2((t.x - mean) * rstd * g.x + b.x, (t.y - mean) * rstd * g.y + b.y);
+        packed.y = pack2((t.z - mean) * rstd * g.z + b.z, (t.w - mean) * rstd * g.w + b.w);
+        *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+      }
+    }
+  } else if (prm.ln_x != nullptr) {
     __syncthreads();   // the norm's parameters are in place
     const int K = prm.K;
     for (int m = warp; m < M; m += SK_WARPS) {
@@ -383,8 +422,9 @@ static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4
 
 static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool alias = false) {
   const size_t xs = (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16), red = (size_t)SK_WARPS * NT * 128 * sizeof(float);
+  // (with the norm: its scale and shift, and for wide rows a buffer per warp)
   return (alias ? (xs > red ? xs : red) : xs + red) + (size_t)2 * NT * 128 * sizeof(float) +
-         (ln ? (size_t)2 * K * sizeof(float) : 0);
+         (ln ? (size_t)(2 + (K > SK_LN_REG_WIDTH ? SK_WARPS : 0)) * K * sizeof(float) : 0);
 }
 
 constexpr size_t SK_SMEM_LIMIT = 200 * 1024;
@@ -489,7 +529,7 @@ using namespace nib;
 // 1 if the few-rows kernel takes this problem (ln: with the LayerNorm folded in).
 extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const void* w) {
   if (M < 1 || M > SK_MAX_ROWS || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)w & 15)) return 0;
-  if (ln && (M > SK_MAX_LN_ROWS || K > 1024 || (K & 3))) return 0;  // a row is held in registers while normalised
+  if (ln && (M > SK_MAX_LN_ROWS || K > SK_LN_MAX_WIDTH || (K & 3))) return 0;
   const int split = skinny_split(M, 16, K, ln != 0);   // (the split that smem alone asks for)
   if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0) > SK_SMEM_LIMIT) return 0;
   return 1;

@@ -399,7 +399,7 @@ def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd)
 
 
 SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (64, 1000, 120), (128, 257, 64),
-                (16, 768, 3072), (5, 50257, 64)]
+                (16, 768, 3072), (5, 50257, 64), (8, 4800, 1600), (13, 200, 2048), (3, 96, 1104)]
 
 
 @pytest.mark.parametrize("M, N, K", SMALL_SHAPES)
