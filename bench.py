@@ -99,7 +99,7 @@ def main() -> int:
         "warmup": warmup, "ms_per_step": dec["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": dec["tokens_per_s"] / REFERENCE_B8_TOK_S, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": "gpt2-small-124M random weights", "n_layer": cfg.n_layer, "n_layer_full": full_layers,
+            "model": f"{args.preset}-{bs.parameter_count(cfg) / 1e6:.0f}M random weights", "n_layer": cfg.n_layer, "n_layer_full": full_layers,
             "n_embd": cfg.n_embd, "n_head": cfg.n_head, "head_dim": cfg.head_dim, "n_inner": cfg.inner_dim,
             "vocab_size": cfg.vocab_size, "n_positions": cfg.n_positions, "global_batch": args.batch,
             "seq_len": context, "prompt_len": prompt_len, "mean_context": round(dec["mean_context"], 1),

@@ -77,6 +77,14 @@ def weight_bytes_per_step(cfg, itemsize: int) -> int:
     return (cfg.n_layer * per_layer + cfg.vocab_size * c) * itemsize + vectors * 4
 
 
+def parameter_count(cfg) -> int:
+    """All parameters (crates/core/src/config.rs:29-39: 124,439,808 for GPT-2 small)."""
+    c, i = cfg.n_embd, cfg.inner_dim
+    per_layer = (c * 3 * c + 3 * c) + (c * c + c) + (c * i + i) + (i * c + c) + 4 * c
+    head = 0 if getattr(cfg, "tie_word_embeddings", True) else cfg.vocab_size * c
+    return cfg.n_layer * per_layer + cfg.vocab_size * c + cfg.n_positions * c + 2 * c + head
+
+
 def kv_bytes_per_position(cfg, itemsize: int) -> int:
     return 2 * cfg.n_layer * cfg.n_embd * itemsize
 

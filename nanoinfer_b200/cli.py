@@ -146,6 +146,8 @@ def main(argv=None) -> int:
     s.add_argument("--kv-blocks", type=int, default=None,
                    help="pages of 16 positions in the pool (default: max_batch full requests and 8 more)")
     s.add_argument("--seed", type=int, default=7)
+    s.add_argument("--temperature", type=float, default=0.0, help="0 = greedy; else every request samples, seeded by --seed + its number")
+    s.add_argument("--top-k", type=int, default=40)
     s.add_argument("--gantt", type=int, default=32, help="requests in the summary's timeline")
     s.add_argument("--out", default=None, help="append one result line per policy to this file")
     s.add_argument("--summary", default=None, help="write the full summary (JSON) to this file")

@@ -101,8 +101,10 @@ def workload(n_requests: int, prompt_min: int, prompt_max: int, out_min: int, ou
     return reqs
 
 
-def _run(engine, reqs: List[ServeRequest], static: bool) -> Outcome:
-    """Feeds the requests to the engine as they arrive and steps it until all are done."""
+def _run(engine, reqs: List[ServeRequest], static: bool, temperature: float = 0.0, top_k: int = 40,
+         seed: int = 0) -> Outcome:
+    """Feeds the requests to the engine as they arrive and steps it until all are done.  With a
+    temperature every request samples from a generator of its own (seed + its id)."""
     from .sampling.sampler import SamplingParams
 
     sched, cache = engine.scheduler, engine.cache
@@ -123,7 +125,8 @@ def _run(engine, reqs: List[ServeRequest], static: bool) -> Outcome:
         room = engine.scheduler.max_batch if static else len(reqs)
         while may_add and nxt < len(reqs) and reqs[nxt].arrival <= t and room > 0:
             r = reqs[nxt]
-            handle[r.id] = engine.add_request(r.prompt, SamplingParams(max_new_tokens=r.out_len, temperature=0.0))
+            handle[r.id] = engine.add_request(r.prompt, SamplingParams(max_new_tokens=r.out_len, temperature=temperature,
+                                                                       top_k=top_k, seed=seed + r.id))
             rid_of[id(handle[r.id])] = r.id
             nxt += 1
             room -= 1
@@ -162,12 +165,12 @@ def _run(engine, reqs: List[ServeRequest], static: bool) -> Outcome:
     return out
 
 
-def run_continuous(engine, reqs: List[ServeRequest]) -> Outcome:
-    return _run(engine, reqs, static=False)
+def run_continuous(engine, reqs: List[ServeRequest], **sampling) -> Outcome:
+    return _run(engine, reqs, static=False, **sampling)
 
 
-def run_static(engine, reqs: List[ServeRequest]) -> Outcome:
-    return _run(engine, reqs, static=True)
+def run_static(engine, reqs: List[ServeRequest], **sampling) -> Outcome:
+    return _run(engine, reqs, static=True, **sampling)
 
 
 def _pct(xs: List[float], p: float) -> float:
@@ -219,14 +222,18 @@ def run_cli(args) -> int:
 
     cfg = load_config(args.weights)
     limit = getattr(cfg, "n_positions", None)
-    if limit is not None and args.prompt_max + args.out_max > limit:
-        print(f"prompt_max + out_max > {limit}", file=sys.stderr)
+    if limit is not None and args.prompt_max >= limit:
+        print(f"prompt_max must be below the context length {limit}", file=sys.stderr)
         return 2
     page = 16
-    pages_per_request = -(-(args.prompt_max + args.out_max) // page)
+    longest = args.prompt_max + args.out_max if limit is None else min(args.prompt_max + args.out_max, limit)
+    pages_per_request = -(-longest // page)
     kv_blocks = args.kv_blocks or args.max_batch * pages_per_request + 8
     reqs = workload(args.requests, args.prompt_min, args.prompt_max, args.out_min, args.out_max, args.rate, args.seed,
                     cfg.vocab_size)
+    if limit is not None:   # an output that would pass the end of the context is cut there
+        for r in reqs:
+            r.out_len = max(1, min(r.out_len, limit - len(r.prompt)))
     total_in, total_out = sum(len(r.prompt) for r in reqs), sum(r.out_len for r in reqs)
     print(f"serve-bench: {args.requests} requests (prompt {args.prompt_min}-{args.prompt_max}, output "
           f"{args.out_min}-{args.out_max}; {total_in} prompt + {total_out} output tokens), rate {args.rate} req/s, "
@@ -238,12 +245,14 @@ def run_cli(args) -> int:
                       page_size=page)
 
     eng = engine()
-    run_continuous(eng, reqs[:min(len(reqs), 4)])           # warm up: kernels built, first graphs captured
-    s_static = summarise("static", reqs, run_static(eng, reqs), page, args.gantt)
-    s_cont = summarise("continuous", reqs, run_continuous(eng, reqs), page, args.gantt)
+    sampling = {"temperature": args.temperature, "top_k": args.top_k, "seed": args.seed}
+    run_continuous(eng, reqs[:min(len(reqs), 4)], **sampling)   # warm up: kernels built, first graphs captured
+    s_static = summarise("static", reqs, run_static(eng, reqs, **sampling), page, args.gantt)
+    s_cont = summarise("continuous", reqs, run_continuous(eng, reqs, **sampling), page, args.gantt)
     print(f"continuous / static throughput: {s_cont['throughput_tok_s'] / s_static['throughput_tok_s']:.2f}x")
     summary = {"requests": args.requests, "max_batch": args.max_batch, "prefill_budget": args.prefill_budget,
                "kv_blocks": kv_blocks, "dtype": args.dtype, "seed": args.seed, "rate": args.rate, "note": args.note,
+               "temperature": args.temperature, "top_k": args.top_k,
                "policies": [s_static, s_cont]}
     if args.summary:
         with open(args.summary, "w") as fh:
