@@ -238,8 +238,15 @@ class Workspace:
     def __init__(self, device: torch.device):
         self.device = device
         self._bufs: Dict[str, torch.Tensor] = {}
+        # the views handed out, by (name, shape, dtype): a step asks for the same ones again and
+        # again, and making a view costs more than a launch's share of a step
+        self._views: Dict[tuple, torch.Tensor] = {}
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
+        key = (name, shape, dtype)
+        view = self._views.get(key)
+        if view is not None:
+            return view
         n = 1
         for s in shape:
             n *= int(s)
@@ -247,7 +254,13 @@ class Workspace:
         if buf is None or buf.dtype != dtype or buf.numel() < n:
             buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
-        return buf[:n].view(*shape)
+            for k in [k for k in self._views if k[0] == name]:   # views of the buffer that was replaced
+                del self._views[k]
+        view = buf[:n].view(*shape)
+        if len(self._views) > 4096:
+            self._views.clear()
+        self._views[key] = view
+        return view
 
     def get_zeroed(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         """Like ``get``, but the memory is zero when first handed out (and whenever it has to grow);
@@ -259,6 +272,8 @@ class Workspace:
         if buf is None or buf.dtype != dtype or buf.numel() < n:
             buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
             self._bufs[name] = buf
+            for k in [k for k in self._views if k[0] == name]:
+                del self._views[k]
         return buf[:n].view(*shape)
 
     def nbytes(self) -> int:
