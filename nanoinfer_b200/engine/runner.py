@@ -241,7 +241,7 @@ class ModelRunner:
             # into the cache's spare page, state in its spare slot.  Batches that shrink and grow by
             # a request then share a graph instead of each running uncaptured, then being captured.
             if (self.use_graphs and self.cache.pad_slot is not None and E > PAD_FROM and len(want_rows) == E):
-                n_pad = min(-(-E // PAD_TO) * PAD_TO, self.max_entries) - E
+                n_pad = min(-(-E // PAD_TO) * PAD_TO, self.max_entries, self.max_rows) - E
                 tokens_in += [0] * n_pad
                 pos0s += [0] * n_pad
                 slots += [self.cache.pad_slot] * n_pad
