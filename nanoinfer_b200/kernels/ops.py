@@ -375,7 +375,15 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
 
 
 SKINNY_MAX_ROWS = 64
-PAIR_MIN_ROWS = 1536
+PAIR_MIN_ROWS = 256      # the pair kernel's smallest step
+
+
+def pair_pays(M: int, N: int, K: int) -> bool:
+    """Whether a product runs faster by pairs of blocks (one 256-row MMA over two SMs) than on the
+    single-block kernel: always from 1536 rows on (measured in whole prefill steps of 2048 rows at
+    three model sizes); below that from about one wave of tiles on, or with enough work per output
+    (measured alone at widths 768, 1024 and 1600 for the four products of a layer at 256 to 1280 rows)."""
+    return M >= 1536 or (M >= PAIR_MIN_ROWS and (M * N >= 3_000_000 or M * N * K >= 3_500_000_000))
 
 
 def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=0) -> bool:
@@ -462,9 +470,9 @@ def linear(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tens
         a = norm.materialise(M)   # (scratch: a second call for the same rows rewrites the same values)
     if _profiler is not None:
         _profiler.label = f"M={M} N={w.shape[0]} K={w.shape[1]}"
-    # measured: from about two thousand rows on, pairs of blocks on one 256-row MMA (half of the weight
-    # tile per SM) beat the single-block kernel, by 5 to 40 per cent
-    if M >= PAIR_MIN_ROWS and linear_tc_pair(a, w, bias, out, M, act, residual):
+    # pairs of blocks on one 256-row MMA (half of the weight tile per SM) beat the single-block kernel
+    # by 5 to 40 per cent where there is enough work
+    if pair_pays(M, w.shape[0], w.shape[1]) and linear_tc_pair(a, w, bias, out, M, act, residual):
         return
     if linear_tc_supported(a, w):
         linear_tc(a, w, bias, out, M, act, residual)
@@ -477,12 +485,14 @@ def linear_qkv(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.
                positions: torch.Tensor, status: torch.Tensor, norm: Optional[NormInput] = None) -> bool:
     """The fused q/k/v projection with the cache append in its epilogue: queries to out[:M, :q_dim],
     keys and values to their slots of ``cache``.  Returns False (and does nothing) where no fused
-    kernel applies: between 129 rows and the pair kernel's minimum, float32, or a shape the tensor
-    cores refuse."""
+    kernel applies: between 129 rows and the pair kernel's minimum (256), float32, or a shape the
+    tensor cores refuse."""
     if cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         return False
     kv = (cache, block_table, row_entry, positions, q_dim)
-    if M >= PAIR_MIN_ROWS:   # many rows: the pair kernel writes the cache from its epilogue too
+    # from the pair kernel's smallest step on: it writes the cache from its epilogue, which beats the
+    # single-block kernel and a separate append from about 400 rows on and is one launch less
+    if M >= PAIR_MIN_ROWS:
         if norm is not None:
             a, norm = norm.materialise(M), None
         return linear_tc_pair(a, w, bias, out, M, kv=kv)

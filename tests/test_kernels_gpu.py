@@ -579,7 +579,8 @@ def test_product_by_pairs_declines_what_it_cannot_take():
 
 
 @pytest.mark.parametrize("n_head, n_kv_head, hd, lens", [(12, 12, 64, [1024, 700, 324]), (6, 2, 32, [1600]),
-                                                         (4, 4, 16, [513, 500, 600])])
+                                                         (4, 4, 16, [513, 500, 600]), (12, 12, 64, [130, 1, 126]),
+                                                         (25, 25, 64, [300, 41]), (8, 2, 48, [257])])
 def test_fused_qkv_projection_for_many_rows(n_head, n_kv_head, hd, lens):
     """The q/k/v projection of prompt portions by the pair kernel: queries to the output, keys and values
     from the epilogue into the rows' slots of scattered pages (portions that start in mid-page)."""
