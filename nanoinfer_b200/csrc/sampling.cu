@@ -1,4 +1,5 @@
-// Greedy and temperature / top-k sampling on the device, one block per logits row.
+// Greedy and temperature / top-k sampling on the device: a greedy row is shared by sixteen blocks,
+// a sampled row by the eight blocks of a cluster (or is one block's work when there are many).
 //
 // Semantics are the reference sampler's (crates/core/src/sampler.rs:4-78):
 //   * temperature <= 0: argmax, ties to the lowest index;
@@ -11,10 +12,12 @@
 // per-slot arrays indexed by the row's state slot, so a request's draws do not depend on what
 // else is in the batch.
 //
-// Instead of sorting, the walk is a radix select over order-preserving keys of the
-// scaled logits, four passes of eight bits: first by count (which key is the k-th
-// largest), then by probability mass (where the running sum reaches r).  Mass is kept
-// in 32.32 fixed point so that the sums do not depend on the order of the additions.
+// Instead of sorting, the walk is two selects over order-preserving keys of the scaled
+// logits: first by count (which key is the k-th largest), then by probability mass (where
+// the running sum reaches r).  A select sorts the row into bins that are linear in the
+// distance from the maximum, picks the bin, and settles the exact key among that bin's few
+// tokens with four passes of eight bits.  Mass is kept in 32.32 fixed point so that the
+// sums do not depend on the order of the additions.
 #include "api.h"
 #include "common.cuh"
 
