@@ -480,12 +480,16 @@ extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const 
                           cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (n_rows > 65535 || scratch == nullptr) return NIB_ERR_BAD_ARGUMENT;
-  dim3 grid(SAMPLE_CHUNKS, n_rows);
   // teams != 0: some rows may be sampled, and the launch is made of clusters of SAMPLE_TEAM blocks
   // (a greedy row does not care); a launch of greedy rows only needs no clusters
   static_assert(SAMPLE_CHUNKS % SAMPLE_TEAM == 0, "a row's grid line is whole clusters");
   // (only while all of them fit on the device at once: more rows are better off one block each)
   const int team = (teams && n_rows * SAMPLE_TEAM <= 128) ? SAMPLE_TEAM : 1;
+  // Blocks per row: as many as keep the grid within one wave (a block of 1024 threads has an SM to
+  // itself), at most SAMPLE_CHUNKS, and whole clusters where there are teams.
+  int chunks = SAMPLE_CHUNKS;
+  while (chunks > team && n_rows * chunks > 148) chunks /= 2;
+  dim3 grid(chunks, n_rows);
   launch_pdl_cluster(sample_kernel, dim3(grid), dim3(SAMPLE_THREADS), 0, stream, team, logits, ld, V, row_slot,
                      temperature, top_k, rng_state, out, last_token, scratch, team);
   NIB_LAUNCH_CHECK();
