@@ -433,7 +433,7 @@ constexpr size_t SK_SMEM_TWO_PER_SM = 110 * 1024;
 static int skinny_k_per(int K, int split) { return (((K + split - 1) / split) + 31) / 32 * 32; }
 
 // How many blocks split K.  An exchange through the cluster costs about a microsecond, so K is split
-// only while every block keeps at least 512 of it and no SM gets more than two blocks; and where the
+// only while every block keeps at least 768 of it and no SM gets more than two blocks; and where the
 // rows would not fit in shared memory otherwise.
 static int skinny_split(int M, int N, int K, bool ln) {
   if (ln) return 1;   // the norm needs whole rows
@@ -444,7 +444,7 @@ static int skinny_split(int M, int N, int K, bool ln) {
     if ((s2 - 1) * kp >= K) break;
     // (rows that leave room for one block per SM only are still better unsplit: measured at 64 rows)
     const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_LIMIT;
-    if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 512)) break;
+    if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 768)) break;
     split = s2;
   }
   return split;

@@ -440,9 +440,16 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
     K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
     normed rows and is not split here."""
     N, K = w.shape
-    # measured: up to 16 rows the MMA kernel wins everywhere; up to 64 everywhere but the widest
-    # outputs (the head), where its 16-feature tiles read the rows too often
-    mma = M <= 16 or (M <= SKINNY_MAX_ROWS and N <= 8192)
+    # measured (widths 768, 1024, 1600): up to 16 rows the MMA kernel wins everywhere; up to 32
+    # everywhere but the widest outputs (the head), where its 16-feature tiles read the rows too often;
+    # up to 64 while the rows fit a block's shared memory unsplit (K up to about a thousand) or the
+    # weights are small: beyond that every block would bring in a forced split of long rows
+    if M <= 16:
+        mma = True
+    elif N > 8192 or M > SKINNY_MAX_ROWS:
+        mma = False
+    else:
+        mma = M <= 32 or K <= 1088 or N * K <= 5_000_000
     if mma:
         if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
             return True
