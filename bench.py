@@ -42,6 +42,8 @@ def main() -> int:
     ap.add_argument("--preset", default="gpt2-small")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the preset (recorded in config)")
     ap.add_argument("--skip-points", action="store_true")
+    ap.add_argument("--preheat", type=float, default=1.5,
+                    help="seconds of untimed prefill steps before the timed loops (0: none)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -73,12 +75,14 @@ def main() -> int:
 
     def decode_point(batch: int):
         eng = bs.build_engine(model_dir, "bfloat16", batch, context, max_rows=2048)
+        bs.preheat(eng, args.preheat)
         d = bs.time_decode(eng, batch, prompt_len, steps, warmup)
         del eng
         torch.cuda.empty_cache()
         return d
 
     eng = bs.build_engine(model_dir, "bfloat16", args.batch, context, max_rows=2048)
+    bs.preheat(eng, args.preheat)   # untimed: the device leaves its idle state before anything is timed
     dec = bs.time_decode(eng, args.batch, prompt_len, steps, warmup, clocks=bs.ClockSampler())
     launches = dec["launches_per_step"]
     clock_record = dec["clocks"]

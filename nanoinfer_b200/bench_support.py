@@ -159,9 +159,12 @@ class ClockSampler:
 
 # ----------------------------------------------------------------------------- workloads
 class L2Flusher:
-    """Writes a buffer larger than the 126 MB L2 so that the next step starts with a cold cache."""
+    """Writes a buffer larger than the 126 MB L2 so that the next step starts with a cold cache.
+    The write (1 GiB, about 0.3 ms) also covers the host's preparation of the step that follows it
+    on the stream: the events around the step then bracket device work only, whatever the host's
+    speed (with a 256 MB write the host's packing could outlast it, and the gap was counted)."""
 
-    def __init__(self, device, nbytes: int = 256 << 20):
+    def __init__(self, device, nbytes: int = 1 << 30):
         self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
 
     def flush(self) -> None:
@@ -221,6 +224,31 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     return {"clocks": clock_record, "ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "mean_context": ctx_sum / (len(times) * batch),
             "steps": len(times), "launches_per_step": eng.runner.launches_last_step,
             "graph_replays": eng.runner.graph_replays}
+
+
+def preheat(eng, seconds: float = 1.5, prompt_len: int = 512) -> int:
+    """Keeps the GPU busy with untimed prefill steps for about ``seconds``: a device that has idled
+    (while weights were made on the host, or after another program's pause) takes a moment to reach
+    the clocks and power state it then holds, and the few warm-up steps of a timed loop are over
+    sooner than that.  Returns the number of steps run."""
+    import time
+
+    from .engine.runner import StepItem
+
+    cfg = eng.model.config
+    limit = cfg.n_positions if getattr(cfg, "n_positions", None) else prompt_len
+    n = max(1, min(prompt_len, limit - 1, eng.runner.max_rows))
+    tokens = [(7 * i + 1) % cfg.vocab_size for i in range(n)]
+    t0, steps = time.perf_counter(), 0
+    while time.perf_counter() - t0 < seconds:
+        r = eng.cache.open_request()
+        eng.runner.step([StepItem(r, tokens, [n - 1])])
+        eng.cache.close_request(r)
+        steps += 1
+        if steps % 8 == 0:
+            torch.cuda.synchronize()
+    torch.cuda.synchronize()
+    return steps
 
 
 def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, seed: int = 1) -> Dict[str, float]:
