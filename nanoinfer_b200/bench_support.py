@@ -204,8 +204,9 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     ctx_sum = 0
     torch.cuda.synchronize()
     for s in range(warmup + steps):
-        if s == warmup and clocks is not None:
-            clocks.start()  # sample clocks and throttle reasons during the timed steps only
+        if s == 0 and clocks is not None:
+            clocks.start()  # clocks and throttle reasons under load: the sampler takes a moment to start,
+                            # so it is started with the warm-up steps and runs through the timed ones
         items = [StepItem(r, [t], [0]) for r, t in zip(reqs, last)]
         if flusher is not None:
             flusher.flush()
