@@ -188,6 +188,10 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
 
     cfg = eng.model.config
     g = torch.Generator().manual_seed(seed)
+    if clocks is not None:
+        # clocks and throttle reasons under load: the sampler takes a moment to start, so it is started
+        # before the batch's prompts are run and goes on through the warm-up and the timed steps
+        clocks.start()
     reqs = [eng.cache.open_request() for _ in range(batch)]
     from .sampling.sampler import SamplingParams
     for r in reqs:
@@ -204,9 +208,6 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     ctx_sum = 0
     torch.cuda.synchronize()
     for s in range(warmup + steps):
-        if s == 0 and clocks is not None:
-            clocks.start()  # clocks and throttle reasons under load: the sampler takes a moment to start,
-                            # so it is started with the warm-up steps and runs through the timed ones
         items = [StepItem(r, [t], [0]) for r, t in zip(reqs, last)]
         if flusher is not None:
             flusher.flush()
