@@ -88,10 +88,11 @@ def main() -> int:
     clock_record = dec["clocks"]
     e2e = bs.time_e2e_decode(eng, args.batch, prompt_len, steps, warmup)
     pre = bs.time_prefill(eng, 2, 1024, runs=5, warmup=3)
+    weight_bytes, n_params, kv_groups = bs.weight_bytes_per_step(eng.model), bs.parameter_count(eng.model), eng.cache
     del eng
     torch.cuda.empty_cache()
 
-    step_bytes = bs.weight_bytes_per_step(cfg, 2) + args.batch * dec["mean_context"] * bs.kv_bytes_per_position(cfg, 2)
+    step_bytes = weight_bytes + bs.kv_bytes(kv_groups, [dec["mean_context"]] * args.batch)
     achieved_gbs = step_bytes / (dec["ms_per_step"] / 1e3) / 1e9
     prefill_frac = pre["flops"] / (pre["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12)
     points = {}
@@ -103,7 +104,7 @@ def main() -> int:
         "warmup": warmup, "ms_per_step": dec["ms_per_step"], "higher_is_better": True, "scaling": "weak",
         "vs_baseline": dec["tokens_per_s"] / REFERENCE_B8_TOK_S, "dtype": "bf16", "data": "synthetic",
         "config": {
-            "model": f"{args.preset}-{bs.parameter_count(cfg) / 1e6:.0f}M random weights", "n_layer": cfg.n_layer, "n_layer_full": full_layers,
+            "model": f"{args.preset}-{n_params / 1e6:.0f}M random weights", "n_layer": cfg.n_layer, "n_layer_full": full_layers,
             "n_embd": cfg.n_embd, "n_head": cfg.n_head, "head_dim": cfg.head_dim, "n_inner": cfg.inner_dim,
             "vocab_size": cfg.vocab_size, "n_positions": cfg.n_positions, "global_batch": args.batch,
             "seq_len": context, "prompt_len": prompt_len, "mean_context": round(dec["mean_context"], 1),

@@ -1,10 +1,11 @@
 """Measurement shared by ``bench.py`` and the ``bench`` command: timed decode steps and
 prefill on the engine's own step function, with the byte and FLOP counts of the reference's
-bench (crates/cli/src/bench.rs:261-271, crates/cli/src/metal_batch.rs:113-114,157-160):
+bench (crates/cli/src/bench.rs:261-271, crates/cli/src/metal_batch.rs:113-114,157-160), taken
+from the built model (``measure.py``):
   * decode step bytes = every weight the step uses, once, plus the cached keys and values of
     the live requests;
-  * matrix FLOPs per token = 2 * (layers * (4 C^2 + 2 C I) + V C), the head counted once per
-    logits row, plus the attention products 4 * C * keys per row and layer.
+  * FLOPs = 2 per weight element and row, the head counted once per logits row, plus the
+    attention products 4 * heads * head size * keys per row and layer.
 """
 from __future__ import annotations
 
@@ -68,38 +69,16 @@ def model_folder(preset: str, seed: int, dtype: torch.dtype, n_layer: Optional[i
 
 
 # ----------------------------------------------------------------------------- counts
-def weight_bytes_per_step(cfg, itemsize: int) -> int:
-    """Bytes of the matrices a decode step streams: the blocks and the head (the position table is
-    touched one row per token and left out, as crates/core/src/config.rs:41-48 does)."""
-    c, i = cfg.n_embd, cfg.inner_dim
-    per_layer = c * 3 * c + c * c + c * i + i * c
-    vectors = cfg.n_layer * (3 * c + c + i + c + 4 * c) + 2 * c
-    return (cfg.n_layer * per_layer + cfg.vocab_size * c) * itemsize + vectors * 4
+# (taken from the built model and its cache: ``measure.py``)
+from .measure import kv_bytes, parameter_count, step_flops, weight_bytes_per_step  # noqa: E402
 
 
-def parameter_count(cfg) -> int:
-    """All parameters (crates/core/src/config.rs:29-39: 124,439,808 for GPT-2 small)."""
-    c, i = cfg.n_embd, cfg.inner_dim
-    per_layer = (c * 3 * c + 3 * c) + (c * c + c) + (c * i + i) + (i * c + c) + 4 * c
-    head = 0 if getattr(cfg, "tie_word_embeddings", True) else cfg.vocab_size * c
-    return cfg.n_layer * per_layer + cfg.vocab_size * c + cfg.n_positions * c + 2 * c + head
+def vocabulary(eng) -> int:
+    return eng.model.vocab_size
 
 
-def kv_bytes_per_position(cfg, itemsize: int) -> int:
-    return 2 * cfg.n_layer * cfg.n_embd * itemsize
-
-
-def matrix_flops_per_token(cfg) -> float:
-    c, i = cfg.n_embd, cfg.inner_dim
-    return 2.0 * cfg.n_layer * (4 * c * c + 2 * c * i)
-
-
-def step_flops(cfg, row_contexts: List[int], n_logit_rows: int) -> float:
-    """FLOPs of one step whose rows see ``row_contexts`` keys each."""
-    flops = matrix_flops_per_token(cfg) * len(row_contexts)
-    flops += 2.0 * cfg.vocab_size * cfg.n_embd * n_logit_rows
-    flops += 4.0 * cfg.n_embd * cfg.n_layer * float(sum(row_contexts))
-    return flops
+def context_limit(eng, default: int) -> int:
+    return eng.model.max_positions or default
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -186,7 +165,7 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     flush between steps."""
     from .engine.runner import StepItem
 
-    cfg = eng.model.config
+    vocab = vocabulary(eng)
     g = torch.Generator().manual_seed(seed)
     if clocks is not None:
         # clocks and throttle reasons under load: the sampler takes a moment to start, so it is started
@@ -200,7 +179,7 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     budget = max(1, eng.runner.max_rows // max(1, prompt_len))
     for i in range(0, batch, budget):
         chunk = reqs[i:i + budget]
-        items = [StepItem(r, torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
+        items = [StepItem(r, torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
                  for r in chunk]
         last += eng.runner.step(items, sampler=eng.sampler).tolist()
     flusher = L2Flusher(eng.device) if flush else None
@@ -237,10 +216,9 @@ def preheat(eng, seconds: float = 1.5, prompt_len: int = 512) -> int:
 
     from .engine.runner import StepItem
 
-    cfg = eng.model.config
-    limit = cfg.n_positions if getattr(cfg, "n_positions", None) else prompt_len
+    limit = context_limit(eng, prompt_len + 1)
     n = max(1, min(prompt_len, limit - 1, eng.runner.max_rows))
-    tokens = [(7 * i + 1) % cfg.vocab_size for i in range(n)]
+    tokens = [(7 * i + 1) % vocabulary(eng) for i in range(n)]
     t0, steps = time.perf_counter(), 0
     while time.perf_counter() - t0 < seconds:
         r = eng.cache.open_request()
@@ -257,7 +235,7 @@ def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, s
     """Device time of ONE step that prefills ``n_prompts`` prompts of ``prompt_len`` tokens."""
     from .engine.runner import StepItem
 
-    cfg = eng.model.config
+    vocab = vocabulary(eng)
     g = torch.Generator().manual_seed(seed)
     flusher = L2Flusher(eng.device)
     times = []
@@ -265,7 +243,7 @@ def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, s
         warmup = max(warmup, 4)   # the step function captures a step with prompts the fourth time it sees its shape
     for s in range(warmup + runs):
         reqs = [eng.cache.open_request() for _ in range(n_prompts)]
-        items = [StepItem(r, torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
+        items = [StepItem(r, torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
                  for r in reqs]
         flusher.flush()
         torch.cuda.synchronize()
@@ -283,7 +261,7 @@ def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, s
     tokens = n_prompts * prompt_len
     contexts = [p + 1 for _ in range(n_prompts) for p in range(prompt_len)]
     return {"ms": ms, "tokens": tokens, "tokens_per_s": tokens / (ms / 1e3),
-            "flops": step_flops(cfg, contexts, n_prompts)}
+            "flops": step_flops(eng.model, contexts, n_prompts)}
 
 
 def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 2) -> Dict[str, float]:
@@ -292,11 +270,10 @@ def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, s
     back to the host.  Wall-clock time around the timed steps, device idle before and after."""
     from .sampling.sampler import SamplingParams
 
-    cfg = eng.model.config
     g = torch.Generator().manual_seed(seed)
     params = SamplingParams(max_new_tokens=warmup + steps + 1, temperature=0.0)
     for _ in range(batch):
-        eng.add_request(torch.randint(0, cfg.vocab_size, (prompt_len,), generator=g).tolist(), params)
+        eng.add_request(torch.randint(0, vocabulary(eng), (prompt_len,), generator=g).tolist(), params)
     while any(r.n_pending > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
         eng.step()  # prefill
     for _ in range(warmup):
@@ -374,10 +351,11 @@ def run_cli_bench(args) -> int:
     batches = [int(b) for b in str(args.batch).split(",") if b]
     from .registry import load_config
 
-    cfg = load_config(args.weights)
-    itemsize = 2 if args.dtype == "bfloat16" else 4
-    if args.prompt_len + args.tokens + args.warmup > cfg.n_positions:
-        print(f"prompt_len + tokens must be <= {cfg.n_positions}", file=sys.stderr)
+    from .registry import get_architecture
+    config = load_config(args.weights)
+    limit = get_architecture(config.architecture).build_spec(config).max_positions
+    if limit is not None and args.prompt_len + args.tokens + args.warmup > limit:
+        print(f"prompt_len + tokens must be <= {limit}", file=sys.stderr)
         return 2
     results = []
     for b in batches:
@@ -385,7 +363,7 @@ def run_cli_bench(args) -> int:
                            max_rows=max(2048, b))
         dec = time_decode(eng, b, args.prompt_len, args.tokens, max(3, args.warmup))
         pre = time_prefill(eng, 1, args.prompt_len, args.runs, max(1, args.warmup))
-        step_bytes = weight_bytes_per_step(cfg, itemsize) + b * dec["mean_context"] * kv_bytes_per_position(cfg, itemsize)
+        step_bytes = weight_bytes_per_step(eng.model) + kv_bytes(eng.cache, [dec["mean_context"]] * b)
         ceiling = bw * 1e9 / step_bytes * b
         line = {"dtype": args.dtype, "batch": b, "prompt_len": args.prompt_len, "tokens": args.tokens,
                 "decode_tok_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],

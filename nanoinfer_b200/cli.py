@@ -46,7 +46,10 @@ def cmd_random_weights(args) -> int:
     cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     write_random_model(cfg, args.out, args.seed, dtype)
-    print(f"wrote {args.out} ({cfg.n_params() / 1e6:.1f}M params, {args.dtype}, seed {args.seed})", file=sys.stderr)
+    from .measure import parameter_count_of_spec
+    from .models.model import Model
+    n_params = parameter_count_of_spec(Model(get_architecture(cfg.architecture).build_spec(cfg), cfg))
+    print(f"wrote {args.out} ({n_params / 1e6:.1f}M params, {args.dtype}, seed {args.seed})", file=sys.stderr)
     return 0
 
 
@@ -62,7 +65,8 @@ def cmd_generate(args) -> int:
     prompt = _ids(args.prompt_ids)
     t0 = time.perf_counter()
     eng = Engine(args.weights, dtype=args.dtype, max_batch=1, max_rows=max(64, len(prompt)))
-    print(f"loaded {args.weights} ({eng.model.config.n_params() / 1e6:.1f}M params) in "
+    from .measure import parameter_count
+    print(f"loaded {args.weights} ({parameter_count(eng.model) / 1e6:.1f}M params) in "
           f"{time.perf_counter() - t0:.2f}s", file=sys.stderr)
     params = SamplingParams(max_new_tokens=args.tokens, temperature=args.temperature, top_k=args.top_k,
                             seed=args.seed)

@@ -23,23 +23,6 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
-// Development aid: with -DNIB_AT_TIMING the first softmax thread of every block adds up the cycles it
-// spends in each part of its loop into a buffer set by nib_attention_prefill_tc_timing(); the normal
-// build carries none of it.
-#ifdef NIB_AT_TIMING
-__device__ long long* g_at_stamps = nullptr;
-#define AT_T0 long long at_t_ = clock64(); long long at_acc_[8] = {0, 0, 0, 0, 0, 0, 0, 0}; const long long at_start_ = at_t_
-#define AT_LAP(i) do { const long long n_ = clock64(); at_acc_[(i)] += n_ - at_t_; at_t_ = n_; } while (0)
-#define AT_FLUSH(n_it) do { long long* b_ = g_at_stamps; if (b_ && threadIdx.x == 64) { b_ += 16 * (blockIdx.y * gridDim.x + blockIdx.x); \
-    for (int i_ = 0; i_ < 8; ++i_) b_[i_] = at_acc_[i_]; b_[8] = clock64() - at_start_; b_[9] = (n_it); } } while (0)
-#define AT_FLUSH_MMA() do { long long* b_ = g_at_stamps; if (b_) { b_ += 16 * (blockIdx.y * gridDim.x + blockIdx.x); \
-    for (int i_ = 0; i_ < 4; ++i_) b_[10 + i_] = at_acc_[i_]; } } while (0)
-#else
-#define AT_T0 do { } while (0)
-#define AT_LAP(i) do { } while (0)
-#define AT_FLUSH(n_it) do { } while (0)
-#define AT_FLUSH_MMA() do { } while (0)
-#endif
 
 namespace nib {
 
@@ -227,12 +210,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const uint32_t idesc_o = umma_idesc(AT_BM, AT_HD) | (1u << 16);   // B (= V) is MN-major: keys down the rows
       const uint32_t o_tmem = tmem_base + O_COL;
       // scores of tile `it` into buffer it % AT_NBUF (free: P of tile it - AT_NBUF was made from it)
-      AT_T0;
       auto issue_s = [&](int it) -> bool {
         const int st = it % AT_STAGES;
-        AT_LAP(3);
         if (!mbar_wait(&k_full[st], (it / AT_STAGES) & 1, abort_flag)) return false;
-        AT_LAP(0);
         tc_fence_after();
         const uint32_t qa = smem_u32(q_s), kb = smem_u32(k_s + st * AT_KV_STAGE);
 #pragma unroll
@@ -248,11 +228,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       for (int a = 1; ok && a < AT_NBUF && a < n_it; ++a) ok = issue_s(a);
       for (int it = 0; ok && it < n_it; ++it) {
         const int st = it % AT_STAGES, b = it % AT_NBUF;
-        AT_LAP(3);
         if (!mbar_wait(&v_full[st], (it / AT_STAGES) & 1, abort_flag)) break;
-        AT_LAP(1);
         if (!mbar_wait(&p_full[b], (it / AT_NBUF) & 1, abort_flag)) break;
-        AT_LAP(2);
         tc_fence_after();
         const uint32_t vb = smem_u32(v_s + st * AT_KV_STAGE);
         const uint32_t pa = smem_u32(p_s + b * P_BYTES);
@@ -264,8 +241,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_commit(&v_empty[st]);
         if (it + AT_NBUF < n_it) ok = issue_s(it + AT_NBUF);
       }
-      AT_LAP(3);
-      AT_FLUSH_MMA();
     }
     __syncwarp();
   } else {
@@ -279,19 +254,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const float scale2 = prm.scale * 1.4426950408889634f;
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
-    AT_T0;
     for (int it = 0; it < n_it; ++it) {
       const int b = it % AT_NBUF;
       ok = warp_mbar_wait(&s_full[b], (it / AT_NBUF) & 1, abort_flag, lane);
       if (!ok) break;
       tc_fence_after();
-      AT_LAP(0);
       const int j0 = (tile_first + it) * AT_BN;
       const bool edge = j0 + AT_BN - 1 > wp0 || (window > 0 && j0 < wp1 - window + 1);   // only these tiles need the mask
       float v[AT_BN];
 #pragma unroll
       for (int c = 0; c < AT_BN / 32; ++c) tmem_ld32(lane_addr + (uint32_t)(b * AT_BN + c * 32), v + c * 32);
-      AT_LAP(1);
       if (edge) {
 #pragma unroll
         for (int i = 0; i < AT_BN; ++i)
@@ -309,7 +281,6 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mx *= scale2;   // (scale2 > 0)
       // Raise the running maximum?  At the first tile it is set; later only when some row of the warp
       // exceeds its own by more than 2^AT_RAISE (or has had no key yet), and then O is scaled down.
-      AT_LAP(2);
       const bool raise = it == 0 || __any_sync(0xffffffffu, mx > m + AT_RAISE || (m == -INFINITY && mx > m));
       if (raise) {
         const float m_new = fmaxf(m, mx);
@@ -333,13 +304,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       // a row with no key yet (all masked so far) keeps m = -inf; 2^(-inf - -inf) is avoided
       const float ms = (m == -INFINITY) ? 0.0f : m;
-      AT_LAP(3);
       // P of tile it - AT_NBUF (the last user of this buffer) has been read by its MMA
       if (it >= AT_NBUF) {
         ok = warp_mbar_wait(&o_full[b], ((it - AT_NBUF) / AT_NBUF) & 1, abort_flag, lane);
         if (!ok) break;
       }
-      AT_LAP(4);
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       uint8_t* blk0 = p_s + b * P_BYTES + r * 128;
 #pragma unroll
@@ -355,16 +324,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             make_uint4(pack_bf16(e8[0], e8[1]), pack_bf16(e8[2], e8[3]), pack_bf16(e8[4], e8[5]), pack_bf16(e8[6], e8[7]));
       }
       l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
-      AT_LAP(5);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the MMAs
       tc_fence_before();
       asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(&p_full[b])) : "memory");
-      AT_LAP(6);
     }
     // the last MMA into O
     if (ok) ok = warp_mbar_wait(&o_full[(n_it - 1) % AT_NBUF], ((n_it - 1) / AT_NBUF) & 1, abort_flag, lane);
-    AT_LAP(7);
-    AT_FLUSH(n_it);
     if (ok) {
       tc_fence_after();
       const float inv = l > 0.0f ? 1.0f / l : 0.0f;
@@ -439,8 +404,3 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
   NIB_LAUNCH_CHECK();
 }
 
-#ifdef NIB_AT_TIMING
-extern "C" int nib_attention_prefill_tc_timing(long long* buf) {
-  return (int)cudaMemcpyToSymbol(g_at_stamps, &buf, sizeof(buf));
-}
-#endif

@@ -31,16 +31,6 @@
 #include "common.cuh"
 #include "tcgen05.cuh"
 
-// Development aid: with -DNIB_TC_TIMING every block writes cycle stamps of its phases to a buffer set
-// by nib_linear_tc_timing(); the normal build carries none of it.
-#ifdef NIB_TC_TIMING
-__device__ long long* g_tc_stamps = nullptr;
-#define TC_STAMP_INIT long long* tc_stamps_ = g_tc_stamps ? g_tc_stamps + 64 * (blockIdx.z * gridDim.y * gridDim.x + blockIdx.y * gridDim.x + blockIdx.x) : nullptr
-#define TC_STAMP(i) do { if (tc_stamps_) tc_stamps_[(i)] = clock64(); } while (0)
-#else
-#define TC_STAMP_INIT do { } while (0)
-#define TC_STAMP(i) do { } while (0)
-#endif
 
 namespace nib {
 
@@ -108,8 +98,6 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                  const __grid_constant__ CUtensorMap map_o, const TcParams prm) {
   pdl_trigger();
-  TC_STAMP_INIT;
-  if (threadIdx.x == 0) TC_STAMP(0);
   extern __shared__ uint8_t smem_raw[];
   // tiles must start on a 1024-byte boundary for the 128-byte swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -163,7 +151,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
   // Only the producer goes on before the kernel ahead has finished: it asks for the WEIGHT tiles of
   // the first stages (they do not depend on that kernel), and waits before it asks for activations.
   if (warp != 0) pdl_wait();
-  if (threadIdx.x == 32) TC_STAMP(1);
 
   if (warp == 0) {
     // ---------------- TMA producer.  Issuing a stage costs one thread several hundred cycles (a wait,
@@ -191,7 +178,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     if (lane < L) {
       for (int kb = lane; kb < first_round; kb += L) {
         uint8_t* sp = smem + (size_t)kb * stage_bytes;
-        if (kb < 12) TC_STAMP(8 + kb);
         for (int sub = 0; sub < k_sub; ++sub) {
           const int kb64 = kb_begin + kb * k_sub + sub;
           const int kx = (kb64 < kb_end ? kb64 : (prm.K + TC_BK - 1) / TC_BK) * TC_BK;
@@ -205,7 +191,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
         const uint32_t parity = ((kb / stages) & 1) ^ 1;
         if (!mbar_wait(&empty_bar[s], parity, abort_flag)) break;
         uint8_t* sp = smem + (size_t)s * stage_bytes;
-        if (kb < 12) TC_STAMP(8 + kb);
         mbar_expect_tx(&full_bar[s], stage_bytes);
         for (int sub = 0; sub < k_sub; ++sub) {
           // a block past this split's end is asked for past the end of K: it arrives as zeros
@@ -242,7 +227,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
       if (!warp_mbar_wait(&full_bar[s], parity, abort_flag, lane)) break;
       tc_fence_after();
       if (lane == 0) {
-        if (kb < 12) TC_STAMP(20 + kb);
         for (int sub = 0; sub < k_sub; ++sub) {
           const uint32_t pa = lo_stage + sub * p_step;
           const uint32_t qa = ln ? q_res0 + (uint32_t)(kb * k_sub + sub) * q_step : lo_stage + q_off + sub * q_step;
@@ -267,7 +251,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     }
     if (lane == 0) {
       umma_commit(&tmem_full_bar);  // arrives when every MMA above has finished
-      TC_STAMP(2);
     }
     __syncwarp();
   } else {
@@ -325,7 +308,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const bool ok = (epi_ok_sh[0] & epi_ok_sh[1] & epi_ok_sh[2] & epi_ok_sh[3]) != 0;
     tc_fence_after();
-    if (threadIdx.x == 64) TC_STAMP(3);
     const bool p_ok = p < prm.p_rows;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
 
@@ -377,7 +359,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             }
           }
         }
-        if (threadIdx.x == 64) TC_STAMP(4);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
         asm volatile("bar.sync 1, 128;" ::: "memory");                // the four epilogue warps
         if (warp == 2 && lane == 0) {
@@ -389,7 +370,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           }
           asm volatile("cp.async.bulk.commit_group;" ::: "memory");
           asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
-          TC_STAMP(5);
         }
       } else {
         // out[p, q0 + c0 + j] with plain stores: this thread writes 16 consecutive features of its row
@@ -499,7 +479,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
           }
         }
         if (prm.tma_store) {
-          if (threadIdx.x == 64) TC_STAMP(4);
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to TMA
           asm volatile("bar.sync 1, 128;" ::: "memory");
           if (warp == 2 && lane == 0) {
@@ -507,7 +486,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             else tma_store_2d(&map_o, smem, p0, q0);
             asm volatile("cp.async.bulk.commit_group;" ::: "memory");
             asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // shared memory may go away now
-            TC_STAMP(5);
           }
         }
       }
@@ -520,7 +498,6 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
     tmem_dealloc(tmem_base, tmem_cols);
   }
   if (threadIdx.x == 0 && abort_sh) *prm.status = NIB_STATUS_WAIT_TIMEOUT;
-  if (threadIdx.x == 0) TC_STAMP(6);
 }
 
 // ------------------------------------------------------------------ host side
@@ -774,8 +751,3 @@ extern "C" int nib_linear_tc_small(int out_dtype, const void* a, int lda, const 
                    cache ? &kv : nullptr, fix_partials ? &fix : nullptr, status, stream);
 }
 
-#ifdef NIB_TC_TIMING
-extern "C" int nib_linear_tc_timing(long long* buf) {
-  return (int)cudaMemcpyToSymbol(g_tc_stamps, &buf, sizeof(buf));
-}
-#endif

@@ -34,7 +34,7 @@ import torch
 from ..cache.manager import CacheManager, RequestCache
 from ..kernels import ops
 from ..models.model import Model
-from ..parts.base import StepContext, Workspace
+from ..parts.base import StepContext, StepLimits, Workspace
 
 
 class StepError(ValueError):
@@ -89,8 +89,6 @@ class _Captured:
     launches: int
 
 
-#: decode graphs are shaped by the longest key range rounded up to this many positions
-GRAPH_KEY_BUCKET = 256
 #: batches of more than PAD_FROM single tokens are padded to a multiple of PAD_TO rows
 PAD_FROM, PAD_TO = 8, 8
 
@@ -105,10 +103,19 @@ class ModelRunner:
         self.max_rows, self.max_entries = int(max_rows), int(max_entries)
         self.check_status = check_status
         on_gpu = self.device.type == "cuda"
-        # a mixer with state of its own may plan its work on the host, which a graph would freeze
-        self.use_graphs = bool(use_graphs) and on_gpu and not model.state_needs()
+        # a mixer may plan its work on the host in ways that a graph would freeze: every mixer says
+        # whether its launches follow from the step's shape alone
+        self.use_graphs = bool(use_graphs) and on_gpu and model.capture_safe()
         self.max_graphs = max_graphs
         self.workspace = Workspace(self.device)
+        #: what each kind of part derives on the host from a step's shape, by name
+        self._planners = model.step_planners()
+        # Scratch is sized here, once, for the largest step: a captured graph holds raw addresses,
+        # so no buffer may move while graphs are live (the reference sizes every buffer once as
+        # well, from max_rows and max_seqs: crates/metal/src/batch.rs:159-193).
+        limit = model.max_positions or max(cache.max_blocks, default=0) * cache.page_size
+        model.reserve(self.workspace, StepLimits(self.max_rows, self.max_entries, int(limit), model.dtype))
+        self._graph_generation = self.workspace.generation
         self.status = ops.status_word() if on_gpu else torch.zeros(1, dtype=torch.int32)
         n_tables = sum(self.max_entries * mb for mb in cache.max_blocks)
         cap = 7 * self.max_rows + 8 * self.max_entries + 16 + n_tables
@@ -124,6 +131,8 @@ class ModelRunner:
         self._meta_dev = torch.empty(cap, dtype=torch.int32, device=self.device)
         self._arange = np.arange(self.max_entries + 1, dtype=np.int32)
         self._graphs: Dict[tuple, _Captured] = {}
+        #: how often the graphs had to be dropped because a scratch buffer was replaced
+        self.graph_drops = 0
         self._seen: Dict[tuple, int] = {}
         self.steps_run = 0
         self.graph_replays = 0
@@ -164,6 +173,8 @@ class ModelRunner:
             for w in it.want:
                 if not 0 <= int(w) < n:
                     raise StepError(f"want index {w} is outside the item's {n} tokens")
+            if len(set(int(w) for w in it.want)) != len(it.want):
+                raise StepError("a want index is given twice")   # (one logits row per place, whatever the mix)
             n_rows += n
         if n_rows > self.max_rows:
             raise TooManyRows(f"{n_rows} rows > max_rows {self.max_rows}")
@@ -190,7 +201,26 @@ class ModelRunner:
         lay.tabs, lay.total = tuple(tabs), o
         return lay
 
-    def _context(self, lay: _Layout, plan, starts, pos0s, slots, max_q: int, max_kv: int, sampler=None):
+    def _plans(self, starts, pos0s):
+        """The step's plans by name, and their words in one list."""
+        plans = {name: make(starts, pos0s, self.use_graphs) for name, make in self._planners.items()}
+        words: List[int] = []
+        for p in plans.values():
+            words += p.words
+        return plans, words
+
+    def _drop_graphs(self) -> None:
+        """A scratch buffer was replaced by a larger one: every captured graph may hold the old
+        address.  Drop them all; only then is the replaced memory let go."""
+        if self._graphs:
+            self.graph_drops += 1
+        self._graphs.clear()
+        self._seen.clear()
+        torch.cuda.synchronize(self.device)      # nothing in flight still uses the old buffers
+        self.workspace.release_retired()
+        self._graph_generation = self.workspace.generation
+
+    def _context(self, lay: _Layout, plans, starts, pos0s, slots, max_q: int, max_kv: int, sampler=None):
         dev = self._meta_dev
         T, E, M = lay.T, lay.E, lay.M
         ctx = StepContext(
@@ -201,8 +231,11 @@ class ModelRunner:
             host_entry_start=starts, host_entry_pos0=pos0s, host_entry_slot=slots,
             max_q_len=max_q, max_kv_len=max_kv, token_feedback=getattr(sampler, "last_token", None),
         )
-        plan.bind(dev[lay.plan:lay.plan + lay.n_plan])
-        ctx.attention_plan = plan
+        at = lay.plan
+        for p in plans.values():
+            p.bind(dev[at:at + len(p.words)] if p.words else None)
+            at += len(p.words)
+        ctx.plans = plans
         tables = [dev[off:off + E * mb].view(E, mb) for off, mb in zip(lay.tabs, self.cache.max_blocks)]
         caches = self.cache.layer_views(tables)
         logit_rows = dev[lay.lrow:lay.lrow + M] if M else None
@@ -251,10 +284,8 @@ class ModelRunner:
             starts = self._arange[:E + 1].tolist()
             M = len(want_rows)
             max_q, max_kv = 1, max(pos0s) + 1
-            plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
-            if self.use_graphs:  # the split of the keys must not change from step to step of a graph
-                plan.max_decode_keys = -(-plan.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
-            lay = self._layout(T, E, M, len(plan.host))
+            plans, plan_words = self._plans(starts, pos0s)
+            lay = self._layout(T, E, M, len(plan_words))
             buf[lay.tok:lay.tok + T] = tokens_in
             buf[lay.pos:lay.pos + T] = pos0s
             buf[lay.ent:lay.ent + T] = self._arange[:E]
@@ -270,10 +301,8 @@ class ModelRunner:
                 pos0s.append(p0)
                 slots.append(it.request.slot)
                 max_q, max_kv = max(max_q, n), max(max_kv, p0 + n)
-            plan = ops.AttentionPlan(starts, pos0s, self.device, bind=False)
-            if self.use_graphs:
-                plan.max_decode_keys = -(-plan.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
-            lay = self._layout(T, E, M, len(plan.host))
+            plans, plan_words = self._plans(starts, pos0s)
+            lay = self._layout(T, E, M, len(plan_words))
             lrow = lay.lrow
             for e, it in enumerate(items):
                 a, n, p0 = starts[e], len(it.tokens), pos0s[e]
@@ -288,7 +317,7 @@ class ModelRunner:
         buf[lay.pos0:lay.pos0 + E] = pos0s
         buf[lay.slot:lay.slot + E] = slots
         if lay.n_plan:
-            buf[lay.plan:lay.plan + lay.n_plan] = plan.host
+            buf[lay.plan:lay.plan + lay.n_plan] = plan_words
         for gi, (off, mb) in enumerate(zip(lay.tabs, self.cache.max_blocks)):
             tab = buf[off:off + E * mb].reshape(E, mb)
             for e, it in enumerate(items):
@@ -302,12 +331,17 @@ class ModelRunner:
             copied.record()
         self.last_logit_slot = self._meta_dev[lay.lslot:lay.lslot + M] if M else None
 
-        # a graph bakes in the shape of the step only: row, entry and logits counts, how the rows
-        # split into single tokens and 64-row prompt tiles, and the split of the decode keys
+        # a graph bakes in the shape of the step only: row, entry and logits counts, and what each
+        # plan says it fixes (for attention: how the rows split into single tokens and prompt tiles,
+        # and the split of the decode keys)
         key = None
         if self.use_graphs:
-            key = (T, E, M, plan.n_decode, plan.n_prefill_rows, plan.n_tiles, plan.n_wide_tiles,
-                   plan.max_decode_keys, id(sampler), getattr(sampler, "any_sampled", None))
+            if self.workspace.generation != self._graph_generation:
+                self._drop_graphs()
+            key = (T, E, M, tuple((name, p.graph_key()) for name, p in plans.items()), id(sampler),
+                   getattr(sampler, "any_sampled", None), getattr(sampler, "generation", None))
+        elif self.workspace.retired:
+            self.workspace.release_retired()     # no graphs: the stream's order alone protects old buffers
         cap = self._graphs.get(key) if key is not None else None
         if cap is not None:
             self._graphs[key] = self._graphs.pop(key)   # most recently used last
@@ -316,7 +350,7 @@ class ModelRunner:
             logits, tokens = cap.logits, cap.tokens
             self.launches_last_step = cap.launches
         else:
-            args = self._context(lay, plan, starts, pos0s, slots, max_q, max_kv, sampler)
+            args = self._context(lay, plans, starts, pos0s, slots, max_q, max_kv, sampler)
             n_seen = self._seen.get(key, 0) if key is not None else 0
             # A shape that was run already (scratch is sized, attributes are set) is captured: a batch
             # of single tokens the second time it comes, since it will come again step after step; a
@@ -339,11 +373,20 @@ class ModelRunner:
                 finally:
                     if gc_was_on:
                         gc.enable()
-                cap = _Captured(graph, logits, tokens, ops.launch_count() - before)
-                self._graphs[key] = cap
-                graph.replay()
-                self.graph_replays += 1
-                self.launches_last_step = cap.launches
+                if self.workspace.generation != self._graph_generation or (
+                        getattr(sampler, "generation", None) != key[-1]):
+                    # a buffer moved while the step was being captured (a shape that was run before
+                    # never does this; a part that sizes scratch by something else might): the new
+                    # graph mixes old and new addresses, so it is not kept, and the step runs plainly
+                    del graph
+                    self._drop_graphs()
+                    logits, tokens = self._run(*args, M, sampler)
+                else:
+                    cap = _Captured(graph, logits, tokens, ops.launch_count() - before)
+                    self._graphs[key] = cap
+                    graph.replay()
+                    self.graph_replays += 1
+                    self.launches_last_step = cap.launches
             else:
                 before = ops.launch_count()
                 logits, tokens = self._run(*args, M, sampler)

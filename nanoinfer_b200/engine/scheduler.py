@@ -139,6 +139,11 @@ class Scheduler:
             req.cache = None
         if req in self.running:
             self.running.remove(req)
+        # a request that was preempted waits in the queue while its last token is still read one
+        # step late: an end token found then must take it out of the queue as well, or it would be
+        # admitted again and go on past its end
+        if req.state == WAITING and req in self.waiting:
+            self.waiting.remove(req)
         req.state, req.finish_reason = FINISHED, reason
 
     def _preempt(self, req: Request) -> None:

@@ -535,12 +535,25 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
            "attention_simt")
 
 
+#: blocks of the decode attention that the device holds at once (six an SM): the keys are split so
+#: that (rows x heads x splits) stays within it, which also bounds the scratch of the partial results
+DECODE_RESIDENT_BLOCKS = 888
+
+
 def decode_split(n_rows: int, n_head: int, max_keys: int) -> tuple:
     """(chunk, n_splits): keys per split (a multiple of 64) so that the blocks fill the GPU once: six
     blocks an SM are resident, and a block that comes after the first wave runs nearly alone."""
-    want = max(1, 888 // max(1, n_rows * n_head))
+    want = max(1, DECODE_RESIDENT_BLOCKS // max(1, n_rows * n_head))
     chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
     return chunk, max(1, -(-max_keys // chunk))
+
+
+def attention_decode_reserve(workspace, n_head: int, head_dim: int) -> None:
+    """Size the decode attention's scratch for good: keys are split only while rows x heads x splits
+    fits the resident blocks, so that many partial results (head_dim values, a maximum and a sum
+    each) and that many arrival counters are the most any step needs."""
+    workspace.reserve("attention.partials", DECODE_RESIDENT_BLOCKS * (head_dim + 2), torch.float32)
+    workspace.reserve("attention.arrivals", DECODE_RESIDENT_BLOCKS, torch.int32, zeroed=True)
 
 
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
@@ -555,8 +568,10 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     chunk, n_splits = decode_split(n_rows, n_head, max_keys)
     scratch = counters = None
     if n_splits > 1:
-        scratch = workspace.get("attention.partials", (n_rows * n_head * n_splits * (head_dim + 2),), torch.float32)
-        counters = workspace.get_zeroed("attention.arrivals", (n_rows * n_head,), torch.int32)
+        # (never more than the resident blocks: the same size every step, so that the buffers stay put)
+        assert n_rows * n_head * n_splits <= DECODE_RESIDENT_BLOCKS
+        scratch = workspace.get("attention.partials", (DECODE_RESIDENT_BLOCKS * (head_dim + 2),), torch.float32)
+        counters = workspace.get_zeroed("attention.arrivals", (DECODE_RESIDENT_BLOCKS,), torch.int32)
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
@@ -596,56 +611,13 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, b
            "attention_prefill")
 
 
-class AttentionPlan:
-    """Which rows of a step are single decoded tokens and which belong to prompt portions; the
-    same for every layer of the step."""
-
-    def __init__(self, entry_start, entry_pos0, device, bind=True):
-        dec, pre, tiles = [], [], []
-        self.max_decode_keys = 0
-        for e in range(len(entry_start) - 1):
-            a, b = entry_start[e], entry_start[e + 1]
-            if b - a == 1:
-                dec.append(a)
-                self.max_decode_keys = max(self.max_decode_keys, entry_pos0[e] + 1)
-            else:
-                pre.extend(range(a, b))
-                tiles.extend((e, off) for off in range(0, b - a, 64))
-        # the same portions in tiles of 128 rows, for the tcgen05 kernel
-        wide = [(e, off) for e in range(len(entry_start) - 1) if entry_start[e + 1] - entry_start[e] > 1
-                for off in range(0, entry_start[e + 1] - entry_start[e], 128)]
-        # the tiles that reach furthest back have the most keys to go through: they are launched first,
-        # so that the short ones fill the gaps at the end
-        tiles.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
-        wide.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
-        self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
-        self.n_wide_tiles = len(wide)
-        flat = dec + pre + [v for t in tiles for v in t] + [v for t in wide for v in t]
-        self.host = flat
-        if bind:
-            self.bind(torch.tensor(flat, dtype=torch.int32, device=device) if flat else None)
-
-    def bind(self, buf) -> None:
-        """``buf``: a device int32 tensor holding ``self.host``."""
-        nd, npre = self.n_decode, self.n_prefill_rows
-        all_decode = npre == 0
-        # rows 0..n-1 in order need no index list
-        self.decode_rows = None if all_decode or nd == 0 else buf[:nd]
-        self.prefill_rows = None if nd == 0 or npre == 0 else buf[nd:nd + npre]
-        self.tiles = buf[nd + npre:nd + npre + 2 * self.n_tiles] if self.n_tiles else None
-        at = nd + npre + 2 * self.n_tiles
-        self.wide_tiles = buf[at:at + 2 * self.n_wide_tiles] if self.n_wide_tiles else None
-
-
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
-              n_head: int, scale: float, window: int) -> None:
-    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's StepContext.
-    Single decoded tokens go to the split-KV kernel; prompt portions go to the tiled tensor-core
-    kernel in bfloat16 (head sizes 16..128 in steps of 16) and to the general kernel otherwise."""
-    plan = getattr(ctx, "attention_plan", None)
-    if plan is None:
-        plan = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, q.device)
-        ctx.attention_plan = plan
+              n_head: int, scale: float, window: int, plan) -> None:
+    """Causal attention of the step's rows over one cache layer.  ``ctx`` is the step's StepContext,
+    ``plan`` says which rows are single decoded tokens and how the prompt portions are cut into
+    tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
+    prompt portions go to the tiled tensor-core kernels in bfloat16 (head sizes 16..128 in steps of
+    16) and to the general kernel otherwise."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     fast_pages = page_size % 16 == 0 and head_dim % 8 == 0 and head_dim <= 128
     if not fast_pages:
@@ -679,27 +651,24 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
            "argmax")
 
 
-_sample_scratch: Optional[torch.Tensor] = None
-
-
 def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperature: torch.Tensor,
-           top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor,
+           top_k: torch.Tensor, rng_state: torch.Tensor, out: torch.Tensor, scratch: torch.Tensor,
            last_token: Optional[torch.Tensor] = None, teams: bool = True) -> None:
     """One token per row.  ``temperature``, ``top_k`` and ``rng_state`` are per-slot arrays and
     ``row_slot`` names each row's slot: greedy where the slot's temperature <= 0, else
     temperature / top-k sampling that advances the slot's xorshift64* word.  ``last_token``: a
     per-slot array that also receives the tokens (for the next step's embedding).  ``teams``: launch
     clusters of blocks that share a sampled row's passes over the vocabulary (False when every row
-    is known to be greedy; the tokens are the same either way)."""
+    is known to be greedy; the tokens are the same either way).  ``scratch``: two int64 words per
+    row that the kernel finds zero and leaves zero (the caller owns them, so that they stay where
+    they are for as long as a captured launch may use them)."""
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("sample: logits must be float32 with contiguous rows")
     if rng_state.dtype != torch.int64 or temperature.dtype != torch.float32:
         raise KernelError("sample: rng_state must be int64 words, temperature float32")
     _i32(row_slot, "row_slot"); _i32(top_k, "top_k"); _i32(out, "out")
-    global _sample_scratch
-    if _sample_scratch is None or _sample_scratch.numel() < 2 * n_rows:
-        # two words per row that the kernel finds zero and leaves zero
-        _sample_scratch = torch.zeros(2 * max(n_rows, 256), dtype=torch.int64, device=logits.device)
+    if scratch.dtype != torch.int64 or scratch.numel() < 2 * n_rows or out.numel() < n_rows:
+        raise KernelError("sample: scratch must hold two int64 words per row, out one int32")
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
                                 _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
-                                _ptr(last_token), _ptr(_sample_scratch), int(bool(teams)), _stream()), "sample")
+                                _ptr(last_token), _ptr(scratch), int(bool(teams)), _stream()), "sample")

@@ -43,17 +43,19 @@ class Model:
             if ls.arrangement not in BLOCKS:
                 raise KeyError(f"unknown block arrangement {ls.arrangement!r}; registered: {sorted(BLOCKS)}")
             w = f"layers[{i}]"
-            mixer_args = dict(ls.mixer.args)
-            if ls.mixer_position is not None:
-                mixer_args["position"] = self._build(P.POSITIONS, ls.mixer_position, w + ".mixer_position")
-            mixer = self._build(P.MIXERS, PartSpec(ls.mixer.kind, mixer_args, ls.mixer.tensors), w + ".mixer")
-            self.layers.append(BLOCKS[ls.arrangement](
-                spec.width,
-                self._build(P.NORMS, ls.norm_1, w + ".norm_1"),
-                mixer,
-                self._build(P.NORMS, ls.norm_2, w + ".norm_2"),
-                self._build(P.FEED_FORWARDS, ls.feed_forward, w + ".feed_forward"),
-            ))
+            cls = BLOCKS[ls.arrangement]
+            built: Dict[str, P.Part] = {}
+            for name, ps in ls.parts.items():
+                if name not in cls.slots:
+                    raise ValueError(f"{w}: the {ls.arrangement!r} arrangement has no part {name!r} "
+                                     f"(it is made of {sorted(cls.slots)})")
+                registry = cls.slots[name]
+                if registry is P.MIXERS and ls.mixer_position is not None:
+                    args = dict(ps.args)
+                    args["position"] = self._build(P.POSITIONS, ls.mixer_position, f"{w}.mixer_position")
+                    ps = PartSpec(ps.kind, args, ps.tensors)
+                built[name] = self._build(registry, ps, f"{w}.{name}")
+            self.layers.append(cls(spec.width, built))
         self.final_norm = self._build(P.NORMS, spec.final_norm, "final_norm")
         self.head = self._build(P.HEADS, spec.head, "head")
         self.schedule = list(spec.schedule)
@@ -81,11 +83,15 @@ class Model:
             if e.cache_of is not None:
                 if not 0 <= e.cache_of < i or self.schedule[e.cache_of].cache_of is not None:
                     raise ValueError(f"schedule[{i}].cache_of must name an earlier entry that owns a cache")
-                a = self.layers[e.layer].mixer.kv_spec()
-                b = self.layers[self.schedule[e.cache_of].layer].mixer.kv_spec()
+                a = self._kv_spec(e.layer)
+                b = self._kv_spec(self.schedule[e.cache_of].layer)
                 if a is None or a != b:
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {e.cache_of}: "
                                      f"their key/value needs differ ({a} vs {b})")
+
+    def _kv_spec(self, layer: int) -> Optional[P.KVCacheSpec]:
+        mixer = self.layers[layer].mixer
+        return mixer.kv_spec() if mixer is not None else None
 
     def bindings(self) -> List[Binding]:
         return list(self._bindings)
@@ -120,7 +126,7 @@ class Model:
         """(schedule index, need) for every run that owns paged keys and values."""
         out = []
         for i, e in enumerate(self.schedule):
-            spec = self.layers[e.layer].mixer.kv_spec()
+            spec = self._kv_spec(e.layer)
             if spec is not None and e.cache_of is None:
                 out.append((i, spec))
         return out
@@ -129,10 +135,38 @@ class Model:
         """(schedule index, need) for every run whose mixer keeps per-request state of fixed size."""
         out = []
         for i, e in enumerate(self.schedule):
-            spec = self.layers[e.layer].mixer.state_spec()
+            mixer = self.layers[e.layer].mixer
+            spec = mixer.state_spec() if mixer is not None else None
             if spec is not None:
                 out.append((i, spec))
         return out
+
+    def capture_safe(self) -> bool:
+        """Whether a step of this model may be captured in a CUDA graph: every mixer says so."""
+        return all(getattr(blk.mixer, "capture_safe", True) for blk in self.layers if blk.mixer is not None)
+
+    def step_planners(self) -> Dict[str, object]:
+        """name -> factory of the per-step plans that the model's parts ask for (parts that give the
+        same name share one plan a step)."""
+        out: Dict[str, object] = {}
+        for part in self.all_parts():
+            got = part.step_planner()
+            if got is not None:
+                out.setdefault(got[0], got[1])
+        return out
+
+    def reserve(self, workspace: P.Workspace, limits: P.StepLimits) -> None:
+        """Size the scratch of the forward pass and of every part for the largest step.  Logits are
+        sized for one row per batch entry (what generation asks for); a step that wants more (a
+        replay that asks for every position) makes them grow, which drops captured graphs."""
+        workspace.reserve("model.residual", limits.max_rows * self.width, torch.float32)
+        n = max(limits.max_entries, 1)
+        workspace.reserve("model.final", n * self.width, limits.dtype)
+        workspace.reserve("model.logits", n * _round_up(self.vocab_size, 16), torch.float32)
+        for part in self.all_parts():
+            part.reserve(workspace, limits)
+        for blk in self.layers:
+            blk.reserve(workspace, limits)
 
     @property
     def vocab_size(self) -> int:

@@ -22,15 +22,26 @@ class PartSpec:
     tensors: Dict[str, TensorRef] = field(default_factory=dict)   # parameter key -> checkpoint tensor
 
 
-@dataclass
 class LayerSpec:
-    arrangement: str                            # registered name of the block arrangement
-    norm_1: PartSpec
-    mixer: PartSpec
-    norm_2: PartSpec
-    feed_forward: PartSpec
-    #: a position encoding that acts inside the mixer (on queries and keys), if any
-    mixer_position: Optional[PartSpec] = None
+    """One layer: the registered name of its arrangement and a part for each of the names that
+    arrangement is made of (for the pre-norm block: ``norm_1``, ``mixer``, ``norm_2``,
+    ``feed_forward``), given as keywords or as the ``parts`` dictionary."""
+
+    def __init__(self, arrangement: str, parts: Optional[Dict[str, PartSpec]] = None,
+                 mixer_position: Optional[PartSpec] = None, **named: PartSpec):
+        self.arrangement = arrangement              # registered name of the block arrangement
+        self.parts: Dict[str, PartSpec] = {**(parts or {}), **named}
+        #: a position encoding that acts inside the mixer (on queries and keys), if any
+        self.mixer_position = mixer_position
+
+    def __getattr__(self, name: str) -> PartSpec:
+        parts = self.__dict__.get("parts", {})
+        if name in parts:
+            return parts[name]
+        raise AttributeError(name)
+
+    def __repr__(self) -> str:
+        return f"LayerSpec({self.arrangement!r}, {self.parts!r}, mixer_position={self.mixer_position!r})"
 
 
 @dataclass

@@ -17,7 +17,58 @@ import torch
 
 from ..kernels import ops
 from .base import (MATRIX, VECTOR, KVCacheSpec, KVCacheView, Mixer, ParamSpec, PositionEncoding, StepContext,
-                   register_mixer)
+                   StepLimits, StepPlan, Workspace, register_mixer)
+
+#: a plan made for a graph rounds the longest key range of the decoded rows up to this many positions:
+#: the split of the keys then stays the same from step to step while the requests grow
+GRAPH_KEY_BUCKET = 256
+
+
+class AttentionPlan(StepPlan):
+    """Which rows of a step are single decoded tokens and which belong to prompt portions, and the
+    portions cut into tiles of 64 and of 128 query rows, longest key range first; the same for
+    every attention layer of the step.  Words: [decoded rows | portion rows | (entry, first row)
+    per 64-row tile | the same per 128-row tile]."""
+
+    def __init__(self, entry_start, entry_pos0, for_graph: bool = False, device=None):
+        dec, pre, tiles = [], [], []
+        self.max_decode_keys = 0
+        for e in range(len(entry_start) - 1):
+            a, b = entry_start[e], entry_start[e + 1]
+            if b - a == 1:
+                dec.append(a)
+                self.max_decode_keys = max(self.max_decode_keys, entry_pos0[e] + 1)
+            else:
+                pre.extend(range(a, b))
+                tiles.extend((e, off) for off in range(0, b - a, 64))
+        # the same portions in tiles of 128 rows, for the tcgen05 kernel
+        wide = [(e, off) for e in range(len(entry_start) - 1) if entry_start[e + 1] - entry_start[e] > 1
+                for off in range(0, entry_start[e + 1] - entry_start[e], 128)]
+        # the tiles that reach furthest back have the most keys to go through: they are launched first,
+        # so that the short ones fill the gaps at the end
+        tiles.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
+        wide.sort(key=lambda t: -(entry_pos0[t[0]] + t[1]))
+        self.n_decode, self.n_prefill_rows, self.n_tiles = len(dec), len(pre), len(tiles)
+        self.n_wide_tiles = len(wide)
+        if for_graph:
+            self.max_decode_keys = -(-self.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
+        self.words = dec + pre + [v for t in tiles for v in t] + [v for t in wide for v in t]
+        if device is not None:
+            self.bind(torch.tensor(self.words, dtype=torch.int32, device=device) if self.words else None)
+
+    def graph_key(self) -> tuple:
+        return (self.n_decode, self.n_prefill_rows, self.n_tiles, self.n_wide_tiles, self.max_decode_keys)
+
+    def bind(self, buf) -> None:
+        """``buf``: a device int32 tensor holding ``self.words``."""
+        nd, npre = self.n_decode, self.n_prefill_rows
+        all_decode = npre == 0
+        # rows 0..n-1 in order need no index list
+        self.decode_rows = None if all_decode or nd == 0 else buf[:nd]
+        self.prefill_rows = None if nd == 0 or npre == 0 else buf[nd:nd + npre]
+        self.tiles = buf[nd + npre:nd + npre + 2 * self.n_tiles] if self.n_tiles else None
+        at = nd + npre + 2 * self.n_tiles
+        self.wide_tiles = buf[at:at + 2 * self.n_wide_tiles] if self.n_wide_tiles else None
 
 
 def _split(xn):
@@ -53,6 +104,18 @@ class CausalSelfAttention(Mixer):
     def kv_spec(self) -> Optional[KVCacheSpec]:
         return KVCacheSpec(self.n_kv_head, self.head_dim, self.window)
 
+    def step_planner(self):
+        return "causal_attention", AttentionPlan
+
+    def flops_per_key(self) -> float:
+        return 4.0 * self.q_dim
+
+    def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
+        n = limits.max_rows
+        workspace.reserve("attention.qkv", n * (self.q_dim + 2 * self.kv_dim), self.dtype)
+        workspace.reserve("attention.out", n * self.q_dim, self.dtype)
+        ops.attention_decode_reserve(workspace, self.n_head, self.head_dim)
+
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
                 state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
         if cache is None:
@@ -81,5 +144,9 @@ class CausalSelfAttention(Mixer):
             if self.position is not None:
                 self.position.on_qk(q[:T], None, ctx)
         att = ws.get("attention.out", (ctx.max_rows, self.q_dim), self.dtype)
-        ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window)
+        plan = ctx.plans.get("causal_attention")
+        if plan is None:    # a caller that drives the part without the step function
+            plan = ctx.plans["causal_attention"] = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0,
+                                                                 device=x.device)
+        ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window, plan)
         ops.linear(att, p["out_weight"], p.get("out_bias"), x, T, residual=True)

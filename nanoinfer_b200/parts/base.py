@@ -77,6 +77,58 @@ class Part:
         """Called once after ``bind`` with the engine's dtype."""
         self.dtype, self.device = dtype, device
 
+    def reserve(self, workspace: "Workspace", limits: "StepLimits") -> None:
+        """Optional: size the part's scratch for the largest step ahead of time
+        (``workspace.reserve``), so that no buffer has to grow once steps are captured in graphs.
+        A part that does not is still safe: a buffer that grows later makes the step function drop
+        its graphs."""
+
+    def matrix_flops_per_row(self) -> float:
+        """FLOPs this part's matrix products spend on one row: 2 per element of every ``matrix``
+        parameter unless the part says otherwise (a routed feed-forward counts the experts a row
+        visits; a head, whose matrix is a ``table``, counts it all)."""
+        total = 0
+        for spec in self.param_specs():
+            if spec.kind == MATRIX or isinstance(self, Head):
+                n = 1
+                for d in spec.shape:
+                    n *= int(d)
+                total += n
+        return 2.0 * total
+
+    def step_planner(self) -> Optional[Tuple[str, Callable[..., "StepPlan"]]]:
+        """Optional: (name, factory) of what this kind of part derives on the host from the shape
+        of a step.  The step function calls ``factory(entry_start, entry_pos0, for_graph)`` once
+        per step and name (parts that give the same name share the plan), sends the plan's words to
+        the device with the step's other tables, and hands it to the parts as ``ctx.plans[name]``."""
+        return None
+
+
+@dataclass(frozen=True)
+class StepLimits:
+    """The largest step the engine will run: what scratch is sized for."""
+    max_rows: int
+    max_entries: int
+    max_positions: int
+    dtype: torch.dtype
+
+
+class StepPlan:
+    """What a kind of part works out on the host from the shape of a step (which rows are single
+    decoded tokens, how work is cut into tiles): ``words`` are int32 values that travel to the
+    device with the step's tables, ``bind`` receives the device tensor that holds them, and
+    ``graph_key`` names everything about the plan that a captured graph of the step bakes in: two
+    steps whose keys are equal run the same launches with the same sizes.  ``for_graph`` asks the
+    factory to round what may be rounded (a key range, say) so that steps share graphs."""
+
+    words: List[int] = []
+
+    def graph_key(self) -> tuple:
+        return (len(self.words),)
+
+    def bind(self, buf: Optional[torch.Tensor]) -> None:
+        pass
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
@@ -124,6 +176,20 @@ class Mixer(Part):
 
     def state_spec(self) -> Optional[StateSpec]:
         return None
+
+    def flops_per_key(self) -> float:
+        """FLOPs spent per row and visible key beyond the matrix products (attention: the score
+        and the weighted sum, 4 per query head and head element)."""
+        return 0.0
+
+    @property
+    def capture_safe(self) -> bool:
+        """Whether ``forward`` only enqueues work whose shape follows from the step's shape and its
+        plans' graph keys, reading everything else (tokens, positions, slots, tables) on the device,
+        so that a step may be captured in a CUDA graph and replayed with other contents.  A mixer
+        without state of its own is; one with state says so itself if it is (a ``forward`` that
+        loops over ``ctx.host_entry_slot`` on the host is not)."""
+        return self.state_spec() is None
 
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: "StepContext", cache: Optional["KVCacheView"],
                 state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
@@ -223,9 +289,8 @@ class StepContext:
     host_entry_slot: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
-    #: which rows are single decoded tokens and which are prompt portions (set by the step function;
-    #: the attention kernels build it themselves when it is absent)
-    attention_plan: Optional[object] = None
+    #: the step's plans by name (``Part.step_planner``); a part that finds none builds its own
+    plans: Dict[str, StepPlan] = field(default_factory=dict)
     #: int32 [slots]: the token last sampled for each slot, left on the device by the sampler; a
     #: negative entry -(s + 1) of ``tokens`` stands for ``token_feedback[s]``
     token_feedback: Optional[torch.Tensor] = None
@@ -233,7 +298,15 @@ class StepContext:
 
 class Workspace:
     """Named scratch buffers that live as long as the engine: a part asks for a buffer by name,
-    shape and dtype and gets the same memory every step (grown if a larger one is asked for)."""
+    shape and dtype and gets the same memory every step.
+
+    A captured CUDA graph holds the raw addresses of the buffers its kernels were given, so a
+    buffer must not move while a graph that uses it can still be replayed.  Scratch is therefore
+    sized ahead where its bound is known (``reserve``, called by the step function at construction
+    with the largest step).  Should a larger buffer be asked for all the same, the old one is not
+    freed but kept in ``retired`` and ``generation`` goes up: whoever holds graphs compares the
+    generation before every replay, drops its graphs when it changed, and only then calls
+    ``release_retired``.  Nothing that a live graph can write to is ever handed out again."""
 
     def __init__(self, device: torch.device):
         self.device = device
@@ -241,6 +314,27 @@ class Workspace:
         # the views handed out, by (name, shape, dtype): a step asks for the same ones again and
         # again, and making a view costs more than a launch's share of a step
         self._views: Dict[tuple, torch.Tensor] = {}
+        #: goes up whenever a buffer that was handed out before is replaced by a larger one
+        self.generation = 0
+        #: replaced buffers, kept alive until ``release_retired``
+        self.retired: List[torch.Tensor] = []
+
+    def _buffer(self, name: str, n: int, dtype: torch.dtype, zeroed: bool) -> torch.Tensor:
+        buf = self._bufs.get(name)
+        if buf is None or buf.dtype != dtype or buf.numel() < n:
+            if buf is not None:
+                self.retired.append(buf)
+                self.generation += 1
+            make = torch.zeros if zeroed else torch.empty
+            buf = make(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[name] = buf
+            for k in [k for k in self._views if k[0] == name]:   # views of the buffer that was replaced
+                del self._views[k]
+        return buf
+
+    def reserve(self, name: str, n: int, dtype: torch.dtype, zeroed: bool = False) -> None:
+        """Make sure that buffer ``name`` holds at least ``n`` elements from now on."""
+        self._buffer(name, int(n), dtype, zeroed)
 
     def get(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         key = (name, shape, dtype)
@@ -250,13 +344,7 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        buf = self._bufs.get(name)
-        if buf is None or buf.dtype != dtype or buf.numel() < n:
-            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
-            self._bufs[name] = buf
-            for k in [k for k in self._views if k[0] == name]:   # views of the buffer that was replaced
-                del self._views[k]
-        view = buf[:n].view(*shape)
+        view = self._buffer(name, n, dtype, False)[:n].view(*shape)
         if len(self._views) > 4096:
             self._views.clear()
         self._views[key] = view
@@ -268,13 +356,12 @@ class Workspace:
         n = 1
         for s in shape:
             n *= int(s)
-        buf = self._bufs.get(name)
-        if buf is None or buf.dtype != dtype or buf.numel() < n:
-            buf = torch.zeros(max(n, 1), dtype=dtype, device=self.device)
-            self._bufs[name] = buf
-            for k in [k for k in self._views if k[0] == name]:
-                del self._views[k]
-        return buf[:n].view(*shape)
+        return self._buffer(name, n, dtype, True)[:n].view(*shape)
+
+    def release_retired(self) -> None:
+        """Free the buffers that were replaced.  Only when nothing can refer to them any more: the
+        caller has dropped every graph captured before the current generation."""
+        self.retired.clear()
 
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())

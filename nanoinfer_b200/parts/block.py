@@ -1,14 +1,16 @@
 """How the parts of a layer are arranged.  The pre-norm block is the reference's
 (crates/core/src/stages/blocks.rs:4-8):
     x = x + mixer(norm_1(x));   x = x + feed_forward(norm_2(x))
-Another arrangement is another class registered under another name."""
+Another arrangement is another class registered under another name.  An arrangement names the
+parts it is made of and the registry each comes from (``slots``); a layer's specification gives a
+part for each of these names, and the model builds them."""
 from __future__ import annotations
 
-from typing import Callable, Dict, Optional, Type
+from typing import Callable, ClassVar, Dict, Optional, Type
 
 import torch
 
-from .base import FeedForward, KVCacheView, Mixer, Norm, StepContext
+from .base import FEED_FORWARDS, MIXERS, NORMS, KVCacheView, Mixer, Part, Registry, StepContext, StepLimits, Workspace
 
 BLOCKS: Dict[str, Type["Block"]] = {}
 
@@ -21,13 +23,30 @@ def register_block(name: str) -> Callable[[Type["Block"]], Type["Block"]]:
 
 
 class Block:
-    def __init__(self, width: int, norm_1: Norm, mixer: Mixer, norm_2: Norm, feed_forward: FeedForward):
-        self.width = int(width)
-        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+    #: part name -> the registry it is built from.  At most one of them may be a mixer: the cache
+    #: manager gives a run of the layer one set of pages or one state slot tensor.
+    slots: ClassVar[Dict[str, Registry]] = {}
 
-    def parts(self):
-        return {"norm_1": self.norm_1, "mixer": self.mixer, "norm_2": self.norm_2,
-                "feed_forward": self.feed_forward}
+    def __init__(self, width: int, parts: Dict[str, Part]):
+        missing, unknown = set(self.slots) - set(parts), set(parts) - set(self.slots)
+        if missing or unknown:
+            raise ValueError(f"{type(self).__name__} is made of {sorted(self.slots)}: missing {sorted(missing)}, "
+                             f"unknown {sorted(unknown)}")
+        self.width = int(width)
+        self._parts = dict(parts)
+        for name, part in parts.items():
+            setattr(self, name, part)
+        mixers = [p for p in parts.values() if isinstance(p, Mixer)]
+        if len(mixers) > 1:
+            raise ValueError("a block holds at most one mixer")
+        #: the part that mixes across positions (None: the layer has none)
+        self.mixer: Optional[Mixer] = mixers[0] if mixers else None
+
+    def parts(self) -> Dict[str, Part]:
+        return dict(self._parts)
+
+    def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
+        """Size the arrangement's own scratch (the parts size theirs themselves)."""
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
                 state: Optional[torch.Tensor], writes_cache: bool, dtype: torch.dtype) -> None:
@@ -36,6 +55,11 @@ class Block:
 
 @register_block("pre_norm")
 class PreNormBlock(Block):
+    slots = {"norm_1": NORMS, "mixer": MIXERS, "norm_2": NORMS, "feed_forward": FEED_FORWARDS}
+
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("block.normed", limits.max_rows * self.width, limits.dtype)
+
     def _normed(self, norm, part, x, ctx, dtype):
         """The part's input: a foldable norm input where both the norm and the part can do that,
         else the norm's output in scratch."""

@@ -29,6 +29,9 @@ class DenseMLP(FeedForward):
             specs += [ParamSpec("fc_bias", (self.inner,), VECTOR), ParamSpec("proj_bias", (self.width,), VECTOR)]
         return specs
 
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("mlp.fc", limits.max_rows * self.inner, self.dtype)
+
     def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext) -> None:
         T, p = ctx.n_rows, self.params
         fc = ctx.workspace.get("mlp.fc", (ctx.max_rows, self.inner), self.dtype)

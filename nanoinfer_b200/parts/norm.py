@@ -22,6 +22,10 @@ class LayerNorm(Norm):
             ParamSpec("bias", (self.width,), VECTOR, INIT_NORMAL),
         ]
 
+    def reserve(self, workspace, limits) -> None:
+        # where a product cannot fold the norm into its own kernel it normalises into this buffer
+        workspace.reserve("norm.fallback", limits.max_rows * self.width, limits.dtype)
+
     def as_input(self, x: torch.Tensor, ctx, dtype: torch.dtype, rows: Optional[torch.Tensor] = None):
         """This norm applied to the residual stream, in the form a matrix product can take as its
         activations (the product then normalises the rows itself where it can)."""

@@ -54,9 +54,18 @@ class Sampler:
         #: the token last sampled for each slot: the next step's embedding can read it from here
         #: before the host has seen it
         self.last_token = slots.register(("sampler", "last_token"), (), torch.int32)
-        self._out = torch.zeros(max(1, slots.n_slots), dtype=torch.int32, device=slots.device)
+        #: the step's tokens and the kernel's two zero-invariant words per row.  Sized for 256 rows or
+        #: one per slot; a call with more rows (logits wanted at many places of a prompt) replaces both,
+        #: and ``generation`` tells holders of captured graphs that the old addresses are gone
+        self.generation = 0
+        self._size(max(256, slots.n_slots + 1))
         #: slots whose request samples with a temperature (a slot stays here until its next request)
         self._sampled_slots = set()
+
+    def _size(self, n: int) -> None:
+        dev = self.slots.device
+        self._out = torch.zeros(n, dtype=torch.int32, device=dev)
+        self._scratch = torch.zeros(2 * n, dtype=torch.int64, device=dev)
 
     def set_request(self, slot: int, params: SamplingParams, n_draws_done: int = 0) -> None:
         """Write a request's options into its slot; ``n_draws_done`` restores the generator of a
@@ -80,7 +89,8 @@ class Sampler:
         """One token per logits row (int32, on the device; valid until the next call)."""
         n = logits.shape[0]
         if n > self._out.numel():
-            self._out = torch.zeros(n, dtype=torch.int32, device=logits.device)
-        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out, self.last_token,
-                   teams=self.any_sampled)
+            self._size(n)
+            self.generation += 1
+        ops.sample(logits, n, row_slot, self.temperature, self.top_k, self.rng, self._out, self._scratch,
+                   self.last_token, teams=self.any_sampled)
         return self._out[:n]

@@ -151,6 +151,90 @@ def test_graph_table_keeps_the_most_recently_used_shapes(model_dirs):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_graphs_survive_larger_steps_between_their_replays(dtype, model_dirs, plain_logits):
+    """A captured graph holds the raw addresses of the step's scratch.  Eight requests with hundreds
+    of keys decode side by side (the keys are split over blocks, so the partial results and arrival
+    counters go through scratch) until their step is captured; then forty rows, then sixty-four rows
+    with a sampler, then the eight again, replayed.  No scratch buffer may have moved in between:
+    every logits row is the plain implementation's, and the step function reports no replacement.
+    Then a step that does make a buffer grow (logits at 200 places of a prompt): the graphs are
+    dropped, captured anew, and the eight rows are still right."""
+    from plain_gpt2 import XorShiftSampler
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    from nanoinfer_b200.kernels import ops
+    from nanoinfer_b200.sampling import Sampler, SamplingParams
+    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    d = model_dirs("LONG", dtype)
+    vocab, n_head = TINY["LONG"]["vocab_size"], TINY["LONG"]["n_head"]
+    m = load_model(d, dtype, "cuda")
+    base = [random_tokens(vocab, 340, 500 + i) for i in range(8)]
+    want = [plain_logits(d, b) for b in base]
+    lens = [260 + (37 * i) % 41 for i in range(64)]               # 260..300 tokens are in the cache at first
+    cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=64 * 352, max_requests=64, page_size=16,
+                         dtype=dtype, device=torch.device("cuda"), max_positions=m.max_positions, padding=True)
+    runner = ModelRunner(m, cache, max_rows=1280, max_entries=64)
+    sampler = Sampler(cache.slots)
+    generation = runner.workspace.generation
+    reqs = [cache.open_request() for _ in range(64)]
+    for i in range(0, 64, 4):
+        runner.step([StepItem(reqs[j], base[j % 8][:lens[j]], []) for j in range(i, i + 4)])
+    at = list(lens)
+    assert ops.decode_split(8, n_head, 512)[1] > 1 and ops.decode_split(64, n_head, 512)[1] > 1
+
+    def decode(ids, sampler=None):
+        out = runner.step([StepItem(reqs[j], [base[j % 8][at[j]]], [0]) for j in ids], sampler=sampler)
+        for j in ids:
+            at[j] += 1
+        return out
+
+    def check(ids, logits):
+        for row, j in enumerate(ids):
+            diff = float((logits[row].float().cpu() - want[j % 8][at[j] - 1]).abs().max())
+            assert diff <= tol, f"request {j} at position {at[j] - 1}: {diff:.3e}"
+
+    eight, forty, all64 = list(range(8)), list(range(40)), list(range(64))
+    for _ in range(3):                                            # uncaptured, captured, replayed
+        check(eight, decode(eight))
+    replays = runner.graph_replays
+    assert replays >= 2
+    for _ in range(2):
+        check(forty, decode(forty))
+    # sixty-four rows through the sampler: even slots greedy, odd ones with a temperature
+    plain_samplers = {}
+    for j in all64:
+        sp = SamplingParams(temperature=0.0 if j % 2 == 0 else 0.8, top_k=0 if j % 4 == 1 else 12, seed=900 + j)
+        sampler.set_request(reqs[j].slot, sp)
+        plain_samplers[j] = XorShiftSampler(sp.temperature, sp.top_k, sp.seed)
+    differ = 0
+    for _ in range(2):
+        toks = decode(all64, sampler).tolist()
+        for j in all64:
+            ref = want[j % 8][at[j] - 1]
+            tok = plain_samplers[j].sample(ref)
+            if dtype == torch.float32:
+                differ += int(toks[j] != tok)     # may differ where a draw falls within rounding of a boundary
+            elif j % 2 == 0 and toks[j] != tok:   # bfloat16: the greedy rows, unless two logits are nearly tied
+                assert float(ref[tok] - ref[toks[j]]) < 2 * tol, f"request {j}: greedy token {toks[j]}, plain {tok}"
+    assert differ <= 1, f"{differ} of 128 tokens differ from the plain sampler"
+    for _ in range(3):                                            # the eight again: their graph is replayed
+        check(eight, decode(eight))
+    assert runner.graph_replays >= replays + 3
+    assert runner.workspace.generation == generation and runner.graph_drops == 0, "a scratch buffer was replaced"
+    # now make a buffer grow: logits at 200 places of one prompt are more rows than the scratch was sized for
+    cache.close_request(reqs[63])
+    r = cache.open_request()
+    lg = runner.step([StepItem(r, base[3][:200], range(200))])
+    assert float((lg.float().cpu() - want[3][:200]).abs().max()) <= tol
+    assert runner.workspace.generation > generation
+    for _ in range(3):                                            # dropped, run plainly, captured again
+        check(eight, decode(eight))
+    assert runner.graph_drops == 1 and not runner.workspace.retired
+    cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_batches_padded_to_a_graph_shape_give_the_same_logits(dtype, model_dirs, plain_logits):
     """Eleven, then ten, then nine requests decode side by side: the step function fills the batch
     up to sixteen rows with rows of no request (so that the three sizes share one graph); the real
@@ -207,12 +291,15 @@ def test_sampling_with_seeds_is_reproducible_and_independent_of_the_batch(model_
     from plain_gpt2 import PlainGPT2, XorShiftSampler
     plain, s = PlainGPT2(d), XorShiftSampler(0.9, 20, 100)
     toks = list(prompts[0])
+    differ = 0
     for k in range(12):
         lg = plain.logits(toks)[-1].float()
         t = s.sample(lg)
-        if t != together[0][k]:
-            pytest.skip("a draw fell within rounding of a boundary")   # not expected with these seeds
-        toks.append(t)
+        differ += int(t != together[0][k])
+        toks.append(together[0][k])      # go on from the engine's token: the generators stay in step
+    # the walks agree except where a draw falls within rounding of the boundary between two tokens
+    # (the rule of the kernel's own test): at most one of the twelve
+    assert differ <= 1, f"{differ} of 12 sampled tokens differ from the reference walk"
 
 
 def test_few_pages_preemption_gives_the_same_tokens(model_dirs):

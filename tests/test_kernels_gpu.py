@@ -22,6 +22,11 @@ def gen(seed=0):
     return torch.Generator().manual_seed(seed)
 
 
+def attention_plan(ctx):
+    from nanoinfer_b200.parts.attention import AttentionPlan
+    return AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, device=torch.device(DEV))
+
+
 class Ctx:
     """The few fields of a StepContext that the attention kernels read."""
 
@@ -175,7 +180,7 @@ def test_attention_over_scattered_pages(dtype, case):
     q = torch.cat(c["qs"]).to(dtype).to(DEV)
     out = torch.zeros_like(q)
     ctx = Ctx(c["row_entry"], c["positions"])
-    ops().attention(q, c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, scale, window)
+    ops().attention(q, c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, scale, window, attention_plan(ctx))
     assert int(ctx.status.item()) == 0
     tol = 2e-5 if dtype == torch.float32 else 2e-2
     assert (out.cpu().double() - want).abs().max() < tol
@@ -196,7 +201,7 @@ def test_both_prefill_attention_kernels_at_head_size_64(case):
         for q, k, v in zip(c["qs"], c["ks"], c["vs"])])
     q = torch.cat(c["qs"]).to(torch.bfloat16).to(DEV)
     ctx = Ctx(c["row_entry"], c["positions"])
-    plan = o.AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, torch.device(DEV))
+    plan = attention_plan(ctx)
     rows = [t for e in range(len(lengths)) if q_lens[e] > 1
             for t in range(ctx.host_entry_start[e], ctx.host_entry_start[e + 1])]
     cache, table = c["cache"].to(DEV), c["table"].to(DEV)
@@ -225,7 +230,7 @@ def test_attention_finds_one_far_key_among_hundreds():
             c["cache"][page, 0, h, far % ps] = 40.0 * q[0, h * hd:(h + 1) * hd] / q[0, h * hd:(h + 1) * hd].norm()
         out = torch.zeros(1, n_head * hd, device=DEV)
         ctx = Ctx(c["row_entry"], c["positions"])
-        ops().attention(q.to(DEV), c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, 1.0, 0)
+        ops().attention(q.to(DEV), c["cache"].to(DEV), out, c["table"].to(DEV), ctx, n_head, 1.0, 0, attention_plan(ctx))
         assert (out.cpu() - v[far]).abs().max() < 1e-3, f"key {far} was not found"
 
 
@@ -292,10 +297,11 @@ def test_sampling_follows_the_reference_walk(V, teams):
         t_dev[sl], k_dev[sl], rng[sl] = temps[r], topk[r], seeds[r]
     plain = [P.XorShiftSampler(temps[r], topk[r], seeds[r]) for r in range(R)]
     out = torch.zeros(R, dtype=torch.int32, device=DEV)
+    scratch = torch.zeros(2 * R, dtype=torch.int64, device=DEV)
     dev = lg.to(DEV)
     agree = total = 0
     for _ in range(12):
-        o.sample(dev, R, slots, t_dev, k_dev, rng, out, teams=teams)
+        o.sample(dev, R, slots, t_dev, k_dev, rng, out, scratch, teams=teams)
         got = out.tolist()
         want = [plain[r].sample(lg[r]) for r in range(R)]
         assert got[2] == want[2]                                    # greedy row

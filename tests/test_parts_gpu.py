@@ -128,16 +128,16 @@ def register_toys():
                              "proj_weight": TensorRef(name + ".proj.w"), "proj_bias": TensorRef(name + ".proj.b")})
 
         layers = [
-            LayerSpec("pre_norm", norm("l0.n1"), attn("l0.att", 4, 2, 16, cfg.window, 0.3), norm("l0.n2"),
-                      mlp("l0.mlp", 96, "tanh")),
-            LayerSpec("pre_norm", norm("l1.n1"),
-                      PartSpec("toy_decay_mixer", dict(width=c, decay=cfg.decay), {"weight": TensorRef("l1.mix.w")}),
-                      norm("l1.n2"),
-                      PartSpec("toy_routed_ffn", dict(width=c, inner=40, n_expert=cfg.n_expert),
-                               {"router": TensorRef("l1.moe.router"), "up": TensorRef("l1.moe.up"),
-                                "down": TensorRef("l1.moe.down")})),
-            LayerSpec("pre_norm", norm("l2.n1"), attn("l2.att", 2, 2, 32, 0, 0.25), norm("l2.n2"),
-                      mlp("l2.mlp", 80, "erf"),
+            LayerSpec("pre_norm", norm_1=norm("l0.n1"), mixer=attn("l0.att", 4, 2, 16, cfg.window, 0.3),
+                      norm_2=norm("l0.n2"), feed_forward=mlp("l0.mlp", 96, "tanh")),
+            LayerSpec("pre_norm", norm_1=norm("l1.n1"),
+                      mixer=PartSpec("toy_decay_mixer", dict(width=c, decay=cfg.decay), {"weight": TensorRef("l1.mix.w")}),
+                      norm_2=norm("l1.n2"),
+                      feed_forward=PartSpec("toy_routed_ffn", dict(width=c, inner=40, n_expert=cfg.n_expert),
+                                            {"router": TensorRef("l1.moe.router"), "up": TensorRef("l1.moe.up"),
+                                             "down": TensorRef("l1.moe.down")})),
+            LayerSpec("pre_norm", norm_1=norm("l2.n1"), mixer=attn("l2.att", 2, 2, 32, 0, 0.25),
+                      norm_2=norm("l2.n2"), feed_forward=mlp("l2.mlp", 80, "erf"),
                       mixer_position=PartSpec("toy_phase", dict(head_dim=32, base=50.0))),
         ]
         return ModelSpec(
@@ -304,6 +304,181 @@ def test_state_slot_is_zeroed_for_a_new_request(toy_folder):
     assert torch.equal(first, again)
 
 
+# ----------------------------------------------------------------------------- a second toy: another arrangement
+def register_parallel_toy():
+    """A block arrangement of its own (ONE norm; mixer and feed-forward both read it and both add to
+    the stream), a layer without any mixer, and a mixer with per-request state whose work is all
+    on the device, so that steps of the model are captured in graphs like any other."""
+    from nanoinfer_b200 import parts as P
+    from nanoinfer_b200.config.base import ModelConfig, field
+    from nanoinfer_b200.models.spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from nanoinfer_b200.parts.base import FEED_FORWARDS, MATRIX, MIXERS, NORMS, ParamSpec, StateSpec, TensorRef
+    from nanoinfer_b200.parts.block import Block, register_block
+    from nanoinfer_b200.registry import architectures, register_architecture
+
+    if "ToyParallelLM" in architectures():
+        return
+
+    @P.register_mixer("toy_running_sum")
+    class RunningSum(P.Mixer):
+        """x_t += rate * sum_{j <= t} (W xn_j): the sum over the request's earlier steps is its state.
+        Everything runs on the device from the step's tables; only shapes are read on the host."""
+
+        capture_safe = True
+
+        def __init__(self, width, rate):
+            self.width, self.rate = width, rate
+
+        def param_specs(self):
+            return [ParamSpec("weight", (self.width, self.width), MATRIX)]
+
+        def state_spec(self):
+            return StateSpec((self.width,), torch.float32)
+
+        def forward(self, xn, x, ctx, cache, state, writes_cache=True):
+            T = ctx.n_rows
+            u = xn[:T].float() @ self.params["weight"].float().T
+            c = torch.cumsum(u, 0)
+            first = ctx.entry_start[:-1].long()                 # [entries], on the device
+            last = ctx.entry_start[1:].long() - 1
+            ent, slots = ctx.row_entry.long(), ctx.entry_slot.long()
+            before = (c[first] - u[first])                       # the running sum ahead of each entry's rows
+            within = c - before[ent]
+            x[:T] += self.rate * (state[slots][ent] + within)
+            state.index_add_(0, slots, within[last])
+
+    @register_block("toy_parallel")
+    class ParallelBlock(Block):
+        slots = {"norm": NORMS, "mixer": MIXERS, "feed_forward": FEED_FORWARDS}
+
+        def forward(self, x, ctx, cache, state, writes_cache, dtype):
+            xn = ctx.workspace.get("toy_parallel.normed", (ctx.max_rows, self.width), dtype)
+            self.norm.forward(x, xn, ctx.n_rows)
+            self.mixer.forward(xn, x, ctx, cache, state, writes_cache)
+            self.feed_forward.forward(xn, x, ctx)
+
+    @register_block("toy_ffn_only")
+    class FFNOnly(Block):
+        slots = {"norm": NORMS, "feed_forward": FEED_FORWARDS}
+
+        def forward(self, x, ctx, cache, state, writes_cache, dtype):
+            xn = ctx.workspace.get("toy_parallel.normed", (ctx.max_rows, self.width), dtype)
+            self.norm.forward(x, xn, ctx.n_rows)
+            self.feed_forward.forward(xn, x, ctx)
+
+    @dataclasses.dataclass
+    class ParallelConfig(ModelConfig):
+        architecture_names: ClassVar[Tuple[str, ...]] = ("ToyParallelLM",)
+        vocab_size: int = field()
+        width: int = field()
+        inner: int = field()
+        eps: float = field()
+        rate: float = field()
+
+        def to_dict(self):
+            return dict(architectures=["ToyParallelLM"], **super().to_dict())
+
+    def build(cfg):
+        c = cfg.width
+
+        def norm(name):
+            return PartSpec("layernorm", dict(width=c, eps=cfg.eps),
+                            {"weight": TensorRef(name + ".g"), "bias": TensorRef(name + ".b")})
+
+        def mlp(name):
+            return PartSpec("dense_mlp", dict(width=c, inner=cfg.inner, activation="tanh", bias=True),
+                            {"fc_weight": TensorRef(name + ".fc.w"), "fc_bias": TensorRef(name + ".fc.b"),
+                             "proj_weight": TensorRef(name + ".proj.w"), "proj_bias": TensorRef(name + ".proj.b")})
+
+        layers = [
+            LayerSpec("toy_parallel", norm=norm("l0.n"), feed_forward=mlp("l0.mlp"),
+                      mixer=PartSpec("toy_running_sum", dict(width=c, rate=cfg.rate), {"weight": TensorRef("l0.mix")})),
+            LayerSpec("toy_ffn_only", parts={"norm": norm("l1.n"), "feed_forward": mlp("l1.mlp")}),
+        ]
+        return ModelSpec(
+            width=c,
+            embedding=PartSpec("token_embedding", dict(vocab_size=cfg.vocab_size, width=c), {"table": TensorRef("emb")}),
+            position=None, layers=layers, schedule=[ScheduleEntry(0), ScheduleEntry(1)], final_norm=norm("final"),
+            head=PartSpec("linear_head", dict(vocab_size=cfg.vocab_size, width=c), {"weight": TensorRef("emb")}),
+            max_positions=None)
+
+    register_architecture("ToyParallelLM", ParallelConfig, build)
+
+
+PARALLEL = dict(architectures=["ToyParallelLM"], vocab_size=150, width=48, inner=72, eps=1e-5, rate=0.05)
+
+
+def plain_parallel_logits(folder, tokens):
+    import plain_gpt2 as P
+    from safetensors.torch import load_file
+    w = {k: v.double() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
+    x = w["emb"][torch.tensor(tokens)]
+
+    def ln(name, x):
+        return P.layernorm(x, w[name + ".g"], w[name + ".b"], PARALLEL["eps"])
+
+    def mlp(name, h):
+        return P.gelu_tanh(h @ w[name + ".fc.w"].T + w[name + ".fc.b"]) @ w[name + ".proj.w"].T + w[name + ".proj.b"]
+
+    h = ln("l0.n", x)
+    x = x + PARALLEL["rate"] * torch.cumsum(h @ w["l0.mix"].T, 0) + mlp("l0.mlp", h)
+    x = x + mlp("l1.mlp", ln("l1.n", x))
+    return (ln("final", x) @ w["emb"].T).float()
+
+
+def test_another_arrangement_with_a_stateful_mixer_runs_in_graphs_and_is_measured(tmp_path):
+    """A block arrangement with one norm, a layer without a mixer and a mixer with per-request state
+    that declares itself safe to capture are registered from this file: the step function captures
+    its decode steps in graphs as for any model (the state lives in the request's slot, the graph
+    bakes in the step's shape only), the results agree with the plain computation, and the byte
+    and FLOP counts of the measurement come from the built model, not from a configuration's field
+    names."""
+    register_parallel_toy()
+    from nanoinfer_b200 import load_model, measure
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    from nanoinfer_b200.registry import get_architecture
+    from nanoinfer_b200.weights import write_random_model
+    cfg = get_architecture("ToyParallelLM").config_cls.from_dict(PARALLEL)
+    d = write_random_model(cfg, str(tmp_path / "par"), seed=5, dtype=torch.float32, std=0.1)
+    m = load_model(d, torch.float32, "cuda")
+    assert [type(b).__name__ for b in m.layers] == ["ParallelBlock", "FFNOnly"] and m.layers[1].mixer is None
+    assert m.kv_needs() == [] and [i for i, _ in m.state_needs()] == [0] and m.capture_safe()
+    cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=512, max_requests=3, page_size=16,
+                         dtype=torch.float32, device=torch.device("cuda"), max_positions=None, padding=True)
+    runner = ModelRunner(m, cache, max_rows=64, max_entries=3)
+    assert runner.use_graphs
+    seqs = [random_tokens(150, n, 40 + i) for i, n in enumerate([50, 33, 41])]
+    want = [plain_parallel_logits(d, s) for s in seqs]
+    reqs = [cache.open_request() for _ in seqs]
+    got = [[] for _ in seqs]
+    # a portion of each prompt in one step, then single tokens side by side (the same shape step after
+    # step: captured the second time and replayed from then on; requests drop out as they end)
+    lg = runner.step([StepItem(r, s[:20 + 3 * i], range(20 + 3 * i)) for i, (r, s) in enumerate(zip(reqs, seqs))]).cpu()
+    at, prog = 0, []
+    for i in range(3):
+        n = 20 + 3 * i
+        got[i].append(lg[at:at + n].clone())
+        at, prog = at + n, prog + [n]
+    while any(p < len(s) for p, s in zip(prog, seqs)):
+        live = [i for i, s in enumerate(seqs) if prog[i] < len(s)]
+        lg = runner.step([StepItem(reqs[i], [seqs[i][prog[i]]], [0]) for i in live]).cpu()
+        for row, i in enumerate(live):
+            got[i].append(lg[row:row + 1].clone())
+            prog[i] += 1
+    assert runner.graph_replays > 20 and runner.graph_drops == 0
+    for g, w in zip(got, want):
+        assert (torch.cat(g) - w).abs().max() < 2e-4
+    # measurement from the built model: the tied table is one tensor and is streamed (it is the head),
+    # FLOPs are 2 per matrix element and row for each run, plus the head per logits row
+    c, i, v = PARALLEL["width"], PARALLEL["inner"], PARALLEL["vocab_size"]
+    n_params = v * c + c * c + 2 * (2 * c * i + i + c) + 3 * 2 * c
+    assert measure.parameter_count(m) == n_params == measure.parameter_count_of_spec(m)
+    assert measure.weight_bytes_per_step(m) == 4 * n_params
+    assert measure.kv_bytes(cache, [100, 7]) == 0
+    assert measure.step_flops(m, [5, 9, 2], 2) == 3 * 2.0 * (c * c + 4 * c * i) + 2 * 2.0 * v * c
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_norm_embedding_mlp_and_head_parts_alone(dtype):
     """Each built-in part alone, built through its registry with sizes of its own."""
@@ -411,11 +586,11 @@ def test_attention_mixer_and_block_alone(dtype, n_head, n_kv_head, hd, window):
                                     scale=scale, window=window),
                     qkv_weight=w_qkv, qkv_bias=b_qkv, out_weight=w_out, out_bias=b_out)
 
-    block = NP.BLOCKS["pre_norm"](
-        C, bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g1, bias=be1), attention_part(),
-        bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g2, bias=be2),
-        bind(NP.FEED_FORWARDS.build("dense_mlp", width=C, inner=I, activation="tanh"),
-             fc_weight=w1, fc_bias=b1, proj_weight=w2, proj_bias=b2))
+    block = NP.BLOCKS["pre_norm"](C, dict(
+        norm_1=bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g1, bias=be1), mixer=attention_part(),
+        norm_2=bind(NP.NORMS.build("layernorm", width=C, eps=2e-5), weight=g2, bias=be2),
+        feed_forward=bind(NP.FEED_FORWARDS.build("dense_mlp", width=C, inner=I, activation="tanh"),
+                          fc_weight=w1, fc_bias=b1, proj_weight=w2, proj_bias=b2)))
     want_block = []
     for x0 in x0_all:
         x = x0.double()

@@ -195,6 +195,93 @@ def test_tokens_recorded_as_stand_ins_get_their_values_one_step_later():
     assert s.on_tokens_read(items, [9]) == [] and c.finish_reason == "eos" and c.output == [9]
 
 
+def _token_of(req, index):
+    """The token a model would give: a function of the request and of the token's place only."""
+    return 9 if (req.id * 7 + index * 3) % 11 == 0 else 5
+
+
+def _run_reading_every_step(cache, s):
+    while s.has_work():
+        items = s.schedule()
+        if items:
+            cache.append([(i.request.cache, i.n_tokens) for i in items])
+            for i in items:
+                cache.commit(i.request.cache, i.n_tokens)
+        s.on_step_done(items, [_token_of(i.request, len(i.request.output)) for i in items if i.samples])
+        cache.check()
+
+
+def _run_one_step_ahead(cache, s):
+    """The engine's loop when it launches a step before it has read the tokens of the one before."""
+    in_flight, ended = None, []
+
+    def read():
+        nonlocal in_flight, ended
+        if in_flight is not None:
+            items, values, done = in_flight
+            in_flight = None
+            ended += done + s.on_tokens_read(items, values)
+
+    while s.has_work() or in_flight is not None:
+        while True:
+            items = s.schedule()
+            ended += s.ended_without_step
+            if in_flight is not None and any(i.n_tokens > 1 and any(t < 0 for t in i.request.next_tokens(i.n_tokens))
+                                             for i in items):
+                read()      # a portion must not hold a stand-in
+                continue
+            break
+        if not items:
+            read()
+            continue
+        cache.append([(i.request.cache, i.n_tokens) for i in items])
+        for i in items:
+            cache.commit(i.request.cache, i.n_tokens)
+        values = [_token_of(i.request, len(i.request.output)) for i in items if i.samples]
+        done = s.on_step_done(items, [-(i.request.cache.slot + 1) for i in items if i.samples])
+        flight = (items, values, done)
+        read()
+        in_flight = flight
+        cache.check()
+    return ended
+
+
+def test_an_end_token_read_after_its_request_was_preempted_ends_it_in_the_queue_too():
+    """A request can be preempted while its newest token is still a stand-in.  When the value turns
+    out to be its end token, the request must leave the waiting queue: it is neither admitted again
+    nor reported twice, and its output ends at the end token."""
+    for seed in range(40):
+        rng = random.Random(seed)
+        lens = [(rng.randint(1, 40), rng.randint(2, 30)) for _ in range(6)]
+        outs = []
+        for run in (_run_reading_every_step, _run_one_step_ahead):
+            cache, s = setup(max_tokens=96, max_batch=4, max_rows=48, budget=24, max_positions=80)
+            reqs = [s.add([1] * p, SamplingParams(max_new_tokens=n, eos_token_id=9)) for p, n in lens]
+            ended = run(cache, s)
+            assert not s.waiting and not s.running and cache.pages_used() == [0]
+            for r in reqs:
+                assert r.state == FINISHED and all(t >= 0 for t in r.output)
+                assert 9 not in r.output[:-1]
+            if ended is not None:
+                assert sorted(r.id for r in ended) == sorted(r.id for r in reqs)    # each reported once
+            outs.append([(r.output, r.finish_reason) for r in reqs])
+        assert outs[0] == outs[1]
+    # the order named in the scheduler's own words: stand-in recorded, preempted, then the end token is read
+    cache, s = setup(max_tokens=512, max_positions=64)
+    a = s.add([1] * 4, SamplingParams(max_new_tokens=50, eos_token_id=9))
+    b = s.add([1] * 4, SamplingParams(max_new_tokens=50, eos_token_id=9))
+    items = s.schedule()
+    cache.append([(i.request.cache, i.n_tokens) for i in items])
+    for i in items:
+        cache.commit(i.request.cache, i.n_tokens)
+    s.on_step_done(items, [-(i.request.cache.slot + 1) for i in items])
+    s._preempt(b)
+    assert b in s.waiting and b.state == WAITING
+    assert s.on_tokens_read(items, [5, 9]) == [b]
+    assert b not in s.waiting and b not in s.running and b.state == FINISHED and b.output == [9]
+    assert [i.request for i in s.schedule()] == [a]
+
+
 def test_next_tokens_is_a_slice_of_prompt_and_output():
     _, s = setup(max_tokens=512)
     r = s.add([1, 2, 3, 4], SamplingParams())

@@ -5,7 +5,8 @@ to a pool of their own at start-up, or they call from inside a stream callback o
 or their sandbox forbids it.  For them the library carries its scratch memory inside itself.  This
 test calls that entry point through its exported C symbol, twice in a row on the same inputs and once
 on others, and checks each result against the ordinary entry point, which takes its scratch from the
-caller.  It also checks that a call too large for the built-in scratch is refused, not run.
+caller, and against the plain attention formula of the tests (so that the two entry points cannot
+be wrong together).  It also checks that a call too large for the built-in scratch is refused, not run.
 
 The file is named to be collected last, so that a run that stops at the first failure has already
 run every other test; it passes alone in a fresh process as well."""
@@ -35,6 +36,24 @@ def _case(seed, n_rows, n_head, hd, lengths, dtype):
     positions = torch.tensor([n - 1 for n in lengths], dtype=torch.int32)
     return (q.to(DEV), cache.to(DEV), table.to(DEV), torch.arange(n_rows, dtype=torch.int32, device=DEV),
             positions.to(DEV))
+
+
+def _plain(q, cache, table, lengths, n_head, hd, scale):
+    """The plain attention of each row over its request's keys, gathered from the pages by hand."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    import plain_gpt2 as P
+    ps = cache.shape[3]
+    rows = []
+    for e, n in enumerate(lengths):
+        pages = table[e, :-(-n // ps)].long().cpu()
+        kv = cache.cpu().double()[pages]                                  # [blocks, 2, heads, page, hd]
+        k = kv[:, 0].permute(0, 2, 1, 3).reshape(-1, n_head * hd)[:n]     # [positions, heads * hd]
+        v = kv[:, 1].permute(0, 2, 1, 3).reshape(-1, n_head * hd)[:n]
+        rows.append(P.causal_attention(q[e:e + 1].cpu().double(), k, v, n_head, n_head, scale=scale, window=0,
+                                       q_pos0=n - 1))
+    return torch.cat(rows)
 
 
 def _static_call(lib, q, cache, table, row_entry, positions, out, n_head, scale, chunk, n_splits, status):
@@ -75,6 +94,8 @@ def test_static_scratch_entry_matches_the_ordinary_one(dtype, tol):
         torch.cuda.synchronize()
         assert int(status.item()) == 0
         assert (got.float() - want.float()).abs().max().item() <= tol
+        plain = _plain(q, cache, table, lengths, n_head, hd, scale)
+        assert (got.cpu().double() - plain).abs().max().item() <= tol
 
 
 def test_static_scratch_refuses_what_does_not_fit():

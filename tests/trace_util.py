@@ -13,11 +13,11 @@ TRACE_RUN = os.path.join(ROOT, "bin", "trace_run")
 
 
 class TraceSession:
-    def __init__(self, model_dir, dtype, out_dir, max_tokens, vocab):
+    def __init__(self, model_dir, dtype, out_dir, max_tokens, vocab, extra=()):
         self.out_dir, self.vocab = str(out_dir), vocab
         self.proc = subprocess.Popen(
             [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", self.out_dir,
-             "--max-tokens", str(max_tokens)],
+             "--max-tokens", str(max_tokens), *extra],
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, bufsize=1)
         self.step_no = 0
         #: per request id: {position: logits row}
@@ -63,6 +63,19 @@ class TraceSession:
         assert sorted(got) == list(range(n)), f"request {rid}: positions {sorted(got)[:5]}... of {n}"
         return torch.stack([got[p] for p in range(n)])
 
+    def pages(self):
+        """With ``--log-pages``: [{request id: [page ids per cache group]}] for every step."""
+        with open(os.path.join(self.out_dir, "pages.jsonl")) as fh:
+            return [json.loads(line)["pages"] for line in fh]
+
 
 def max_diff(a, b):
     return float((a - b).abs().max())
+
+
+def max_kl(ref, got):
+    """The largest KL(plain || engine) of the next-token distributions over the rows, in float64
+    (the reference's second measure of a reduced-precision path: crates/core/tests/reference.rs:29-45)."""
+    lp = torch.log_softmax(ref.double(), dim=-1)
+    lq = torch.log_softmax(got.double(), dim=-1)
+    return float((lp.exp() * (lp - lq)).sum(-1).max())
