@@ -446,7 +446,7 @@ def test_another_arrangement_with_a_stateful_mixer_runs_in_graphs_and_is_measure
     assert m.kv_needs() == [] and [i for i, _ in m.state_needs()] == [0] and m.capture_safe()
     cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=512, max_requests=3, page_size=16,
                          dtype=torch.float32, device=torch.device("cuda"), max_positions=None, padding=True)
-    runner = ModelRunner(m, cache, max_rows=64, max_entries=3)
+    runner = ModelRunner(m, cache, max_rows=96, max_entries=3)
     assert runner.use_graphs
     seqs = [random_tokens(150, n, 40 + i) for i, n in enumerate([50, 33, 41])]
     want = [plain_parallel_logits(d, s) for s in seqs]
