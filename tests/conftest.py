@@ -38,7 +38,20 @@ WIDE = dict(architectures=["GPT2LMHeadModel"], vocab_size=2003, n_positions=1024
 XLW = dict(architectures=["GPT2LMHeadModel"], vocab_size=1501, n_positions=512, n_embd=1600, n_layer=1, n_head=25,
            n_inner=6400, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
            scale_attn_by_inverse_layer_idx=False)
-TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE, "XLW": XLW}
+# GPT-2 medium's layer sizes (width 1024, 16 heads of 64, inner 4096) with two layers.
+MEDW = dict(architectures=["GPT2LMHeadModel"], vocab_size=1777, n_positions=1024, n_embd=1024, n_layer=2, n_head=16,
+            n_inner=4096, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+            scale_attn_by_inverse_layer_idx=False)
+# One layer of GPT-2 small's sizes with the real vocabulary: 50257 is no multiple of anything a tile likes.
+V50K = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=256, n_embd=768, n_layer=1, n_head=12,
+            n_inner=3072, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+            scale_attn_by_inverse_layer_idx=False)
+# GPT-2 small whole: twelve layers, the real vocabulary, 1024 positions (the sizes the benchmark runs).
+SMALL = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=1024, n_embd=768, n_layer=12, n_head=12,
+             n_inner=3072, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+             scale_attn_by_inverse_layer_idx=False)
+TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE, "XLW": XLW, "MEDW": MEDW, "V50K": V50K,
+        "SMALL": SMALL}
 
 
 def sharpen_attention(tensors, factor):
@@ -93,12 +106,13 @@ def plain_logits():
 
     models, cache = {}, {}
 
-    def get(model_dir, tokens):
+    def get(model_dir, tokens, device="cpu"):
         key = (model_dir, tuple(tokens))
         if key not in cache:
             if model_dir not in models:
-                models[model_dir] = PlainGPT2(model_dir)
-            cache[key] = models[model_dir].logits(list(tokens)).to(torch.float32)
+                models.clear()             # one plain model at a time: the large ones take gigabytes
+                models[model_dir] = PlainGPT2(model_dir, device=device)
+            cache[key] = models[model_dir].logits(list(tokens)).to(torch.float32).cpu()
         return cache[key]
 
     return get

@@ -25,10 +25,10 @@ import torch
 # --------------------------------------------------------------------------- parts
 def embed(wte: torch.Tensor, wpe: Optional[torch.Tensor], tokens: Sequence[int], pos0: int = 0) -> torch.Tensor:
     """x[t] = wte[tok_t] + wpe[pos0 + t]  (crates/core/src/kernels/reference.rs:86-94)."""
-    tok = torch.as_tensor(list(tokens), dtype=torch.long)
+    tok = torch.as_tensor(list(tokens), dtype=torch.long, device=wte.device)
     x = wte[tok]
     if wpe is not None:
-        pos = torch.arange(pos0, pos0 + len(tok))
+        pos = torch.arange(pos0, pos0 + len(tok), device=wte.device)
         x = x + wpe[pos]
     return x
 
@@ -91,7 +91,7 @@ def causal_attention(
     group = n_head // n_kv_head
     if scale is None:
         scale = 1.0 / math.sqrt(hd)
-    out = torch.zeros(n_q, n_head * hd, dtype=q.dtype)
+    out = torch.zeros(n_q, n_head * hd, dtype=q.dtype, device=q.device)
     for i in range(n_q):
         p = q_pos0 + i
         lo = max(0, p - window + 1) if window > 0 else 0
@@ -110,7 +110,9 @@ class PlainGPT2:
     """Whole-sequence GPT-2 forward (crates/core/src/stages/naive.rs:21-45 with the
     block of stages/blocks.rs:4-8), returning the logits of every position."""
 
-    def __init__(self, model_dir: str, dtype: torch.dtype = torch.float64):
+    def __init__(self, model_dir: str, dtype: torch.dtype = torch.float64, device: str = "cpu"):
+        """``device``: where the same torch formulas run; the tests use the CPU except for models of
+        full size, whose float64 products take minutes there."""
         from safetensors.torch import load_file
 
         with open(os.path.join(model_dir, "config.json")) as fh:
@@ -120,7 +122,7 @@ class PlainGPT2:
         for name, t in raw.items():
             if name.startswith("transformer."):
                 name = name[len("transformer."):]
-            self.w[name] = t.to(dtype)
+            self.w[name] = t.to(device=device, dtype=dtype)
         self.dtype = dtype
         c = self.cfg
         self.n_layer = c["n_layer"]

@@ -302,6 +302,26 @@ def test_sampling_with_seeds_is_reproducible_and_independent_of_the_batch(model_
     assert differ <= 1, f"{differ} of 12 sampled tokens differ from the reference walk"
 
 
+def test_sampling_over_the_real_vocabulary_together_and_alone(model_dirs):
+    """Temperature 0.8 over a vocabulary of 50257 through the entry point (a sampled row is shared by
+    a cluster of blocks there): eight requests together give the tokens that each gives alone, and a
+    request's first token is the plain sampler's on the plain logits."""
+    import nanoinfer_b200 as nb
+    from plain_gpt2 import PlainGPT2, XorShiftSampler
+    d = model_dirs("V50K", torch.float32, sharpen=2.5)
+    prompts = [random_tokens(50257, 4 + 3 * i, 860 + i) for i in range(8)]
+    params = [nb.SamplingParams(max_new_tokens=6, temperature=0.8, top_k=0 if i % 2 else 40, seed=300 + i)
+              for i in range(8)]
+    together = engine(d, "float32", max_batch=8, max_rows=64).generate(prompts, params)
+    alone_engine = engine(d, "float32", max_batch=1, max_rows=64)
+    alone = [alone_engine.generate([p], [sp])[0] for p, sp in zip(prompts, params)]
+    assert together == alone
+    plain = PlainGPT2(d)
+    first = [XorShiftSampler(0.8, sp.top_k, sp.seed).sample(plain.logits(p)[-1].float()) for p, sp in
+             zip(prompts[:3], params[:3])]
+    assert sum(int(a != b[0]) for a, b in zip(first, together)) <= 1     # (a draw within rounding of a boundary)
+
+
 def test_few_pages_preemption_gives_the_same_tokens(model_dirs):
     """With a pool too small for all requests the scheduler preempts and recomputes; greedy tokens
     must be what an ample pool gives."""

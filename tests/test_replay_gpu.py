@@ -205,3 +205,131 @@ def test_xl_layer_sizes(dtype, model_dirs, plain_logits, tmp_path):
             d = max_diff(row, ref[pos])
             assert d <= TOL[dtype], f"request {rid} position {pos}: max |logit difference| {d:.3e} > {TOL[dtype]}"
         assert len(s.logits[rid]) == 5 + len(toks) - first[int(rid[1:])]
+
+
+def compare_rows(s, reqs, model_dir, plain_logits, dtype, device="cpu"):
+    """Every logits row that was asked for against the plain implementation; returns (rows, worst)."""
+    rows, worst = 0, 0.0
+    for rid, toks in reqs.items():
+        if rid not in s.logits:
+            continue
+        ref = plain_logits(model_dir, toks, device=device)
+        for pos, row in s.logits[rid].items():
+            d = max_diff(row, ref[pos])
+            assert d <= TOL[dtype], f"request {rid} position {pos}: max |logit difference| {d:.3e} > {TOL[dtype]}"
+            kl = max_kl(ref[pos], row)
+            assert kl <= KL_BOUND[dtype], f"request {rid} position {pos}: KL(plain || engine) {kl:.3e}"
+            rows, worst = rows + 1, max(worst, d)
+    return rows, worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name, sharpen", [("WIDE", 2.5), ("XLW", 2.0)])
+def test_dozens_of_requests_decode_side_by_side_at_real_widths(name, sharpen, dtype, model_dirs, plain_logits, tmp_path):
+    """Sixty-four, then forty, then twenty-four live requests decode side by side at GPT-2 small's
+    and GPT-2 XL's layer widths, after prompts of different lengths that came in mixed steps: the
+    steps of 17 to 64 rows are those of a loaded server (a norm kernel of its own, the few-row
+    product with K split over blocks or the tensor-memory product with the weights on the M side,
+    batches padded to a graph's shape)."""
+    model_dir = model_dirs(name, TORCH_DTYPE[dtype], sharpen=sharpen)
+    vocab = TINY[name]["vocab_size"]
+    base = [random_tokens(vocab, 150, 700 + i) for i in range(8)]          # a request is a prefix of one of these
+    n_req = 64
+    prompt_len = [20 + (29 * i) % 101 for i in range(n_req)]                # 20..120
+    ids = [f"q{i}" for i in range(n_req)]
+    total = {rid: prompt_len[i] + (6 if i < 24 else 4 if i < 40 else 2) for i, rid in enumerate(ids)}
+    reqs = {rid: base[i % 8][:total[rid]] for i, rid in enumerate(ids)}
+    s = TraceSession(model_dir, dtype, tmp_path / "many", n_req * 192, vocab, extra=["--max-requests", "64"])
+    # prompts, sixteen requests a step, each wanting its last row; the second group beside decoded tokens of the first
+    at = {}
+    for g in range(0, n_req, 16):
+        entries = [(ids[i], reqs[ids[i]][:prompt_len[i]], [prompt_len[i] - 1]) for i in range(g, g + 16)]
+        if g == 16:
+            entries += [(ids[i], reqs[ids[i]][at[ids[i]]:at[ids[i]] + 1], [0]) for i in range(0, 16)]
+            for i in range(0, 16):
+                at[ids[i]] += 1
+        s.step(entries)
+        for i in range(g, g + 16):
+            at[ids[i]] = prompt_len[i]
+    live = list(ids)
+    sizes = []
+    while live:
+        ended = [rid for rid in live if at[rid] + 1 == total[rid]]
+        s.step([(rid, reqs[rid][at[rid]:at[rid] + 1], [0]) for rid in live], end=ended)
+        sizes.append(len(live))
+        for rid in live:
+            at[rid] += 1
+        live = [rid for rid in live if rid not in ended]
+    s.close()
+    assert 64 in sizes and 40 in sizes and 24 in sizes
+    # (a request is a prefix of its base sequence, and a position's logits depend on nothing after it:
+    # the plain implementation runs once for each of the eight)
+    rows, _ = compare_rows(s, {rid: base[i % 8] for i, rid in enumerate(ids)}, model_dir, plain_logits, dtype)
+    assert rows == n_req + sum(total[rid] - prompt_len[i] for i, rid in enumerate(ids))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_medium_layer_sizes(dtype, model_dirs, plain_logits, tmp_path):
+    """GPT-2 medium's layer sizes (width 1024, sixteen heads, inner 4096), two layers: a long prompt in
+    one step, a mixed step (a portion beside single tokens), then single tokens side by side."""
+    model_dir = model_dirs("MEDW", TORCH_DTYPE[dtype], sharpen=2.5)
+    vocab = TINY["MEDW"]["vocab_size"]
+    reqs = {"r0": random_tokens(vocab, 930, 800), "r1": random_tokens(vocab, 310, 801), "r2": random_tokens(vocab, 40, 802)}
+    s = TraceSession(model_dir, dtype, tmp_path / "med", 960 + 320 + 64, vocab)
+    s.step([("r0", reqs["r0"][:900], [0, 127, 128, 511, 899])])
+    s.step([("r1", reqs["r1"][:300], [0, 63, 64, 299]), ("r0", reqs["r0"][900:901], [0]), ("r2", reqs["r2"][:2], [0, 1])])
+    s.step([("r2", reqs["r2"][2:33], range(31)), ("r0", reqs["r0"][901:902], [0]), ("r1", reqs["r1"][300:301], [0])])
+    at = {"r0": 902, "r1": 301, "r2": 33}
+    while at:
+        ended = [r for r, p in at.items() if p + 1 == len(reqs[r])]
+        s.step([(r, reqs[r][p:p + 1], [0]) for r, p in at.items()], end=ended)
+        at = {r: p + 1 for r, p in at.items() if r not in ended}
+    s.close()
+    rows, _ = compare_rows(s, reqs, model_dir, plain_logits, dtype)
+    assert rows == 5 + 4 + 2 + 31 + (930 - 900) + (310 - 300) + (40 - 33)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_real_vocabulary_inside_a_step(dtype, model_dirs, plain_logits, tmp_path):
+    """One layer of GPT-2 small's sizes with the vocabulary of 50257: logits wanted at three rows of a
+    prompt (the head's few-row product over 50257 features, whose pitch is no multiple of a tile),
+    then for eight requests that decode side by side, then at forty rows of a portion (the head
+    through the tensor-memory product with the vocabulary on its M side)."""
+    model_dir = model_dirs("V50K", TORCH_DTYPE[dtype], sharpen=2.5)
+    vocab = TINY["V50K"]["vocab_size"]
+    reqs = {f"r{i}": random_tokens(vocab, 30 + 7 * i, 820 + i) for i in range(8)}
+    reqs["p"] = random_tokens(vocab, 70, 830)
+    s = TraceSession(model_dir, dtype, tmp_path / "v50k", 9 * 128, vocab, extra=["--max-requests", "9"])
+    s.step([("r0", reqs["r0"][:27], [0, 13, 26])])
+    s.step([(f"r{i}", reqs[f"r{i}"][:27 + 7 * i], []) for i in range(1, 8)])
+    for t in range(3):
+        s.step([(f"r{i}", reqs[f"r{i}"][27 + 7 * i + t:28 + 7 * i + t], [0]) for i in range(8)],
+               end=[f"r{i}" for i in range(8)] if t == 2 else [])
+    s.step([("p", reqs["p"][:30], [])])
+    s.step([("p", reqs["p"][30:], range(40))], end=["p"])
+    s.close()
+    rows, _ = compare_rows(s, reqs, model_dir, plain_logits, dtype)
+    assert rows == 3 + 24 + 40
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_gpt2_small_whole_against_the_plain_implementation(dtype, model_dirs, plain_logits, tmp_path):
+    """The model the benchmark runs, whole: twelve layers, width 768, the vocabulary of 50257, random
+    weights with sharpened attention.  A prompt of 700 tokens in one step, a second request's prompt
+    in portions beside the first one's decoded tokens, then both side by side.  The plain
+    implementation's float64 formulas run on the GPU here (on the CPU this model takes minutes)."""
+    model_dir = model_dirs("SMALL", TORCH_DTYPE[dtype], sharpen=2.0)
+    vocab = TINY["SMALL"]["vocab_size"]
+    reqs = {"a": random_tokens(vocab, 716, 850), "b": random_tokens(vocab, 150, 851)}
+    s = TraceSession(model_dir, dtype, tmp_path / "small", 768 + 192, vocab)
+    s.step([("a", reqs["a"][:700], [0, 1, 255, 256, 699])])
+    s.step([("a", reqs["a"][700:701], [0]), ("b", reqs["b"][:97], [0, 96])])
+    s.step([("b", reqs["b"][97:140], [0, 42]), ("a", reqs["a"][701:702], [0])])
+    for t in range(10):
+        s.step([("a", reqs["a"][702 + t:703 + t], [0]), ("b", reqs["b"][140 + t:141 + t], [0])],
+               end=["b"] if t == 9 else [])
+    for p in range(712, 716):
+        s.step([("a", reqs["a"][p:p + 1], [0])], end=["a"] if p == 715 else [])
+    s.close()
+    rows, worst = compare_rows(s, reqs, model_dir, plain_logits, dtype, device="cuda")
+    assert rows == 5 + 1 + 2 + 2 + 1 + 20 + 4
