@@ -13,6 +13,8 @@ from __future__ import annotations
 
 from typing import Dict, Iterable, List, Sequence
 
+import torch
+
 from .parts import base as P
 
 
@@ -54,7 +56,8 @@ def weight_bytes_per_step(model) -> int:
 
 def kv_bytes_per_position(cache) -> List[tuple]:
     """(bytes per cached position over all layers of the group, window) for every cache group."""
-    return [(g.bytes_per_page // cache.page_size, g.spec.window) for g in cache.groups]
+    itemsize = torch.empty(0, dtype=cache.dtype).element_size()
+    return [(g.bytes_per_page(itemsize) // cache.page_size, g.spec.window) for g in cache.groups]
 
 
 def kv_bytes(cache, contexts: Iterable[float]) -> float:
