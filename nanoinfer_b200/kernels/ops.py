@@ -59,6 +59,10 @@ _SIGNATURES = {
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                              _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                              _c_int, _c_ptr, _c_ptr, _c_ptr],
+    "nib_attention_decode_mma_supported": [_c_int, _c_int],
+    "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
+                                 _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
+                                 _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
@@ -540,10 +544,14 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
 DECODE_RESIDENT_BLOCKS = 888
 
 
-def decode_split(n_rows: int, n_head: int, max_keys: int) -> tuple:
+#: the bfloat16 decode attention on warp-level MMAs where the shape allows (False: always the streaming kernel)
+USE_DECODE_MMA = True
+
+
+def decode_split(n_rows: int, n_head: int, max_keys: int, resident: int = DECODE_RESIDENT_BLOCKS) -> tuple:
     """(chunk, n_splits): keys per split (a multiple of 64) so that the blocks fill the GPU once: six
     blocks an SM are resident, and a block that comes after the first wave runs nearly alone."""
-    want = max(1, DECODE_RESIDENT_BLOCKS // max(1, n_rows * n_head))
+    want = max(1, resident // max(1, n_rows * n_head))
     chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
     return chunk, max(1, -(-max_keys // chunk))
 
@@ -561,17 +569,31 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                      window: int, status: torch.Tensor, max_keys: int, workspace,
                      rows: Optional[torch.Tensor] = None) -> None:
     """Split-KV attention for rows that are single decoded tokens.  ``max_keys``: the longest key
-    range among them; partial results go through ``workspace``."""
+    range among them; partial results go through ``workspace``.  bfloat16 with a head size of 32, 64,
+    96 or 128 runs on the warp-level MMA kernel, everything else (and float32, in true 32-bit
+    arithmetic) on the streaming kernel."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
-    chunk, n_splits = decode_split(n_rows, n_head, max_keys)
+    mma = USE_DECODE_MMA and q.dtype == torch.bfloat16 and _can("nib_attention_decode_mma_supported", head_dim, page_size) \
+        and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
+    # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
+    resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
+    chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident)
     scratch = counters = None
     if n_splits > 1:
         # (never more than the resident blocks: the same size every step, so that the buffers stay put)
         assert n_rows * n_head * n_splits <= DECODE_RESIDENT_BLOCKS
         scratch = workspace.get("attention.partials", (DECODE_RESIDENT_BLOCKS * (head_dim + 2),), torch.float32)
         counters = workspace.get_zeroed("attention.arrivals", (DECODE_RESIDENT_BLOCKS,), torch.int32)
+    if mma:
+        _check(library().nib_attention_decode_mma(_ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
+                                                  out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
+                                                  _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head,
+                                                  head_dim, page_size, n_pages, float(scale), int(window), chunk,
+                                                  n_splits, _ptr(counters), _ptr(status), _stream()),
+               "attention_decode_mma")
+        return
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,

@@ -218,6 +218,70 @@ def test_both_prefill_attention_kernels_at_head_size_64(case):
         assert (out.cpu().double()[rows] - want[rows]).abs().max() < 2e-2, kernel
 
 
+DECODE_CASES = [
+    # n_head, n_kv_head, head_dim, page, lengths (one single-token row each), window
+    (12, 12, 64, 16, [1024, 1000, 513, 1], 0),
+    (6, 2, 64, 16, [130, 64, 65, 17], 0),
+    (5, 5, 24, 16, [40, 33, 2], 0),
+    (3, 1, 128, 32, [70, 9, 300], 0),
+    (4, 2, 32, 16, [100, 45, 16], 24),
+    (2, 2, 96, 48, [300, 31], 0),
+    (4, 2, 64, 16, [700, 300, 5], 100),
+    (2, 2, 80, 16, [250, 16], 0),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("case", DECODE_CASES)
+def test_both_decode_attention_kernels_at_every_split(dtype, case):
+    """Single decoded tokens over scattered pages, each kernel called directly with 1 to 16 splits of the
+    keys: the streaming kernel (both dtypes, every head size) and, in bfloat16 at head sizes 32, 64,
+    96 and 128, the kernel that takes 16 keys at a time with warp-level MMAs; against the plain
+    attention.  Positions past a row's own in its last page hold NaN, as a page that was used before
+    may: a key that is not the row's must not reach the result, not even times zero."""
+    o = ops()
+    n_head, n_kv_head, hd, ps, lengths, window = case
+    c = paged_case(dtype, n_head, n_kv_head, hd, ps, lengths, [1] * len(lengths), seed=3 * hd + len(lengths))
+    for e, n in enumerate(lengths):                     # poison what lies behind each request's last position
+        if n % ps:
+            c["cache"][int(c["table"][e, (n - 1) // ps]), :, :, n % ps:] = float("nan")
+    scale = 0.7 / math.sqrt(hd)
+    want = torch.cat([
+        P.causal_attention(q.double(), k.double(), v.double(), n_head, n_kv_head, scale=scale, window=window,
+                           q_pos0=len(k) - 1)
+        for q, k, v in zip(c["qs"], c["ks"], c["vs"])])
+    q = torch.cat(c["qs"]).to(dtype).to(DEV)
+    ctx = Ctx(c["row_entry"], c["positions"])
+    cache, table = c["cache"].to(DEV), c["table"].to(DEV)
+    n_rows, max_keys = len(lengths), (min(max(lengths), window) if window else max(lengths))
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    lib = o.library()
+    dt = 0 if dtype == torch.float32 else 1
+    stream = torch.cuda.current_stream().cuda_stream
+    kernels = ["streaming"]
+    if dtype == torch.bfloat16 and lib.nib_attention_decode_mma_supported(hd, ps):
+        kernels.append("mma")
+    assert ("mma" in kernels) == (dtype == torch.bfloat16 and hd in (32, 64, 96, 128))
+    scratch = torch.zeros(o.DECODE_RESIDENT_BLOCKS * (hd + 2), device=DEV)
+    counters = torch.zeros(o.DECODE_RESIDENT_BLOCKS, dtype=torch.int32, device=DEV)
+    for kernel in kernels:
+        for ns in (1, 2, 5, 16):
+            chunk = max(16, -(-(-(-max_keys // ns)) // 16) * 16)
+            n_splits = -(-max_keys // chunk)
+            if n_rows * n_head * n_splits > o.DECODE_RESIDENT_BLOCKS:
+                continue
+            out = torch.full_like(q, 7.0)
+            args = (q.data_ptr(), q.stride(0), cache.data_ptr(), scratch.data_ptr(), out.data_ptr(), out.stride(0),
+                    table.data_ptr(), table.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), n_rows,
+                    n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, chunk, n_splits, counters.data_ptr(),
+                    ctx.status.data_ptr(), stream)
+            code = lib.nib_attention_decode(dt, *args) if kernel == "streaming" else lib.nib_attention_decode_mma(*args)
+            assert code == 0 and int(ctx.status.item()) == 0, (kernel, n_splits)
+            diff = (out.cpu().double() - want).abs().max()
+            assert diff < tol, f"{kernel}, {n_splits} splits: {float(diff):.3e}"     # (NaN fails here too)
+            assert int(counters.abs().sum().item()) == 0     # found zero, left zero
+
+
 def test_attention_finds_one_far_key_among_hundreds():
     """One key far back is made to match the query: the output must be that key's value, whichever
     page it lies on."""
