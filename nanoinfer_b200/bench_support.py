@@ -267,11 +267,21 @@ def time_prefill(eng, n_prompts: int, prompt_len: int, runs: int, warmup: int, s
 def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed: int = 2) -> Dict[str, float]:
     """Decode throughput through the public entry point: requests are added with host token lists,
     ``Engine.step`` runs scheduler, step function and sampler, and every step's tokens are read
-    back to the host.  Wall-clock time around the timed steps, device idle before and after."""
+    back to the host.  Wall-clock time around the timed steps, device idle before and after.
+
+    Prompts enter under the engine's row budget, so the requests begin to decode a few steps apart;
+    prompts are that many tokens shorter than ``prompt_len`` and every request is given more new
+    tokens than the run takes, so that all ``batch`` requests decode in every timed step (a request
+    that ended inside the timed steps would leave a smaller batch of another shape behind).
+    ``host_ms_per_step``: what the host spends on a step (scheduling, packing, launching,
+    bookkeeping) without its waits for the device: where it is below the device's time per step,
+    the host is hidden behind the device."""
     from .sampling.sampler import SamplingParams
 
     g = torch.Generator().manual_seed(seed)
-    params = SamplingParams(max_new_tokens=warmup + steps + 1, temperature=0.0)
+    lag = -(-batch * prompt_len // max(1, min(eng.scheduler.prefill_budget, eng.runner.max_rows))) + 1
+    prompt_len = max(1, prompt_len - lag)
+    params = SamplingParams(max_new_tokens=warmup + steps + 2 * lag + 4, temperature=0.0)
     for _ in range(batch):
         eng.add_request(torch.randint(0, vocabulary(eng), (prompt_len,), generator=g).tolist(), params)
     while any(r.n_pending > 1 for r in eng.scheduler.running) or eng.scheduler.waiting:
@@ -279,21 +289,60 @@ def time_e2e_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, s
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()
+    eng.wait_seconds = 0.0
+    rows = 0
     t0 = time.perf_counter()
     for _ in range(steps):
         eng.step()
+        rows += len(eng.scheduler.running)
+    host = time.perf_counter() - t0 - eng.wait_seconds
     torch.cuda.synchronize()
     dt = time.perf_counter() - t0
+    full = rows == batch * steps
     while eng.has_work():
         eng.step()
-    return {"tokens_per_s": batch * steps / dt, "ms_per_step": dt / steps * 1e3,
+    return {"tokens_per_s": batch * steps / dt, "ms_per_step": dt / steps * 1e3, "host_ms_per_step": host / steps * 1e3,
+            "all_rows_in_every_step": full,
             "h2d_bytes_per_step": eng.runner.last_meta_bytes, "d2h_bytes_per_step": 4 * batch}
 
 
-def profile_step(eng, items, sampler=None, repeats: int = 3):
-    """Per-kernel device time of one step, run eagerly ``repeats`` times (the requests are cut back
-    after each run, so the same step is measured); returns {(launcher, label): (ms per step, calls)}."""
-    from .kernels import ops
+# ----------------------------------------------------------------------------- provenance
+def provenance() -> Dict[str, object]:
+    """Where a number comes from: the commit and whether the tree was clean, the tools, the device
+    and the time (the reference stamps its ledger lines the same way: crates/cli/src/bench.rs:151-175)."""
+    def git(*args):
+        try:
+            return subprocess.run(["git", "-C", repo_root(), *args], capture_output=True, text=True, timeout=10).stdout.strip()
+        except (OSError, subprocess.SubprocessError):
+            return ""
+    sha = git("rev-parse", "--short=12", "HEAD")
+    dirty: Optional[bool] = bool(git("status", "--porcelain")) if sha else None
+    if not sha:
+        # a copy of the tree without its history (a snapshot sent to another machine): the build step
+        # leaves the commit it was made from beside the kernel library
+        try:
+            with open(os.path.join(repo_root(), "nanoinfer_b200", "_build", "git_state.json")) as fh:
+                state = json.load(fh)
+            sha, dirty = state.get("git_sha") or "", state.get("git_dirty")
+        except (OSError, ValueError):
+            pass
+    out: Dict[str, object] = {"git_sha": sha or None, "git_dirty": dirty,
+                              "torch": torch.__version__, "cuda": torch.version.cuda,
+                              "time": time.strftime("%Y-%m-%dT%H:%M:%SZ", time.gmtime())}
+    if torch.cuda.is_available():
+        out["gpu"] = torch.cuda.get_device_name(0)
+    try:
+        out["load_1m"] = os.getloadavg()[0]
+    except OSError:
+        pass
+    return out
+
+
+# ----------------------------------------------------------------------------- the per-op profile
+def profile_step(eng, items, sampler=None, repeats: int = 3, phase: str = "decode"):
+    """One step run eagerly ``repeats`` times under a trace recorder (the requests are cut back after
+    each run, so the same step is measured); returns name -> (calls, ms, FLOPs, bytes) per step."""
+    from . import trace
 
     graphs = eng.runner.use_graphs
     eng.runner.use_graphs = False
@@ -302,81 +351,99 @@ def profile_step(eng, items, sampler=None, repeats: int = 3):
         eng.runner.step(items, sampler=sampler)
         for it, n in zip(items, lens):
             eng.cache.truncate(it.request, n)
-        prof = ops.start_profile()
+        rec = trace.start()
         for _ in range(repeats):
+            rec.begin_step(phase, sum(len(it.tokens) for it in items), 0)
             eng.runner.step(items, sampler=sampler)
             for it, n in zip(items, lens):
                 eng.cache.truncate(it.request, n)
-        out = prof.summary()
+        table = rec.table()
     finally:
-        ops.stop_profile()
+        trace.stop()
         eng.runner.use_graphs = graphs
-    return {k: (ms / repeats, n // repeats) for k, (ms, n) in out.items()}
+    return {k: (n // repeats, ms / repeats, fl / repeats, by / repeats) for k, (n, ms, fl, by) in table.items()}
 
 
-def format_profile(table) -> str:
-    total = sum(ms for ms, _ in table.values())
-    lines = [f"{'kernel':<28}{'shape':<26}{'calls':>6}{'ms':>10}{'%':>7}"]
-    for (name, label), (ms, n) in sorted(table.items(), key=lambda kv: -kv[1][0]):
-        lines.append(f"{name[4:]:<28}{label if 'linear' in name else '':<26}{n:>6}{ms:>10.4f}{100 * ms / total:>7.1f}")
-    lines.append(f"{'total':<60}{total:>10.4f}")
-    return "\n".join(lines)
-
-
-def print_profile(eng, prompt) -> None:
-    """The per-kernel breakdown of a prefill of ``prompt`` and of one decode step after it."""
+def print_profile(eng, prompt, out=None) -> None:
+    """Where the time of a prefill of ``prompt`` and of one decode step after it goes, op by op, with
+    each op's GFLOP/s, GB/s and fraction of the roofline (the reference's ``--profile``:
+    crates/cli/src/report.rs:22-58)."""
     import sys
 
+    from . import trace
     from .engine.runner import StepItem
     from .sampling.sampler import SamplingParams
 
+    out = out or sys.stderr
+    peaks = measured_peaks()
     r = eng.cache.open_request()
     eng.sampler.set_request(r.slot, SamplingParams(temperature=0.0))
-    pre = profile_step(eng, [StepItem(r, list(prompt), [len(prompt) - 1])], eng.sampler)
-    print(f"-- prefill of {len(prompt)} tokens", file=sys.stderr)
-    print(format_profile(pre), file=sys.stderr)
+    pre = profile_step(eng, [StepItem(r, list(prompt), [len(prompt) - 1])], eng.sampler, phase="prefill")
+    print(trace.format_table(pre, peaks["hbm_gbs"], peaks["bf16_tflops"],
+                             f"\nprefill of {len(prompt)} tokens (kernels launched one by one; peaks {peaks['source']})"), file=out)
     eng.runner.step([StepItem(r, list(prompt), [len(prompt) - 1])], sampler=eng.sampler)
     dec = profile_step(eng, [StepItem(r, [int(prompt[-1])], [0])], eng.sampler)
-    print(f"-- one decode step at context {len(prompt) + 1}", file=sys.stderr)
-    print(format_profile(dec), file=sys.stderr)
+    print(trace.format_table(dec, peaks["hbm_gbs"], peaks["bf16_tflops"],
+                             f"\none decode step at context {len(prompt) + 1}"), file=out)
     eng.cache.close_request(r)
 
 
 # ----------------------------------------------------------------------------- the bench command
-def run_cli_bench(args) -> int:
+def decode_points(model_dir: str, dtype: str, batches, prompt_len: int, tokens: int, warmup: int = 3,
+                  bandwidth_gbs: Optional[float] = None, runs: int = 3, profile: bool = False) -> List[dict]:
+    """The reference's bench at each batch size (crates/cli/src/bench.rs:240-373,
+    crates/cli/src/metal_batch.rs:113-160): ``batch`` requests with prompts of ``prompt_len`` tokens
+    decode ``tokens`` tokens; tokens a second, the bytes a step must read over its time, and the
+    share of the ceiling that the memory's rate sets; the pages the requests hold at the end of
+    ``pages_total``."""
     import sys
 
     peaks = measured_peaks()
-    bw = args.bandwidth_gbs or peaks["hbm_gbs"]
-    batches = [int(b) for b in str(args.batch).split(",") if b]
-    from .registry import load_config
-
-    from .registry import get_architecture
-    config = load_config(args.weights)
-    limit = get_architecture(config.architecture).build_spec(config).max_positions
-    if limit is not None and args.prompt_len + args.tokens + args.warmup > limit:
-        print(f"prompt_len + tokens must be <= {limit}", file=sys.stderr)
-        return 2
-    results = []
+    bw = bandwidth_gbs or peaks["hbm_gbs"]
+    out = []
     for b in batches:
-        eng = build_engine(args.weights, args.dtype, b, args.prompt_len + args.tokens + args.warmup,
-                           max_rows=max(2048, b))
-        dec = time_decode(eng, b, args.prompt_len, args.tokens, max(3, args.warmup))
-        pre = time_prefill(eng, 1, args.prompt_len, args.runs, max(1, args.warmup))
+        eng = build_engine(model_dir, dtype, b, prompt_len + tokens + warmup, max_rows=max(2048, b))
+        dec = time_decode(eng, b, prompt_len, tokens, max(3, warmup))
+        pre = time_prefill(eng, 1, prompt_len, runs, 1)
         step_bytes = weight_bytes_per_step(eng.model) + kv_bytes(eng.cache, [dec["mean_context"]] * b)
         ceiling = bw * 1e9 / step_bytes * b
-        line = {"dtype": args.dtype, "batch": b, "prompt_len": args.prompt_len, "tokens": args.tokens,
-                "decode_tok_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],
-                "decode_gbs": step_bytes / (dec["ms_per_step"] / 1e3) / 1e9,
-                "ceiling_tok_s": ceiling, "pct_of_ceiling": 100.0 * dec["tokens_per_s"] / ceiling,
-                "prefill_tok_s": pre["tokens_per_s"], "note": args.note}
-        print(f"{args.dtype} B={b}: prefill {pre['tokens_per_s']:.0f} tok/s | decode {dec['tokens_per_s']:.1f} tok/s "
-              f"({line['decode_gbs']:.1f} GB/s) | {line['pct_of_ceiling']:.2f}% of {ceiling:.0f} tok/s ceiling")
-        results.append(line)
+        pages_total = [g.pool.n_pages for g in eng.cache.groups]
+        pages_used = [-(-(prompt_len + tokens + warmup) // eng.cache.page_size) * b for _ in eng.cache.groups]
+        out.append({"dtype": dtype, "batch": b, "prompt_len": prompt_len, "tokens": tokens,
+                    "decode_tok_s": dec["tokens_per_s"], "decode_ms_per_step": dec["ms_per_step"],
+                    "decode_gbs": step_bytes / (dec["ms_per_step"] / 1e3) / 1e9, "ceiling_tok_s": ceiling,
+                    "frac_of_hbm": dec["tokens_per_s"] / ceiling, "peaks": peaks["source"],
+                    "prefill_tok_s": pre["tokens_per_s"], "prefill_ms": pre["ms"],
+                    "pages_used": pages_used, "pages_total": pages_total})
+        if profile:
+            print(f"-- batch {b}", file=sys.stderr)
+            print_profile(eng, [(7 * i + 1) % vocabulary(eng) for i in range(prompt_len)])
         del eng
         torch.cuda.empty_cache()
+    return out
+
+
+def run_cli_bench(args) -> int:
+    import sys
+
+    from .registry import get_architecture, load_config
+
+    batches = [int(b) for b in str(args.batch).split(",") if b]
+    config = load_config(args.weights)
+    limit = get_architecture(config.architecture).build_spec(config).max_positions
+    if limit is not None and args.prompt_len + args.tokens + max(3, args.warmup) > limit:
+        print(f"prompt_len + tokens + warm-up must be <= {limit}", file=sys.stderr)
+        return 2
+    results = decode_points(args.weights, args.dtype, batches, args.prompt_len, args.tokens, args.warmup,
+                            args.bandwidth_gbs, args.runs, getattr(args, "profile", False))
+    stamp = provenance()
+    for line in results:
+        line["note"] = args.note
+        print(f"{args.dtype} B={line['batch']}: prefill {line['prefill_tok_s']:.0f} tok/s | decode "
+              f"{line['decode_tok_s']:.1f} tok/s ({line['decode_gbs']:.1f} GB/s) | {100 * line['frac_of_hbm']:.2f}% of "
+              f"{line['ceiling_tok_s']:.0f} tok/s ceiling | pages {line['pages_used']} of {line['pages_total']}")
     if args.out:
         with open(args.out, "a") as fh:
             for line in results:
-                fh.write(json.dumps(line) + "\n")
+                fh.write(json.dumps({**line, **stamp}) + "\n")
     return 0

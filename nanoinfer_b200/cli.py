@@ -64,7 +64,12 @@ def cmd_generate(args) -> int:
         return 2
     prompt = _ids(args.prompt_ids)
     t0 = time.perf_counter()
-    eng = Engine(args.weights, dtype=args.dtype, max_batch=1, max_rows=max(64, len(prompt)))
+    eng = Engine(args.weights, dtype=args.dtype, max_batch=1, max_rows=max(64, len(prompt)),
+                 use_graphs=not args.trace_out, run_ahead=not args.trace_out)
+    rec = None
+    if args.trace_out:
+        from . import trace
+        rec = trace.start()
     from .measure import parameter_count
     print(f"loaded {args.weights} ({parameter_count(eng.model) / 1e6:.1f}M params) in "
           f"{time.perf_counter() - t0:.2f}s", file=sys.stderr)
@@ -76,6 +81,9 @@ def cmd_generate(args) -> int:
     t_first = None
     printed = 0
     while eng.has_work():
+        if rec is not None:   # (one scheduler decision is one step: the whole prompt, then a token at a time)
+            n_in = eng.scheduler.running[0].n_pending if eng.scheduler.running else len(prompt)
+            rec.begin_step("prefill" if n_in > 1 else "decode", n_in, len(prompt) + len(req.output) + (n_in > 1))
         eng.step()
         # (the engine runs a step ahead of its reads: the newest entry may still be a negative stand-in)
         while printed < len(req.output) and req.output[printed] >= 0:
@@ -90,6 +98,18 @@ def cmd_generate(args) -> int:
     print(f"[{args.dtype}] prompt {len(prompt)} tok, prefill {t_first * 1e3:.1f} ms "
           f"({len(prompt) / t_first:.1f} tok/s), decode {(n - 1) / max(total - t_first, 1e-9):.2f} tok/s",
           file=sys.stderr)
+    if rec is not None:
+        from . import trace
+        from .measure import kv_bytes
+        trace.stop()
+        limit = eng.model.max_positions or (len(prompt) + n)
+        trace.write_jsonl(rec, args.trace_out,
+                          {"config": {"model": os.path.basename(os.path.normpath(args.weights)), "dtype": args.dtype,
+                                      "backend": "sm_100a", "step": "paged-kv", "params": parameter_count(eng.model)},
+                           "prompt_tokens": prompt},
+                          [{"id": t} for t in req.output],
+                          {"len": len(prompt) + n, "capacity": limit, "bytes": int(kv_bytes(eng.cache, [len(prompt) + n]))})
+        print(f"wrote {len(rec.events)} launches of {len(rec.steps)} steps to {args.trace_out}", file=sys.stderr)
     if args.profile:
         from .bench_support import print_profile
         print_profile(eng, prompt)
@@ -121,7 +141,11 @@ def main(argv=None) -> int:
     g.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
     g.add_argument("--top-k", type=int, default=40)
     g.add_argument("--seed", type=int, default=42)
-    g.add_argument("--profile", action="store_true", help="print a per-kernel time breakdown afterwards")
+    g.add_argument("--profile", action="store_true",
+                   help="print afterwards where the time goes, op by op, with GFLOP/s, GB/s and the fraction of the roofline")
+    g.add_argument("--trace-out", default=None,
+                   help="write every launch of the run (op, layer, time, FLOPs, bytes) as JSON lines to this file; "
+                        "the run then launches its kernels one by one instead of replaying graphs")
     g.set_defaults(fn=cmd_generate)
 
     b = sub.add_parser("bench", help="measure prefill and decode throughput")
@@ -133,8 +157,10 @@ def main(argv=None) -> int:
     b.add_argument("--warmup", type=int, default=1)
     b.add_argument("--bandwidth-gbs", type=float, default=None,
                    help="memory bandwidth for the decode ceiling (default: the measured peak)")
-    b.add_argument("--out", default=None, help="append the result line to this file")
+    b.add_argument("--out", default=None, help="append the result line (with commit, tools and time) to this file")
     b.add_argument("--note", default="")
+    b.add_argument("--profile", action="store_true",
+                   help="also print, per batch size, where a prefill and a decode step spend their time, op by op")
     b.set_defaults(fn=cmd_bench)
 
     s = sub.add_parser("serve-bench", help="many requests of random lengths: continuous against static batching")

@@ -8,6 +8,7 @@ continuous-batching scheduler (crates/cli/src/metal_serve.rs:255-363).
 """
 from __future__ import annotations
 
+import time
 from typing import Dict, List, Optional, Sequence, Union
 
 import torch
@@ -59,6 +60,9 @@ class Engine:
                 self._token_ring.append((torch.empty(max(max_batch, 1), dtype=torch.int32).pin_memory(),
                                          torch.cuda.Event()))
         self._token_ring_next = 0
+        #: seconds the host has spent waiting for the device to hand over a step's tokens (a caller
+        #: that measures the host's own share of a step sets it to zero and reads it back)
+        self.wait_seconds = 0.0
 
     def _on_admit(self, req: Request) -> None:
         self.sampler.set_request(req.cache.slot, req.params, n_draws_done=len(req.output))
@@ -99,7 +103,9 @@ class Engine:
             return []
         items, host, event, n, ended = self._in_flight
         self._in_flight = None
+        t0 = time.perf_counter()
         event.synchronize()
+        self.wait_seconds += time.perf_counter() - t0
         ended = ended + self.scheduler.on_tokens_read(items, host[:n].tolist())
         return ended
 

@@ -72,40 +72,37 @@ _SIGNATURES = {
 }
 
 
-class Profiler:
-    """Per-kernel device time, measured with CUDA events around every launcher call while active
-    (the per-op breakdown of the reference's ``--profile``, crates/cli/src/report.rs:22-58)."""
-
-    def __init__(self):
-        self.records = []   # (launcher name, label, start event, end event)
-        self.label = ""
-
-    def summary(self):
-        torch.cuda.synchronize()
-        out = {}
-        for name, label, e0, e1 in self.records:
-            key = (name, label)
-            ms, n = out.get(key, (0.0, 0))
-            out[key] = (ms + e0.elapsed_time(e1), n + 1)
-        return out
+#: the active trace recorder (``trace.start`` puts it here), or None
+_rec = None
 
 
-_profiler: Optional[Profiler] = None
+def _recorder():
+    return _rec
 
 
-def start_profile() -> Profiler:
-    global _profiler
-    _profiler = Profiler()
-    return _profiler
+#: the analytic description of the launch about to be made (set by the faces while a recorder is active)
+_pending_op = None
 
 
-def stop_profile() -> None:
-    global _profiler
-    _profiler = None
+def _note(kind: str, name: str, dims, flops: float, nbytes: float) -> None:
+    global _pending_op
+    from ..trace import Op
+    _pending_op = Op(kind, name, tuple(int(d) for d in dims), float(flops), float(nbytes))
+
+
+def tracing() -> bool:
+    """Whether a trace recorder is active (the faces then describe every launch to it)."""
+    return _rec is not None
+
+
+def trace_scope(layer: int = -1, name: str = "") -> None:
+    """Tell the active recorder which layer, and which named product, the next launches belong to."""
+    if _rec is not None:
+        _rec.layer, _rec.name = layer, name
 
 
 class _Library:
-    """The launchers of the kernel library; with a profiler active each call is bracketed by events."""
+    """The launchers of the kernel library; with a trace recorder active each call is bracketed by events."""
 
     def __init__(self, lib: ctypes.CDLL):
         for name, argtypes in _SIGNATURES.items():
@@ -117,15 +114,25 @@ class _Library:
 
     @staticmethod
     def _wrap(name, fn):
+        counted = name not in ("nib_linear_tc_supported", "nib_linear_tc_pair_supported", "nib_linear_skinny_supported",
+                               "nib_attention_prefill_tc_supported", "nib_attention_prefill_supported",
+                               "nib_attention_decode_mma_supported")
+
         def call(*args):
-            prof = _profiler
-            if prof is None:
+            global _pending_op
+            rec = _recorder() if counted else None
+            if rec is None:
                 return fn(*args)
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             code = fn(*args)
             e1.record()
-            prof.records.append((name, prof.label, e0, e1))
+            op, _pending_op = _pending_op, None
+            if code == 0:
+                if op is None:
+                    from ..trace import Op
+                    op = Op("other", name[4:], (0, 0, 0), 0.0, 0.0)
+                rec.add(op, name, e0, e1)
             return code
         return call
 
@@ -217,6 +224,8 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
         _i32(positions, "positions")
     if feedback is not None:
         _i32(feedback, "feedback")
+    if tracing():
+        _note("embed", "embed", (T, C, 0), T * C, T * C * ((2 if pos_table is not None else 1) * table.element_size() + 4))
     _check(library().nib_embed(_dt(table), _ptr(tokens), _ptr(positions), _ptr(table), _ptr(pos_table),
                                _ptr(feedback), _ptr(out), T, C, _stream()), "embed")
 
@@ -233,6 +242,8 @@ def layernorm(x: torch.Tensor, gamma: torch.Tensor, beta: torch.Tensor, eps: flo
         raise KernelError("layernorm: out must be contiguous [n_rows, C]")
     if rows is not None:
         _i32(rows, "rows")
+    if tracing():
+        _note("ln", "ln", (n_rows, C, 0), 8.0 * n_rows * C, n_rows * C * (4 + out.element_size()) + 8 * C)
     _check(library().nib_layernorm(_dt(out), _ptr(x), _ptr(rows), _ptr(gamma), _ptr(beta), _ptr(out),
                                    n_rows, C, float(eps), _stream()), "layernorm")
 
@@ -313,12 +324,22 @@ def linear_tc_pair(a: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     _, kv_args = _option_args(None, kv)
     if kv is not None and (kv[4] % 64 or kv[0].shape[4] % 16 or out.dtype != torch.bfloat16 or residual):
         return False
-    if _profiler is not None:
-        _profiler.label = f"M={M} N={N} K={K}" + (" kv" if kv else "")
+    if tracing():
+        _note_linear(a, None, w, bias, out, M, residual)
     _check(library().nib_linear_tc_pair(_dt(out), _ptr(a), a.stride(0), _ptr(w), w.stride(0), _ptr(bias), _ptr(out),
                                         out.stride(0), M, N, K, act, int(residual), int(bq), int(splits), *kv_args,
                                         _ptr(status_word()), _stream()), "linear_tc_pair")
     return True
+
+
+def _note_linear(a, norm, w, bias, out, M, residual) -> None:
+    """[M, K, N]: 2 M K N + M N FLOPs; weights, bias, input and output once (the residual stream is read
+    and written where the product adds into it)."""
+    N, K = w.shape
+    in_bytes = M * K * (4 if norm is not None else a.element_size())
+    out_bytes = M * N * out.element_size() * (2 if residual else 1)
+    _note("matmul", "matmul", (M, K, N), 2.0 * M * K * N + M * N,
+          N * K * w.element_size() + (4 * N if bias is not None else 0) + in_bytes + out_bytes)
 
 
 class NormInput:
@@ -403,8 +424,8 @@ def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=Non
     if not _can("nib_linear_skinny_supported", M, K, w.stride(0), int(norm is not None), 16 + (_ptr(w) & 15)):
         return False
     ln_args, kv_args = _option_args(norm, kv)
-    if _profiler is not None:
-        _profiler.label = f"M={M} N={N} K={K}" + (" ln" if norm is not None else "") + (" kv" if kv else "")
+    if tracing():
+        _note_linear(a, norm, w, bias, out, M, residual)
     code = lib.nib_linear_skinny(_dt(out), _ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0),
                                  _ptr(bias), _ptr(out), out.stride(0), M, N, K, act, int(residual), *ln_args,
                                  *kv_args, int(split), _ptr(status_word()), _stream())
@@ -426,8 +447,8 @@ def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=N
         return False
     parts, counters = _split_buffers(w.device) if split else (None, None)
     ln_args, kv_args = _option_args(norm, kv)
-    if _profiler is not None:
-        _profiler.label = f"M={M} N={N} K={K}" + (" ln" if norm is not None else "") + (" kv" if kv else "")
+    if tracing():
+        _note_linear(a, norm, w, bias, out, M, residual)
     code = lib.nib_linear_tc_small(_dt(out), _ptr(a), a.stride(0) if a is not None else 0, _ptr(w), w.stride(0),
                                    _ptr(bias), _ptr(out), out.stride(0), M, N, K, act, int(residual), *ln_args,
                                    *kv_args, _ptr(parts), parts.numel() if split else 0, _ptr(counters),
@@ -479,8 +500,8 @@ def linear(a: Optional[torch.Tensor], w: torch.Tensor, bias: Optional[torch.Tens
         return
     if norm is not None:
         a = norm.materialise(M)   # (scratch: a second call for the same rows rewrites the same values)
-    if _profiler is not None:
-        _profiler.label = f"M={M} N={w.shape[0]} K={w.shape[1]}"
+    if tracing():
+        _note_linear(a, None, w, bias, out, M, residual)
     # pairs of blocks on one 256-row MMA (half of the weight tile per SM) beat the single-block kernel
     # by 5 to 40 per cent where there is enough work
     if pair_pays(M, w.shape[0], w.shape[1]) and linear_tc_pair(a, w, bias, out, M, act, residual):
@@ -518,6 +539,8 @@ def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, bl
     if two != 2 or not cache.is_contiguous() or cache.dtype != src.dtype or src.stride(1) != 1:
         raise KernelError("kv_append: cache must be contiguous [pages, 2, kv_heads, page, head_dim] of src's dtype")
     _i32(block_table, "block_table")
+    if tracing():
+        _note("kv_write", "kv_write", (T, 2 * n_kv_head * head_dim, 0), 0.0, 2.0 * T * 2 * n_kv_head * head_dim * src.element_size())
     _check(library().nib_kv_append(_dt(src), _ptr(src), src.stride(0), k_off, v_off, _ptr(cache),
                                    _ptr(block_table), block_table.shape[1], _ptr(row_entry), _ptr(positions),
                                    T, n_kv_head, head_dim, page_size, n_pages, _ptr(status), _stream()),
@@ -554,6 +577,15 @@ def decode_split(n_rows: int, n_head: int, max_keys: int, resident: int = DECODE
     want = max(1, resident // max(1, n_rows * n_head))
     chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
     return chunk, max(1, -(-max_keys // chunk))
+
+
+def _note_attention(n_q: int, keys_seen: float, kv_rows: float, n_head: int, n_kv_head: int, head_dim: int,
+                    itemsize: int) -> None:
+    """[queries, keys seen by them in all, width]: per key and head the score (2 hd), the softmax (~5)
+    and the weighted sum (2 hd); the queries and outputs, and ``kv_rows`` key and value rows read once."""
+    width = n_head * head_dim
+    _note("attn", "attn", (n_q, int(keys_seen), width), keys_seen * (4.0 * width + 5.0 * n_head),
+          itemsize * (2.0 * n_q * width + 2.0 * kv_rows * n_kv_head * head_dim))
 
 
 def attention_decode_reserve(workspace, n_head: int, head_dim: int) -> None:
@@ -642,15 +674,25 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
     16) and to the general kernel otherwise."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     fast_pages = page_size % 16 == 0 and head_dim % 8 == 0 and head_dim <= 128
+    traced = tracing()   # (the counts leave a window out: they are those of attention over all keys)
     if not fast_pages:
+        if traced:
+            _note_attention(ctx.n_rows, plan.decode_keys + plan.prefill_keys, plan.decode_keys + plan.prefill_kv_rows,
+                            n_head, n_kv_head, head_dim, q.element_size())
         attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
                        window, ctx.status)
         return
     if plan.n_decode:
         keys = plan.max_decode_keys if window <= 0 else min(plan.max_decode_keys, window)
+        if traced:
+            _note_attention(plan.n_decode, plan.decode_keys, plan.decode_keys, n_head, n_kv_head, head_dim,
+                            q.element_size())
         attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
                          window, ctx.status, keys, ctx.workspace, plan.decode_rows)
     if plan.n_prefill_rows:
+        if traced:
+            _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
+                            q.element_size())
         if q.dtype == torch.bfloat16 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
@@ -669,6 +711,8 @@ def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:
     if logits.dtype != torch.float32 or logits.stride(1) != 1:
         raise KernelError("argmax: logits must be float32 with contiguous rows")
     _i32(out, "out")
+    if tracing():
+        _note("sample", "sample", (n_rows, logits.shape[1], 0), n_rows * logits.shape[1], 4.0 * n_rows * logits.shape[1])
     _check(library().nib_argmax(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(out), _stream()),
            "argmax")
 
@@ -691,6 +735,8 @@ def sample(logits: torch.Tensor, n_rows: int, row_slot: torch.Tensor, temperatur
     _i32(row_slot, "row_slot"); _i32(top_k, "top_k"); _i32(out, "out")
     if scratch.dtype != torch.int64 or scratch.numel() < 2 * n_rows or out.numel() < n_rows:
         raise KernelError("sample: scratch must hold two int64 words per row, out one int32")
+    if tracing():
+        _note("sample", "sample", (n_rows, logits.shape[1], 0), n_rows * logits.shape[1], 4.0 * n_rows * logits.shape[1])
     _check(library().nib_sample(_ptr(logits), logits.stride(0), n_rows, logits.shape[1], _ptr(row_slot),
                                 _ptr(temperature), _ptr(top_k), _ptr(rng_state), _ptr(out),
                                 _ptr(last_token), _ptr(scratch), int(bool(teams)), _stream()), "sample")

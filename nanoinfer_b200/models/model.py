@@ -186,7 +186,9 @@ class Model:
         self.embedding.forward(ctx, x, self.position)
         for i, e in enumerate(self.schedule):
             owner = i if e.cache_of is None else e.cache_of
+            ctx.layer = i
             self.layers[e.layer].forward(x, ctx, caches.get(owner), states.get(i), e.cache_of is None, self.dtype)
+        ctx.layer = -1
         if n_logits <= 0:
             return None
         # the final norm runs on the wanted rows only; the head folds it into its product where it can

@@ -33,14 +33,21 @@ class AttentionPlan(StepPlan):
     def __init__(self, entry_start, entry_pos0, for_graph: bool = False, device=None):
         dec, pre, tiles = [], [], []
         self.max_decode_keys = 0
+        #: for the trace's counts: keys seen by the decoded rows, keys seen by the portions' rows, and the
+        #: key/value rows the portions' requests hold (each is read once)
+        self.decode_keys = self.prefill_keys = self.prefill_kv_rows = 0
         for e in range(len(entry_start) - 1):
             a, b = entry_start[e], entry_start[e + 1]
             if b - a == 1:
                 dec.append(a)
                 self.max_decode_keys = max(self.max_decode_keys, entry_pos0[e] + 1)
+                self.decode_keys += entry_pos0[e] + 1
             else:
                 pre.extend(range(a, b))
                 tiles.extend((e, off) for off in range(0, b - a, 64))
+                n = b - a
+                self.prefill_keys += n * entry_pos0[e] + n * (n + 1) // 2
+                self.prefill_kv_rows += entry_pos0[e] + n
         # the same portions in tiles of 128 rows, for the tcgen05 kernel
         wide = [(e, off) for e in range(len(entry_start) - 1) if entry_start[e + 1] - entry_start[e] > 1
                 for off in range(0, entry_start[e + 1] - entry_start[e], 128)]
@@ -126,6 +133,7 @@ class CausalSelfAttention(Mixer):
         if writes_cache:
             qkv = ws.get("attention.qkv", (ctx.max_rows, self.q_dim + 2 * self.kv_dim), self.dtype)
             # small steps: keys and values go to the cache from the projection's epilogue
+            ops.trace_scope(ctx.layer, "qkv")
             fused = self.position is None and ops.linear_qkv(
                 xn, p["qkv_weight"], p.get("qkv_bias"), qkv, T, self.q_dim, cache.layer, cache.block_table,
                 ctx.row_entry, ctx.positions, ctx.status, norm=norm)
@@ -140,6 +148,7 @@ class CausalSelfAttention(Mixer):
             # this layer reads another layer's keys and values: only the queries are projected
             q = ws.get("attention.q", (ctx.max_rows, self.q_dim), self.dtype)
             qb = p.get("qkv_bias")
+            ops.trace_scope(ctx.layer, "qkv")
             ops.linear(xn, p["qkv_weight"][:self.q_dim], None if qb is None else qb[:self.q_dim], q, T, norm=norm)
             if self.position is not None:
                 self.position.on_qk(q[:T], None, ctx)
@@ -149,4 +158,5 @@ class CausalSelfAttention(Mixer):
             plan = ctx.plans["causal_attention"] = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0,
                                                                  device=x.device)
         ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window, plan)
+        ops.trace_scope(ctx.layer, "attn_proj")
         ops.linear(att, p["out_weight"], p.get("out_bias"), x, T, residual=True)

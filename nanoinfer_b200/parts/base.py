@@ -289,6 +289,8 @@ class StepContext:
     host_entry_slot: List[int] = field(default_factory=list)
     max_q_len: int = 0
     max_kv_len: int = 0
+    #: the schedule entry that is running (set by the model's forward pass; -1 outside the layers)
+    layer: int = -1
     #: the step's plans by name (``Part.step_planner``); a part that finds none builds its own
     plans: Dict[str, StepPlan] = field(default_factory=dict)
     #: int32 [slots]: the token last sampled for each slot, left on the device by the sampler; a

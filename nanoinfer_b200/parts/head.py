@@ -27,6 +27,7 @@ class LinearHead(Head):
 
     def forward(self, h, out: torch.Tensor, n_rows: int, ctx: StepContext) -> None:
         """``h``: the normed rows, or a foldable norm input (``Norm.as_input``) of the rows wanted."""
+        ops.trace_scope(-1, "lm_head")
         if isinstance(h, ops.NormInput):
             ops.linear(None, self.params["weight"], None, out, n_rows, norm=h)
         else:

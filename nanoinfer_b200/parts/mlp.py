@@ -36,5 +36,7 @@ class DenseMLP(FeedForward):
         T, p = ctx.n_rows, self.params
         fc = ctx.workspace.get("mlp.fc", (ctx.max_rows, self.inner), self.dtype)
         xn, norm = (None, xn) if isinstance(xn, ops.NormInput) else (xn, None)
+        ops.trace_scope(ctx.layer, "fc")
         ops.linear(xn, p["fc_weight"], p.get("fc_bias"), fc, T, act=ops.ACT_CODES[self.activation], norm=norm)
+        ops.trace_scope(ctx.layer, "fc_proj")
         ops.linear(fc, p["proj_weight"], p.get("proj_bias"), x, T, residual=True)

@@ -178,7 +178,8 @@ def _pct(xs: List[float], p: float) -> float:
     return xs[int(round((len(xs) - 1) * p))] if xs else 0.0
 
 
-def summarise(name: str, reqs: List[ServeRequest], o: Outcome, page_size: int, gantt: int = 32) -> dict:
+def summarise(name: str, reqs: List[ServeRequest], o: Outcome, page_size: int, gantt: int = 32,
+              quiet: bool = False) -> dict:
     gen = sum(l.generated for l in o.logs)
     ttft = [l.first_token - r.arrival for r, l in zip(reqs, o.logs)]
     tpot = [(l.finished - l.first_token) / (r.out_len - 1) for r, l in zip(reqs, o.logs) if r.out_len > 1]
@@ -188,10 +189,11 @@ def summarise(name: str, reqs: List[ServeRequest], o: Outcome, page_size: int, g
     busy = sum(i.dt for i in o.iters)
     kv_avg = sum(i.kv_pages * i.dt for i in o.iters) / max(busy, 1e-12)
     stride = max(1, -(-len(o.iters) // 120))
-    print(f"{name:<11} {gen / o.makespan:>8.0f} tok/s  makespan {o.makespan:>6.2f} s  iters {len(o.iters):>5}  "
-          f"TTFT p50 {1e3 * _pct(ttft, 0.5):>7.1f} ms p99 {1e3 * _pct(ttft, 0.99):>7.1f} ms  "
-          f"TPOT p50 {1e3 * _pct(tpot, 0.5):>6.2f} ms p99 {1e3 * _pct(tpot, 0.99):>6.2f} ms  "
-          f"e2e p50 {_pct(e2e, 0.5):>6.2f} s  KV peak {o.pages_peak} pages")
+    if not quiet:
+        print(f"{name:<11} {gen / o.makespan:>8.0f} tok/s  makespan {o.makespan:>6.2f} s  iters {len(o.iters):>5}  "
+              f"TTFT p50 {1e3 * _pct(ttft, 0.5):>7.1f} ms p99 {1e3 * _pct(ttft, 0.99):>7.1f} ms  "
+              f"TPOT p50 {1e3 * _pct(tpot, 0.5):>6.2f} ms p99 {1e3 * _pct(tpot, 0.99):>6.2f} ms  "
+              f"e2e p50 {_pct(e2e, 0.5):>6.2f} s  KV peak {o.pages_peak} pages")
     return {
         "policy": name,
         "throughput_tok_s": gen / o.makespan,
@@ -216,52 +218,95 @@ def summarise(name: str, reqs: List[ServeRequest], o: Outcome, page_size: int, g
     }
 
 
-def run_cli(args) -> int:
+def run_serving(model_dir: str, dtype: str = "bfloat16", requests: int = 128, max_batch: int = 32,
+                prompt_min: int = 16, prompt_max: int = 256, out_min: int = 16, out_max: int = 256, rate: float = 0.0,
+                prefill_budget: int = 256, kv_blocks: Optional[int] = None, seed: int = 7, temperature: float = 0.0,
+                top_k: int = 40, gantt: int = 32, policies=("static", "continuous"), quiet: bool = False) -> dict:
+    """The serving workload through the engine, once per policy; returns the summary (the options are
+    those of the reference's ``metal-serve``: crates/cli/src/metal_serve.rs:33-79).  Every number that
+    describes the model (context limit, vocabulary, bytes a step must read) is taken from the engine
+    that was built, not from a configuration's field names."""
+    from .bench_support import measured_peaks
     from .engine.engine import Engine
-    from .registry import load_config
+    from .measure import kv_bytes_per_position, weight_bytes_per_step
 
-    cfg = load_config(args.weights)
-    limit = getattr(cfg, "n_positions", None)
-    if limit is not None and args.prompt_max >= limit:
-        print(f"prompt_max must be below the context length {limit}", file=sys.stderr)
-        return 2
     page = 16
-    longest = args.prompt_max + args.out_max if limit is None else min(args.prompt_max + args.out_max, limit)
-    pages_per_request = -(-longest // page)
-    kv_blocks = args.kv_blocks or args.max_batch * pages_per_request + 8
-    reqs = workload(args.requests, args.prompt_min, args.prompt_max, args.out_min, args.out_max, args.rate, args.seed,
-                    cfg.vocab_size)
+
+    def engine(n_blocks):
+        return Engine(model_dir, dtype=dtype, max_tokens=n_blocks * page, max_batch=max_batch,
+                      max_rows=max(512, prefill_budget + max_batch), prefill_budget=prefill_budget, page_size=page)
+
+    probe_blocks = kv_blocks or max_batch * (-(-(prompt_max + out_max) // page)) + 8
+    eng = engine(probe_blocks)
+    limit, vocab = eng.model.max_positions, eng.model.vocab_size
+    if limit is not None and prompt_max >= limit:
+        raise ValueError(f"prompt_max must be below the context length {limit}")
+    longest = prompt_max + out_max if limit is None else min(prompt_max + out_max, limit)
+    n_blocks = kv_blocks or max_batch * (-(-longest // page)) + 8
+    if n_blocks != probe_blocks:
+        del eng
+        torch_empty_cache()
+        eng = engine(n_blocks)
+    reqs = workload(requests, prompt_min, prompt_max, out_min, out_max, rate, seed, vocab)
     if limit is not None:   # an output that would pass the end of the context is cut there
         for r in reqs:
             r.out_len = max(1, min(r.out_len, limit - len(r.prompt)))
     total_in, total_out = sum(len(r.prompt) for r in reqs), sum(r.out_len for r in reqs)
-    print(f"serve-bench: {args.requests} requests (prompt {args.prompt_min}-{args.prompt_max}, output "
-          f"{args.out_min}-{args.out_max}; {total_in} prompt + {total_out} output tokens), rate {args.rate} req/s, "
-          f"max batch {args.max_batch}, {kv_blocks} KV pages, {args.dtype}", file=sys.stderr)
-
-    def engine():
-        return Engine(args.weights, dtype=args.dtype, max_tokens=kv_blocks * page, max_batch=args.max_batch,
-                      max_rows=max(512, args.prefill_budget + args.max_batch), prefill_budget=args.prefill_budget,
-                      page_size=page)
-
-    eng = engine()
-    sampling = {"temperature": args.temperature, "top_k": args.top_k, "seed": args.seed}
+    if not quiet:
+        print(f"serve-bench: {requests} requests (prompt {prompt_min}-{prompt_max}, output {out_min}-{out_max}; "
+              f"{total_in} prompt + {total_out} output tokens), rate {rate} req/s, max batch {max_batch}, "
+              f"{n_blocks} KV pages, {dtype}", file=sys.stderr)
+    sampling = {"temperature": temperature, "top_k": top_k, "seed": seed}
     run_continuous(eng, reqs[:min(len(reqs), 4)], **sampling)   # warm up: kernels built, first graphs captured
-    s_static = summarise("static", reqs, run_static(eng, reqs, **sampling), page, args.gantt)
-    s_cont = summarise("continuous", reqs, run_continuous(eng, reqs, **sampling), page, args.gantt)
-    print(f"continuous / static throughput: {s_cont['throughput_tok_s'] / s_static['throughput_tok_s']:.2f}x")
-    summary = {"requests": args.requests, "max_batch": args.max_batch, "prefill_budget": args.prefill_budget,
-               "kv_blocks": kv_blocks, "dtype": args.dtype, "seed": args.seed, "rate": args.rate, "note": args.note,
-               "temperature": args.temperature, "top_k": args.top_k,
-               "policies": [s_static, s_cont]}
+    peaks = measured_peaks()
+    weights = weight_bytes_per_step(eng.model)
+    page_bytes = sum(per_pos for per_pos, _ in kv_bytes_per_position(eng.cache)) * page
+    out = []
+    for name in policies:
+        o = (run_static if name == "static" else run_continuous)(eng, reqs, **sampling)
+        s = summarise(name, reqs, o, page, gantt, quiet=quiet)
+        # what the steps had to read (every weight once a step, and the pages in use) over the time
+        # the engine was busy, against the memory's rate
+        must_read = sum(weights + i.kv_pages * page_bytes for i in o.iters)
+        s["hbm_gbs"] = must_read / max(s["engine_busy_s"], 1e-12) / 1e9
+        s["hbm_frac"] = s["hbm_gbs"] / peaks["hbm_gbs"]
+        s["kv_pages_total"] = n_blocks
+        out.append(s)
+    return {"requests": requests, "max_batch": max_batch, "prefill_budget": prefill_budget, "kv_blocks": n_blocks,
+            "dtype": dtype, "seed": seed, "rate": rate, "temperature": temperature, "top_k": top_k,
+            "prompt_tokens": total_in, "output_tokens": total_out, "peaks": peaks["source"], "policies": out}
+
+
+def torch_empty_cache() -> None:
+    import torch
+    torch.cuda.empty_cache()
+
+
+def run_cli(args) -> int:
+    from .bench_support import provenance
+
+    try:
+        summary = run_serving(args.weights, args.dtype, args.requests, args.max_batch, args.prompt_min, args.prompt_max,
+                              args.out_min, args.out_max, args.rate, args.prefill_budget, args.kv_blocks, args.seed,
+                              args.temperature, args.top_k, args.gantt)
+    except ValueError as e:
+        print(str(e), file=sys.stderr)
+        return 2
+    summary["note"] = args.note
+    by = {s["policy"]: s for s in summary["policies"]}
+    print(f"continuous / static throughput: {by['continuous']['throughput_tok_s'] / by['static']['throughput_tok_s']:.2f}x")
+    stamp = provenance()
+    summary.update(stamp)
     if args.summary:
         with open(args.summary, "w") as fh:
             json.dump(summary, fh)
     if args.out:
         with open(args.out, "a") as fh:
-            for s in (s_static, s_cont):
+            for s in summary["policies"]:
                 fh.write(json.dumps({"stage": f"serve-{s['policy']}", "dtype": args.dtype,
                                      "throughput_tok_s": s["throughput_tok_s"], "ttft_ms": s["ttft_ms"],
-                                     "tpot_ms": s["tpot_ms"], "e2e_s": s["e2e_s"], "requests": args.requests,
-                                     "max_batch": args.max_batch, "note": args.note}) + "\n")
+                                     "tpot_ms": s["tpot_ms"], "e2e_s": s["e2e_s"], "hbm_frac": s["hbm_frac"],
+                                     "kv_pages_peak": s["kv_pages_peak"], "kv_pages_total": s["kv_pages_total"],
+                                     "requests": args.requests, "max_batch": args.max_batch, "note": args.note,
+                                     **stamp}) + "\n")
     return 0
