@@ -113,6 +113,12 @@ int nib_attention_prefill(const void* q, int ldq, const void* cache, void* out, 
                           int head_dim, int page_size, int n_pages, float scale, int window, int* status,
                           cudaStream_t stream);
 
+// Loading: src holds [rows, cols] values as a checkpoint stores them (src_dtype 0: 32-bit floats, 1:
+// bfloat16, 2: 16-bit floats); element (r, c) is converted to dst_dtype and written to
+// dst[(r0 + r) * ld + c], or with `transpose` to dst[c * ld + r0 + r].
+int nib_convert(int src_dtype, const void* src, int rows, int cols, int dst_dtype, void* dst, long long ld,
+                long long r0, int transpose, cudaStream_t stream);
+
 int nib_argmax(const float* logits, int ld, int n_rows, int V, int* out, cudaStream_t stream);
 
 // One token per logits row.  temperature, top_k and rng_state are per-slot arrays indexed by

@@ -5,6 +5,8 @@
 // LayerNorm two-pass with biased variance, rstd = 1/sqrt(var + eps) (reference.rs:42-51);
 // K/V rows of the fused qkv buffer copied to the cache slot of their position
 // (crates/core/src/stages/kv_cache.rs:44-57, crates/metal/src/shaders/batch.metal:329-344).
+#include <cuda_fp16.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -252,4 +254,60 @@ extern "C" int nib_kv_append(int dtype, const void* src, int ld, int k_off, int 
     return launch_kv_append<bf16>((const bf16*)src, ld, k_off, v_off, (bf16*)cache, block_table, max_blocks,
                                   row_entry, positions, T, n_kv_head, head_dim, page_size, n_pages, status, stream);
   return NIB_ERR_BAD_ARGUMENT;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Loading: a checkpoint tensor's rows, as the file stores them (32-bit or 16-bit floats), into the
+// engine's tensor: converted, and transposed where the file stores a matrix [in, out]
+// (crates/core/src/weights.rs:48-57 transposes on the host; here the bytes go to the device as they
+// lie in the file and this kernel puts them in place).
+namespace nib {
+
+enum : int { SRC_F32 = 0, SRC_BF16 = 1, SRC_F16 = 2 };
+
+__device__ __forceinline__ float load_as_float(const void* src, int src_dt, size_t i) {
+  if (src_dt == SRC_F32) return reinterpret_cast<const float*>(src)[i];
+  if (src_dt == SRC_BF16) return __bfloat162float(reinterpret_cast<const bf16*>(src)[i]);
+  return __half2float(reinterpret_cast<const __half*>(src)[i]);
+}
+
+// src: [rows, cols] as stored.  dst (row stride ld): element (r, c) goes to dst[(r0 + r) * ld + c], or
+// with `transpose` to dst[c * ld + r0 + r]; tiles of 32 x 32 pass through shared memory so that both
+// sides are read and written along their rows.
+template <typename D>
+__global__ void convert_kernel(const void* __restrict__ src, int src_dt, int rows, int cols, D* __restrict__ dst,
+                               long long ld, long long r0, int transpose) {
+  __shared__ float tile[32][33];
+  const int bx = blockIdx.x * 32, by = blockIdx.y * 32;   // first column, first row of the tile
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    const int r = by + j, c = bx + threadIdx.x;
+    tile[j][threadIdx.x] = (r < rows && c < cols) ? load_as_float(src, src_dt, (size_t)r * cols + c) : 0.0f;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+    if (!transpose) {
+      const int r = by + j, c = bx + threadIdx.x;
+      if (r < rows && c < cols) dst[(size_t)(r0 + r) * ld + c] = from_float<D>(tile[j][threadIdx.x]);
+    } else {
+      const int c = bx + j, r = by + threadIdx.x;         // the tile read the other way round
+      if (r < rows && c < cols) dst[(size_t)c * ld + r0 + r] = from_float<D>(tile[threadIdx.x][j]);
+    }
+  }
+}
+
+}  // namespace nib
+
+extern "C" int nib_convert(int src_dtype, const void* src, int rows, int cols, int dst_dtype, void* dst,
+                           long long ld, long long r0, int transpose, cudaStream_t stream) {
+  if (rows <= 0 || cols <= 0) return 0;
+  if (src_dtype < 0 || src_dtype > 2) return NIB_ERR_BAD_ARGUMENT;
+  const dim3 grid((cols + 31) / 32, (rows + 31) / 32), block(32, 8);
+  if (grid.y > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (dst_dtype == DT_F32)
+    convert_kernel<float><<<grid, block, 0, stream>>>(src, src_dtype, rows, cols, (float*)dst, ld, r0, transpose);
+  else if (dst_dtype == DT_BF16)
+    convert_kernel<bf16><<<grid, block, 0, stream>>>(src, src_dtype, rows, cols, (bf16*)dst, ld, r0, transpose);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
 }

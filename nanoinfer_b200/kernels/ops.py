@@ -66,6 +66,7 @@ _SIGNATURES = {
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
+    "nib_convert": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
                    _c_ptr],
@@ -705,6 +706,20 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         else:
             attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_prefill_rows, n_head,
                            scale, window, ctx.status, plan.prefill_rows)
+
+
+_SRC_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
+
+
+def convert_rows(src: torch.Tensor, src_dtype: torch.dtype, rows: int, cols: int, dst: torch.Tensor, r0: int,
+                 transpose: bool) -> None:
+    """Loading: ``src`` holds the raw bytes of ``rows`` x ``cols`` values as a checkpoint stores them;
+    they are converted to ``dst``'s dtype and written to dst[r0:r0 + rows, :] or, transposed, to
+    dst[:, r0:r0 + rows]."""
+    if src_dtype not in _SRC_CODES or not dst.is_contiguous() or dst.dim() != 2:
+        raise KernelError("convert: 16- or 32-bit floats into a contiguous matrix")
+    _check(library().nib_convert(_SRC_CODES[src_dtype], _ptr(src), rows, cols, _dt(dst), _ptr(dst), dst.stride(0),
+                                 int(r0), int(bool(transpose)), _stream()), "convert")
 
 
 def argmax(logits: torch.Tensor, out: torch.Tensor, n_rows: int) -> None:

@@ -11,9 +11,16 @@ How tensors are held on the device:
   * integer tables: int32.
 A tensor the file stores [in, out] (Conv1D) is transposed to [out, in] once, here
 (crates/core/src/weights.rs:48-57).
+
+On a CUDA device the bytes take the short way (the reference maps the file and reads it in
+place: crates/cli/src/main.rs:91-106): from the memory map into one of two pinned staging
+buffers, from there to the device with an asynchronous copy, and a kernel converts and
+transposes them into the tensor the engine computes with, while the host fills the other
+buffer.  No tensor is converted, transposed or even held whole on the host.
 """
 from __future__ import annotations
 
+import math
 import os
 import re
 from typing import Dict, List, Tuple
@@ -102,6 +109,47 @@ def check_weights(model: Model, st: SafetensorsFile) -> str:
     return prefix
 
 
+#: bytes of each of the two pinned staging buffers of the streamed load
+STAGING_BYTES = 64 << 20
+_STREAMED = {"F32": torch.float32, "BF16": torch.bfloat16, "F16": torch.float16}
+
+
+class _Stager:
+    """Two pinned host buffers and their device twins, used by turns: while the device copies and
+    converts one, the host fills the other from the memory map."""
+
+    def __init__(self, device: torch.device, nbytes: int = 0):
+        nbytes = self.nbytes = nbytes or STAGING_BYTES
+        self.host = [torch.empty(nbytes, dtype=torch.uint8).pin_memory() for _ in range(2)]
+        self.dev = [torch.empty(nbytes, dtype=torch.uint8, device=device) for _ in range(2)]
+        self.done = [torch.cuda.Event() for _ in range(2)]
+        self.turn = 0
+        self.bytes_moved = 0
+
+    def load(self, st: SafetensorsFile, name: str, dst: torch.Tensor, transposed: bool) -> None:
+        """The file's tensor ``name`` ([rows, cols] as stored, or a vector) into ``dst``."""
+        from ..kernels import ops
+
+        info = st.info(name)
+        src_dtype = _STREAMED[info.dtype]
+        rows, cols = info.shape if len(info.shape) == 2 else (1, math.prod(info.shape))
+        raw = st.raw(name)
+        item = raw.size // max(1, rows * cols)
+        out = dst if dst.dim() == 2 else dst.view(1, -1)
+        per = max(1, self.nbytes // (cols * item))           # rows of the file per piece
+        for r0 in range(0, rows, per):
+            n = min(per, rows - r0)
+            k = self.turn
+            self.turn ^= 1
+            self.done[k].synchronize()                          # the device is through with this buffer
+            nb = n * cols * item
+            self.host[k].numpy()[:nb] = raw[r0 * cols * item:r0 * cols * item + nb]
+            self.dev[k][:nb].copy_(self.host[k][:nb], non_blocking=True)
+            ops.convert_rows(self.dev[k], src_dtype, n, cols, out, r0, transposed)
+            self.done[k].record()
+            self.bytes_moved += nb
+
+
 def load_weights(model: Model, model_dir: str, dtype: torch.dtype, device: torch.device) -> None:
     """Check ``model_dir/model.safetensors`` against ``model``, then bind every parameter."""
     if dtype not in (torch.float32, torch.bfloat16):
@@ -115,8 +163,16 @@ def load_weights(model: Model, model_dir: str, dtype: torch.dtype, device: torch
         loaded: Dict[Tuple, torch.Tensor] = {}
         per_part: Dict[int, Dict[str, torch.Tensor]] = {}
         parts = {}
+        stager = _Stager(device) if device.type == "cuda" else None
         for b in model.bindings():
             key = (b.ref.name, b.ref.transposed, b.spec.kind)
+            if key not in loaded and stager is not None and b.spec.kind != INT_TABLE \
+                    and st.info(prefix + b.ref.name).dtype in _STREAMED and len(b.spec.shape) <= 2:
+                # the short way: bytes as stored to the device, converted and transposed there
+                want = dtype if b.spec.kind in (MATRIX, TABLE) else torch.float32
+                dst = torch.empty(tuple(b.spec.shape), dtype=want, device=device)
+                stager.load(st, prefix + b.ref.name, dst, b.ref.transposed)
+                loaded[key] = dst
             if key not in loaded:
                 t = st.tensor(prefix + b.ref.name)
                 if b.ref.transposed:
@@ -135,6 +191,8 @@ def load_weights(model: Model, model_dir: str, dtype: torch.dtype, device: torch
         for part in model.all_parts():
             if not hasattr(part, "params"):
                 part.bind({})
+        if stager is not None:
+            torch.cuda.synchronize(device)     # the map is closed below: every copy out of it has been made
     finally:
         st.close()
     model.prepare(dtype, device)

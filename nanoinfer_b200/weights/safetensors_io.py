@@ -118,6 +118,12 @@ class SafetensorsFile:
             t = t.to(torch.bool)
         return t.reshape(info.shape)
 
+    def raw(self, name: str) -> np.ndarray:
+        """The tensor's bytes as they lie in the memory map (no copy; valid until ``close``)."""
+        info = self.tensors[name]
+        return np.frombuffer(self._map, dtype=np.uint8, count=info.end - info.start,
+                             offset=self._data_start + info.start)
+
     def close(self) -> None:
         self._map.close()
 

@@ -154,3 +154,31 @@ def test_missing_files(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_A))
     with pytest.raises(FileNotFoundError, match="model.safetensors"):
         load_model(str(tmp_path), "float32", "cpu")
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("stored", [torch.float32, torch.bfloat16, torch.float16])
+def test_streamed_load_on_the_device_gives_the_host_path_s_tensors(tmp_path, stored, monkeypatch):
+    """On a CUDA device the file's bytes go through pinned staging buffers and a kernel converts and
+    transposes them in place.  Every bound tensor must be bit-for-bit what the host path makes (file
+    in 32-bit, bfloat16 or 16-bit floats; engine in either dtype), also when the staging buffers are
+    so small that every matrix goes over in many pieces."""
+    from nanoinfer_b200.weights import loader, random_tensors, write_safetensors
+    from nanoinfer_b200.models.model import Model
+    from nanoinfer_b200.registry import get_architecture
+    cfg = GPT2Config.from_dict(TINY_B)
+    model = Model(get_architecture(cfg.architecture).build_spec(cfg), cfg)
+    tensors = {k: v.to(stored) for k, v in random_tensors(model, 5, 0.05, torch.float32).items()}
+    d = str(tmp_path)
+    with open(os.path.join(d, "config.json"), "w") as fh:
+        json.dump(cfg.to_dict(), fh)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    for engine_dtype in (torch.float32, torch.bfloat16):
+        host = load_model(d, engine_dtype, "cpu")
+        for staging in (loader.STAGING_BYTES, 4096):
+            monkeypatch.setattr(loader, "STAGING_BYTES", staging)
+            dev = load_model(d, engine_dtype, "cuda")
+            for a, b in zip(host.bindings(), dev.bindings()):
+                ta, tb = a.part.params[a.spec.key], b.part.params[b.spec.key]
+                assert tb.is_cuda and ta.dtype == tb.dtype and ta.shape == tb.shape, b.where
+                assert torch.equal(ta, tb.cpu()), f"{b.where}.{b.spec.key}"
