@@ -1,5 +1,6 @@
 """Command line in the manner of the reference's ``nanoinfer`` binary (crates/cli/src/main.rs:28-83):
 
+    python -m nanoinfer_b200 --weights DIR generate --prompt "Hello" --tokens 40
     python -m nanoinfer_b200 --weights DIR generate --prompt-ids 464,3616 --tokens 40
     python -m nanoinfer_b200 --weights DIR bench --tokens 64 --prompt-len 64 --batch 1,8,64
     python -m nanoinfer_b200 --weights DIR serve-bench --requests 128 --max-batch 32
@@ -7,8 +8,9 @@
 
 ``--weights`` is the reference's global option (main.rs:30-32): the folder with
 ``model.safetensors`` (and here ``config.json``).  ``generate`` keeps the reference's options
-and defaults (main.rs:48-72): ``--tokens 40 --temperature 0.0 --top-k 40 --seed 42
---profile``; the prompt is given as token ids.  ``bench`` keeps ``--tokens 64 --prompt-len 64
+and defaults (main.rs:48-72): ``--prompt TEXT --tokens 40 --temperature 0.0 --top-k 40 --seed 42
+--profile --trace-out FILE``; a text prompt needs the tokenizer's ``vocab.json`` and ``merges.txt``
+in the folder (main.rs:85-89), token ids can be given instead with ``--prompt-ids``.  ``bench`` keeps ``--tokens 64 --prompt-len 64
 --runs 5 --warmup 1 --bandwidth-gbs`` (crates/cli/src/bench.rs:24-58) and ``--batch``/``--dtype``
 of the batch sweep (crates/cli/src/metal_batch.rs:20-58).  The reference chooses a strategy
 with ``--stage``; here the one choice left is ``--dtype``.  ``serve-bench`` keeps the options of the
@@ -39,6 +41,7 @@ def cmd_random_weights(args) -> int:
 
     from .registry import get_architecture
     from .config.base import architecture_name
+    from .models.model import Model
     from .weights.random_init import write_random_model
 
     with open(_preset_path(args.config)) as fh:
@@ -46,8 +49,10 @@ def cmd_random_weights(args) -> int:
     cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
     dtype = torch.bfloat16 if args.dtype == "bfloat16" else torch.float32
     write_random_model(cfg, args.out, args.seed, dtype)
+    if args.tokenizer:
+        from .tokenizer import write_byte_tokenizer
+        write_byte_tokenizer(args.out, Model(get_architecture(cfg.architecture).build_spec(cfg), cfg).vocab_size)
     from .measure import parameter_count_of_spec
-    from .models.model import Model
     n_params = parameter_count_of_spec(Model(get_architecture(cfg.architecture).build_spec(cfg), cfg))
     print(f"wrote {args.out} ({n_params / 1e6:.1f}M params, {args.dtype}, seed {args.seed})", file=sys.stderr)
     return 0
@@ -59,10 +64,23 @@ def cmd_generate(args) -> int:
     from .engine.engine import Engine
     from .sampling.sampler import SamplingParams
 
-    if args.prompt_ids is None:
-        print("generate: give the prompt as --prompt-ids a,b,c (token ids)", file=sys.stderr)
+    tok = None
+    if args.prompt_ids is not None:
+        prompt = _ids(args.prompt_ids)
+    elif args.prompt is not None:
+        from .tokenizer import Tokenizer, TokenizerError
+        try:
+            tok = Tokenizer.from_folder(args.weights)
+        except TokenizerError as e:
+            print(str(e), file=sys.stderr)
+            return 2
+        prompt = tok.encode(args.prompt)
+    else:
+        print("generate: give the prompt as --prompt TEXT, or as token ids with --prompt-ids a,b,c", file=sys.stderr)
         return 2
-    prompt = _ids(args.prompt_ids)
+    if not prompt:
+        print("generate: the prompt is empty", file=sys.stderr)
+        return 2
     t0 = time.perf_counter()
     eng = Engine(args.weights, dtype=args.dtype, max_batch=1, max_rows=max(64, len(prompt)),
                  use_graphs=not args.trace_out, run_ahead=not args.trace_out)
@@ -80,6 +98,9 @@ def cmd_generate(args) -> int:
     t0 = time.perf_counter()
     t_first = None
     printed = 0
+    pending = b""       # bytes of tokens that do not yet end a character
+    if tok is not None:
+        print(args.prompt, end="", flush=True)
     while eng.has_work():
         if rec is not None:   # (one scheduler decision is one step: the whole prompt, then a token at a time)
             n_in = eng.scheduler.running[0].n_pending if eng.scheduler.running else len(prompt)
@@ -89,7 +110,14 @@ def cmd_generate(args) -> int:
         while printed < len(req.output) and req.output[printed] >= 0:
             if t_first is None:
                 t_first = time.perf_counter() - t0
-            print(req.output[printed], end=" ", flush=True)
+            if tok is None:
+                print(req.output[printed], end=" ", flush=True)
+            else:      # a token may be part of a multi-byte character: print what is whole
+                pending += tok.token_bytes(req.output[printed])
+                text = pending.decode("utf-8", errors="ignore")
+                if text and text.encode("utf-8") == pending or len(pending) > 8:
+                    print(pending.decode("utf-8", errors="replace"), end="", flush=True)
+                    pending = b""
             printed += 1
     total = time.perf_counter() - t0
     print()
@@ -136,6 +164,7 @@ def main(argv=None) -> int:
 
     g = sub.add_parser("generate", help="generate tokens from a prompt")
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    g.add_argument("--prompt", default=None, help="the prompt as text (needs vocab.json and merges.txt in the folder)")
     g.add_argument("--prompt-ids", default=None, help="the prompt as comma-separated token ids")
     g.add_argument("--tokens", type=int, default=40, help="number of tokens to generate")
     g.add_argument("--temperature", type=float, default=0.0, help="0 = greedy")
@@ -190,6 +219,8 @@ def main(argv=None) -> int:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--out", required=True)
     r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--tokenizer", action="store_true",
+                   help="also write a byte-level tokenizer (256 byte tokens, no merges), so that text can be given")
     r.set_defaults(fn=cmd_random_weights)
 
     args = ap.parse_args(argv)

@@ -415,3 +415,36 @@ def test_command_line_random_weights_writes_a_loadable_folder(tmp_path):
     eng = engine(out, "float32", max_batch=2, max_rows=32)
     got = eng.generate([[1, 2, 3]], nb.SamplingParams(max_new_tokens=4, temperature=0.0))
     assert len(got[0]) == 4
+
+
+def test_command_line_generates_from_text_and_writes_a_trace(tmp_path, capsys):
+    """The command line as the reference's: a model folder from ``random-weights`` (with the byte
+    tokenizer, so that text can be given), ``generate --prompt TEXT`` with a profile and a trace file,
+    the same tokens from ``--prompt-ids``, and a clear answer when the tokenizer's files are absent."""
+    import json
+    from nanoinfer_b200.cli import main
+    d = str(tmp_path / "m")
+    assert main(["random-weights", "--config", "gpt2-tiny-a", "--seed", "4", "--out", d, "--dtype", "float32",
+                 "--tokenizer"]) == 0
+    capsys.readouterr()
+    trace = str(tmp_path / "trace.jsonl")
+    assert main(["--weights", d, "generate", "--dtype", "float32", "--prompt", "Hi é", "--tokens", "6", "--profile",
+                 "--trace-out", trace]) == 0
+    out, err = capsys.readouterr()
+    assert out.startswith("Hi é") and "of roof" in err and "decode" in err
+    lines = [json.loads(l) for l in open(trace)]
+    assert lines[0]["t"] == "run_start" and lines[0]["prompt_tokens"] == list("Hi é".encode())
+    assert lines[-1]["t"] == "run_end" and lines[-1]["n_gen"] == 6 and lines[-1]["n_prompt"] == 5
+    ops_seen = {l["op"] for l in lines if l["t"] == "op"}
+    assert {"qkv", "attn", "attn_proj", "fc", "fc_proj", "lm_head", "embed", "sample"} <= ops_seen
+    assert all(l["flops"] >= 0 and l["bytes"] > 0 and l["dur_us"] > 0 for l in lines if l["t"] == "op")
+    tokens = [l["id"] for l in lines if l["t"] == "token"]
+    assert len(tokens) == 6
+    ids = ",".join(str(b) for b in "Hi é".encode())
+    assert main(["--weights", d, "generate", "--dtype", "float32", "--prompt-ids", ids, "--tokens", "6"]) == 0
+    out, _ = capsys.readouterr()
+    assert [int(t) for t in out.split()] == tokens
+    import os
+    os.remove(os.path.join(d, "merges.txt"))
+    assert main(["--weights", d, "generate", "--prompt", "Hi"]) == 2
+    assert "merges.txt" in capsys.readouterr().err
