@@ -39,12 +39,17 @@ template <> struct Piece<bf16> {
   }
 };
 
-// 2^x by the hardware's approximation (relative error about 2^-22; 2^-inf = 0)
-__device__ __forceinline__ float pow2(float x) {
+// 2^x.  The bfloat16 kernel takes the hardware's approximation (relative error about 2^-22, far below
+// the rounding of the values it multiplies; 2^-inf = 0); the 32-bit kernel takes the accurate library
+// function, as the general attention kernel that serves its prompt portions does, so that no
+// approximate instruction stands anywhere in the true 32-bit path.
+template <typename T> __device__ __forceinline__ float pow2(float x);
+template <> __device__ __forceinline__ float pow2<bf16>(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+template <> __device__ __forceinline__ float pow2<float>(float x) { return exp2f(x); }
 
 // partial layout: o [row][head][split][head_dim], ml [row][head][split][2]
 //
@@ -186,14 +191,14 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
 #pragma unroll
     for (int b = 0; b < BATCH; ++b) m_new = fmaxf(m_new, sc[b]);
     if (m_new == -INFINITY) continue;   // the group has had no key yet
-    const float corr = pow2(m - m_new);  // (2^-inf = 0 for the first keys)
+    const float corr = pow2<T>(m - m_new);  // (2^-inf = 0 for the first keys)
     m = m_new;
     l *= corr;
 #pragma unroll
     for (int e = 0; e < VN; ++e) o[e] *= corr;
 #pragma unroll
     for (int b = 0; b < BATCH; ++b) {
-      const float p = pow2(sc[b] - m);   // 0 for a key that is not there
+      const float p = pow2<T>(sc[b] - m);   // 0 for a key that is not there
       l += p;
       if (has_piece && ((live >> b) & 1u)) {
         float f[VN];
@@ -218,10 +223,10 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   float M = -INFINITY;
   for (int w = 0; w < ALL_GROUPS; ++w) M = fmaxf(M, gm[w]);
   float L = 0.0f;
-  for (int w = 0; w < ALL_GROUPS; ++w) L += (gm[w] == -INFINITY) ? 0.0f : gl[w] * pow2(gm[w] - M);
+  for (int w = 0; w < ALL_GROUPS; ++w) L += (gm[w] == -INFINITY) ? 0.0f : gl[w] * pow2<T>(gm[w] - M);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
-    for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2(gm[w] - M);
+    for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2<T>(gm[w] - M);
     if (n_splits == 1)
       out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L);
     else if (cluster_merge)
@@ -267,13 +272,13 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ 
   float Lx = 0.0f;
   for (int sp = 0; sp < n_splits; ++sp) {
     const float ls = part_ml[2 * (base + sp) + 1];
-    if (ls > 0.0f) Lx += ls * pow2(part_ml[2 * (base + sp)] - Mx);
+    if (ls > 0.0f) Lx += ls * pow2<T>(part_ml[2 * (base + sp)] - Mx);
   }
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
       const float ls = part_ml[2 * (base + sp) + 1];
-      if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * pow2(part_ml[2 * (base + sp)] - Mx);
+      if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * pow2<T>(part_ml[2 * (base + sp)] - Mx);
     }
     out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / Lx);
   }

@@ -30,6 +30,7 @@
 namespace nib {
 
 constexpr int DM_WARPS = 4;
+constexpr int DM_MAX_CLUSTER = 8;   // the portable cluster size
 
 __device__ __forceinline__ void dm_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -68,12 +69,18 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
                             int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                             const int* __restrict__ positions, int n_head, int n_kv_head, int page_size,
                             int n_pages, float scale, int window, int chunk, int n_splits,
-                            int* __restrict__ counters, int* __restrict__ status) {
+                            int* __restrict__ counters, int* __restrict__ status, int cluster_merge) {
   constexpr int HALVES = HD / 32;                    // a 16-byte piece per lane covers 32 of a row's values
   pdl_trigger();
   __shared__ __align__(16) float wo[DM_WARPS][HD];   // the warps' unnormalised outputs
   __shared__ float wm[DM_WARPS], wl[DM_WARPS];
   __shared__ int is_last_sh;
+  // When the splits of a (row, head) are the blocks of one cluster (at most eight), they hand their
+  // results to the first of them through distributed shared memory instead of through global scratch,
+  // an arrival counter and a second read: two trips to memory less at the end of the chain.
+  __shared__ __align__(16) float xo[DM_MAX_CLUSTER][HD];
+  __shared__ float xml[DM_MAX_CLUSTER][2];
+  if (cluster_merge) cluster_arrive();               // met below, before the first store into another block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int fr = lane >> 2, kl = lane & 3;           // this lane's key row of a tile (and + 8), its piece of a row
   const int split = blockIdx.x, h = blockIdx.y, r = blockIdx.z;
@@ -122,11 +129,17 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
   const bool early = n_mine > 0 && (((first_tile + warp) << 4) + 15) < pos;
   if (early) fetch(0);
   pdl_wait();
+  if (cluster_merge) cluster_wait();                 // every block of the cluster runs by now
 
   if (empty) {
     if (threadIdx.x == 0 && n_splits > 1) {
-      part_ml[2 * pidx] = -INFINITY;
-      part_ml[2 * pidx + 1] = 0.0f;
+      if (cluster_merge) {
+        store_to_rank(&xml[split][0], 0, -INFINITY);
+        store_to_rank(&xml[split][1], 0, 0.0f);
+      } else {
+        part_ml[2 * pidx] = -INFINITY;
+        part_ml[2 * pidx + 1] = 0.0f;
+      }
     }
   } else {
     // the query in column 0 of the 8-column operand: the lanes 0..3 hold its pieces, the others zeros
@@ -230,39 +243,59 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
       for (int w = 0; w < DM_WARPS; ++w) o += (wm[w] == -INFINITY) ? 0.0f : wo[w][d] * dm_pow2(wm[w] - M);
       if (n_splits == 1)
         out[(size_t)t * ldo + h * HD + d] = __float2bfloat16_rn(L > 0.0f ? o / L : 0.0f);
+      else if (cluster_merge)
+        store_to_rank(&xo[split][d], 0, o);
       else
         part_o[pidx * HD + d] = o;
     }
     if (n_splits > 1 && threadIdx.x == 0) {
-      part_ml[2 * pidx] = M;                         // (in the power-of-two scale)
-      part_ml[2 * pidx + 1] = L;
+      if (cluster_merge) {
+        store_to_rank(&xml[split][0], 0, M);
+        store_to_rank(&xml[split][1], 0, L);
+      } else {
+        part_ml[2 * pidx] = M;                       // (in the power-of-two scale)
+        part_ml[2 * pidx + 1] = L;
+      }
     }
   }
   if (n_splits == 1) return;
-  // ---- the block that finishes last merges the splits of its (row, head), in split order
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const int arrived = atomicAdd(&counters[r * n_head + h], 1);
-    is_last_sh = arrived == n_splits - 1;
-    if (is_last_sh) counters[r * n_head + h] = 0;    // zero again for the next launch
+  const float* mo;    // the splits' outputs [n_splits][HD] and (maximum, sum) pairs, wherever they met
+  const float* ml;
+  if (cluster_merge) {
+    // ---- the first block of the cluster merges the splits, in split order
+    cluster_arrive();
+    cluster_wait();
+    if (split != 0) return;
+    mo = &xo[0][0];
+    ml = &xml[0][0];
+  } else {
+    // ---- the block that finishes last merges the splits of its (row, head), in split order
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const int arrived = atomicAdd(&counters[r * n_head + h], 1);
+      is_last_sh = arrived == n_splits - 1;
+      if (is_last_sh) counters[r * n_head + h] = 0;  // zero again for the next launch
+    }
+    __syncthreads();
+    if (!is_last_sh) return;
+    __threadfence();
+    const size_t base = ((size_t)r * n_head + h) * n_splits;
+    mo = part_o + base * HD;
+    ml = part_ml + 2 * base;
   }
-  __syncthreads();
-  if (!is_last_sh) return;
-  __threadfence();
-  const size_t base = ((size_t)r * n_head + h) * n_splits;
   float Mx = -INFINITY;
-  for (int sp = 0; sp < n_splits; ++sp) Mx = fmaxf(Mx, part_ml[2 * (base + sp)]);
+  for (int sp = 0; sp < n_splits; ++sp) Mx = fmaxf(Mx, ml[2 * sp]);
   float Lx = 0.0f;
   for (int sp = 0; sp < n_splits; ++sp) {
-    const float ls = part_ml[2 * (base + sp) + 1];
-    if (ls > 0.0f) Lx += ls * dm_pow2(part_ml[2 * (base + sp)] - Mx);
+    const float ls = ml[2 * sp + 1];
+    if (ls > 0.0f) Lx += ls * dm_pow2(ml[2 * sp] - Mx);
   }
   for (int d = threadIdx.x; d < HD; d += blockDim.x) {
     float o = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
-      const float ls = part_ml[2 * (base + sp) + 1];
-      if (ls > 0.0f) o += part_o[(base + sp) * HD + d] * dm_pow2(part_ml[2 * (base + sp)] - Mx);
+      const float ls = ml[2 * sp + 1];
+      if (ls > 0.0f) o += mo[sp * HD + d] * dm_pow2(ml[2 * sp] - Mx);
     }
     out[(size_t)t * ldo + h * HD + d] = __float2bfloat16_rn(Lx > 0.0f ? o / Lx : 0.0f);
   }
@@ -279,29 +312,33 @@ extern "C" int nib_attention_decode_mma_supported(int head_dim, int page_size) {
 }
 
 // Arguments as for nib_attention_decode (bfloat16): scratch holds nib_attention_decode_scratch(...)
-// floats and counters n_rows * n_head zeroed ints when n_splits > 1.  q, out and the cache layer must be
+// floats and counters n_rows * n_head zeroed ints when n_splits > 1, unless `cluster` is set: then the
+// 2 to 8 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and the cache layer must be
 // 16-byte aligned with row strides that are multiples of 8 values.
 extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cache, float* scratch, void* out,
                                         int ldo, const int* block_table, int max_blocks, const int* rows,
                                         const int* row_entry, const int* positions, int n_rows, int n_head,
                                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
                                         int window, int chunk, int n_splits, int* counters, int* status,
-                                        cudaStream_t stream) {
+                                        int cluster, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (!nib_attention_decode_mma_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows > 65535 || n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || (ldq & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
-  if (n_splits > 1 && (scratch == nullptr || counters == nullptr)) return NIB_ERR_BAD_ARGUMENT;
+  // cluster != 0: the splits of a (row, head) are one cluster and merge inside it (2 to 8 splits)
+  if (cluster && (n_splits < 2 || n_splits > DM_MAX_CLUSTER)) return NIB_ERR_BAD_ARGUMENT;
+  if (n_splits > 1 && !cluster && (scratch == nullptr || counters == nullptr)) return NIB_ERR_BAD_ARGUMENT;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)n_rows * n_head * n_splits * head_dim : nullptr;
   const dim3 grid(n_splits, n_head, n_rows), block(DM_WARPS * 32);
   cudaError_t e;
 #define NIB_DM_LAUNCH(HD)                                                                                      \
-  e = launch_pdl(attention_decode_mma_kernel<HD>, grid, block, 0, stream, (const bf16*)q, ldq, (const bf16*)cache, \
-                 part_o, part_ml, (bf16*)out, ldo, block_table, max_blocks, rows, row_entry, positions, n_head, \
-                 n_kv_head, page_size, n_pages, scale, window, chunk, n_splits, counters, status)
+  e = launch_pdl_cluster(attention_decode_mma_kernel<HD>, grid, block, 0, stream, cluster ? n_splits : 1,         \
+                         (const bf16*)q, ldq, (const bf16*)cache, part_o, part_ml, (bf16*)out, ldo, block_table, \
+                         max_blocks, rows, row_entry, positions, n_head, n_kv_head, page_size, n_pages, scale,   \
+                         window, chunk, n_splits, counters, status, cluster ? 1 : 0)
   switch (head_dim) {
     case 32: NIB_DM_LAUNCH(32); break;
     case 64: NIB_DM_LAUNCH(64); break;

@@ -62,7 +62,7 @@ _SIGNATURES = {
     "nib_attention_decode_mma_supported": [_c_int, _c_int],
     "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
-                                 _c_ptr, _c_ptr, _c_ptr],
+                                 _c_ptr, _c_ptr, _c_int, _c_ptr],
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_ptr, _c_ptr],
@@ -568,14 +568,22 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
 DECODE_RESIDENT_BLOCKS = 888
 
 
+#: numbers of splits that the MMA decode attention runs as one cluster, merging through distributed
+#: shared memory instead of global scratch
+DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
+
 #: the bfloat16 decode attention on warp-level MMAs where the shape allows (False: always the streaming kernel)
 USE_DECODE_MMA = True
 
 
-def decode_split(n_rows: int, n_head: int, max_keys: int, resident: int = DECODE_RESIDENT_BLOCKS) -> tuple:
+def decode_split(n_rows: int, n_head: int, max_keys: int, resident: int = DECODE_RESIDENT_BLOCKS,
+                 at_most: int = 0) -> tuple:
     """(chunk, n_splits): keys per split (a multiple of 64) so that the blocks fill the GPU once: six
-    blocks an SM are resident, and a block that comes after the first wave runs nearly alone."""
+    blocks an SM are resident, and a block that comes after the first wave runs nearly alone.
+    ``at_most``: an upper bound on the number of splits (0: none)."""
     want = max(1, resident // max(1, n_rows * n_head))
+    if at_most:
+        want = min(want, at_most)
     chunk = max(64, -(-(-(-max_keys // want)) // 64) * 64)
     return chunk, max(1, -(-max_keys // chunk))
 
@@ -612,7 +620,9 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
     resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
-    chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident)
+    # (the MMA kernel merges up to eight splits inside a cluster, which costs two trips to memory less
+    # than the merge through scratch: eight splits of twice the keys beat sixteen)
+    chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident, max(DECODE_CLUSTER_SPLITS, default=0) if mma else 0)
     scratch = counters = None
     if n_splits > 1:
         # (never more than the resident blocks: the same size every step, so that the buffers stay put)
@@ -624,7 +634,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                                                   out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                                   _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head,
                                                   head_dim, page_size, n_pages, float(scale), int(window), chunk,
-                                                  n_splits, _ptr(counters), _ptr(status), _stream()),
+                                                  n_splits, _ptr(counters), _ptr(status),
+                                                  int(n_splits in DECODE_CLUSTER_SPLITS), _stream()),
                "attention_decode_mma")
         return
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),

@@ -264,18 +264,23 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
     assert ("mma" in kernels) == (dtype == torch.bfloat16 and hd in (32, 64, 96, 128))
     scratch = torch.zeros(o.DECODE_RESIDENT_BLOCKS * (hd + 2), device=DEV)
     counters = torch.zeros(o.DECODE_RESIDENT_BLOCKS, dtype=torch.int32, device=DEV)
+    if "mma" in kernels:
+        kernels.append("mma, splits in a cluster")
     for kernel in kernels:
-        for ns in (1, 2, 5, 16):
+        for ns in (1, 2, 5, 16) if "cluster" not in kernel else (2, 3, 4, 5, 6, 7, 8):
             chunk = max(16, -(-(-(-max_keys // ns)) // 16) * 16)
             n_splits = -(-max_keys // chunk)
             if n_rows * n_head * n_splits > o.DECODE_RESIDENT_BLOCKS:
                 continue
             out = torch.full_like(q, 7.0)
+            if "cluster" in kernel and not 2 <= n_splits <= 8:
+                continue
             args = (q.data_ptr(), q.stride(0), cache.data_ptr(), scratch.data_ptr(), out.data_ptr(), out.stride(0),
                     table.data_ptr(), table.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), n_rows,
                     n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, chunk, n_splits, counters.data_ptr(),
-                    ctx.status.data_ptr(), stream)
-            code = lib.nib_attention_decode(dt, *args) if kernel == "streaming" else lib.nib_attention_decode_mma(*args)
+                    ctx.status.data_ptr())
+            code = lib.nib_attention_decode(dt, *args, stream) if kernel == "streaming" else \
+                lib.nib_attention_decode_mma(*args, int("cluster" in kernel), stream)
             assert code == 0 and int(ctx.status.item()) == 0, (kernel, n_splits)
             diff = (out.cpu().double() - want).abs().max()
             assert diff < tol, f"{kernel}, {n_splits} splits: {float(diff):.3e}"     # (NaN fails here too)
