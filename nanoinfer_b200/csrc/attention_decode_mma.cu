@@ -62,7 +62,11 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
 
 // partial layout as in the streaming kernel: o [row][head][split][head_dim], ml [row][head][split][2]
 // (a tile's keys and values are 16 registers per 32 of head size: six blocks an SM up to 64, three beyond)
-template <int HD>
+// RING: a warp's tiles pass through a ring of two stages of its own in shared memory, filled by
+// `cp.async`: two tiles of keys and values are on their way while a third is multiplied, at no cost in
+// registers (a batch of 64 rows has one block per row and head and is bound by how many bytes are in
+// flight; without the ring a warp has one tile's loads, 4 KB, in flight at a time).
+template <int HD, bool RING>
 __global__ void __launch_bounds__(DM_WARPS * 32, HD <= 64 ? 6 : 3)
 attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache, float* part_o,
                             float* part_ml, bf16* __restrict__ out, int ldo, const int* __restrict__ block_table,
@@ -80,6 +84,7 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
   // an arrival counter and a second read: two trips to memory less at the end of the chain.
   __shared__ __align__(16) float xo[DM_MAX_CLUSTER][HD];
   __shared__ float xml[DM_MAX_CLUSTER][2];
+  extern __shared__ __align__(16) uint8_t dm_ring[]; // RING: [warp][stage][keys | values][16 rows][HD]
   if (cluster_merge) cluster_arrive();               // met below, before the first store into another block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int fr = lane >> 2, kl = lane & 3;           // this lane's key row of a tile (and + 8), its piece of a row
@@ -125,11 +130,61 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
       vb[hh] = ok_b ? *reinterpret_cast<const uint4*>(kr + kv_stride + 8 * HD + hh * 32) : make_uint4(0, 0, 0, 0);
     }
   };
-  // none of the first tile's keys is the one that the kernel ahead writes
+  // ---- RING: the same tile by asynchronous copies into stage i % 2 of this warp's ring.  A row of
+  // 128 or 256 bytes starts at the same bank as the row before it: odd rows keep their 16-byte pieces
+  // four places further (modulo the row), so that a fragment load of eight lanes (two rows, four
+  // pieces each) touches every bank once.
+  constexpr int PIECES = HD / 8;
+  constexpr bool SWZ = HD % 64 == 0;
+  bf16* my_ring = reinterpret_cast<bf16*>(dm_ring) + (size_t)warp * 2 * 2 * 16 * HD;
+  bool stage_ok[2] = {false, false};                 // whether the stage's page is one of the pool's
+  auto issue = [&](int i) {
+    const int j0 = (first_tile + warp + i * DM_WARPS) << 4;
+    const int page = table[j0 / page_size];
+    const bool pok = page >= 0 && page < n_pages;
+    if (!pok && lane == 0) *status = NIB_STATUS_BAD_PAGE;       // recorded, never followed
+    stage_ok[i & 1] = pok;
+    const bf16* src = cache + ((size_t)(pok ? page : 0) * 2 * n_kv_head + hk) * page_size * HD +
+                      (size_t)(j0 % page_size) * HD;
+    bf16* dst = my_ring + (size_t)(i & 1) * 2 * 16 * HD;
+#pragma unroll
+    for (int idx = lane; idx < 16 * PIECES; idx += 32) {
+      const int row = idx / PIECES, pc = idx % PIECES;
+      const int j = j0 + row;
+      const bool ok = pok && j >= k_begin && j < k_end;         // (a key that is not this split's: zeros)
+      const int ps = SWZ ? (pc ^ ((row & 1) * 4)) : pc;
+      cp_async16(dst + row * HD + ps * 8, src + (size_t)row * HD + pc * 8, ok);
+      cp_async16(dst + (16 + row) * HD + ps * 8, src + kv_stride + (size_t)row * HD + pc * 8, ok);
+    }
+    cp_async_commit();
+  };
+  // the stage's fragments: this lane's pieces of the rows fr and fr + 8
+  auto take = [&](int i) {
+    const bf16* st = my_ring + (size_t)(i & 1) * 2 * 16 * HD;
+    page_ok = stage_ok[i & 1];
+#pragma unroll
+    for (int hh = 0; hh < HALVES; ++hh) {
+      const int pc = kl + 4 * hh;
+      const int ps = SWZ ? (pc ^ ((fr & 1) * 4)) : pc;
+      ka[hh] = *reinterpret_cast<const uint4*>(st + fr * HD + ps * 8);
+      kb[hh] = *reinterpret_cast<const uint4*>(st + (fr + 8) * HD + ps * 8);
+      va[hh] = *reinterpret_cast<const uint4*>(st + (16 + fr) * HD + ps * 8);
+      vb[hh] = *reinterpret_cast<const uint4*>(st + (24 + fr) * HD + ps * 8);
+    }
+  };
+  // none of the first tiles' keys is the one that the kernel ahead writes: they may be asked for now
   const bool early = n_mine > 0 && (((first_tile + warp) << 4) + 15) < pos;
-  if (early) fetch(0);
+  int issued = 0;
+  if (RING) {
+    while (issued < 2 && issued < n_mine && (((first_tile + warp + issued * DM_WARPS) << 4) + 15) < pos) issue(issued++);
+  } else if (early) {
+    fetch(0);
+  }
   pdl_wait();
   if (cluster_merge) cluster_wait();                 // every block of the cluster runs by now
+  if (RING) {
+    while (issued < 2 && issued < n_mine) issue(issued++);
+  }
 
   if (empty) {
     if (threadIdx.x == 0 && n_splits > 1) {
@@ -156,7 +211,13 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
     float m = -INFINITY, l = 0.0f;
 
     for (int i = 0; i < n_mine; ++i) {
-      if (i > 0 || !early) fetch(i);
+      if (RING) {
+        if (i + 1 < issued) cp_async_wait<1>(); else cp_async_wait<0>();   // tile i has landed (i + 1 may be on its way)
+        __syncwarp();
+        take(i);
+      } else if (i > 0 || !early) {
+        fetch(i);
+      }
       const int j0 = (first_tile + warp + i * DM_WARPS) << 4;
       // ---- S = K . q: column 0 comes out in the lanes with kl == 0, c[0] for key fr and c[2] for key fr + 8
       float s[4] = {0.0f, 0.0f, 0.0f, 0.0f};
@@ -182,35 +243,40 @@ attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __r
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
       mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
       const float m_new = fmaxf(m, mx);
-      if (m_new == -INFINITY) continue;              // (the same in every lane) no key of this split so far
-      const float corr = dm_pow2(m - m_new);         // (2^-inf = 0 for the first keys)
-      m = m_new;
-      float sum = 0.0f;
+      if (m_new != -INFINITY) {                      // (the same in every lane; else: no key of this split so far)
+        const float corr = dm_pow2(m - m_new);         // (2^-inf = 0 for the first keys)
+        m = m_new;
+        float sum = 0.0f;
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        p[e] = dm_pow2(p[e] - m);                    // 0 for a key that is not there
-        sum += p[e];
+        for (int e = 0; e < 4; ++e) {
+          p[e] = dm_pow2(p[e] - m);                    // 0 for a key that is not there
+          sum += p[e];
+        }
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        l = l * corr + sum;
+#pragma unroll
+        for (int a = 0; a < 2 * HALVES; ++a) {
+          acc[a][0] *= corr;
+          acc[a][2] *= corr;
+        }
+        // ---- O^T += V^T . P^T: P in column 0 (the lanes 0..3 hold it), the value rows transposed in registers.
+        // Register x of a lane's piece holds the values 8 kl + 2 x (+1) of a 32-wide part of the row: the four
+        // lanes' registers x make an 8x8 tile whose column 2 kl + e stands for that value.  Tiles x = 0, 1 give
+        // the 16 rows of one product, tiles 2, 3 those of the next.
+        const uint32_t pb0 = fr == 0 ? dm_pack(p[0], p[1]) : 0u;
+        const uint32_t pb1 = fr == 0 ? dm_pack(p[2], p[3]) : 0u;
+#pragma unroll
+        for (int hh = 0; hh < HALVES; ++hh) {
+          dm_mma(acc[2 * hh], dm_transpose(va[hh].x), dm_transpose(va[hh].y), dm_transpose(vb[hh].x),
+                 dm_transpose(vb[hh].y), pb0, pb1);
+          dm_mma(acc[2 * hh + 1], dm_transpose(va[hh].z), dm_transpose(va[hh].w), dm_transpose(vb[hh].z),
+                 dm_transpose(vb[hh].w), pb0, pb1);
+        }
       }
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      l = l * corr + sum;
-#pragma unroll
-      for (int a = 0; a < 2 * HALVES; ++a) {
-        acc[a][0] *= corr;
-        acc[a][2] *= corr;
-      }
-      // ---- O^T += V^T . P^T: P in column 0 (the lanes 0..3 hold it), the value rows transposed in registers.
-      // Register x of a lane's piece holds the values 8 kl + 2 x (+1) of a 32-wide part of the row: the four
-      // lanes' registers x make an 8x8 tile whose column 2 kl + e stands for that value.  Tiles x = 0, 1 give
-      // the 16 rows of one product, tiles 2, 3 those of the next.
-      const uint32_t pb0 = fr == 0 ? dm_pack(p[0], p[1]) : 0u;
-      const uint32_t pb1 = fr == 0 ? dm_pack(p[2], p[3]) : 0u;
-#pragma unroll
-      for (int hh = 0; hh < HALVES; ++hh) {
-        dm_mma(acc[2 * hh], dm_transpose(va[hh].x), dm_transpose(va[hh].y), dm_transpose(vb[hh].x),
-               dm_transpose(vb[hh].y), pb0, pb1);
-        dm_mma(acc[2 * hh + 1], dm_transpose(va[hh].z), dm_transpose(va[hh].w), dm_transpose(vb[hh].z),
-               dm_transpose(vb[hh].w), pb0, pb1);
+      if (RING && issued < n_mine) {                 // the stage that was just used takes the tile after next
+        __syncwarp();
+        issue(issued++);
       }
     }
     // ---- column 0 of the accumulators: lane 4 f (kl == 0) holds, in tile a = 2 hh + u, c[0] for the row
@@ -320,7 +386,7 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
                                         const int* row_entry, const int* positions, int n_rows, int n_head,
                                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
                                         int window, int chunk, int n_splits, int* counters, int* status,
-                                        int cluster, cudaStream_t stream) {
+                                        int cluster, int ring, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (!nib_attention_decode_mma_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -333,12 +399,29 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)n_rows * n_head * n_splits * head_dim : nullptr;
   const dim3 grid(n_splits, n_head, n_rows), block(DM_WARPS * 32);
-  cudaError_t e;
-#define NIB_DM_LAUNCH(HD)                                                                                      \
-  e = launch_pdl_cluster(attention_decode_mma_kernel<HD>, grid, block, 0, stream, cluster ? n_splits : 1,         \
-                         (const bf16*)q, ldq, (const bf16*)cache, part_o, part_ml, (bf16*)out, ldo, block_table, \
-                         max_blocks, rows, row_entry, positions, n_head, n_kv_head, page_size, n_pages, scale,   \
-                         window, chunk, n_splits, counters, status, cluster ? 1 : 0)
+  // ring != 0: keys and values pass through two shared-memory stages per warp (two tiles in flight)
+  const size_t ring_bytes = (size_t)DM_WARPS * 2 * 2 * 16 * head_dim * sizeof(bf16);
+  cudaError_t e = cudaSuccess;
+#define NIB_DM_LAUNCH_R(HD, RING)                                                                                \
+  do {                                                                                                           \
+    if (RING && ring_bytes > 32 * 1024) {  /* (static shared memory counts against the 48 KB default too) */     \
+      static bool attr_set = false;                                                                              \
+      if (!attr_set) {                                                                                           \
+        e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 (int)ring_bytes);                                                               \
+        if (e != cudaSuccess) return (int)e;                                                                     \
+        attr_set = true;                                                                                         \
+      }                                                                                                          \
+    }                                                                                                            \
+    e = launch_pdl_cluster(attention_decode_mma_kernel<HD, RING>, grid, block, RING ? ring_bytes : 0, stream,    \
+                           cluster ? n_splits : 1, (const bf16*)q, ldq, (const bf16*)cache, part_o, part_ml,     \
+                           (bf16*)out, ldo, block_table, max_blocks, rows, row_entry, positions, n_head,         \
+                           n_kv_head, page_size, n_pages, scale, window, chunk, n_splits, counters, status,      \
+                           cluster ? 1 : 0);                                                                     \
+  } while (0)
+#define NIB_DM_LAUNCH(HD)            \
+  if (ring) NIB_DM_LAUNCH_R(HD, true); \
+  else NIB_DM_LAUNCH_R(HD, false)
   switch (head_dim) {
     case 32: NIB_DM_LAUNCH(32); break;
     case 64: NIB_DM_LAUNCH(64); break;
@@ -346,6 +429,7 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
     default: NIB_DM_LAUNCH(128); break;
   }
 #undef NIB_DM_LAUNCH
+#undef NIB_DM_LAUNCH_R
   if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();
 }
