@@ -113,6 +113,19 @@ def test_linear_rows_do_not_depend_on_the_batch():
     one = torch.zeros(1, 130, device=DEV)
     o.linear_simt(a[41:42].to(DEV), w.to(DEV), None, one, 1)
     assert torch.equal(one[0], full[41])
+    # steps of at most 16 rows run on a kernel of their own (a thread per feature, K in chunks of 64 asked
+    # for ahead): every output is still one accumulator in index order, so the bits are those of the tiled
+    # kernel; with bias, both activations and the residual sum, and sizes that no tile divides
+    bias = torch.randn(130, generator=g)
+    for act in (o.ACT_NONE, o.ACT_GELU_TANH, o.ACT_GELU_ERF):
+        for residual in (False, True):
+            base = torch.randn(70, 130, generator=g).to(DEV)
+            full = base.clone()
+            o.linear_simt(a.to(DEV), w.to(DEV), bias.to(DEV), full, 70, act, residual)
+            for m0, n in ((0, 1), (3, 5), (20, 8), (33, 13), (50, 16)):
+                few = base[m0:m0 + n].clone()
+                o.linear_simt(a[m0:m0 + n].to(DEV), w.to(DEV), bias.to(DEV), few, n, act, residual)
+                assert torch.equal(few, full[m0:m0 + n]), (act, residual, m0, n)
 
 
 def paged_case(dtype, n_head, n_kv_head, hd, page_size, lengths, q_lens, seed):
