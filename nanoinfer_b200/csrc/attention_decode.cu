@@ -62,14 +62,15 @@ template <> __device__ __forceinline__ float pow2<float>(float x) { return exp2f
 // shuffles; every group runs an online softmax of its own over its keys, BATCH keys at a time, and
 // keeps the output for its lanes' pieces.  The groups, then the warps, are merged once at the end,
 // in a fixed order.
+// (q, cache and out carry no __restrict__: the kernel ahead writes them; see pdl_wait in common.cuh)
 template <typename T, int LPR>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 6)   // six blocks an SM: what the host's choice of splits counts on
-attention_decode_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache, float* part_o,
-                        float* part_ml, T* __restrict__ out, int ldo,
+attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
+                        float* part_ml, T* out, int ldo,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
-                        int chunk, int n_splits, int* __restrict__ counters, int* __restrict__ status,
+                        int chunk, int n_splits, int* counters, int* status,
                         int cluster_merge) {
   constexpr int VN = Piece<T>::N;
   constexpr int BATCH = LPR / 2 < 4 ? LPR / 2 : 4;   // keys per lane group and batch

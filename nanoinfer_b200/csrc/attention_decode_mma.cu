@@ -62,18 +62,19 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
 
 // partial layout as in the streaming kernel: o [row][head][split][head_dim], ml [row][head][split][2]
 // (a tile's keys and values are 16 registers per 32 of head size: six blocks an SM up to 64, three beyond)
+// (q, cache and out carry no __restrict__: the kernel ahead writes them; see pdl_wait in common.cuh)
 // RING: a warp's tiles pass through a ring of two stages of its own in shared memory, filled by
 // `cp.async`: two tiles of keys and values are on their way while a third is multiplied, at no cost in
 // registers (a batch of 64 rows has one block per row and head and is bound by how many bytes are in
 // flight; without the ring a warp has one tile's loads, 4 KB, in flight at a time).
 template <int HD, bool RING>
 __global__ void __launch_bounds__(DM_WARPS * 32, HD <= 64 ? 6 : 3)
-attention_decode_mma_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache, float* part_o,
-                            float* part_ml, bf16* __restrict__ out, int ldo, const int* __restrict__ block_table,
+attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* part_o,
+                            float* part_ml, bf16* out, int ldo, const int* __restrict__ block_table,
                             int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                             const int* __restrict__ positions, int n_head, int n_kv_head, int page_size,
                             int n_pages, float scale, int window, int chunk, int n_splits,
-                            int* __restrict__ counters, int* __restrict__ status, int cluster_merge) {
+                            int* counters, int* status, int cluster_merge) {
   constexpr int HALVES = HD / 32;                    // a 16-byte piece per lane covers 32 of a row's values
   pdl_trigger();
   __shared__ __align__(16) float wo[DM_WARPS][HD];   // the warps' unnormalised outputs

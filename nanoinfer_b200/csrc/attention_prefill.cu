@@ -56,7 +56,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
 
 template <int HD>
 __global__ void __launch_bounds__(PF_THREADS)
-attention_prefill_kernel(const bf16* __restrict__ q, int ldq, const bf16* __restrict__ cache, bf16* __restrict__ out,
+attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
                          int ldo, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tiles, const int* __restrict__ entry_start,
                          const int* __restrict__ entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages,

@@ -17,8 +17,8 @@ constexpr int ATT_MAX_ND = 8;  // head_dim <= 256
 
 template <typename T>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
-attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ cache,
-                      T* __restrict__ out, int ldo, const int* __restrict__ block_table,
+attention_simt_kernel(const T* q, int ldq, const T* cache,
+                      T* out, int ldo, const int* __restrict__ block_table,
                       int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                       const int* __restrict__ positions, int n_head, int n_kv_head, int head_dim,
                       int page_size, int n_pages, float scale, int window, int* __restrict__ status) {

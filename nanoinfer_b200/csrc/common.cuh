@@ -85,6 +85,14 @@ __device__ __forceinline__ size_t kv_offset(int page, int kv, int head, int slot
 // pdl_wait() before its first access to global memory (which returns once the kernel before it has
 // finished and its writes are visible).  A step is a chain of a hundred short kernels, and this
 // hides each one's launch latency behind its predecessor.
+//
+// A rule that follows: a pointer to anything that a kernel of the same step writes (activations, the
+// residual stream, queries, the cache, logits) is NEVER declared `const T* __restrict__`.  The compiler
+// treats loads through such a pointer as invariant for the kernel's lifetime (ld.global.nc) and is
+// free to move them above pdl_wait(), asm memory clobber or not; it did so in a kernel that asked for
+// its weights before the wait, and read the step's rows there too, before they were written.  Only
+// what no kernel of the step writes (weights, biases, norm parameters, the step's tables, which the
+// host copied in before the step) may be read through a const __restrict__ pointer.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 

@@ -16,7 +16,7 @@ namespace nib {
 template <typename T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ positions,
                              const T* __restrict__ table, const T* __restrict__ pos_table,
-                             const int* __restrict__ feedback, float* __restrict__ out, int C) {
+                             const int* feedback, float* out, int C) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -47,9 +47,9 @@ __device__ __forceinline__ void store4(bf16* p, float a, float b, float c, float
 // One block per output row.  The row is staged in shared memory as 32-bit floats,
 // so the mean and the variance are two true passes over the same values.
 template <typename OutT>
-__global__ void layernorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+__global__ void layernorm_kernel(const float* x, const int* __restrict__ rows,
                                  const float* __restrict__ gamma, const float* __restrict__ beta,
-                                 OutT* __restrict__ out, int C, float eps) {
+                                 OutT* out, int C, float eps) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float smem[];
@@ -80,8 +80,8 @@ __global__ void layernorm_kernel(const float* __restrict__ x, const int* __restr
 // shared memory and no block-wide barrier.  Same two true passes as above.
 template <typename OutT, int NV>
 __global__ void __launch_bounds__(256)
-layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gamma,
-                      const float* __restrict__ beta, OutT* __restrict__ out, int n_rows, int C, float eps) {
+layernorm_rows_kernel(const float* x, const int* __restrict__ rows, const float* __restrict__ gamma,
+                      const float* __restrict__ beta, OutT* out, int n_rows, int C, float eps) {
   pdl_trigger();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * 8 + warp;
@@ -121,11 +121,11 @@ layernorm_rows_kernel(const float* __restrict__ x, const int* __restrict__ rows,
 // ------------------------------------------------------------------ kv append
 // src is the fused projection output [T, ld]; keys start at column k_off, values at v_off.
 template <typename T>
-__global__ void kv_append_kernel(const T* __restrict__ src, int ld, int k_off, int v_off,
-                                 T* __restrict__ cache, const int* __restrict__ block_table,
+__global__ void kv_append_kernel(const T* src, int ld, int k_off, int v_off,
+                                 T* cache, const int* __restrict__ block_table,
                                  int max_blocks, const int* __restrict__ row_entry,
                                  const int* __restrict__ positions, int n_kv_head, int head_dim,
-                                 int page_size, int n_pages, int* __restrict__ status) {
+                                 int page_size, int n_pages, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
@@ -149,10 +149,10 @@ __global__ void kv_append_kernel(const T* __restrict__ src, int ld, int k_off, i
 // are multiples of the piece).
 template <typename T>
 __global__ void __launch_bounds__(256)
-kv_append_pieces_kernel(const T* __restrict__ src, int ld, int k_off, int v_off, T* __restrict__ cache,
+kv_append_pieces_kernel(const T* src, int ld, int k_off, int v_off, T* cache,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ row_entry,
                         const int* __restrict__ positions, int n_rows, int n_kv_head, int head_dim, int page_size,
-                        int n_pages, int* __restrict__ status) {
+                        int n_pages, int* status) {
   constexpr int VN = 16 / sizeof(T);
   pdl_trigger();
   const int per_head = head_dim / VN, per_row = 2 * n_kv_head * per_head;

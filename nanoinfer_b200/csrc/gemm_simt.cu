@@ -18,8 +18,8 @@ constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;  // 256 threads, 4 x 4 
 
 template <typename InT, typename OutT>
 __global__ void __launch_bounds__(256)
-linear_simt_kernel(const InT* __restrict__ a, int lda, const InT* __restrict__ w, int ldw,
-                   const float* __restrict__ bias, OutT* __restrict__ out, int ldo, int M, int N,
+linear_simt_kernel(const InT* a, int lda, const InT* __restrict__ w, int ldw,
+                   const float* __restrict__ bias, OutT* out, int ldo, int M, int N,
                    int K, int act, int residual) {
   pdl_trigger();
   pdl_wait();
@@ -85,10 +85,12 @@ linear_simt_kernel(const InT* __restrict__ a, int lda, const InT* __restrict__ w
 // order with the same fused multiply-adds: the bits are those of the tiled kernel, whatever the batch.
 constexpr int RB_N = 64, RB_K = 64;
 
+// (`a` and `out` carry no __restrict__: see pdl_wait in common.cuh.  With it, the compiler read the
+// step's rows beside the weights, above the wait, before the kernel that writes them had finished.)
 template <typename InT, typename OutT, int ROWS>
 __global__ void __launch_bounds__(256)
-linear_simt_rows_kernel(const InT* __restrict__ a, int lda, const InT* __restrict__ w, int ldw,
-                        const float* __restrict__ bias, OutT* __restrict__ out, int ldo, int M, int N, int K,
+linear_simt_rows_kernel(const InT* a, int lda, const InT* __restrict__ w, int ldw,
+                        const float* __restrict__ bias, OutT* out, int ldo, int M, int N, int K,
                         int act, int residual) {
   constexpr int RPT = ROWS / 4;                      // rows per thread
   constexpr int WPT = RB_N * RB_K / 256;             // weight values a thread stages per chunk: 16

@@ -88,8 +88,7 @@ __device__ int block_argmax(const float* __restrict__ row, int V, BestPair* scra
   return r.i == 0x7fffffff ? 0 : r.i;
 }
 
-__global__ void __launch_bounds__(256) argmax_kernel(const float* __restrict__ logits, int ld, int V,
-                                                     int* __restrict__ out) {
+__global__ void __launch_bounds__(256) argmax_kernel(const float* logits, int ld, int V, int* out) {
   pdl_trigger();
   pdl_wait();
   __shared__ BestPair scratch[32];
@@ -323,10 +322,10 @@ __device__ void radix_select(const float* __restrict__ row, int V, float tempera
 // as clusters of SAMPLE_TEAM blocks) one cluster, whose blocks share the passes over all tokens.
 // `scratch` holds 2 words per row (the folded maximum and the arrival count), zero between launches.
 __global__ void __launch_bounds__(SAMPLE_THREADS, 1)
-sample_kernel(const float* __restrict__ logits, int ld, int V, const int* __restrict__ row_slot,
+sample_kernel(const float* logits, int ld, int V, const int* __restrict__ row_slot,
               const float* __restrict__ temperature, const int* __restrict__ top_k,
-              unsigned long long* __restrict__ rng_state, int* __restrict__ out,
-              int* __restrict__ last_token, unsigned long long* __restrict__ scratch, int team_size) {
+              unsigned long long* rng_state, int* out,
+              int* last_token, unsigned long long* scratch, int team_size) {
   pdl_trigger();
   pdl_wait();
   __shared__ BestPair best_scratch[32];
