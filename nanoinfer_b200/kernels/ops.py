@@ -573,10 +573,11 @@ DECODE_RESIDENT_BLOCKS = 888
 DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
 
 #: whether the MMA decode attention passes its keys and values through a ring of shared-memory stages
-#: (two tiles in flight per warp), given the number of blocks of the launch.  It pays where the launch
-#: fills the device with unsplit rows (measured: -7 % a step at batch 64, +3 to +7 % at batch 1 to 32,
-#: where a block's 32 KB of shared memory keep it from starting beside the kernel ahead)
-DECODE_RING = lambda n_blocks: n_blocks >= 592   # noqa: E731
+#: (two tiles in flight per warp), given the launch's rows x heads and its number of splits.  It pays where
+#: the launch fills the device with unsplit rows (measured: -7 % a step at batch 64, +3 to +7 % at batch 1
+#: to 32, where the keys are split and a block's 32 KB of shared memory keep it from starting beside the
+#: kernel ahead)
+DECODE_RING = lambda n_blocks, n_splits: n_splits == 1 and n_blocks >= 592   # noqa: E731
 
 #: the bfloat16 decode attention on warp-level MMAs where the shape allows (False: always the streaming kernel)
 USE_DECODE_MMA = True
@@ -642,7 +643,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                                                   head_dim, page_size, n_pages, float(scale), int(window), chunk,
                                                   n_splits, _ptr(counters), _ptr(status),
                                                   int(n_splits in DECODE_CLUSTER_SPLITS),
-                                                  int(DECODE_RING(n_rows * n_head * n_splits)), _stream()),
+                                                  int(DECODE_RING(n_rows * n_head, n_splits)), _stream()),
                "attention_decode_mma")
         return
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
