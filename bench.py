@@ -20,7 +20,8 @@ One JSON line is printed.  A "step" is one decode step of the whole batch.
              outputs of 16 to 255, temperature 0.8: generated tokens a second, time to first token,
              time per output token, pages, bytes the steps had to read over the memory's rate); with
              ``--preset gpt2-xl`` decode at batch 1, 8 and 64 with prompts of 512 tokens and 256 new
-             ones, and the pages they fill of the pool.
+             ones, and the pages they fill of the pool; with the default preset the same layers
+             with 8,192 positions, decoding at batch 1, 8 and 32 behind prompts of 8,144 tokens.
   provenance the commit, whether the tree was clean, the tools, the device, the time.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the fallback
 figures (6.65 TB/s, 1.59 PFLOP/s).  More than one GPU is out of scope: --gpus N>1 says so and
@@ -126,6 +127,13 @@ def main() -> int:
                                        "frac": p8["flops"] / (p8["ms"] / 1e3) / (peaks["bf16_tflops"] * 1e12)}
         del big
         torch.cuda.empty_cache()
+        if args.preset == "gpt2-small":
+            # the same layers with a context of 8,192 positions: a decode step is then mostly keys and values
+            far_dir, _ = bs.model_folder(args.preset, seed=1234, dtype=dtype, n_layer=args.layers,
+                                         overrides={"n_positions": 8192})
+            far = bs.decode_points(far_dir, "bfloat16", [1, 8, 32], 8192 - 48, 32, warmup=6, runs=2)
+            workloads["context_8192"] = {f"b{p['batch']}": {k: p[k] for k in (
+                "decode_tok_s", "decode_ms_per_step", "frac_of_hbm", "prefill_tok_s", "prefill_ms")} for p in far}
         if args.preset == "gpt2-medium":
             from nanoinfer_b200.serve_bench import run_serving
             s = run_serving(model_dir, "bfloat16", requests=64, max_batch=64, prompt_min=16, prompt_max=1023, out_min=16,

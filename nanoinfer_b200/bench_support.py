@@ -42,9 +42,11 @@ def measured_peaks() -> Dict[str, float]:
         return dict(FALLBACK_PEAKS)
 
 
-def model_folder(preset: str, seed: int, dtype: torch.dtype, n_layer: Optional[int] = None) -> Tuple[str, object]:
+def model_folder(preset: str, seed: int, dtype: torch.dtype, n_layer: Optional[int] = None,
+                 overrides: Optional[Dict[str, object]] = None) -> Tuple[str, object]:
     """A folder with seeded random weights of the preset's sizes (made once per process tree, in the
-    temporary folder); ``n_layer`` may reduce the depth, never the layer sizes."""
+    temporary folder); ``n_layer`` may reduce the depth, never the layer sizes; ``overrides`` replaces
+    other keys of the preset's config.json (a longer context, for instance)."""
     from .cli import _preset_path
     from .config.base import architecture_name
     from .registry import get_architecture
@@ -54,6 +56,7 @@ def model_folder(preset: str, seed: int, dtype: torch.dtype, n_layer: Optional[i
         raw = json.load(fh)
     if n_layer is not None:
         raw["n_layer"] = int(n_layer)
+    raw.update(overrides or {})
     cfg = get_architecture(architecture_name(raw)).config_cls.from_dict(raw)
     key = hashlib.sha1(json.dumps([raw, seed, str(dtype)], sort_keys=True).encode()).hexdigest()[:12]
     d = os.path.join(tempfile.gettempdir(), f"nanoinfer_b200_model_{os.getuid()}_{key}")
@@ -179,9 +182,13 @@ def time_decode(eng, batch: int, prompt_len: int, steps: int, warmup: int, seed:
     budget = max(1, eng.runner.max_rows // max(1, prompt_len))
     for i in range(0, batch, budget):
         chunk = reqs[i:i + budget]
-        items = [StepItem(r, torch.randint(0, vocab, (prompt_len,), generator=g).tolist(), [prompt_len - 1])
-                 for r in chunk]
-        last += eng.runner.step(items, sampler=eng.sampler).tolist()
+        prompts = [torch.randint(0, vocab, (prompt_len,), generator=g).tolist() for _ in chunk]
+        # (a prompt longer than a step's rows goes in portions, one request at a time)
+        for at in range(0, prompt_len, eng.runner.max_rows):
+            n = min(eng.runner.max_rows, prompt_len - at)
+            items = [StepItem(r, p[at:at + n], [n - 1] if at + n == prompt_len else []) for r, p in zip(chunk, prompts)]
+            toks = eng.runner.step(items, sampler=eng.sampler)
+        last += toks.tolist()
     flusher = L2Flusher(eng.device) if flush else None
     times = []
     ctx_sum = 0
@@ -402,7 +409,7 @@ def decode_points(model_dir: str, dtype: str, batches, prompt_len: int, tokens: 
     bw = bandwidth_gbs or peaks["hbm_gbs"]
     out = []
     for b in batches:
-        eng = build_engine(model_dir, dtype, b, prompt_len + tokens + warmup, max_rows=max(2048, b))
+        eng = build_engine(model_dir, dtype, b, prompt_len + tokens + warmup, max_rows=max(2048, b, prompt_len))
         dec = time_decode(eng, b, prompt_len, tokens, max(3, warmup))
         pre = time_prefill(eng, 1, prompt_len, runs, 1)
         step_bytes = weight_bytes_per_step(eng.model) + kv_bytes(eng.cache, [dec["mean_context"]] * b)

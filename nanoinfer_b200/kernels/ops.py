@@ -572,6 +572,10 @@ DECODE_RESIDENT_BLOCKS = 888
 #: shared memory instead of global scratch
 DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
 
+#: keys per split from which the MMA decode attention gives up the merge inside a cluster (eight splits
+#: at most) for twice as many splits or more, merged through scratch (measured at 2 K to 16 K keys, batch 1 to 8)
+DECODE_DEEP_KEYS = 512
+
 #: whether the MMA decode attention passes its keys and values through a ring of shared-memory stages
 #: (two tiles in flight per warp), given the launch's rows x heads and its number of splits.  It pays where
 #: the launch fills the device with unsplit rows (measured: -7 % a step at batch 64, +3 to +7 % at batch 1
@@ -628,8 +632,16 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
     resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
     # (the MMA kernel merges up to eight splits inside a cluster, which costs two trips to memory less
-    # than the merge through scratch: eight splits of twice the keys beat sixteen)
-    chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident, max(DECODE_CLUSTER_SPLITS, default=0) if mma else 0)
+    # than the merge through scratch: eight splits of twice the keys beat sixteen, until a split has
+    # DECODE_DEEP_KEYS keys to walk and the device has room for twice as many splits: a lone row at
+    # 16 K keys takes 0.44 ms a step in 72 splits against 0.72 ms in 8)
+    at_most = 0
+    if mma:
+        at_most = max(DECODE_CLUSTER_SPLITS, default=0)
+        deep = min(resident // max(1, n_rows * n_head), max_keys // (DECODE_DEEP_KEYS // 2))
+        if deep >= 2 * at_most:
+            at_most = deep
+    chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident, at_most)
     scratch = counters = None
     if n_splits > 1:
         # (never more than the resident blocks: the same size every step, so that the buffers stay put)

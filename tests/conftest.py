@@ -50,7 +50,12 @@ V50K = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=256
 SMALL = dict(architectures=["GPT2LMHeadModel"], vocab_size=50257, n_positions=1024, n_embd=768, n_layer=12, n_head=12,
              n_inner=3072, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
              scale_attn_by_inverse_layer_idx=False)
-TINY = {"A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE, "XLW": XLW, "MEDW": MEDW, "V50K": V50K,
+# a context of thousands of positions, heads of 64 (the tensor-core decode attention): a decoded token's keys
+# are then cut into more splits than one cluster holds
+FAR = dict(architectures=["GPT2LMHeadModel"], vocab_size=300, n_positions=4608, n_embd=128, n_layer=2, n_head=2,
+           n_inner=192, layer_norm_epsilon=1e-5, activation_function="gelu_new", tie_word_embeddings=True,
+           scale_attn_by_inverse_layer_idx=False)
+TINY = {"FAR": FAR, "A": TINY_A, "B": TINY_B, "LONG": TINY_LONG, "WIDE": WIDE, "XLW": XLW, "MEDW": MEDW, "V50K": V50K,
         "SMALL": SMALL}
 
 

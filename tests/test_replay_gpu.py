@@ -334,3 +334,28 @@ def test_gpt2_small_whole_against_the_plain_implementation(dtype, model_dirs, pl
     s.close()
     rows, worst = compare_rows(s, reqs, model_dir, plain_logits, dtype, device="cuda")
     assert rows == 5 + 1 + 2 + 2 + 1 + 20 + 4
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_thousands_of_keys_behind_a_decoded_token(dtype, model_dirs, plain_logits, tmp_path):
+    """A request of 4600 tokens (portions of 2000, 2000 and 568, then 32 single tokens) beside a short one
+    that decodes in the same steps: the long row's keys are cut into more splits than one cluster
+    merges (they meet through scratch), and the short row has keys for the first split only.  The
+    attention is sharpened so that single far keys carry the result."""
+    model_dir = model_dirs("FAR", TORCH_DTYPE[dtype], sharpen=3.0)
+    vocab = TINY["FAR"]["vocab_size"]
+    if dtype == "bfloat16":
+        from nanoinfer_b200.kernels import ops
+        chunk, n_splits = 256, 18    # what the rule below must give for 4608 keys and 2 rows of 2 heads
+        assert ops.DECODE_DEEP_KEYS == 512 and ops.decode_split(2, 2, 4608, at_most=18) == (chunk, n_splits)
+    reqs = {"far": random_tokens(vocab, 4600, 410), "near": random_tokens(vocab, 60, 411)}
+    s = TraceSession(model_dir, dtype, tmp_path / "far", 4608 + 64, vocab)
+    s.step([("far", reqs["far"][:2000], [0, 1999])])
+    s.step([("far", reqs["far"][2000:4000], [0, 1999]), ("near", reqs["near"][:28], [27])])
+    s.step([("far", reqs["far"][4000:4568], [0, 567])])
+    for i in range(32):
+        s.step([("near", reqs["near"][28 + i:29 + i], [0]), ("far", reqs["far"][4568 + i:4569 + i], [0])],
+               end=["far", "near"] if i == 31 else [])
+    s.close()
+    rows, worst = compare_rows(s, reqs, model_dir, plain_logits, dtype)
+    assert rows == 6 + 1 + 64
