@@ -137,9 +137,9 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // What the epilogue needs and the kernel ahead does not write: the first tile's bias, and for the
   // cache-writing projection the place of each row's slot (two dependent lookups in the step's
   // tables).  Asked for now, they are there when the sums are; asked for then, each would be a round
-  // trip to L2 at the very end of the chain.  (Kept to the steps of at most 16 rows: registers.)
+  // trip to L2 at the very end of the chain (at 64 rows: 4 sums a thread, 128 registers, no spills).
   constexpr int OUTS = (NT * 128 + SK_WARPS * 32 - 1) / (SK_WARPS * 32);   // sums per thread
-  constexpr bool AHEAD = NT <= 2;
+  constexpr bool AHEAD = true;
   float bias_r[OUTS];
   float res_r[OUTS];
   long long kv_base[OUTS];   // element offset of (page, K, head 0, slot, 0) in the cache layer; -1: bad page

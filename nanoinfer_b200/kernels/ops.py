@@ -568,6 +568,10 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
 DECODE_RESIDENT_BLOCKS = 888
 
 
+#: the same bound for the MMA decode attention, whose splits are the blocks of a cluster: clusters do not
+#: pack the last tenth of the device (24 rows of 12 heads take 0.62 ms a step in 2 splits, 0.68 ms in 3)
+DECODE_CLUSTER_BLOCKS = 768
+
 #: numbers of splits that the MMA decode attention runs as one cluster, merging through distributed
 #: shared memory instead of global scratch
 DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
@@ -578,10 +582,10 @@ DECODE_DEEP_KEYS = 512
 
 #: whether the MMA decode attention passes its keys and values through a ring of shared-memory stages
 #: (two tiles in flight per warp), given the launch's rows x heads and its number of splits.  It pays where
-#: the launch fills the device with unsplit rows (measured: -7 % a step at batch 64, +3 to +7 % at batch 1
-#: to 32, where the keys are split and a block's 32 KB of shared memory keep it from starting beside the
-#: kernel ahead)
-DECODE_RING = lambda n_blocks, n_splits: n_splits == 1 and n_blocks >= 592   # noqa: E731
+#: the launch fills the device with unsplit rows (measured: -7 to -10 % a step at batch 40 to 64, +3 to
+#: +7 % at batch 1 to 32, where the keys are split and a block's 32 KB of shared memory keep it from
+#: starting beside the kernel ahead)
+DECODE_RING = lambda n_blocks, n_splits: n_splits == 1 and n_blocks >= 440   # noqa: E731
 
 #: the bfloat16 decode attention on warp-level MMAs where the shape allows (False: always the streaming kernel)
 USE_DECODE_MMA = True
@@ -630,7 +634,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     mma = USE_DECODE_MMA and q.dtype == torch.bfloat16 and _can("nib_attention_decode_mma_supported", head_dim, page_size) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
-    resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
+    resident = DECODE_RESIDENT_BLOCKS if not mma else (DECODE_CLUSTER_BLOCKS if head_dim <= 64 else DECODE_CLUSTER_BLOCKS // 2)
     # (the MMA kernel merges up to eight splits inside a cluster, which costs two trips to memory less
     # than the merge through scratch: eight splits of twice the keys beat sixteen, until a split has
     # DECODE_DEEP_KEYS keys to walk and the device has room for twice as many splits: a lone row at
