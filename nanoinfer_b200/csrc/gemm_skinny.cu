@@ -11,9 +11,10 @@
 // block finishing a share of the rows: every sum still has one fixed order.
 //
 // Folded in, because each is one round trip less for a decode step:
-//   * the LayerNorm that stands before the product, for steps of at most 16 rows (the rows are
-//     normalised into shared memory while the first weights are on their way; formula of
-//     crates/core/src/kernels/reference.rs:42-51);
+//   * the LayerNorm that stands before the product (the rows are normalised into shared memory while
+//     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51).  A
+//     block normalises at most 16 rows: with more, the blocks of a cluster of 2 or 4 share the work,
+//     each writing its rows into the shared memory of all of them;
 //   * the bias, GELU and residual epilogues (crates/metal/src/shaders/batch.metal:94-97,148-165);
 //   * the write of keys and values into the paged cache for the fused q/k/v projection
 //     (batch.metal:155-164).
@@ -29,10 +30,11 @@ namespace nib {
 
 constexpr int SK_WARPS = 8;
 constexpr int SK_MAX_ROWS = 64;
-constexpr int SK_MAX_LN_ROWS = 16;   // the norm is folded in for steps of at most this many rows
+constexpr int SK_LN_ROWS_PER_BLOCK = 16;   // rows that one block normalises; more are shared out over a cluster
 constexpr int SK_LN_REG_WIDTH = 1024;   // rows up to this wide are normalised in registers ...
 constexpr int SK_LN_MAX_WIDTH = 4096;   // ... wider ones, up to this, in shared memory
 constexpr int SK_MAX_SPLIT = 8;      // blocks of a cluster that split K
+constexpr int SK_MAX_LN_SHARE = 4;   // blocks of a cluster that share the normalisation of the rows
 
 struct SkinnyParams {
   const bf16* a;        // [M, K] activations (null when ln_x is given)
@@ -50,6 +52,7 @@ struct SkinnyParams {
   int ldo, out_f32, residual, act;
   int M, N, K;
   int split, k_per;     // blocks of a cluster and the slice of K that each takes (a multiple of 32)
+  int ln_share;         // with ln_x: blocks of a cluster that share the normalisation of the rows (1, 2 or 4; split is 1)
   int alias;            // 1: every block has one tile, and the warps' sums take the place of the rows
   // optional: features from kv_q_dim on go to the paged cache
   bf16* kv_cache;
@@ -94,6 +97,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = prm.M, S = prm.split;
   const int rank = S > 1 ? cluster_rank() : 0;
+  const int R = prm.ln_share;                          // blocks that share the normalisation (each its own tiles)
+  const int lrank = R > 1 ? cluster_rank() : 0;
   const int walker = blockIdx.x / S, n_walkers = gridDim.x / S;
   const int k0 = rank * prm.k_per;                     // this block's slice of K
   const int Ks = min(prm.K - k0, prm.k_per);
@@ -107,7 +112,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // [2][split][rows of a block][16] sums of the other blocks
   float* xch = reinterpret_cast<float*>(sk_smem + (prm.alias ? (xs_bytes > red_bytes ? xs_bytes : red_bytes)
                                                              : xs_bytes + red_bytes));
-  float* ln_gb = xch + 2 * NT * 128;                   // [2][K] the norm's scale and shift
+  float* ln_gb = xch + (S > 1 ? 2 * NT * 128 : 0);     // [2][K] the norm's scale and shift (no exchange without a split)
   const int n_tiles = (prm.N + 15) / 16;
   const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of the slice
   const int fr = lane >> 2, kl = lane & 3;         // this lane's feature row (and +8) and piece within a step
@@ -162,7 +167,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
       }
     }
   }
-  if (S > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
+  if (S > 1 || R > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
   pdl_wait();
   // the residual stream's old values, asked for as early as the kernel ahead allows
   auto fetch_residual = [&](int f0) {
@@ -185,9 +190,13 @@ linear_skinny_kernel(const SkinnyParams prm) {
     // Rows too wide for a lane's registers: a warp brings its row into a buffer of its own in shared
     // memory (summing on the way) and makes the other two passes there.
     __syncthreads();   // the norm's parameters are in place
+    if (R > 1) cluster_wait();
     const int K = prm.K;
     float* mine = ln_gb + 2 * K + (size_t)warp * K;
-    for (int m = warp; m < M; m += SK_WARPS) {
+    for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
+      uint32_t dst[SK_MAX_LN_SHARE];
+#pragma unroll
+      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = r < R ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
       float sum = 0.0f;
       for (int k = lane * 4; k < K; k += 128) {
@@ -210,13 +219,23 @@ linear_skinny_kernel(const SkinnyParams prm) {
         uint2 packed;
         packed.x = pack2((t.x - mean) * rstd * g.x + b.x, (t.y - mean) * rstd * g.y + b.y);
         packed.y = pack2((t.z - mean) * rstd * g.z + b.z, (t.w - mean) * rstd * g.w + b.w);
-        *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+        if (R == 1) *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+        else {
+#pragma unroll
+          for (int r = 0; r < SK_MAX_LN_SHARE; ++r)
+            if (r < R) cluster_store2(dst[r] + k * 2, packed.x, packed.y);
+        }
       }
     }
   } else if (prm.ln_x != nullptr) {
     __syncthreads();   // the norm's parameters are in place
+    if (R > 1) cluster_wait();
     const int K = prm.K;
-    for (int m = warp; m < M; m += SK_WARPS) {
+    // (with a cluster: block b takes rows b, b + R, ..., and writes them into every block's shared memory)
+    for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
+      uint32_t dst[SK_MAX_LN_SHARE];
+#pragma unroll
+      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = r < R ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
       // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
       float v[32];
@@ -256,7 +275,12 @@ linear_skinny_kernel(const SkinnyParams prm) {
           uint2 packed;
           packed.x = *reinterpret_cast<uint32_t*>(&lo);
           packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+          if (R == 1) *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
+          else {
+#pragma unroll
+            for (int r = 0; r < SK_MAX_LN_SHARE; ++r)
+              if (r < R) cluster_store2(dst[r] + k * 2, packed.x, packed.y);
+          }
         }
       }
     }
@@ -268,6 +292,10 @@ linear_skinny_kernel(const SkinnyParams prm) {
         cp_async16(xs + (size_t)m * ldx + c * 8, prm.a + (size_t)m * prm.lda + k0 + c * 8, true);
     cp_async_commit();
     cp_async_wait<0>();
+  }
+  if (R > 1) {   // every block's rows have arrived in this block's shared memory
+    cluster_arrive();
+    cluster_wait();
   }
   __syncthreads();
 
@@ -420,10 +448,12 @@ linear_skinny_kernel(const SkinnyParams prm) {
 
 static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)); }
 
-static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool alias = false) {
+static int skinny_ln_share(int M) { return (skinny_tiles(M) * 8 + SK_LN_ROWS_PER_BLOCK - 1) / SK_LN_ROWS_PER_BLOCK; }
+
+static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool exchange, bool alias = false) {
   const size_t xs = (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16), red = (size_t)SK_WARPS * NT * 128 * sizeof(float);
-  // (with the norm: its scale and shift, and for wide rows a buffer per warp)
-  return (alias ? (xs > red ? xs : red) : xs + red) + (size_t)2 * NT * 128 * sizeof(float) +
+  // (with a split of K: the other blocks' sums; with the norm: its scale and shift, and for wide rows a buffer per warp)
+  return (alias ? (xs > red ? xs : red) : xs + red) + (exchange ? (size_t)2 * NT * 128 * sizeof(float) : 0) +
          (ln ? (size_t)(2 + (K > SK_LN_REG_WIDTH ? SK_WARPS : 0)) * K * sizeof(float) : 0);
 }
 
@@ -443,7 +473,7 @@ static int skinny_split(int M, int N, int K, bool ln) {
     const int s2 = split * 2, kp = skinny_k_per(K, s2);
     if ((s2 - 1) * kp >= K) break;
     // (rows that leave room for one block per SM only are still better unsplit: measured at 64 rows)
-    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_LIMIT;
+    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false, split > 1) > SK_SMEM_LIMIT;
     if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 768)) break;
     split = s2;
   }
@@ -466,11 +496,13 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   attr[1].id = cudaLaunchAttributeClusterDimension;
-  attr[1].val.clusterDim.x = prm.split;
+  // a cluster is the blocks that split K, or (with the norm folded in, K unsplit) those that share the rows' normalisation
+  const int cluster = prm.split > 1 ? prm.split : prm.ln_share;
+  attr[1].val.clusterDim.x = cluster;
   attr[1].val.clusterDim.y = 1;
   attr[1].val.clusterDim.z = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = prm.split > 1 ? 2 : 1;
+  cfg.numAttrs = cluster > 1 ? 2 : 1;
   // One wave: at most two blocks per SM (one when the rows take much shared memory), each cluster
   // then walks several tiles with the rows in place.  How many clusters the device holds at once is
   // asked of the runtime (a cluster's blocks share a GPC, so it is fewer than SMs / blocks): a
@@ -478,43 +510,45 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   int err = 0;
   auto clusters_at_once = [&](size_t smem) {
     const int per_sm = smem <= SK_SMEM_TWO_PER_SM ? 2 : 1;
-    if (prm.split == 1) return per_sm * 148;
+    if (cluster == 1) return per_sm * 148;
     static std::mutex mu;
     static std::map<std::pair<int, size_t>, int> held;   // (blocks of a cluster, shared memory) -> clusters at once
     std::lock_guard<std::mutex> lock(mu);
-    auto it = held.find({prm.split, smem});
+    auto it = held.find({cluster, smem});
     if (it == held.end()) {
       int n = 0;
       cudaLaunchConfig_t q = cfg;
-      q.gridDim = dim3(prm.split * 148);
+      q.gridDim = dim3(cluster * 148);
       q.dynamicSmemBytes = smem;
       q.attrs = attr + 1;      // the query takes the cluster shape only
       q.numAttrs = 1;
       cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT>, &q);
       if (e != cudaSuccess) { err = (int)e; return 0; }
       if (n < 1) { err = NIB_ERR_UNSUPPORTED_SIZE; return 0; }
-      it = held.emplace(std::make_pair(prm.split, smem), n).first;
+      it = held.emplace(std::make_pair(cluster, smem), n).first;
     }
     const int cap = it->second;
-    return cap < per_sm * 148 / prm.split ? cap : per_sm * 148 / prm.split;
+    return cap < per_sm * 148 / cluster ? cap : per_sm * 148 / cluster;
   };
   const int n_tiles = (prm.N + 15) / 16;
   const bool ln = prm.ln_x != nullptr;
-  size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln);
-  int cap = clusters_at_once(smem);
+  // (tiles are walked by clusters that split K, or by single blocks: those of a cluster that shares the norm each walk their own)
+  const int per_cluster = prm.split > 1 ? 1 : cluster;
+  size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln, prm.split > 1);
+  int cap = clusters_at_once(smem) * per_cluster;
   if (err) return err;
   prm.alias = 0;
   if (n_tiles > cap) {
     // More tiles than one wave of blocks: if a block has one tile only, its warps' sums can lie where
     // the rows were, and the smaller blocks may all fit at once.
-    const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, true);
-    const int cap_one = smem_one < smem ? clusters_at_once(smem_one) : 0;
+    const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, prm.split > 1, true);
+    const int cap_one = smem_one < smem ? clusters_at_once(smem_one) * per_cluster : 0;
     if (err) return err;
     if (n_tiles <= cap_one) { prm.alias = 1; smem = smem_one; cap = cap_one; }
   }
-  // as few walkers as finish in the same number of rounds
+  // as few walkers as finish in the same number of rounds (whole clusters: a block without a tile still normalises its rows)
   const int rounds = (n_tiles + cap - 1) / cap;
-  const int walkers = (n_tiles + rounds - 1) / rounds;
+  const int walkers = ((n_tiles + rounds - 1) / rounds + per_cluster - 1) / per_cluster * per_cluster;
   cfg.dynamicSmemBytes = smem;
   cfg.gridDim = dim3(walkers * prm.split);
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
@@ -529,15 +563,15 @@ using namespace nib;
 // 1 if the few-rows kernel takes this problem (ln: with the LayerNorm folded in).
 extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const void* w) {
   if (M < 1 || M > SK_MAX_ROWS || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)w & 15)) return 0;
-  if (ln && (M > SK_MAX_LN_ROWS || K > SK_LN_MAX_WIDTH || (K & 3))) return 0;
+  if (ln && (K > SK_LN_MAX_WIDTH || (K & 3))) return 0;
   const int split = skinny_split(M, 16, K, ln != 0);   // (the split that smem alone asks for)
-  if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0) > SK_SMEM_LIMIT) return 0;
+  if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0, split > 1) > SK_SMEM_LIMIT) return 0;
   return 1;
 }
 
 // The product for steps of at most 64 rows (bfloat16 weights and activations; out bfloat16 or
 // float32).  Options as for nib_linear_tc_small: ln_x != null folds the LayerNorm before the product
-// in (`a` ignored; at most 16 rows); cache != null sends the features from q_dim on to the paged
+// in (`a` ignored); cache != null sends the features from q_dim on to the paged
 // cache.  split: blocks of a cluster that split K (0: chosen here; 1, 2, 4 or 8).
 extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias,
                                  void* out, int ldo, int M, int N, int K, int act, int residual, const float* ln_x,
@@ -558,7 +592,7 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   if (ln && split != 1) return NIB_ERR_BAD_ARGUMENT;
   const int k_per = skinny_k_per(K, split);
   if ((split - 1) * k_per >= K) return NIB_ERR_BAD_ARGUMENT;   // a block would have nothing
-  if (skinny_smem(skinny_tiles(M), k_per, K, ln) > SK_SMEM_LIMIT) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (skinny_smem(skinny_tiles(M), k_per, K, ln, split > 1) > SK_SMEM_LIMIT) return NIB_ERR_UNSUPPORTED_SIZE;
   SkinnyParams prm;
   prm.a = (const bf16*)a; prm.lda = lda;
   prm.ln_x = ln_x; prm.ln_ldx = ln_ldx; prm.ln_gamma = ln_gamma; prm.ln_beta = ln_beta; prm.ln_rows = ln_rows;
@@ -566,6 +600,7 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   prm.w = (const bf16*)w; prm.ldw = ldw; prm.bias = bias; prm.out = out; prm.ldo = ldo;
   prm.out_f32 = out_dtype == DT_F32; prm.residual = residual; prm.act = act;
   prm.M = M; prm.N = N; prm.K = K; prm.split = split; prm.k_per = k_per;
+  prm.ln_share = ln ? skinny_ln_share(M) : 1;
   prm.kv_cache = (bf16*)cache; prm.kv_block_table = block_table; prm.kv_row_entry = row_entry;
   prm.kv_positions = positions; prm.kv_max_blocks = max_blocks; prm.kv_q_dim = q_dim; prm.kv_heads = n_kv_head;
   prm.kv_head_dim = head_dim; prm.kv_page_size = page_size; prm.kv_n_pages = n_pages;

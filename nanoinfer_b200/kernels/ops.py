@@ -401,6 +401,11 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
 
 
 SKINNY_MAX_ROWS = 64
+#: most rows of a step for which the dispatcher lets the few-row kernel normalise the rows itself.  Beyond 16
+#: rows the blocks of a cluster share that work: with 2 blocks (17 to 32 rows) a decode step of GPT-2 small
+#: or medium is 4 to 6 % shorter than with the norm as a kernel of its own; with 4 blocks (33 to 64 rows)
+#: it is 1 to 2 % shorter at 40 to 48 rows and 4 % longer at 64
+SKINNY_LN_MAX_ROWS = 32
 PAIR_MIN_ROWS = 256      # the pair kernel's smallest step
 
 
@@ -414,8 +419,7 @@ def pair_pays(M: int, N: int, K: int) -> bool:
 
 def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=0) -> bool:
     """The warp-level MMA kernel for steps of at most 64 rows (bfloat16): every SM streams weight
-    rows, a few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in (at
-    most 16 rows); ``kv``: (cache layer, block table, row_entry, positions, q_dim) sends keys and
+    rows, a few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in; ``kv``: (cache layer, block table, row_entry, positions, q_dim) sends keys and
     values straight to the cache; ``split``: blocks of a cluster that split K (0: chosen by the
     library).  False if the kernel does not apply."""
     if M > SKINNY_MAX_ROWS or not _small_inputs_ok(a, norm, w, out):
@@ -461,7 +465,7 @@ def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=N
 
 
 def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
-    """Steps of at most 128 rows: up to 64 rows the warp-level MMA kernel (up to 16 with the
+    """Steps of at most 128 rows: up to 64 rows the warp-level MMA kernel (with the
     LayerNorm folded in), beyond that tcgen05.  Folding the norm into the tcgen05 kernel, or splitting
     K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
     normed rows and is not split here."""
@@ -477,6 +481,8 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
     else:
         mma = M <= 32 or K <= 1088 or N * K <= 5_000_000
     if mma:
+        if norm is not None and M > SKINNY_LN_MAX_ROWS:
+            a, norm = norm.materialise(M), None
         if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
             return True
         if norm is not None:   # too wide or too many rows to be normalised inside the kernel: normalise first

@@ -487,7 +487,10 @@ def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd)
 
 
 SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (64, 1000, 120), (128, 257, 64),
-                (16, 768, 3072), (5, 50257, 64), (8, 4800, 1600), (13, 200, 2048), (3, 96, 1104)]
+                (16, 768, 3072), (5, 50257, 64), (8, 4800, 1600), (13, 200, 2048), (3, 96, 1104),
+                # 17 to 64 rows: with the norm folded in, clusters of 2 and 4 blocks share its work
+                (24, 2304, 768), (32, 3072, 768), (64, 2304, 768), (50, 3072, 1024), (20, 4800, 1600), (40, 96, 768),
+                (17, 1000, 1104)]
 
 
 @pytest.mark.parametrize("M, N, K", SMALL_SHAPES)
@@ -552,6 +555,36 @@ def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, k
     out2 = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
     product(a, wd, bd, out2, M, norm=norm)
     assert torch.equal(out1, out2)
+
+
+@pytest.mark.parametrize("M, N, K", [(17, 96, 768), (32, 2304, 768), (33, 70, 1024), (64, 3072, 768), (64, 130, 264),
+                                     (28, 400, 1600)])
+def test_few_row_product_with_the_norm_shared_by_a_cluster_gives_each_row_its_own_bits(M, N, K):
+    """Beyond 16 rows the blocks of a cluster normalise the rows between them and write them into each
+    other's shared memory: a row's results are the bits it gets in a step of its own, whichever block
+    normalised it, and blocks of the cluster that have no tile of features still do their share."""
+    o = ops()
+    from nanoinfer_b200.parts.base import Workspace
+    g = gen(7 * M + N + K)
+    x = torch.randn(M + 3, K, generator=g) * 1.5 - 0.3
+    gamma, beta = 1 + 0.1 * torch.randn(K, generator=g), 0.1 * torch.randn(K, generator=g)
+    rows = torch.randperm(M + 3, generator=g)[:M].to(torch.int32)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    ws = Workspace(torch.device(DEV))
+    xd, gd, bed, wd, bd, rd = x.to(DEV), gamma.to(DEV), beta.to(DEV), w.to(DEV), b.to(DEV), rows.to(DEV)
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
+    norm = o.NormInput(xd, gd, bed, 1e-5, ws, torch.bfloat16, rows=rd)
+    assert o.linear_skinny(None, norm, wd, bd, out, M), "the kernel refused the shape"
+    xn = P.layernorm(x.double(), gamma.double(), beta.double(), 1e-5)[rows.long()].to(torch.bfloat16)
+    y = xn.double() @ w.double().T + b.double()
+    assert (out.cpu().double() - y).abs().max() < 1.5e-2 * max(1.0, float(y.abs().max()))
+    for m in sorted({0, 1, 15, 16, M // 2, M - 2, M - 1}):
+        alone = torch.zeros(1, N, dtype=torch.bfloat16, device=DEV)
+        one = o.NormInput(xd, gd, bed, 1e-5, ws, torch.bfloat16, rows=rd[m:m + 1].contiguous())
+        assert o.linear_skinny(None, one, wd, bd, alone, 1)
+        assert torch.equal(alone[0], out[m]), f"row {m}"
+    assert int(o.status_word().item()) == 0
 
 
 SPLIT_SHAPES = [(1, 96, 768), (8, 768, 3072), (16, 768, 768), (20, 100, 1000), (33, 70, 3072), (64, 1000, 264),
