@@ -470,16 +470,20 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
     K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
     normed rows and is not split here."""
     N, K = w.shape
-    # measured (widths 768, 1024, 1600): up to 16 rows the MMA kernel wins everywhere; up to 32
-    # everywhere but the widest outputs (the head), where its 16-feature tiles read the rows too often;
-    # up to 64 while the rows fit a block's shared memory unsplit (K up to about a thousand) or the
-    # weights are small: beyond that every block would bring in a forced split of long rows
+    # measured in whole decode steps at widths 768, 1024 and 1600 (batch 16 to 64): up to 16 rows the MMA
+    # kernel wins everywhere; up to 32 everywhere but the longest rows (K = 6400, split over a cluster of
+    # eight) and the widest outputs (the head), where its 16-feature tiles read the rows too often; up to
+    # 64 while a block holds the rows unsplit (K up to about a thousand) or the output is narrow and the
+    # weights are small (the MLP's second product at widths 768 and 1024: alone in a chain tcgen05 is
+    # faster there, inside a step it is not)
     if M <= 16:
         mma = True
     elif N > 8192 or M > SKINNY_MAX_ROWS:
         mma = False
+    elif M <= 32:
+        mma = K <= 4096
     else:
-        mma = M <= 32 or K <= 1088 or N * K <= 5_000_000
+        mma = K <= 1088 or (N <= 1024 and N * K <= 5_000_000)
     if mma:
         if norm is not None and M > SKINNY_LN_MAX_ROWS:
             a, norm = norm.materialise(M), None
