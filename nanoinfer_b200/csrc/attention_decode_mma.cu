@@ -63,11 +63,11 @@ __device__ __forceinline__ uint32_t dm_pack(float lo, float hi) {
 // partial layout as in the streaming kernel: o [row][head][split][head_dim], ml [row][head][split][2]
 // (a tile's keys and values are 16 registers per 32 of head size: six blocks an SM up to 64, three beyond)
 // (q, cache and out carry no __restrict__: the kernel ahead writes them; see pdl_wait in common.cuh)
-// RING: a warp's tiles pass through a ring of two stages of its own in shared memory, filled by
-// `cp.async`: two tiles of keys and values are on their way while a third is multiplied, at no cost in
-// registers (a batch of 64 rows has one block per row and head and is bound by how many bytes are in
+// STAGES > 0: a warp's tiles pass through a ring of that many stages of its own in shared memory, filled
+// by `cp.async`: STAGES tiles of keys and values are on their way while another is multiplied, at no cost
+// in registers (a batch of 64 rows has one block per row and head and is bound by how many bytes are in
 // flight; without the ring a warp has one tile's loads, 4 KB, in flight at a time).
-template <int HD, bool RING>
+template <int HD, int STAGES>
 __global__ void __launch_bounds__(DM_WARPS * 32, HD <= 64 ? 6 : 3)
 attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* part_o,
                             float* part_ml, bf16* out, int ldo, const int* __restrict__ block_table,
@@ -76,6 +76,8 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
                             int n_pages, float scale, int window, int chunk, int n_splits,
                             int* counters, int* status, int cluster_merge) {
   constexpr int HALVES = HD / 32;                    // a 16-byte piece per lane covers 32 of a row's values
+  constexpr bool RING = STAGES > 0;
+  constexpr int NS = RING ? STAGES : 1;
   pdl_trigger();
   __shared__ __align__(16) float wo[DM_WARPS][HD];   // the warps' unnormalised outputs
   __shared__ float wm[DM_WARPS], wl[DM_WARPS];
@@ -131,23 +133,23 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
       vb[hh] = ok_b ? *reinterpret_cast<const uint4*>(kr + kv_stride + 8 * HD + hh * 32) : make_uint4(0, 0, 0, 0);
     }
   };
-  // ---- RING: the same tile by asynchronous copies into stage i % 2 of this warp's ring.  A row of
+  // ---- RING: the same tile by asynchronous copies into stage i % STAGES of this warp's ring.  A row of
   // 128 or 256 bytes starts at the same bank as the row before it: odd rows keep their 16-byte pieces
   // four places further (modulo the row), so that a fragment load of eight lanes (two rows, four
   // pieces each) touches every bank once.
   constexpr int PIECES = HD / 8;
   constexpr bool SWZ = HD % 64 == 0;
-  bf16* my_ring = reinterpret_cast<bf16*>(dm_ring) + (size_t)warp * 2 * 2 * 16 * HD;
-  bool stage_ok[2] = {false, false};                 // whether the stage's page is one of the pool's
+  bf16* my_ring = reinterpret_cast<bf16*>(dm_ring) + (size_t)warp * NS * 2 * 16 * HD;
+  uint32_t stage_ok = 0;                             // bit s: the page of stage s is one of the pool's
   auto issue = [&](int i) {
     const int j0 = (first_tile + warp + i * DM_WARPS) << 4;
     const int page = table[j0 / page_size];
     const bool pok = page >= 0 && page < n_pages;
     if (!pok && lane == 0) *status = NIB_STATUS_BAD_PAGE;       // recorded, never followed
-    stage_ok[i & 1] = pok;
+    stage_ok = (stage_ok & ~(1u << (i % NS))) | ((pok ? 1u : 0u) << (i % NS));
     const bf16* src = cache + ((size_t)(pok ? page : 0) * 2 * n_kv_head + hk) * page_size * HD +
                       (size_t)(j0 % page_size) * HD;
-    bf16* dst = my_ring + (size_t)(i & 1) * 2 * 16 * HD;
+    bf16* dst = my_ring + (size_t)(i % NS) * 2 * 16 * HD;
 #pragma unroll
     for (int idx = lane; idx < 16 * PIECES; idx += 32) {
       const int row = idx / PIECES, pc = idx % PIECES;
@@ -161,8 +163,8 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
   };
   // the stage's fragments: this lane's pieces of the rows fr and fr + 8
   auto take = [&](int i) {
-    const bf16* st = my_ring + (size_t)(i & 1) * 2 * 16 * HD;
-    page_ok = stage_ok[i & 1];
+    const bf16* st = my_ring + (size_t)(i % NS) * 2 * 16 * HD;
+    page_ok = (stage_ok >> (i % NS)) & 1u;
 #pragma unroll
     for (int hh = 0; hh < HALVES; ++hh) {
       const int pc = kl + 4 * hh;
@@ -177,14 +179,14 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
   const bool early = n_mine > 0 && (((first_tile + warp) << 4) + 15) < pos;
   int issued = 0;
   if (RING) {
-    while (issued < 2 && issued < n_mine && (((first_tile + warp + issued * DM_WARPS) << 4) + 15) < pos) issue(issued++);
+    while (issued < NS && issued < n_mine && (((first_tile + warp + issued * DM_WARPS) << 4) + 15) < pos) issue(issued++);
   } else if (early) {
     fetch(0);
   }
   pdl_wait();
   if (cluster_merge) cluster_wait();                 // every block of the cluster runs by now
   if (RING) {
-    while (issued < 2 && issued < n_mine) issue(issued++);
+    while (issued < NS && issued < n_mine) issue(issued++);
   }
 
   if (empty) {
@@ -213,7 +215,12 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
 
     for (int i = 0; i < n_mine; ++i) {
       if (RING) {
-        if (i + 1 < issued) cp_async_wait<1>(); else cp_async_wait<0>();   // tile i has landed (i + 1 may be on its way)
+        // tile i has landed (the issued - 1 - i tiles after it may still be on their way)
+        const int behind = issued - 1 - i;
+        if (NS >= 4 && behind >= 3) cp_async_wait<3>();
+        else if (NS >= 3 && behind == 2) cp_async_wait<2>();
+        else if (behind == 1) cp_async_wait<1>();
+        else cp_async_wait<0>();
         __syncwarp();
         take(i);
       } else if (i > 0 || !early) {
@@ -275,7 +282,7 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
                  dm_transpose(vb[hh].w), pb0, pb1);
         }
       }
-      if (RING && issued < n_mine) {                 // the stage that was just used takes the tile after next
+      if (RING && issued < n_mine) {                 // the stage that was just used takes the tile STAGES further on
         __syncwarp();
         issue(issued++);
       }
@@ -388,6 +395,7 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
                                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
                                         int window, int chunk, int n_splits, int* counters, int* status,
                                         int cluster, int ring, cudaStream_t stream) {
+  if (ring != 0 && ring != 2 && ring != 3 && ring != 4) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows <= 0) return 0;
   if (!nib_attention_decode_mma_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -400,12 +408,12 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)n_rows * n_head * n_splits * head_dim : nullptr;
   const dim3 grid(n_splits, n_head, n_rows), block(DM_WARPS * 32);
-  // ring != 0: keys and values pass through two shared-memory stages per warp (two tiles in flight)
-  const size_t ring_bytes = (size_t)DM_WARPS * 2 * 2 * 16 * head_dim * sizeof(bf16);
+  // ring: the number of shared-memory stages per warp that keys and values pass through (2 to 4 tiles in flight; 0: none)
+  const size_t ring_bytes = (size_t)DM_WARPS * ring * 2 * 16 * head_dim * sizeof(bf16);
   cudaError_t e = cudaSuccess;
 #define NIB_DM_LAUNCH_R(HD, RING)                                                                                \
   do {                                                                                                           \
-    if (RING && ring_bytes > 32 * 1024) {  /* (static shared memory counts against the 48 KB default too) */     \
+    if (RING > 0 && ring_bytes > 32 * 1024) {  /* (static shared memory counts against the 48 KB default too) */ \
       static bool attr_set = false;                                                                              \
       if (!attr_set) {                                                                                           \
         e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, RING>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
@@ -414,15 +422,17 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
         attr_set = true;                                                                                         \
       }                                                                                                          \
     }                                                                                                            \
-    e = launch_pdl_cluster(attention_decode_mma_kernel<HD, RING>, grid, block, RING ? ring_bytes : 0, stream,    \
+    e = launch_pdl_cluster(attention_decode_mma_kernel<HD, RING>, grid, block, RING > 0 ? ring_bytes : 0, stream, \
                            cluster ? n_splits : 1, (const bf16*)q, ldq, (const bf16*)cache, part_o, part_ml,     \
                            (bf16*)out, ldo, block_table, max_blocks, rows, row_entry, positions, n_head,         \
                            n_kv_head, page_size, n_pages, scale, window, chunk, n_splits, counters, status,      \
                            cluster ? 1 : 0);                                                                     \
   } while (0)
-#define NIB_DM_LAUNCH(HD)            \
-  if (ring) NIB_DM_LAUNCH_R(HD, true); \
-  else NIB_DM_LAUNCH_R(HD, false)
+#define NIB_DM_LAUNCH(HD)                   \
+  if (ring == 2) NIB_DM_LAUNCH_R(HD, 2);      \
+  else if (ring == 3) NIB_DM_LAUNCH_R(HD, 3); \
+  else if (ring == 4) NIB_DM_LAUNCH_R(HD, 4); \
+  else NIB_DM_LAUNCH_R(HD, 0)
   switch (head_dim) {
     case 32: NIB_DM_LAUNCH(32); break;
     case 64: NIB_DM_LAUNCH(64); break;

@@ -590,12 +590,26 @@ DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
 #: at most) for twice as many splits or more, merged through scratch (measured at 2 K to 16 K keys, batch 1 to 8)
 DECODE_DEEP_KEYS = 512
 
-#: whether the MMA decode attention passes its keys and values through a ring of shared-memory stages
-#: (two tiles in flight per warp), given the launch's rows x heads and its number of splits.  It pays where
-#: the launch fills the device with unsplit rows (measured: -7 to -10 % a step at batch 40 to 64, +3 to
-#: +7 % at batch 1 to 32, where the keys are split and a block's 32 KB of shared memory keep it from
-#: starting beside the kernel ahead)
-DECODE_RING = lambda n_blocks, n_splits: n_splits == 1 and n_blocks >= 440   # noqa: E731
+def decode_ring_stages(n_blocks: int, n_splits: int, head_dim: int) -> int:
+    """How many shared-memory stages per warp the MMA decode attention passes its keys and values through
+    (that many tiles in flight per warp beside the one being multiplied; 0: none, the tiles go through
+    registers).  The ring pays where the launch fills the device with unsplit rows (measured: -7 to -10 %
+    a step at batch 40 to 64, +3 to +7 % at batch 1 to 32, where the keys are split and a block's shared
+    memory keeps it from starting beside the kernel ahead).  It is the deepest of two to four stages that
+    needs no more waves of blocks than two stages do (shared memory sets how many blocks an SM holds: 40 to 48
+    rows of 12 heads take 8 to 9 % less a step with three stages, which still hold them all at once, and
+    so do 64 rows of 16 heads, two full waves of four blocks an SM instead of a full and a thin one of six)."""
+    if n_splits != 1 or n_blocks < 440:
+        return 0
+    stage_bytes = 4 * 2 * 16 * head_dim * 2          # four warps, keys and values of a 16-key tile
+    by_registers = 6 if head_dim <= 64 else 3
+
+    def waves(stages: int) -> int:
+        per_sm = max(1, min(by_registers, (200 * 1024) // (stages * stage_bytes)))
+        return -(-n_blocks // (148 * per_sm))
+
+    return max(st for st in (2, 3, 4) if waves(st) <= waves(2))
+
 
 #: the bfloat16 decode attention on warp-level MMAs where the shape allows (False: always the streaming kernel)
 USE_DECODE_MMA = True
@@ -669,7 +683,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
                                                   head_dim, page_size, n_pages, float(scale), int(window), chunk,
                                                   n_splits, _ptr(counters), _ptr(status),
                                                   int(n_splits in DECODE_CLUSTER_SPLITS),
-                                                  int(DECODE_RING(n_rows * n_head, n_splits)), _stream()),
+                                                  decode_ring_stages(n_rows * n_head, n_splits, head_dim), _stream()),
                "attention_decode_mma")
         return
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),

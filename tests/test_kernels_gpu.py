@@ -278,7 +278,8 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
     scratch = torch.zeros(o.DECODE_RESIDENT_BLOCKS * (hd + 2), device=DEV)
     counters = torch.zeros(o.DECODE_RESIDENT_BLOCKS, dtype=torch.int32, device=DEV)
     if "mma" in kernels:
-        kernels += ["mma, splits in a cluster", "mma, ring", "mma, ring, splits in a cluster"]
+        kernels += ["mma, splits in a cluster", "mma, ring 2", "mma, ring 3", "mma, ring 4", "mma, ring 2, splits in a cluster",
+                    "mma, ring 3, splits in a cluster"]
     for kernel in kernels:
         for ns in (1, 2, 5, 16) if "cluster" not in kernel else (2, 3, 4, 5, 6, 7, 8):
             chunk = max(16, -(-(-(-max_keys // ns)) // 16) * 16)
@@ -293,7 +294,8 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
                     n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, chunk, n_splits, counters.data_ptr(),
                     ctx.status.data_ptr())
             code = lib.nib_attention_decode(dt, *args, stream) if kernel == "streaming" else \
-                lib.nib_attention_decode_mma(*args, int("cluster" in kernel), int("ring" in kernel), stream)
+                lib.nib_attention_decode_mma(*args, int("cluster" in kernel),
+                                             int(kernel.split("ring ")[1][0]) if "ring" in kernel else 0, stream)
             assert code == 0 and int(ctx.status.item()) == 0, (kernel, n_splits)
             diff = (out.cpu().double() - want).abs().max()
             assert diff < tol, f"{kernel}, {n_splits} splits: {float(diff):.3e}"     # (NaN fails here too)
