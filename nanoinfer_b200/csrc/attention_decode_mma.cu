@@ -385,6 +385,33 @@ extern "C" int nib_attention_decode_mma_supported(int head_dim, int page_size) {
          page_size % 16 == 0;
 }
 
+// How many clusters of `cluster` blocks of this kernel (no ring) the device holds at once, as the runtime
+// counts them (a cluster's blocks share a GPC, so it is fewer than blocks an SM x SMs / cluster); 0 if
+// the head size is not taken, a negative CUDA error code if the query fails.
+extern "C" int nib_attention_decode_mma_clusters(int head_dim, int cluster) {
+  if (cluster < 1 || cluster > DM_MAX_CLUSTER) return 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cluster, 1, 4096);
+  cfg.blockDim = dim3(DM_WARPS * 32);
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cluster;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  cudaError_t e = cudaSuccess;
+  switch (head_dim) {
+    case 32: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<32, 0>, &cfg); break;
+    case 64: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<64, 0>, &cfg); break;
+    case 96: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<96, 0>, &cfg); break;
+    case 128: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<128, 0>, &cfg); break;
+    default: return 0;
+  }
+  return e == cudaSuccess ? n : -(int)e;
+}
+
 // Arguments as for nib_attention_decode (bfloat16): scratch holds nib_attention_decode_scratch(...)
 // floats and counters n_rows * n_head zeroed ints when n_splits > 1, unless `cluster` is set: then the
 // 2 to 8 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and the cache layer must be

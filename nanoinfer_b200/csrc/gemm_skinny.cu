@@ -89,7 +89,9 @@ __host__ __device__ inline int skinny_ldx(int k_per) { return k_per + ((32 - k_p
 // 16-byte piece of a weight row feeds two MMAs; since a dot product does not care about the order of
 // its terms, the piece's eight values are dealt to the fragment positions as they come, and the
 // rows' pieces are dealt the same way.
-template <int NT>
+// SHARE: the variant whose blocks share the normalisation of the rows over a cluster (a kernel of its own,
+// so that the others keep the code and the registers they had without it).
+template <int NT, bool SHARE>
 __global__ void __launch_bounds__(SK_WARPS * 32, 2)
 linear_skinny_kernel(const SkinnyParams prm) {
   pdl_trigger();
@@ -97,8 +99,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int M = prm.M, S = prm.split;
   const int rank = S > 1 ? cluster_rank() : 0;
-  const int R = prm.ln_share;                          // blocks that share the normalisation (each its own tiles)
-  const int lrank = R > 1 ? cluster_rank() : 0;
+  const int R = SHARE ? prm.ln_share : 1;              // blocks that share the normalisation (each its own tiles)
+  const int lrank = SHARE ? cluster_rank() : 0;
   const int walker = blockIdx.x / S, n_walkers = gridDim.x / S;
   const int k0 = rank * prm.k_per;                     // this block's slice of K
   const int Ks = min(prm.K - k0, prm.k_per);
@@ -112,7 +114,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // [2][split][rows of a block][16] sums of the other blocks
   float* xch = reinterpret_cast<float*>(sk_smem + (prm.alias ? (xs_bytes > red_bytes ? xs_bytes : red_bytes)
                                                              : xs_bytes + red_bytes));
-  float* ln_gb = xch + (S > 1 ? 2 * NT * 128 : 0);     // [2][K] the norm's scale and shift (no exchange without a split)
+  float* ln_gb = xch + 2 * NT * 128;                   // [2][K] the norm's scale and shift
   const int n_tiles = (prm.N + 15) / 16;
   const int n_steps = (n_chunks + 3) / 4;          // 32-wide steps of the slice
   const int fr = lane >> 2, kl = lane & 3;         // this lane's feature row (and +8) and piece within a step
@@ -196,7 +198,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
     for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
       uint32_t dst[SK_MAX_LN_SHARE];
 #pragma unroll
-      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = r < R ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
+      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
       float sum = 0.0f;
       for (int k = lane * 4; k < K; k += 128) {
@@ -235,7 +237,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
     for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
       uint32_t dst[SK_MAX_LN_SHARE];
 #pragma unroll
-      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = r < R ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
+      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
       // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
       float v[32];
@@ -450,10 +452,11 @@ static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4
 
 static int skinny_ln_share(int M) { return (skinny_tiles(M) * 8 + SK_LN_ROWS_PER_BLOCK - 1) / SK_LN_ROWS_PER_BLOCK; }
 
-static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool exchange, bool alias = false) {
+static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool alias = false) {
   const size_t xs = (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16), red = (size_t)SK_WARPS * NT * 128 * sizeof(float);
-  // (with a split of K: the other blocks' sums; with the norm: its scale and shift, and for wide rows a buffer per warp)
-  return (alias ? (xs > red ? xs : red) : xs + red) + (exchange ? (size_t)2 * NT * 128 * sizeof(float) : 0) +
+  // (the other blocks' sums of a split K, kept without a split too: without them a decode step measured 1 % longer;
+  // with the norm: its scale and shift, and for wide rows a buffer per warp)
+  return (alias ? (xs > red ? xs : red) : xs + red) + (size_t)2 * NT * 128 * sizeof(float) +
          (ln ? (size_t)(2 + (K > SK_LN_REG_WIDTH ? SK_WARPS : 0)) * K * sizeof(float) : 0);
 }
 
@@ -473,18 +476,18 @@ static int skinny_split(int M, int N, int K, bool ln) {
     const int s2 = split * 2, kp = skinny_k_per(K, s2);
     if ((s2 - 1) * kp >= K) break;
     // (rows that leave room for one block per SM only are still better unsplit: measured at 64 rows)
-    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false, split > 1) > SK_SMEM_LIMIT;
+    const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_LIMIT;
     if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 768)) break;
     split = s2;
   }
   return split;
 }
 
-template <int NT>
+template <int NT, bool SHARE>
 static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, SHARE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)SK_SMEM_LIMIT);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -522,7 +525,7 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
       q.dynamicSmemBytes = smem;
       q.attrs = attr + 1;      // the query takes the cluster shape only
       q.numAttrs = 1;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT>, &q);
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT, SHARE>, &q);
       if (e != cudaSuccess) { err = (int)e; return 0; }
       if (n < 1) { err = NIB_ERR_UNSUPPORTED_SIZE; return 0; }
       it = held.emplace(std::make_pair(cluster, smem), n).first;
@@ -534,14 +537,14 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   const bool ln = prm.ln_x != nullptr;
   // (tiles are walked by clusters that split K, or by single blocks: those of a cluster that shares the norm each walk their own)
   const int per_cluster = prm.split > 1 ? 1 : cluster;
-  size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln, prm.split > 1);
+  size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln);
   int cap = clusters_at_once(smem) * per_cluster;
   if (err) return err;
   prm.alias = 0;
   if (n_tiles > cap) {
     // More tiles than one wave of blocks: if a block has one tile only, its warps' sums can lie where
     // the rows were, and the smaller blocks may all fit at once.
-    const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, prm.split > 1, true);
+    const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, true);
     const int cap_one = smem_one < smem ? clusters_at_once(smem_one) * per_cluster : 0;
     if (err) return err;
     if (n_tiles <= cap_one) { prm.alias = 1; smem = smem_one; cap = cap_one; }
@@ -551,7 +554,7 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   const int walkers = ((n_tiles + rounds - 1) / rounds + per_cluster - 1) / per_cluster * per_cluster;
   cfg.dynamicSmemBytes = smem;
   cfg.gridDim = dim3(walkers * prm.split);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT, SHARE>, prm);
   if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();
 }
@@ -565,7 +568,7 @@ extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const 
   if (M < 1 || M > SK_MAX_ROWS || K < 8 || (K & 7) || (ldw & 7) || ((uintptr_t)w & 15)) return 0;
   if (ln && (K > SK_LN_MAX_WIDTH || (K & 3))) return 0;
   const int split = skinny_split(M, 16, K, ln != 0);   // (the split that smem alone asks for)
-  if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0, split > 1) > SK_SMEM_LIMIT) return 0;
+  if (skinny_smem(skinny_tiles(M), skinny_k_per(K, split), K, ln != 0) > SK_SMEM_LIMIT) return 0;
   return 1;
 }
 
@@ -592,7 +595,7 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   if (ln && split != 1) return NIB_ERR_BAD_ARGUMENT;
   const int k_per = skinny_k_per(K, split);
   if ((split - 1) * k_per >= K) return NIB_ERR_BAD_ARGUMENT;   // a block would have nothing
-  if (skinny_smem(skinny_tiles(M), k_per, K, ln, split > 1) > SK_SMEM_LIMIT) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (skinny_smem(skinny_tiles(M), k_per, K, ln) > SK_SMEM_LIMIT) return NIB_ERR_UNSUPPORTED_SIZE;
   SkinnyParams prm;
   prm.a = (const bf16*)a; prm.lda = lda;
   prm.ln_x = ln_x; prm.ln_ldx = ln_ldx; prm.ln_gamma = ln_gamma; prm.ln_beta = ln_beta; prm.ln_rows = ln_rows;
@@ -609,9 +612,9 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   if (ln && ((ln_ldx & 3) || ((uintptr_t)ln_x & 15) || ((uintptr_t)ln_gamma & 15) || ((uintptr_t)ln_beta & 15)))
     return NIB_ERR_UNSUPPORTED_SIZE;
   switch (skinny_tiles(M)) {
-    case 1: return launch_skinny<1>(prm, stream);
-    case 2: return launch_skinny<2>(prm, stream);
-    case 4: return launch_skinny<4>(prm, stream);
-    default: return launch_skinny<8>(prm, stream);
+    case 1: return launch_skinny<1, false>(prm, stream);
+    case 2: return launch_skinny<2, false>(prm, stream);
+    case 4: return prm.ln_share > 1 ? launch_skinny<4, true>(prm, stream) : launch_skinny<4, false>(prm, stream);
+    default: return prm.ln_share > 1 ? launch_skinny<8, true>(prm, stream) : launch_skinny<8, false>(prm, stream);
   }
 }

@@ -60,6 +60,7 @@ _SIGNATURES = {
                              _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                              _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_decode_mma_supported": [_c_int, _c_int],
+    "nib_attention_decode_mma_clusters": [_c_int, _c_int],
     "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                                  _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
                                  _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
@@ -117,7 +118,7 @@ class _Library:
     def _wrap(name, fn):
         counted = name not in ("nib_linear_tc_supported", "nib_linear_tc_pair_supported", "nib_linear_skinny_supported",
                                "nib_attention_prefill_tc_supported", "nib_attention_prefill_supported",
-                               "nib_attention_decode_mma_supported")
+                               "nib_attention_decode_mma_supported", "nib_attention_decode_mma_clusters")
 
         def call(*args):
             global _pending_op
@@ -578,9 +579,23 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
 DECODE_RESIDENT_BLOCKS = 888
 
 
-#: the same bound for the MMA decode attention, whose splits are the blocks of a cluster: clusters do not
-#: pack the last tenth of the device (24 rows of 12 heads take 0.62 ms a step in 2 splits, 0.68 ms in 3)
-DECODE_CLUSTER_BLOCKS = 768
+_cluster_room: dict = {}
+
+
+def decode_cluster_room(head_dim: int, cluster: int) -> int:
+    """How many clusters of ``cluster`` blocks of the MMA decode attention the device holds at once, asked
+    of the runtime once per shape (a cluster's blocks share a GPC: 284 clusters of three, not 296; 142 of
+    six).  The splits of a (row, head) are one cluster, and a launch with a cluster too many waits for a
+    wave to end: 24 rows of 12 heads took 0.68 ms a step in 3 splits and 0.62 ms in 2."""
+    key = (head_dim, cluster)
+    got = _cluster_room.get(key)
+    if got is None:
+        got = int(library().nib_attention_decode_mma_clusters(head_dim, cluster))
+        if got < 0:
+            raise KernelError(f"attention_decode_mma: the occupancy query failed with CUDA error {-got}")
+        _cluster_room[key] = got
+    return got
+
 
 #: numbers of splits that the MMA decode attention runs as one cluster, merging through distributed
 #: shared memory instead of global scratch
@@ -658,16 +673,16 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     mma = USE_DECODE_MMA and q.dtype == torch.bfloat16 and _can("nib_attention_decode_mma_supported", head_dim, page_size) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
-    resident = DECODE_RESIDENT_BLOCKS if not mma else (DECODE_CLUSTER_BLOCKS if head_dim <= 64 else DECODE_CLUSTER_BLOCKS // 2)
+    resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
     # (the MMA kernel merges up to eight splits inside a cluster, which costs two trips to memory less
     # than the merge through scratch: eight splits of twice the keys beat sixteen, until a split has
     # DECODE_DEEP_KEYS keys to walk and the device has room for twice as many splits: a lone row at
     # 16 K keys takes 0.44 ms a step in 72 splits against 0.72 ms in 8)
     at_most = 0
     if mma:
-        at_most = max(DECODE_CLUSTER_SPLITS, default=0)
+        at_most = max([c for c in DECODE_CLUSTER_SPLITS if n_rows * n_head <= decode_cluster_room(head_dim, c)], default=1)
         deep = min(resident // max(1, n_rows * n_head), max_keys // (DECODE_DEEP_KEYS // 2))
-        if deep >= 2 * at_most:
+        if deep >= 2 * max(DECODE_CLUSTER_SPLITS, default=1):
             at_most = deep
     chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident, at_most)
     scratch = counters = None
