@@ -1,4 +1,4 @@
-// out = act(a . w^T + bias) for steps of a few rows (at most 64), in bfloat16, with warp-level MMAs.
+// out = act(a . w^T + bias) for steps of a few rows (at most 128), in bfloat16, with warp-level MMAs.
 //
 // With a few rows the product is a stream of weights with a handful of multiply-adds per weight:
 // the 128-row tcgen05 MMA takes its full 128 cycles however few columns it has, its set-up
@@ -13,7 +13,8 @@
 // Folded in, because each is one round trip less for a decode step:
 //   * the LayerNorm that stands before the product (the rows are normalised into shared memory while
 //     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51).  A
-//     block normalises at most 16 rows: with more, the blocks of a cluster of 2 or 4 share the work,
+//     block normalises at most 16 rows: with more (a block holds up to 32) the two blocks of a cluster share
+//     the work,
 //     each writing its rows into the shared memory of all of them;
 //   * the bias, GELU and residual epilogues (crates/metal/src/shaders/batch.metal:94-97,148-165);
 //   * the write of keys and values into the paged cache for the fused q/k/v projection
@@ -29,12 +30,12 @@
 namespace nib {
 
 constexpr int SK_WARPS = 8;
-constexpr int SK_MAX_ROWS = 64;
+constexpr int SK_MAX_ROWS = 128;
 constexpr int SK_LN_ROWS_PER_BLOCK = 16;   // rows that one block normalises; more are shared out over a cluster
 constexpr int SK_LN_REG_WIDTH = 1024;   // rows up to this wide are normalised in registers ...
 constexpr int SK_LN_MAX_WIDTH = 4096;   // ... wider ones, up to this, in shared memory
 constexpr int SK_MAX_SPLIT = 8;      // blocks of a cluster that split K
-constexpr int SK_MAX_LN_SHARE = 4;   // blocks of a cluster that share the normalisation of the rows
+constexpr int SK_MAX_LN_SHARE = 2;   // blocks of a cluster that share the normalisation of the rows
 
 struct SkinnyParams {
   const bf16* a;        // [M, K] activations (null when ln_x is given)
@@ -52,7 +53,7 @@ struct SkinnyParams {
   int ldo, out_f32, residual, act;
   int M, N, K;
   int split, k_per;     // blocks of a cluster and the slice of K that each takes (a multiple of 32)
-  int ln_share;         // with ln_x: blocks of a cluster that share the normalisation of the rows (1, 2 or 4; split is 1)
+  int ln_share;         // with ln_x: blocks of a cluster that share the normalisation of the rows (1 or 2; split is 1)
   int alias;            // 1: every block has one tile, and the warps' sums take the place of the rows
   // optional: features from kv_q_dim on go to the paged cache
   bf16* kv_cache;
@@ -97,7 +98,10 @@ linear_skinny_kernel(const SkinnyParams prm) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t sk_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int M = prm.M, S = prm.split;
+  // steps of more than 32 rows run as row blocks of 32 (grid y): a block's chain of round trips is that of 32 rows
+  constexpr bool ROW_BLOCKS = NT == 4;
+  const int row0 = ROW_BLOCKS ? blockIdx.y * (NT * 8) : 0;
+  const int M = min(prm.M - row0, NT * 8), S = prm.split;
   const int rank = S > 1 ? cluster_rank() : 0;
   const int R = SHARE ? prm.ln_share : 1;              // blocks that share the normalisation (each its own tiles)
   const int lrank = SHARE ? cluster_rank() : 0;
@@ -144,7 +148,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
   // What the epilogue needs and the kernel ahead does not write: the first tile's bias, and for the
   // cache-writing projection the place of each row's slot (two dependent lookups in the step's
   // tables).  Asked for now, they are there when the sums are; asked for then, each would be a round
-  // trip to L2 at the very end of the chain (at 64 rows: 4 sums a thread, 128 registers, no spills).
+  // trip to L2 at the very end of the chain (at 32 rows: 2 sums a thread).
   constexpr int OUTS = (NT * 128 + SK_WARPS * 32 - 1) / (SK_WARPS * 32);   // sums per thread
   constexpr bool AHEAD = true;
   float bias_r[OUTS];
@@ -159,8 +163,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
       if (o < NT * 128 && m < M) {
         if (prm.bias != nullptr && n < prm.N) bias_r[q] = prm.bias[n];
         if (prm.kv_cache != nullptr) {
-          const int pos = prm.kv_positions[m];
-          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
+          const int pos = prm.kv_positions[row0 + m];
+          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[row0 + m] * prm.kv_max_blocks + pos / prm.kv_page_size];
           kv_base[q] = (page < 0 || page >= prm.kv_n_pages)
                            ? -1
                            : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
@@ -179,7 +183,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
         const int o = threadIdx.x + q * SK_WARPS * 32;
         const int m = o >> 4, n = f0 + (o & 15);
         if (o < NT * 128 && m < M && n < prm.N && (S == 1 || m % S == rank))
-          res_r[q] = ((const float*)prm.out)[(size_t)m * prm.ldo + n];
+          res_r[q] = ((const float*)prm.out)[(size_t)(row0 + m) * prm.ldo + n];
       }
     }
   };
@@ -199,7 +203,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
       uint32_t dst[SK_MAX_LN_SHARE];
 #pragma unroll
       for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
-      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
+      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[row0 + m] : row0 + m) * prm.ln_ldx;
       float sum = 0.0f;
       for (int k = lane * 4; k < K; k += 128) {
         const float4 t = *reinterpret_cast<const float4*>(src + k);
@@ -238,7 +242,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
       uint32_t dst[SK_MAX_LN_SHARE];
 #pragma unroll
       for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
-      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[m] : m) * prm.ln_ldx;
+      const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[row0 + m] : row0 + m) * prm.ln_ldx;
       // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
       float v[32];
       float sum = 0.0f;
@@ -287,11 +291,12 @@ linear_skinny_kernel(const SkinnyParams prm) {
       }
     }
   } else {
-    // asynchronous copies: all of a thread's pieces are in flight at once (with 64 rows the rows are
-    // four times the block's weights, and a loop of loads and stores was a chain of round trips)
+    // asynchronous copies: all of a thread's pieces are in flight at once (a loop of loads and stores
+    // was a chain of round trips; each warp bringing in only the columns of its own steps, and waiting
+    // for those alone, measured the same)
     for (int m = warp; m < M; m += SK_WARPS)
       for (int c = lane; c < n_chunks; c += 32)
-        cp_async16(xs + (size_t)m * ldx + c * 8, prm.a + (size_t)m * prm.lda + k0 + c * 8, true);
+        cp_async16(xs + (size_t)m * ldx + c * 8, prm.a + (size_t)(row0 + m) * prm.lda + k0 + c * 8, true);
     cp_async_commit();
     cp_async_wait<0>();
   }
@@ -424,8 +429,8 @@ linear_skinny_kernel(const SkinnyParams prm) {
         if (AHEAD) {
           base = kv_base[q];
         } else {
-          const int pos = prm.kv_positions[m];
-          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks + pos / prm.kv_page_size];
+          const int pos = prm.kv_positions[row0 + m];
+          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[row0 + m] * prm.kv_max_blocks + pos / prm.kv_page_size];
           base = (page < 0 || page >= prm.kv_n_pages)
                      ? -1
                      : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
@@ -438,17 +443,21 @@ linear_skinny_kernel(const SkinnyParams prm) {
               __float2bfloat16_rn(x);
         }
       } else if (prm.out_f32) {
-        float* dst = (float*)prm.out + (size_t)m * prm.ldo + n;
+        float* dst = (float*)prm.out + (size_t)(row0 + m) * prm.ldo + n;
         *dst = prm.residual ? (AHEAD ? res_r[q] : *dst) + x : x;
       } else {
-        ((bf16*)prm.out)[(size_t)m * prm.ldo + n] = __float2bfloat16_rn(x);
+        ((bf16*)prm.out)[(size_t)(row0 + m) * prm.ldo + n] = __float2bfloat16_rn(x);
       }
     }
   }
   if (S > 1 && round == 0) cluster_wait();   // (a block without a tile still completes the opening barrier)
 }
 
-static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8)); }
+// 8-row MMA tiles a block holds, and the row blocks of 32 that a step of more rows is cut into (grid y):
+// blocks of 64 rows took 6 to 11 us a product where two of 32 rows take 4 to 8 (a decode step of 64
+// rows: -9 % at GPT-2 small's sizes, -16 % at medium's)
+static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : 4); }
+static int skinny_row_blocks(int M) { return (M + 31) / 32; }
 
 static int skinny_ln_share(int M) { return (skinny_tiles(M) * 8 + SK_LN_ROWS_PER_BLOCK - 1) / SK_LN_ROWS_PER_BLOCK; }
 
@@ -538,14 +547,16 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   // (tiles are walked by clusters that split K, or by single blocks: those of a cluster that shares the norm each walk their own)
   const int per_cluster = prm.split > 1 ? 1 : cluster;
   size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln);
-  int cap = clusters_at_once(smem) * per_cluster;
+  const int row_blocks = skinny_row_blocks(prm.M);   // (every walker is there once per row block)
+  auto per_row_block = [&](int c) { const int v = c * per_cluster / row_blocks / per_cluster * per_cluster; return v < per_cluster ? per_cluster : v; };
+  int cap = per_row_block(clusters_at_once(smem));
   if (err) return err;
   prm.alias = 0;
   if (n_tiles > cap) {
     // More tiles than one wave of blocks: if a block has one tile only, its warps' sums can lie where
     // the rows were, and the smaller blocks may all fit at once.
     const size_t smem_one = skinny_smem(NT, prm.k_per, prm.K, ln, true);
-    const int cap_one = smem_one < smem ? clusters_at_once(smem_one) * per_cluster : 0;
+    const int cap_one = smem_one < smem ? per_row_block(clusters_at_once(smem_one)) : 0;
     if (err) return err;
     if (n_tiles <= cap_one) { prm.alias = 1; smem = smem_one; cap = cap_one; }
   }
@@ -553,7 +564,7 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   const int rounds = (n_tiles + cap - 1) / cap;
   const int walkers = ((n_tiles + rounds - 1) / rounds + per_cluster - 1) / per_cluster * per_cluster;
   cfg.dynamicSmemBytes = smem;
-  cfg.gridDim = dim3(walkers * prm.split);
+  cfg.gridDim = dim3(walkers * prm.split, row_blocks);
   cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT, SHARE>, prm);
   if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();
@@ -572,7 +583,7 @@ extern "C" int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const 
   return 1;
 }
 
-// The product for steps of at most 64 rows (bfloat16 weights and activations; out bfloat16 or
+// The product for steps of at most 128 rows (bfloat16 weights and activations; out bfloat16 or
 // float32).  Options as for nib_linear_tc_small: ln_x != null folds the LayerNorm before the product
 // in (`a` ignored); cache != null sends the features from q_dim on to the paged
 // cache.  split: blocks of a cluster that split K (0: chosen here; 1, 2, 4 or 8).
@@ -614,7 +625,6 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   switch (skinny_tiles(M)) {
     case 1: return launch_skinny<1, false>(prm, stream);
     case 2: return launch_skinny<2, false>(prm, stream);
-    case 4: return prm.ln_share > 1 ? launch_skinny<4, true>(prm, stream) : launch_skinny<4, false>(prm, stream);
-    default: return prm.ln_share > 1 ? launch_skinny<8, true>(prm, stream) : launch_skinny<8, false>(prm, stream);
+    default: return prm.ln_share > 1 ? launch_skinny<4, true>(prm, stream) : launch_skinny<4, false>(prm, stream);
   }
 }

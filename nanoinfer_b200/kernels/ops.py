@@ -401,12 +401,12 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
     return a is not None or norm is not None
 
 
-SKINNY_MAX_ROWS = 64
+SKINNY_MAX_ROWS = 128
 #: most rows of a step for which the dispatcher lets the few-row kernel normalise the rows itself.  Beyond 16
-#: rows the blocks of a cluster share that work: with 2 blocks (17 to 32 rows) a decode step of GPT-2 small
-#: or medium is 4 to 6 % shorter than with the norm as a kernel of its own; with 4 blocks (33 to 64 rows)
-#: it is 1 to 2 % shorter at 40 to 48 rows and 4 % longer at 64
-SKINNY_LN_MAX_ROWS = 32
+#: rows the two blocks of a cluster share that work (a block holds up to 32 rows; steps of more run as row
+#: blocks of 32): 24 launches fewer, and a step of GPT-2 small or medium at 17 to 128 rows is up to 6 %
+#: shorter than with the norm as a kernel of its own
+SKINNY_LN_MAX_ROWS = 128
 PAIR_MIN_ROWS = 256      # the pair kernel's smallest step
 
 
@@ -419,7 +419,7 @@ def pair_pays(M: int, N: int, K: int) -> bool:
 
 
 def linear_skinny(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=None, split=0) -> bool:
-    """The warp-level MMA kernel for steps of at most 64 rows (bfloat16): every SM streams weight
+    """The warp-level MMA kernel for steps of at most 128 rows (bfloat16): every SM streams weight
     rows, a few multiply-adds per weight.  ``norm``: the LayerNorm before the product, folded in; ``kv``: (cache layer, block table, row_entry, positions, q_dim) sends keys and
     values straight to the cache; ``split``: blocks of a cluster that split K (0: chosen by the
     library).  False if the kernel does not apply."""
@@ -465,26 +465,28 @@ def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=N
     return True
 
 
+def skinny_pays(M: int, N: int, K: int) -> bool:
+    """Whether a product of at most 128 rows goes to the warp-level MMA kernel rather than to tcgen05.
+    Measured in whole decode steps at widths 768, 1024 and 1600 (batch 16 to 64): up to 16 rows the MMA
+    kernel wins everywhere; beyond that everywhere but the longest rows (K = 6400, which a block of 32 rows
+    cannot hold unsplit: split over a cluster of eight it takes 22 us against 14) and the widest outputs
+    (the head), where its 16-feature tiles read the rows too often."""
+    if M <= 16:
+        return True
+    if N > 8192 or M > SKINNY_MAX_ROWS:
+        return False
+    # (65 to 128 rows, four row blocks: a step of one 80- to 128-token prompt takes 0.71 to 0.76 ms against 1.05 to
+    # 1.35 ms at GPT-2 small's sizes, 1.56 to 1.89 against 2.21 to 2.68 at medium's, 5.6 against 5.3 at XL's)
+    return K <= (4096 if M <= 64 else 1088)
+
+
 def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
-    """Steps of at most 128 rows: up to 64 rows the warp-level MMA kernel (with the
-    LayerNorm folded in), beyond that tcgen05.  Folding the norm into the tcgen05 kernel, or splitting
+    """Steps of at most 128 rows: the warp-level MMA kernel (with the LayerNorm folded in) where
+    ``skinny_pays``, else tcgen05.  Folding the norm into the tcgen05 kernel, or splitting
     K through scratch, costs more round trips than it saves at these sizes, so that kernel is given
     normed rows and is not split here."""
     N, K = w.shape
-    # measured in whole decode steps at widths 768, 1024 and 1600 (batch 16 to 64): up to 16 rows the MMA
-    # kernel wins everywhere; up to 32 everywhere but the longest rows (K = 6400, split over a cluster of
-    # eight) and the widest outputs (the head), where its 16-feature tiles read the rows too often; up to
-    # 64 while a block holds the rows unsplit (K up to about a thousand) or the output is narrow and the
-    # weights are small (the MLP's second product at widths 768 and 1024: alone in a chain tcgen05 is
-    # faster there, inside a step it is not)
-    if M <= 16:
-        mma = True
-    elif N > 8192 or M > SKINNY_MAX_ROWS:
-        mma = False
-    elif M <= 32:
-        mma = K <= 4096
-    else:
-        mma = K <= 1088 or (N <= 1024 and N * K <= 5_000_000)
+    mma = skinny_pays(M, N, K)
     if mma:
         if norm is not None and M > SKINNY_LN_MAX_ROWS:
             a, norm = norm.materialise(M), None

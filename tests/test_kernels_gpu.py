@@ -492,7 +492,9 @@ SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (6
                 (16, 768, 3072), (5, 50257, 64), (8, 4800, 1600), (13, 200, 2048), (3, 96, 1104),
                 # 17 to 64 rows: with the norm folded in, clusters of 2 and 4 blocks share its work
                 (24, 2304, 768), (32, 3072, 768), (64, 2304, 768), (50, 3072, 1024), (20, 4800, 1600), (40, 96, 768),
-                (17, 1000, 1104)]
+                (17, 1000, 1104),
+                # 65 to 128 rows: the few-row kernel in row blocks of 32
+                (100, 2304, 768), (128, 768, 768), (96, 3072, 1024), (65, 70, 768)]
 
 
 @pytest.mark.parametrize("M, N, K", SMALL_SHAPES)
@@ -560,7 +562,7 @@ def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, k
 
 
 @pytest.mark.parametrize("M, N, K", [(17, 96, 768), (32, 2304, 768), (33, 70, 1024), (64, 3072, 768), (64, 130, 264),
-                                     (28, 400, 1600)])
+                                     (28, 400, 1600), (100, 2304, 768), (128, 96, 1024), (65, 768, 768)])
 def test_few_row_product_with_the_norm_shared_by_a_cluster_gives_each_row_its_own_bits(M, N, K):
     """Beyond 16 rows the blocks of a cluster normalise the rows between them and write them into each
     other's shared memory: a row's results are the bits it gets in a step of its own, whichever block
@@ -581,7 +583,7 @@ def test_few_row_product_with_the_norm_shared_by_a_cluster_gives_each_row_its_ow
     xn = P.layernorm(x.double(), gamma.double(), beta.double(), 1e-5)[rows.long()].to(torch.bfloat16)
     y = xn.double() @ w.double().T + b.double()
     assert (out.cpu().double() - y).abs().max() < 1.5e-2 * max(1.0, float(y.abs().max()))
-    for m in sorted({0, 1, 15, 16, M // 2, M - 2, M - 1}):
+    for m in sorted(m for m in {0, 1, 15, 16, 31, 32, M // 2, M - 2, M - 1} if m < M):
         alone = torch.zeros(1, N, dtype=torch.bfloat16, device=DEV)
         one = o.NormInput(xd, gd, bed, 1e-5, ws, torch.bfloat16, rows=rd[m:m + 1].contiguous())
         assert o.linear_skinny(None, one, wd, bd, alone, 1)
@@ -590,7 +592,7 @@ def test_few_row_product_with_the_norm_shared_by_a_cluster_gives_each_row_its_ow
 
 
 SPLIT_SHAPES = [(1, 96, 768), (8, 768, 3072), (16, 768, 768), (20, 100, 1000), (33, 70, 3072), (64, 1000, 264),
-                (64, 768, 3072), (48, 2304, 768)]
+                (64, 768, 3072), (48, 2304, 768), (80, 768, 3072), (128, 100, 1000)]
 
 
 @pytest.mark.parametrize("M, N, K", SPLIT_SHAPES)
@@ -615,7 +617,7 @@ def test_few_row_product_with_k_split_over_a_cluster(M, N, K, split):
             o.linear_skinny(ad, None, wd, bd, out, M, split=split)
         return
     # the step's rows of a block's slice of K must fit in shared memory: else the kernel declines
-    row_tiles = 1 if M <= 8 else 2 if M <= 16 else 4 if M <= 32 else 8
+    row_tiles = 1 if M <= 8 else 2 if M <= 16 else 4      # (more than 32 rows: row blocks of 32)
     pitch = k_per + ((32 - k_per % 64) + 64) % 64
     if split and row_tiles * 8 * pitch * 2 + 10 * row_tiles * 128 * 4 > 200 * 1024:
         out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
