@@ -124,9 +124,6 @@ __device__ __forceinline__ uint32_t cluster_load(uint32_t addr) {
 __device__ __forceinline__ void cluster_store(uint32_t addr, uint32_t v) {
   asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
-__device__ __forceinline__ void cluster_store2(uint32_t addr, uint32_t v0, uint32_t v1) {
-  asm volatile("st.shared::cluster.v2.u32 [%0], {%1, %2};" ::"r"(addr), "r"(v0), "r"(v1) : "memory");
-}
 __device__ __forceinline__ uint32_t cluster_atomic_add(uint32_t addr, uint32_t v) {
   uint32_t old;
   asm volatile("atom.shared::cluster.add.u32 %0, [%1], %2;" : "=r"(old) : "r"(addr), "r"(v) : "memory");

@@ -12,10 +12,7 @@
 //
 // Folded in, because each is one round trip less for a decode step:
 //   * the LayerNorm that stands before the product (the rows are normalised into shared memory while
-//     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51).  A
-//     block normalises at most 16 rows: with more (a block holds up to 32) the two blocks of a cluster share
-//     the work,
-//     each writing its rows into the shared memory of all of them;
+//     the first weights are on their way; formula of crates/core/src/kernels/reference.rs:42-51);
 //   * the bias, GELU and residual epilogues (crates/metal/src/shaders/batch.metal:94-97,148-165);
 //   * the write of keys and values into the paged cache for the fused q/k/v projection
 //     (batch.metal:155-164).
@@ -30,12 +27,10 @@
 namespace nib {
 
 constexpr int SK_WARPS = 8;
-constexpr int SK_MAX_ROWS = 128;
-constexpr int SK_LN_ROWS_PER_BLOCK = 16;   // rows that one block normalises; more are shared out over a cluster
+constexpr int SK_MAX_ROWS = 256;
 constexpr int SK_LN_REG_WIDTH = 1024;   // rows up to this wide are normalised in registers ...
 constexpr int SK_LN_MAX_WIDTH = 4096;   // ... wider ones, up to this, in shared memory
 constexpr int SK_MAX_SPLIT = 8;      // blocks of a cluster that split K
-constexpr int SK_MAX_LN_SHARE = 2;   // blocks of a cluster that share the normalisation of the rows
 
 struct SkinnyParams {
   const bf16* a;        // [M, K] activations (null when ln_x is given)
@@ -53,7 +48,6 @@ struct SkinnyParams {
   int ldo, out_f32, residual, act;
   int M, N, K;
   int split, k_per;     // blocks of a cluster and the slice of K that each takes (a multiple of 32)
-  int ln_share;         // with ln_x: blocks of a cluster that share the normalisation of the rows (1 or 2; split is 1)
   int alias;            // 1: every block has one tile, and the warps' sums take the place of the rows
   // optional: features from kv_q_dim on go to the paged cache
   bf16* kv_cache;
@@ -90,21 +84,17 @@ __host__ __device__ inline int skinny_ldx(int k_per) { return k_per + ((32 - k_p
 // 16-byte piece of a weight row feeds two MMAs; since a dot product does not care about the order of
 // its terms, the piece's eight values are dealt to the fragment positions as they come, and the
 // rows' pieces are dealt the same way.
-// SHARE: the variant whose blocks share the normalisation of the rows over a cluster (a kernel of its own,
-// so that the others keep the code and the registers they had without it).
-template <int NT, bool SHARE>
+template <int NT>
 __global__ void __launch_bounds__(SK_WARPS * 32, 2)
 linear_skinny_kernel(const SkinnyParams prm) {
   pdl_trigger();
   extern __shared__ __align__(16) uint8_t sk_smem[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // steps of more than 32 rows run as row blocks of 32 (grid y): a block's chain of round trips is that of 32 rows
-  constexpr bool ROW_BLOCKS = NT == 4;
-  const int row0 = ROW_BLOCKS ? blockIdx.y * (NT * 8) : 0;
+  // A block holds at most 16 rows; a step of more runs as row blocks of 16 (grid y), every block with its
+  // own copy of the chain weights -> rows -> products -> sums -> epilogue, which grows with the rows it holds.
+  const int row0 = blockIdx.y * (NT * 8);
   const int M = min(prm.M - row0, NT * 8), S = prm.split;
   const int rank = S > 1 ? cluster_rank() : 0;
-  const int R = SHARE ? prm.ln_share : 1;              // blocks that share the normalisation (each its own tiles)
-  const int lrank = SHARE ? cluster_rank() : 0;
   const int walker = blockIdx.x / S, n_walkers = gridDim.x / S;
   const int k0 = rank * prm.k_per;                     // this block's slice of K
   const int Ks = min(prm.K - k0, prm.k_per);
@@ -173,7 +163,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
       }
     }
   }
-  if (S > 1 || R > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
+  if (S > 1) cluster_arrive();   // met before the first exchange: by then every block of the cluster runs
   pdl_wait();
   // the residual stream's old values, asked for as early as the kernel ahead allows
   auto fetch_residual = [&](int f0) {
@@ -196,13 +186,9 @@ linear_skinny_kernel(const SkinnyParams prm) {
     // Rows too wide for a lane's registers: a warp brings its row into a buffer of its own in shared
     // memory (summing on the way) and makes the other two passes there.
     __syncthreads();   // the norm's parameters are in place
-    if (R > 1) cluster_wait();
     const int K = prm.K;
     float* mine = ln_gb + 2 * K + (size_t)warp * K;
-    for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
-      uint32_t dst[SK_MAX_LN_SHARE];
-#pragma unroll
-      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
+    for (int m = warp; m < M; m += SK_WARPS) {
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[row0 + m] : row0 + m) * prm.ln_ldx;
       float sum = 0.0f;
       for (int k = lane * 4; k < K; k += 128) {
@@ -225,23 +211,13 @@ linear_skinny_kernel(const SkinnyParams prm) {
         uint2 packed;
         packed.x = pack2((t.x - mean) * rstd * g.x + b.x, (t.y - mean) * rstd * g.y + b.y);
         packed.y = pack2((t.z - mean) * rstd * g.z + b.z, (t.w - mean) * rstd * g.w + b.w);
-        if (R == 1) *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
-        else {
-#pragma unroll
-          for (int r = 0; r < SK_MAX_LN_SHARE; ++r)
-            if (r < R) cluster_store2(dst[r] + k * 2, packed.x, packed.y);
-        }
+        *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
       }
     }
   } else if (prm.ln_x != nullptr) {
     __syncthreads();   // the norm's parameters are in place
-    if (R > 1) cluster_wait();
     const int K = prm.K;
-    // (with a cluster: block b takes rows b, b + R, ..., and writes them into every block's shared memory)
-    for (int m = lrank + R * warp; m < M; m += R * SK_WARPS) {
-      uint32_t dst[SK_MAX_LN_SHARE];
-#pragma unroll
-      for (int r = 0; r < SK_MAX_LN_SHARE; ++r) dst[r] = (SHARE && r < R) ? cluster_addr(xs + (size_t)m * ldx, r) : 0;
+    for (int m = warp; m < M; m += SK_WARPS) {
       const float* src = prm.ln_x + (size_t)(prm.ln_rows ? prm.ln_rows[row0 + m] : row0 + m) * prm.ln_ldx;
       // one read of the row into registers (K <= 1024: 32 floats a lane), then two passes on them
       float v[32];
@@ -281,12 +257,7 @@ linear_skinny_kernel(const SkinnyParams prm) {
           uint2 packed;
           packed.x = *reinterpret_cast<uint32_t*>(&lo);
           packed.y = *reinterpret_cast<uint32_t*>(&hi);
-          if (R == 1) *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
-          else {
-#pragma unroll
-            for (int r = 0; r < SK_MAX_LN_SHARE; ++r)
-              if (r < R) cluster_store2(dst[r] + k * 2, packed.x, packed.y);
-          }
+          *reinterpret_cast<uint2*>(xs + (size_t)m * ldx + k) = packed;
         }
       }
     }
@@ -299,10 +270,6 @@ linear_skinny_kernel(const SkinnyParams prm) {
         cp_async16(xs + (size_t)m * ldx + c * 8, prm.a + (size_t)(row0 + m) * prm.lda + k0 + c * 8, true);
     cp_async_commit();
     cp_async_wait<0>();
-  }
-  if (R > 1) {   // every block's rows have arrived in this block's shared memory
-    cluster_arrive();
-    cluster_wait();
   }
   __syncthreads();
 
@@ -453,13 +420,12 @@ linear_skinny_kernel(const SkinnyParams prm) {
   if (S > 1 && round == 0) cluster_wait();   // (a block without a tile still completes the opening barrier)
 }
 
-// 8-row MMA tiles a block holds, and the row blocks of 32 that a step of more rows is cut into (grid y):
-// blocks of 64 rows took 6 to 11 us a product where two of 32 rows take 4 to 8 (a decode step of 64
-// rows: -9 % at GPT-2 small's sizes, -16 % at medium's)
-static int skinny_tiles(int M) { return M <= 8 ? 1 : (M <= 16 ? 2 : 4); }
-static int skinny_row_blocks(int M) { return (M + 31) / 32; }
-
-static int skinny_ln_share(int M) { return (skinny_tiles(M) * 8 + SK_LN_ROWS_PER_BLOCK - 1) / SK_LN_ROWS_PER_BLOCK; }
+// 8-row MMA tiles a block holds (one or two), and the row blocks of 16 that a step of more rows is cut into
+// (grid y).  Measured in whole decode steps against blocks of 32 and of 64 rows: 24 to 64 rows of GPT-2
+// small take 8 to 12 % less a step in blocks of 16 than in blocks of 32, which took 9 % less than blocks of
+// 64 at 64 rows; blocks of 8 are slower again from 12 rows on.
+static int skinny_tiles(int M) { return M <= 8 ? 1 : 2; }
+static int skinny_row_blocks(int M) { const int r = skinny_tiles(M) * 8; return (M + r - 1) / r; }
 
 static size_t skinny_smem(int NT, int k_per, int K, bool ln, bool alias = false) {
   const size_t xs = (size_t)NT * 8 * skinny_ldx(k_per) * sizeof(bf16), red = (size_t)SK_WARPS * NT * 128 * sizeof(float);
@@ -492,11 +458,11 @@ static int skinny_split(int M, int N, int K, bool ln) {
   return split;
 }
 
-template <int NT, bool SHARE>
+template <int NT>
 static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, SHARE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)SK_SMEM_LIMIT);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
@@ -508,8 +474,7 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   attr[1].id = cudaLaunchAttributeClusterDimension;
-  // a cluster is the blocks that split K, or (with the norm folded in, K unsplit) those that share the rows' normalisation
-  const int cluster = prm.split > 1 ? prm.split : prm.ln_share;
+  const int cluster = prm.split;   // the blocks that split K
   attr[1].val.clusterDim.x = cluster;
   attr[1].val.clusterDim.y = 1;
   attr[1].val.clusterDim.z = 1;
@@ -534,7 +499,7 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
       q.dynamicSmemBytes = smem;
       q.attrs = attr + 1;      // the query takes the cluster shape only
       q.numAttrs = 1;
-      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT, SHARE>, &q);
+      cudaError_t e = cudaOccupancyMaxActiveClusters(&n, linear_skinny_kernel<NT>, &q);
       if (e != cudaSuccess) { err = (int)e; return 0; }
       if (n < 1) { err = NIB_ERR_UNSUPPORTED_SIZE; return 0; }
       it = held.emplace(std::make_pair(cluster, smem), n).first;
@@ -544,11 +509,9 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
   };
   const int n_tiles = (prm.N + 15) / 16;
   const bool ln = prm.ln_x != nullptr;
-  // (tiles are walked by clusters that split K, or by single blocks: those of a cluster that shares the norm each walk their own)
-  const int per_cluster = prm.split > 1 ? 1 : cluster;
   size_t smem = skinny_smem(NT, prm.k_per, prm.K, ln);
   const int row_blocks = skinny_row_blocks(prm.M);   // (every walker is there once per row block)
-  auto per_row_block = [&](int c) { const int v = c * per_cluster / row_blocks / per_cluster * per_cluster; return v < per_cluster ? per_cluster : v; };
+  auto per_row_block = [&](int c) { return c / row_blocks > 0 ? c / row_blocks : 1; };
   int cap = per_row_block(clusters_at_once(smem));
   if (err) return err;
   prm.alias = 0;
@@ -560,12 +523,12 @@ static int launch_skinny(SkinnyParams prm, cudaStream_t stream) {
     if (err) return err;
     if (n_tiles <= cap_one) { prm.alias = 1; smem = smem_one; cap = cap_one; }
   }
-  // as few walkers as finish in the same number of rounds (whole clusters: a block without a tile still normalises its rows)
+  // as few walkers as finish in the same number of rounds
   const int rounds = (n_tiles + cap - 1) / cap;
-  const int walkers = ((n_tiles + rounds - 1) / rounds + per_cluster - 1) / per_cluster * per_cluster;
+  const int walkers = (n_tiles + rounds - 1) / rounds;
   cfg.dynamicSmemBytes = smem;
   cfg.gridDim = dim3(walkers * prm.split, row_blocks);
-  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT, SHARE>, prm);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, linear_skinny_kernel<NT>, prm);
   if (e != cudaSuccess) return (int)e;
   NIB_LAUNCH_CHECK();
 }
@@ -614,7 +577,6 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   prm.w = (const bf16*)w; prm.ldw = ldw; prm.bias = bias; prm.out = out; prm.ldo = ldo;
   prm.out_f32 = out_dtype == DT_F32; prm.residual = residual; prm.act = act;
   prm.M = M; prm.N = N; prm.K = K; prm.split = split; prm.k_per = k_per;
-  prm.ln_share = ln ? skinny_ln_share(M) : 1;
   prm.kv_cache = (bf16*)cache; prm.kv_block_table = block_table; prm.kv_row_entry = row_entry;
   prm.kv_positions = positions; prm.kv_max_blocks = max_blocks; prm.kv_q_dim = q_dim; prm.kv_heads = n_kv_head;
   prm.kv_head_dim = head_dim; prm.kv_page_size = page_size; prm.kv_n_pages = n_pages;
@@ -623,8 +585,7 @@ extern "C" int nib_linear_skinny(int out_dtype, const void* a, int lda, const vo
   if (ln && ((ln_ldx & 3) || ((uintptr_t)ln_x & 15) || ((uintptr_t)ln_gamma & 15) || ((uintptr_t)ln_beta & 15)))
     return NIB_ERR_UNSUPPORTED_SIZE;
   switch (skinny_tiles(M)) {
-    case 1: return launch_skinny<1, false>(prm, stream);
-    case 2: return launch_skinny<2, false>(prm, stream);
-    default: return prm.ln_share > 1 ? launch_skinny<4, true>(prm, stream) : launch_skinny<4, false>(prm, stream);
+    case 1: return launch_skinny<1>(prm, stream);
+    default: return launch_skinny<2>(prm, stream);
   }
 }

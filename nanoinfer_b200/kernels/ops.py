@@ -402,10 +402,8 @@ def _small_inputs_ok(a, norm, w, out) -> bool:
 
 
 SKINNY_MAX_ROWS = 128
-#: most rows of a step for which the dispatcher lets the few-row kernel normalise the rows itself.  Beyond 16
-#: rows the two blocks of a cluster share that work (a block holds up to 32 rows; steps of more run as row
-#: blocks of 32): 24 launches fewer, and a step of GPT-2 small or medium at 17 to 128 rows is up to 6 %
-#: shorter than with the norm as a kernel of its own
+#: most rows of a step for which the dispatcher lets the few-row kernel normalise the rows itself (every
+#: row block of 16 its own rows: 24 launches fewer than with the norm as a kernel of its own)
 SKINNY_LN_MAX_ROWS = 128
 PAIR_MIN_ROWS = 256      # the pair kernel's smallest step
 
@@ -465,6 +463,10 @@ def linear_small_tc(a, norm, w, bias, out, M, act=ACT_NONE, residual=False, kv=N
     return True
 
 
+#: most rows for which the tcgen05 kernel writes keys and values from its epilogue (its swapped orientation)
+TC_KV_EPILOGUE_MAX_ROWS = 16
+
+
 def skinny_pays(M: int, N: int, K: int) -> bool:
     """Whether a product of at most 128 rows goes to the warp-level MMA kernel rather than to tcgen05.
     Measured in whole decode steps at widths 768, 1024 and 1600 (batch 16 to 64): up to 16 rows the MMA
@@ -475,9 +477,9 @@ def skinny_pays(M: int, N: int, K: int) -> bool:
         return True
     if N > 8192 or M > SKINNY_MAX_ROWS:
         return False
-    # (65 to 128 rows, four row blocks: a step of one 80- to 128-token prompt takes 0.71 to 0.76 ms against 1.05 to
-    # 1.35 ms at GPT-2 small's sizes, 1.56 to 1.89 against 2.21 to 2.68 at medium's, 5.6 against 5.3 at XL's)
-    return K <= (4096 if M <= 64 else 1088)
+    # (33 to 128 rows: while a row block holds its rows unsplit, K up to about a thousand.  The MLP's second
+    # product at GPT-2 medium's sizes, K = 4096, on tcgen05 instead: a decode step of 64 rows 1.17 against 1.37 ms)
+    return K <= (4096 if M <= 32 else 1088)
 
 
 def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
@@ -496,7 +498,7 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
             a, norm = norm.materialise(M), None
             if linear_skinny(a, None, w, bias, out, M, act, residual, kv):
                 return True
-    if M > SMALL_STEP_MAX_ROWS or kv is None:
+    if M > TC_KV_EPILOGUE_MAX_ROWS or kv is None:
         return False          # the plain tensor-core call does as well
     if norm is not None:
         a, norm = norm.materialise(M), None

@@ -490,10 +490,10 @@ def test_fused_qkv_projection_writes_queries_and_cache(M, n_head, n_kv_head, hd)
 
 SMALL_SHAPES = [(1, 96, 768), (8, 2304, 768), (8, 3072, 768), (37, 70, 3072), (64, 1000, 120), (128, 257, 64),
                 (16, 768, 3072), (5, 50257, 64), (8, 4800, 1600), (13, 200, 2048), (3, 96, 1104),
-                # 17 to 64 rows: with the norm folded in, clusters of 2 and 4 blocks share its work
+                # 17 to 64 rows: row blocks of 16, the norm folded into each
                 (24, 2304, 768), (32, 3072, 768), (64, 2304, 768), (50, 3072, 1024), (20, 4800, 1600), (40, 96, 768),
                 (17, 1000, 1104),
-                # 65 to 128 rows: the few-row kernel in row blocks of 32
+                # 65 to 128 rows: up to eight row blocks
                 (100, 2304, 768), (128, 768, 768), (96, 3072, 1024), (65, 70, 768)]
 
 
@@ -563,10 +563,9 @@ def test_small_step_product_with_folded_layernorm_and_split_k(M, N, K, folded, k
 
 @pytest.mark.parametrize("M, N, K", [(17, 96, 768), (32, 2304, 768), (33, 70, 1024), (64, 3072, 768), (64, 130, 264),
                                      (28, 400, 1600), (100, 2304, 768), (128, 96, 1024), (65, 768, 768)])
-def test_few_row_product_with_the_norm_shared_by_a_cluster_gives_each_row_its_own_bits(M, N, K):
-    """Beyond 16 rows the blocks of a cluster normalise the rows between them and write them into each
-    other's shared memory: a row's results are the bits it gets in a step of its own, whichever block
-    normalised it, and blocks of the cluster that have no tile of features still do their share."""
+def test_few_row_product_in_row_blocks_gives_each_row_its_own_bits(M, N, K):
+    """Beyond 16 rows the step is cut into row blocks of 16, each normalising its own rows: a row's
+    results are the bits it gets in a step of its own, whichever block it falls into."""
     o = ops()
     from nanoinfer_b200.parts.base import Workspace
     g = gen(7 * M + N + K)
@@ -617,7 +616,7 @@ def test_few_row_product_with_k_split_over_a_cluster(M, N, K, split):
             o.linear_skinny(ad, None, wd, bd, out, M, split=split)
         return
     # the step's rows of a block's slice of K must fit in shared memory: else the kernel declines
-    row_tiles = 1 if M <= 8 else 2 if M <= 16 else 4      # (more than 32 rows: row blocks of 32)
+    row_tiles = 1 if M <= 8 else 2                        # (more than 16 rows: row blocks of 16)
     pitch = k_per + ((32 - k_per % 64) + 64) % 64
     if split and row_tiles * 8 * pitch * 2 + 10 * row_tiles * 128 * 4 > 200 * 1024:
         out = torch.zeros(M, N, dtype=torch.bfloat16, device=DEV)
