@@ -4,6 +4,7 @@
     python -m nanoinfer_b200 --weights DIR generate --prompt-ids 464,3616 --tokens 40
     python -m nanoinfer_b200 --weights DIR bench --tokens 64 --prompt-len 64 --batch 1,8,64
     python -m nanoinfer_b200 --weights DIR serve-bench --requests 128 --max-batch 32
+    python -m nanoinfer_b200 --weights DIR tokenize "Hello world"
     python -m nanoinfer_b200 random-weights --config gpt2-small --seed 1 --out DIR
 
 ``--weights`` is the reference's global option (main.rs:30-32): the folder with
@@ -55,6 +56,22 @@ def cmd_random_weights(args) -> int:
     from .measure import parameter_count_of_spec
     n_params = parameter_count_of_spec(Model(get_architecture(cfg.architecture).build_spec(cfg), cfg))
     print(f"wrote {args.out} ({n_params / 1e6:.1f}M params, {args.dtype}, seed {args.seed})", file=sys.stderr)
+    return 0
+
+
+def cmd_tokenize(args) -> int:
+    """The reference's ``tokenize TEXT`` (crates/cli/src/main.rs:81-82, 121-128): each id with its piece, then
+    the count; needs no GPU."""
+    from .tokenizer import Tokenizer, TokenizerError
+    try:
+        tok = Tokenizer.from_folder(args.weights)
+    except TokenizerError as e:
+        print(str(e), file=sys.stderr)
+        return 2
+    ids = tok.encode(args.text)
+    for i in ids:
+        print(f"{i:>6}  {tok.decode([i])!r}")
+    print(f"{len(ids)} tokens")
     return 0
 
 
@@ -212,6 +229,10 @@ def main(argv=None) -> int:
     s.add_argument("--summary", default=None, help="write the full summary (JSON) to this file")
     s.add_argument("--note", default="")
     s.set_defaults(fn=cmd_serve_bench)
+
+    t = sub.add_parser("tokenize", help="print the token ids of a text (needs vocab.json and merges.txt in the folder)")
+    t.add_argument("text")
+    t.set_defaults(fn=cmd_tokenize)
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     r.add_argument("--config", required=True, help="a preset name (gpt2-small, gpt2-medium, gpt2-xl, "

@@ -67,3 +67,15 @@ def test_byte_tokenizer_for_random_models(tmp_path):
     assert json.load(open(tmp_path / "vocab.json", encoding="utf-8"))["Ġ"] == 32
     with pytest.raises(TokenizerError, match="at least 257"):
         write_byte_tokenizer(str(tmp_path), 200)
+
+
+def test_command_line_tokenize_prints_ids_and_pieces(tmp_path, capsys):
+    """``tokenize TEXT`` as the reference prints it: an id and its piece per line, then the count."""
+    from nanoinfer_b200.cli import main
+    from nanoinfer_b200.tokenizer import write_byte_tokenizer
+    write_byte_tokenizer(str(tmp_path), 300)
+    assert main(["--weights", str(tmp_path), "tokenize", "Hi!"]) == 0
+    lines = capsys.readouterr().out.strip().splitlines()
+    assert lines[-1] == "3 tokens" and len(lines) == 4
+    assert [line.split()[1] for line in lines[:3]] == ["'H'", "'i'", "'!'"]
+    assert main(["--weights", str(tmp_path / "nothing"), "tokenize", "Hi"]) == 2
