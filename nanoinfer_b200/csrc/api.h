@@ -69,8 +69,8 @@ int nib_linear_tc_pair(int out_dtype, const void* a, int lda, const void* w, int
                        int q_dim, int n_kv_head, int head_dim, int page_size, int n_pages, int* status,
                        cudaStream_t stream);
 
-// The product for steps of at most 64 rows with warp-level MMAs (bfloat16), with the same LayerNorm
-// (at most 16 rows) and cache options as nib_linear_tc_small.  split: blocks of a cluster that split
+// The product for steps of at most 128 rows with warp-level MMAs (bfloat16; row blocks of 16), with the same
+// LayerNorm and cache options as nib_linear_tc_small.  split: blocks of a cluster that split
 // K (0: chosen by the library; else 1, 2, 4 or 8).
 int nib_linear_skinny_supported(int M, int K, int ldw, int ln, const void* w);
 int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int ldw, const float* bias, void* out,

@@ -452,7 +452,6 @@ static int skinny_split(int M, int N, int K, bool ln) {
   while (split < SK_MAX_SPLIT) {
     const int s2 = split * 2, kp = skinny_k_per(K, s2);
     if ((s2 - 1) * kp >= K) break;
-    // (rows that leave room for one block per SM only are still better unsplit: measured at 64 rows)
     const bool too_big = skinny_smem(NT, skinny_k_per(K, split), K, false) > SK_SMEM_LIMIT;
     if (!too_big && (n_tiles * s2 > 2 * 148 || kp < 768)) break;
     split = s2;

@@ -7,9 +7,10 @@
 // out = a . w^T is the reference's matmul (crates/core/src/kernels/reference.rs:26-37).  The tile
 // that feeds the MMA's M side ("P", 128 rows) and the one that feeds its N side ("Q", 16..256
 // rows) are interchangeable:
-//   * many rows (prefill): P = activations, Q = weights;
-//   * few rows (decode):   P = weights, Q = activations ("swap-AB"), so a step of 1..128 tokens
-//     still fills the 128-row MMA and every weight byte is read exactly once.
+//   * P = activations, Q = weights: from 17 rows on (one padded row tile up to 128 rows);
+//   * P = weights, Q = activations ("swap-AB"): every weight byte is read exactly once and the few
+//     rows still fill the 128-row MMA; for at most 16 rows, for the options below, and up to 128
+//     rows where the 128-feature tiles alone fill the device (the head).
 //
 // One CTA computes one P x Q tile: warp 0 issues the TMA loads, warp 1 allocates tensor memory
 // and issues the MMAs, warps 2..5 run the epilogue (each owns the 32 TMEM lanes of its quarter).
