@@ -405,6 +405,8 @@ SKINNY_MAX_ROWS = 128
 #: most rows of a step for which the dispatcher lets the few-row kernel normalise the rows itself (every
 #: row block of 16 its own rows: 24 launches fewer than with the norm as a kernel of its own)
 SKINNY_LN_MAX_ROWS = 128
+#: widest row that the few-row kernel normalises in a lane's registers
+SKINNY_LN_REGISTER_WIDTH = 1024
 PAIR_MIN_ROWS = 256      # the pair kernel's smallest step
 
 
@@ -490,7 +492,10 @@ def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
     N, K = w.shape
     mma = skinny_pays(M, N, K)
     if mma:
-        if norm is not None and M > SKINNY_LN_MAX_ROWS:
+        # (rows wider than SKINNY_LN_REGISTER_WIDTH are normalised through a buffer per warp in shared memory, which
+        # leaves room for one block an SM from 9 rows on: GPT-2 XL at batch 12 to 32 is 2 to 7 % faster with the
+        # norm as a kernel of its own there)
+        if norm is not None and (M > SKINNY_LN_MAX_ROWS or (K > SKINNY_LN_REGISTER_WIDTH and M > 8)):
             a, norm = norm.materialise(M), None
         if linear_skinny(a, norm, w, bias, out, M, act, residual, kv):
             return True
