@@ -482,8 +482,30 @@ extern "C" int nib_sample(const float* logits, int ld, int n_rows, int V, const 
   // teams != 0: some rows may be sampled, and the launch is made of clusters of SAMPLE_TEAM blocks
   // (a greedy row does not care); a launch of greedy rows only needs no clusters
   static_assert(SAMPLE_CHUNKS % SAMPLE_TEAM == 0, "a row's grid line is whole clusters");
-  // (only while all of them fit on the device at once: more rows are better off one block each)
-  const int team = (teams && n_rows * SAMPLE_TEAM <= 128) ? SAMPLE_TEAM : 1;
+  // (the largest of 8, 4 and 2 blocks with which all rows' teams are on the device at once, as the runtime
+  // counts clusters of that size: a team too many waits for a wave to end; beyond that a row is one block's work)
+  int team = 1;
+  if (teams) {
+    static int room[SAMPLE_TEAM + 1] = {};     // clusters of t blocks that the device holds at once (0: not asked yet)
+    for (int t = SAMPLE_TEAM; t > 1; t /= 2) {
+      if (room[t] == 0) {
+        cudaLaunchConfig_t q = {};
+        q.gridDim = dim3(t, 148);
+        q.blockDim = dim3(SAMPLE_THREADS);
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = t;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        q.attrs = attr;
+        q.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, sample_kernel, &q) != cudaSuccess || n < 1) n = -1;
+        room[t] = n;
+      }
+      if (n_rows <= room[t]) { team = t; break; }
+    }
+  }
   // Blocks per row: as many as keep the grid within one wave (a block of 1024 threads has an SM to
   // itself), at most SAMPLE_CHUNKS, and whole clusters where there are teams.
   int chunks = SAMPLE_CHUNKS;
