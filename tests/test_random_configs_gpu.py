@@ -3,7 +3,8 @@ function against the plain implementation, in 32-bit and in bfloat16.
 
 Every size is drawn anew per case (head sizes in steps of 16 up to 128, one to seven heads, one to
 three layers, an inner width that is no multiple of the width, vocabularies that are no power of two,
-the norm's eps, the activation, tied or untied head, the per-layer score scale), the pool holds about
+the norm's eps, the activation, tied or untied head, the per-layer score scale, pages of 16 to 64
+positions), the pool holds about
 60 % of the pages that all requests of a case would need at once, and each step takes a random
 portion (1 to 400 tokens) of a random subset of the live requests and asks for the logits at random
 places.  The seeds are fixed; a failure names the case."""
@@ -65,9 +66,10 @@ def test_random_configuration_cut_at_random(case, dtype, tmp_path):
     lens = [rnd.randint(2, limit) for _ in range(rnd.randint(2, 6))]
     toks = [[rnd.randrange(vocab) for _ in range(n)] for n in lens]
     want = [plain.logits(t).float() for t in toks]
-    pages_of = lambda n: -(-n // 16)
+    page = rnd.choice([16, 32, 48, 64])
+    pages_of = lambda n: -(-n // page)
     pages = max(max(pages_of(n) for n in lens) + 2, int(0.6 * sum(pages_of(n) for n in lens)))
-    cache = CacheManager(model.kv_needs(), model.state_needs(), max_tokens=pages * 16, max_requests=4, page_size=16,
+    cache = CacheManager(model.kv_needs(), model.state_needs(), max_tokens=pages * page, max_requests=4, page_size=page,
                          dtype=torch_dtype, device=torch.device("cuda"), max_positions=model.max_positions)
     runner = ModelRunner(model, cache, max_rows=rnd.choice([64, 200, 512]), max_entries=4)
     pending, live, checked = list(range(len(lens))), {}, 0
