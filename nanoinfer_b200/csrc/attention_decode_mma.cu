@@ -30,7 +30,7 @@
 namespace nib {
 
 constexpr int DM_WARPS = 4;
-constexpr int DM_MAX_CLUSTER = 8;   // the portable cluster size
+constexpr int DM_MAX_CLUSTER = 16;  // (beyond the portable 8 the kernel is marked as taking non-portable cluster sizes)
 
 __device__ __forceinline__ void dm_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                        uint32_t b1) {
@@ -402,19 +402,25 @@ extern "C" int nib_attention_decode_mma_clusters(int head_dim, int cluster) {
   cfg.numAttrs = 1;
   int n = 0;
   cudaError_t e = cudaSuccess;
+#define NIB_DM_ROOM(HD)                                                                                              \
+  do {                                                                                                               \
+    e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, 0>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1); \
+    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<HD, 0>, &cfg);          \
+  } while (0)
   switch (head_dim) {
-    case 32: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<32, 0>, &cfg); break;
-    case 64: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<64, 0>, &cfg); break;
-    case 96: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<96, 0>, &cfg); break;
-    case 128: e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<128, 0>, &cfg); break;
+    case 32: NIB_DM_ROOM(32); break;
+    case 64: NIB_DM_ROOM(64); break;
+    case 96: NIB_DM_ROOM(96); break;
+    case 128: NIB_DM_ROOM(128); break;
     default: return 0;
   }
+#undef NIB_DM_ROOM
   return e == cudaSuccess ? n : -(int)e;
 }
 
 // Arguments as for nib_attention_decode (bfloat16): scratch holds nib_attention_decode_scratch(...)
 // floats and counters n_rows * n_head zeroed ints when n_splits > 1, unless `cluster` is set: then the
-// 2 to 8 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and the cache layer must be
+// 2 to 16 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and the cache layer must be
 // 16-byte aligned with row strides that are multiples of 8 values.
 extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cache, float* scratch, void* out,
                                         int ldo, const int* block_table, int max_blocks, const int* rows,
@@ -429,8 +435,8 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (n_rows > 65535 || n_head > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   if (((uintptr_t)q & 15) || ((uintptr_t)cache & 15) || (ldq & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
-  // cluster != 0: the splits of a (row, head) are one cluster and merge inside it (2 to 8 splits)
-  if (cluster && (n_splits < 2 || n_splits > DM_MAX_CLUSTER)) return NIB_ERR_BAD_ARGUMENT;
+  // cluster != 0: the splits of a (row, head) are one cluster and merge inside it (2 to 16 splits; beyond 8 without a ring)
+  if (cluster && (n_splits < 2 || n_splits > DM_MAX_CLUSTER || (n_splits > 8 && ring != 0))) return NIB_ERR_BAD_ARGUMENT;
   if (n_splits > 1 && !cluster && (scratch == nullptr || counters == nullptr)) return NIB_ERR_BAD_ARGUMENT;
   float* part_o = scratch;
   float* part_ml = scratch ? scratch + (size_t)n_rows * n_head * n_splits * head_dim : nullptr;
@@ -447,6 +453,14 @@ extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cach
                                  (int)ring_bytes);                                                               \
         if (e != cudaSuccess) return (int)e;                                                                     \
         attr_set = true;                                                                                         \
+      }                                                                                                          \
+    }                                                                                                            \
+    if (cluster && n_splits > 8) {  /* (more blocks than the portable cluster size) */                          \
+      static bool wide_set = false;                                                                              \
+      if (!wide_set) {                                                                                           \
+        e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, RING>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1); \
+        if (e != cudaSuccess) return (int)e;                                                                     \
+        wide_set = true;                                                                                         \
       }                                                                                                          \
     }                                                                                                            \
     e = launch_pdl_cluster(attention_decode_mma_kernel<HD, RING>, grid, block, RING > 0 ? ring_bytes : 0, stream, \

@@ -606,13 +606,18 @@ def decode_cluster_room(head_dim: int, cluster: int) -> int:
     return got
 
 
-#: numbers of splits that the MMA decode attention runs as one cluster, merging through distributed
-#: shared memory instead of global scratch
-DECODE_CLUSTER_SPLITS = (2, 3, 4, 5, 6, 7, 8)
+#: numbers of splits that the MMA decode attention runs as one cluster, merging through distributed shared
+#: memory instead of global scratch (beyond 8 blocks the cluster size is "non-portable": the kernel is marked
+#: as taking it; a lone row at 4,096 keys: 0.331 -> 0.308 ms a step with 16 splits of 256 keys, at 1,024 keys
+#: 0.250 -> 0.245 with 16 of 64, one tile a warp)
+DECODE_CLUSTER_SPLITS = tuple(range(2, 17))
 
-#: keys per split from which the MMA decode attention gives up the merge inside a cluster (eight splits
-#: at most) for twice as many splits or more, merged through scratch (measured at 2 K to 16 K keys, batch 1 to 8)
+#: keys per split from which the MMA decode attention gives up the merge inside a cluster for more splits
+#: than a cluster holds, merged through scratch (measured at 2 K to 16 K keys, batch 1 to 8: four rows at
+#: 16 K keys take 0.67 ms a step in 18 splits through scratch and 0.90 ms in a cluster of 14) ...
 DECODE_DEEP_KEYS = 512
+#: ... and the fewest such splits: one more than the largest cluster
+DECODE_DEEP_SPLITS = 17
 
 def decode_ring_stages(n_blocks: int, n_splits: int, head_dim: int) -> int:
     """How many shared-memory stages per warp the MMA decode attention passes its keys and values through
@@ -683,15 +688,15 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
     resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
-    # (the MMA kernel merges up to eight splits inside a cluster, which costs two trips to memory less
-    # than the merge through scratch: eight splits of twice the keys beat sixteen, until a split has
-    # DECODE_DEEP_KEYS keys to walk and the device has room for twice as many splits: a lone row at
-    # 16 K keys takes 0.44 ms a step in 72 splits against 0.72 ms in 8)
+    # (the MMA kernel merges up to sixteen splits inside a cluster, which costs two trips to memory less
+    # than the merge through scratch, until a split has DECODE_DEEP_KEYS keys to walk and the device has
+    # room for more splits than a cluster holds: a lone row at 16 K keys takes 0.44 ms a step in 64 splits
+    # against 0.72 ms in 8)
     at_most = 0
     if mma:
         at_most = max([c for c in DECODE_CLUSTER_SPLITS if n_rows * n_head <= decode_cluster_room(head_dim, c)], default=1)
         deep = min(resident // max(1, n_rows * n_head), max_keys // (DECODE_DEEP_KEYS // 2))
-        if deep >= 2 * max(DECODE_CLUSTER_SPLITS, default=1):
+        if deep >= DECODE_DEEP_SPLITS:
             at_most = deep
     chunk, n_splits = decode_split(n_rows, n_head, max_keys, resident, at_most)
     scratch = counters = None

@@ -281,14 +281,14 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
         kernels += ["mma, splits in a cluster", "mma, ring 2", "mma, ring 3", "mma, ring 4", "mma, ring 2, splits in a cluster",
                     "mma, ring 3, splits in a cluster"]
     for kernel in kernels:
-        for ns in (1, 2, 5, 16) if "cluster" not in kernel else (2, 3, 4, 5, 6, 7, 8):
+        for ns in (1, 2, 5, 16) if "cluster" not in kernel else (2, 3, 4, 5, 6, 7, 8, 11, 16):
             chunk = max(16, -(-(-(-max_keys // ns)) // 16) * 16)
             n_splits = -(-max_keys // chunk)
             if n_rows * n_head * n_splits > o.DECODE_RESIDENT_BLOCKS:
                 continue
             out = torch.full_like(q, 7.0)
-            if "cluster" in kernel and not 2 <= n_splits <= 8:
-                continue
+            if "cluster" in kernel and not 2 <= n_splits <= (8 if "ring" in kernel else 16):
+                continue                     # (beyond the portable cluster size of 8 there is no ring)
             args = (q.data_ptr(), q.stride(0), cache.data_ptr(), scratch.data_ptr(), out.data_ptr(), out.stride(0),
                     table.data_ptr(), table.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), n_rows,
                     n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, chunk, n_splits, counters.data_ptr(),
