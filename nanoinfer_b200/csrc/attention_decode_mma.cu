@@ -404,8 +404,12 @@ extern "C" int nib_attention_decode_mma_clusters(int head_dim, int cluster) {
   cudaError_t e = cudaSuccess;
 #define NIB_DM_ROOM(HD)                                                                                              \
   do {                                                                                                               \
-    e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, 0>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1); \
-    if (e == cudaSuccess) e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<HD, 0>, &cfg);          \
+    if (cluster > 8) {  /* a device or driver that does not take the larger sizes holds none of them */            \
+      e = cudaFuncSetAttribute(attention_decode_mma_kernel<HD, 0>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1); \
+      if (e != cudaSuccess) { (void)cudaGetLastError(); return 0; }                                                 \
+    }                                                                                                                \
+    e = cudaOccupancyMaxActiveClusters(&n, attention_decode_mma_kernel<HD, 0>, &cfg);                                \
+    if (e != cudaSuccess && cluster > 8) { (void)cudaGetLastError(); return 0; }                                     \
   } while (0)
   switch (head_dim) {
     case 32: NIB_DM_ROOM(32); break;
@@ -420,8 +424,8 @@ extern "C" int nib_attention_decode_mma_clusters(int head_dim, int cluster) {
 
 // Arguments as for nib_attention_decode (bfloat16): scratch holds nib_attention_decode_scratch(...)
 // floats and counters n_rows * n_head zeroed ints when n_splits > 1, unless `cluster` is set: then the
-// 2 to 16 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and the cache layer must be
-// 16-byte aligned with row strides that are multiples of 8 values.
+// 2 to 16 splits of a (row, head) run as one cluster and merge through distributed shared memory.  q, out and
+// the cache layer must be 16-byte aligned with row strides that are multiples of 8 values.
 extern "C" int nib_attention_decode_mma(const void* q, int ldq, const void* cache, float* scratch, void* out,
                                         int ldo, const int* block_table, int max_blocks, const int* rows,
                                         const int* row_entry, const int* positions, int n_rows, int n_head,
