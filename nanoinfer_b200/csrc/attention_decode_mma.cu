@@ -85,8 +85,10 @@ attention_decode_mma_kernel(const bf16* q, int ldq, const bf16* cache, float* pa
   // When the splits of a (row, head) are the blocks of one cluster (at most eight), they hand their
   // results to the first of them through distributed shared memory instead of through global scratch,
   // an arrival counter and a second read: two trips to memory less at the end of the chain.
-  __shared__ __align__(16) float xo[DM_MAX_CLUSTER][HD];
-  __shared__ float xml[DM_MAX_CLUSTER][2];
+  // (the ring's variants keep to the portable eight: with sixteen rows here six blocks of them no longer fit an SM)
+  constexpr int XC = RING ? 8 : DM_MAX_CLUSTER;
+  __shared__ __align__(16) float xo[XC][HD];
+  __shared__ float xml[XC][2];
   extern __shared__ __align__(16) uint8_t dm_ring[]; // RING: [warp][stage][keys | values][16 rows][HD]
   if (cluster_merge) cluster_arrive();               // met below, before the first store into another block
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
