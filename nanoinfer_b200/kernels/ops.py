@@ -472,16 +472,18 @@ TC_KV_EPILOGUE_MAX_ROWS = 16
 def skinny_pays(M: int, N: int, K: int) -> bool:
     """Whether a product of at most 128 rows goes to the warp-level MMA kernel rather than to tcgen05.
     Measured in whole decode steps at widths 768, 1024 and 1600 (batch 16 to 64): up to 16 rows the MMA
-    kernel wins everywhere; beyond that everywhere but the longest rows (K = 6400, which a block of 32 rows
-    cannot hold unsplit: split over a cluster of eight it takes 22 us against 14) and the widest outputs
-    (the head), where its 16-feature tiles read the rows too often."""
+    kernel wins everywhere; up to 32 rows everywhere but the longest rows (K of 4096 and more, split over a
+    cluster: GPT-2 medium's second MLP product at 32 rows is 4 % of a step slower here, XL's 20 %) and the
+    widest outputs (the head), where its 16-feature tiles read the rows too often; beyond 32 rows while a row
+    block holds its rows unsplit.  Flipping one product's choice at a time at 24 to 128 rows and three widths
+    moves a step by less than 5 % where the other choice is better and by up to 97 % where it is worse."""
     if M <= 16:
         return True
     if N > 8192 or M > SKINNY_MAX_ROWS:
         return False
     # (33 to 128 rows: while a row block holds its rows unsplit, K up to about a thousand.  The MLP's second
     # product at GPT-2 medium's sizes, K = 4096, on tcgen05 instead: a decode step of 64 rows 1.17 against 1.37 ms)
-    return K <= (4096 if M <= 32 else 1088)
+    return K <= (3072 if M <= 32 else 1088)
 
 
 def _linear_small(a, norm, w, bias, out, M, act, residual, kv=None) -> bool:
