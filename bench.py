@@ -21,7 +21,9 @@ One JSON line is printed.  A "step" is one decode step of the whole batch.
              time per output token, pages, bytes the steps had to read over the memory's rate); with
              ``--preset gpt2-xl`` decode at batch 1, 8 and 64 with prompts of 512 tokens and 256 new
              ones, and the pages they fill of the pool; with the default preset the same layers
-             with 8,192 positions, decoding at batch 1, 8 and 32 behind prompts of 8,144 tokens.
+             with 8,192 positions, decoding at batch 1, 8 and 32 behind prompts of 8,144 tokens, and 512
+             requests arriving at 400 a second (prompts and outputs of 16 to 256 tokens, temperature 0.8)
+             through static and continuous batching.
   provenance the commit, whether the tree was clean, the tools, the device, the time.
 Peaks come from MEASURED_PEAKS.json beside this file when present, else from the fallback
 figures (6.65 TB/s, 1.59 PFLOP/s).  More than one GPU is out of scope: --gpus N>1 says so and
@@ -134,6 +136,14 @@ def main() -> int:
             far = bs.decode_points(far_dir, "bfloat16", [1, 8, 32], 8192 - 48, 32, warmup=6, runs=2)
             workloads["context_8192"] = {f"b{p['batch']}": {k: p[k] for k in (
                 "decode_tok_s", "decode_ms_per_step", "frac_of_hbm", "prefill_tok_s", "prefill_ms")} for p in far}
+            # requests arriving at a steady rate (the reference's serving workload, crates/cli/src/metal_serve.rs:97-131:
+            # prompts and outputs of 16 to 256 tokens), continuous against static batching
+            from nanoinfer_b200.serve_bench import run_serving
+            s = run_serving(model_dir, "bfloat16", requests=512, max_batch=64, prompt_min=16, prompt_max=256, out_min=16,
+                            out_max=256, rate=400.0, prefill_budget=2048, temperature=0.8, top_k=40, seed=7, quiet=True)
+            workloads["arrivals_400_a_second_t0.8"] = {
+                p["policy"]: {k: p[k] for k in ("throughput_tok_s", "generated_tokens", "makespan_s", "iterations",
+                                                "ttft_ms", "tpot_ms", "kv_pages_peak", "preemptions")} for p in s["policies"]}
         if args.preset == "gpt2-medium":
             from nanoinfer_b200.serve_bench import run_serving
             # (at most 2,048 prompt tokens a step, the engine's own default: with 512 the same requests take 0.57 s

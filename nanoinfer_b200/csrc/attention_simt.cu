@@ -29,6 +29,7 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
   const int h = blockIdx.x * ATT_WARPS + warp;
   const int t = rows ? rows[blockIdx.y] : blockIdx.y;
   if (h >= n_head) return;  // whole warps leave; no block-wide barrier follows
+  if (row_entry[t] < 0) return;   // a row of no request (padding): nothing to attend to
   float* qs = smem + (size_t)warp * (head_dim + 32 + 64);
   float* pj = qs + head_dim;                                   // 32 probabilities
   unsigned long long* voff = (unsigned long long*)(pj + 32);   // 32 value-row offsets (8-byte aligned)

@@ -129,8 +129,10 @@ __global__ void kv_append_kernel(const T* src, int ld, int k_off, int v_off,
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x;
+  const int entry = row_entry[t];
+  if (entry < 0) return;   // a row of no request (padding): nothing to keep
   const int pos = positions[t];
-  const int page = block_table[(size_t)row_entry[t] * max_blocks + pos / page_size];
+  const int page = block_table[(size_t)entry * max_blocks + pos / page_size];
   if (page < 0 || page >= n_pages) {
     if (threadIdx.x == 0) *status = NIB_STATUS_BAD_PAGE;
     return;
@@ -159,8 +161,10 @@ kv_append_pieces_kernel(const T* src, int ld, int k_off, int v_off, T* cache,
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const int t = (int)(idx / per_row), piece = (int)(idx - (long long)t * per_row);
   if (t >= n_rows) return;   // (exiting counts as having waited)
+  const int entry = row_entry[t];
+  if (entry < 0) return;     // a row of no request (padding): nothing to keep
   const int pos = positions[t];
-  const int page = block_table[(size_t)row_entry[t] * max_blocks + pos / page_size];
+  const int page = block_table[(size_t)entry * max_blocks + pos / page_size];
   pdl_wait();
   if (page < 0 || page >= n_pages) {
     *status = NIB_STATUS_BAD_PAGE;

@@ -156,8 +156,10 @@ linear_skinny_kernel(const SkinnyParams prm) {
         if (prm.bias != nullptr && n < prm.N) bias_r[q] = prm.bias[n];
         if (prm.kv_cache != nullptr) {
           const int pos = prm.kv_positions[row0 + m];
-          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[row0 + m] * prm.kv_max_blocks + pos / prm.kv_page_size];
-          kv_base[q] = (page < 0 || page >= prm.kv_n_pages)
+          const int entry = prm.kv_row_entry[row0 + m];   // (negative: a row of no request, whose keys and values are dropped)
+          const int page = entry < 0 ? 0 : prm.kv_block_table[(size_t)entry * prm.kv_max_blocks + pos / prm.kv_page_size];
+          kv_base[q] = entry < 0 ? -2
+                       : (page < 0 || page >= prm.kv_n_pages)
                            ? -1
                            : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
                                                   prm.kv_head_dim);
@@ -399,13 +401,17 @@ linear_skinny_kernel(const SkinnyParams prm) {
           base = kv_base[q];
         } else {
           const int pos = prm.kv_positions[row0 + m];
-          const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[row0 + m] * prm.kv_max_blocks + pos / prm.kv_page_size];
-          base = (page < 0 || page >= prm.kv_n_pages)
+          const int entry = prm.kv_row_entry[row0 + m];
+          const int page = entry < 0 ? 0 : prm.kv_block_table[(size_t)entry * prm.kv_max_blocks + pos / prm.kv_page_size];
+          base = entry < 0 ? -2
+                 : (page < 0 || page >= prm.kv_n_pages)
                      ? -1
                      : (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size,
                                             prm.kv_head_dim);
         }
-        if (base < 0) {
+        if (base == -2) {
+          // (a row of no request)
+        } else if (base < 0) {
           *prm.status = NIB_STATUS_BAD_PAGE;
         } else {   // from (page, K, head 0, slot): K|V and the head are whole strides further
           prm.kv_cache[base + ((long long)which * prm.kv_heads + head) * prm.kv_page_size * prm.kv_head_dim + d] =

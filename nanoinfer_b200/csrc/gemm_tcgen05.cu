@@ -462,9 +462,12 @@ linear_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constan
             } else if (m < prm.q_rows && p_ok) {
               if (to_cache) {
                 const int pos = prm.kv_positions[m];
-                const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[m] * prm.kv_max_blocks +
-                                                    pos / prm.kv_page_size];
-                if (page < 0 || page >= prm.kv_n_pages) {
+                const int entry = prm.kv_row_entry[m];
+                const int page = entry < 0 ? 0 : prm.kv_block_table[(size_t)entry * prm.kv_max_blocks +
+                                                                    pos / prm.kv_page_size];
+                if (entry < 0) {
+                  // (a row of no request: its keys and values are dropped)
+                } else if (page < 0 || page >= prm.kv_n_pages) {
                   *prm.status = NIB_STATUS_BAD_PAGE;
                 } else {
                   prm.kv_cache[kv_offset(page, kv_which, kv_head, pos % prm.kv_page_size, prm.kv_heads,

@@ -223,8 +223,10 @@ linear_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
     const bool kv_tile = prm.kv_cache != nullptr && q0 + bq > prm.kv_q_dim;
     if (kv_tile && p0 + pl < prm.M) {
       const int pos = prm.kv_positions[p0 + pl];
-      const int page = prm.kv_block_table[(size_t)prm.kv_row_entry[p0 + pl] * prm.kv_max_blocks + pos / prm.kv_page_size];
-      if (page < 0 || page >= prm.kv_n_pages) *prm.status = NIB_STATUS_BAD_PAGE;
+      const int entry = prm.kv_row_entry[p0 + pl];   // (negative: a row of no request, whose keys and values are dropped)
+      const int page = entry < 0 ? 0 : prm.kv_block_table[(size_t)entry * prm.kv_max_blocks + pos / prm.kv_page_size];
+      if (entry < 0) {}
+      else if (page < 0 || page >= prm.kv_n_pages) *prm.status = NIB_STATUS_BAD_PAGE;
       else kv_base = (long long)kv_offset(page, 0, 0, pos % prm.kv_page_size, prm.kv_heads, prm.kv_page_size, prm.kv_head_dim);
     }
     if (lane == 0) epi_ok_sh[quarter] = mbar_wait(&tmem_full_bar, 0, abort_flag) ? 1 : 0;

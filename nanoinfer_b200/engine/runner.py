@@ -91,6 +91,10 @@ class _Captured:
 
 #: batches of more than PAD_FROM single tokens are padded to a multiple of PAD_TO rows
 PAD_FROM, PAD_TO = 8, 8
+#: a step that carries prompt portions is filled up to a multiple of this many rows with rows of no
+#: request (entry -1: no keys or values kept, no attention, nobody's logits), so that steps which differ
+#: by a few tokens share a graph: a prompt of 70 tokens and one of 80 are both a step of 80 rows
+PAD_ROWS_TO = 16
 
 
 class ModelRunner:
@@ -137,6 +141,8 @@ class ModelRunner:
         self.steps_run = 0
         self.graph_replays = 0
         self.padded_steps = 0
+        #: steps with prompt portions that were filled up with rows of no request
+        self.row_padded_steps = 0
         self.last_meta_bytes = 0
         self.last_logit_slot = None
         #: kernel launches of the last step (counted by the kernel interface)
@@ -302,7 +308,15 @@ class ModelRunner:
                 slots.append(it.request.slot)
                 max_q, max_kv = max(max_q, n), max(max_kv, p0 + n)
             plans, plan_words = self._plans(starts, pos0s)
+            n_real = T
+            if self.use_graphs:
+                T = min(-(-T // PAD_ROWS_TO) * PAD_ROWS_TO, self.max_rows)
             lay = self._layout(T, E, M, len(plan_words))
+            if T > n_real:                      # rows of no request behind the last entry's
+                buf[lay.tok + n_real:lay.tok + T] = 0
+                buf[lay.pos + n_real:lay.pos + T] = 0
+                buf[lay.ent + n_real:lay.ent + T] = -1
+                self.row_padded_steps += 1
             lrow = lay.lrow
             for e, it in enumerate(items):
                 a, n, p0 = starts[e], len(it.tokens), pos0s[e]
@@ -353,11 +367,12 @@ class ModelRunner:
             args = self._context(lay, plans, starts, pos0s, slots, max_q, max_kv, sampler)
             n_seen = self._seen.get(key, 0) if key is not None else 0
             # A shape that was run already (scratch is sized, attributes are set) is captured: a batch
-            # of single tokens the second time it comes, since it will come again step after step; a
-            # step with prompt portions the fourth time only (most such shapes of a serving mix come
+            # of single tokens the second time it comes, since it will come again step after step, and so
+            # a lone prompt portion (filled up to 16 rows, its shape is one of a few dozen); other steps
+            # with prompt portions the fourth time only (most such shapes of a serving mix come
             # once or twice, and a capture costs about two uncaptured steps).  The new graph takes the
             # place of the one that has not been used for the longest time if the table is full.
-            if key is not None and n_seen >= (1 if decode_only else 3):
+            if key is not None and n_seen >= (1 if decode_only or E == 1 else 3):
                 while len(self._graphs) >= self.max_graphs:
                     del self._graphs[next(iter(self._graphs))]
                 graph = torch.cuda.CUDAGraph()

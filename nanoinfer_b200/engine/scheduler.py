@@ -96,6 +96,10 @@ class SchedulerStats:
     peak_pages: int = 0
 
 
+#: the longest lone prompt portion that runs as a step of its own (see ``Scheduler.portions_alone``)
+PORTION_ALONE_MAX_ROWS = 256
+
+
 class Scheduler:
     def __init__(self, cache: CacheManager, max_batch: int = 64, max_rows: int = 2048,
                  prefill_budget: int = 2048, headroom_pages: int = 1, max_positions: Optional[int] = None):
@@ -110,6 +114,13 @@ class Scheduler:
         self._order = itertools.count()
         #: called with (request) after a slot was given to it, so that per-slot state can be set
         self.on_admit = None
+        #: A lone short prompt portion beside decoded tokens runs as a step of its own, by turns with the
+        #: decoded tokens (never two such steps in a row while tokens wait to be decoded).  The engine sets
+        #: this where steps replay as graphs: a step of decoded tokens alone replays one, a step of one
+        #: portion alone repeats its shape (the step function fills it up to 16 rows) and soon does too,
+        #: while the two in one step are a shape that never comes again and is launched kernel by kernel.
+        self.portions_alone = False
+        self._portion_ran_alone = False
 
     # ------------------------------------------------------------------ requests in and out
     def add(self, prompt: Sequence[int], params: SamplingParams) -> Request:
@@ -203,6 +214,7 @@ class Scheduler:
                 return min(room) if room else 1 << 30
 
             items: List[ScheduledItem] = []
+            portions: List[ScheduledItem] = []
             decode_rows, starved = 0, False
             for req in self.running:
                 if req.n_pending == 1:
@@ -217,10 +229,20 @@ class Scheduler:
                     if req.n_pending > 1 and budget > 0:
                         n = min(req.n_pending, budget, max_fit(req))
                         if n >= 1 and take(req, n):
-                            items.append(ScheduledItem(req, n))
+                            portions.append(ScheduledItem(req, n))
                             budget -= n
                         else:
                             self.stats.dropped_portions += 1
+                if (self.portions_alone and items and len(portions) == 1
+                        and portions[0].n_tokens <= PORTION_ALONE_MAX_ROWS):
+                    if self._portion_ran_alone:      # the decoded tokens' turn; the portion waits a step
+                        portions = []
+                    else:
+                        items, decode_rows = [], 0
+                    self._portion_ran_alone = not self._portion_ran_alone
+                else:
+                    self._portion_ran_alone = False
+                items += portions
                 if items or not self.running:
                     break
             # a decoding request found no page, or nothing at all can move: make room

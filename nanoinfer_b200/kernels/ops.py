@@ -794,8 +794,11 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status)
         else:
-            attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_prefill_rows, n_head,
-                           scale, window, ctx.status, plan.prefill_rows)
+            # (portions alone: all of the step's rows, those of no request among them, which the kernel leaves out;
+            # the launch then depends on the step's shape only, as a graph needs it)
+            attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions,
+                           plan.n_prefill_rows if plan.n_decode else ctx.n_rows, n_head, scale, window, ctx.status,
+                           plan.prefill_rows)
 
 
 _SRC_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}

@@ -27,8 +27,8 @@ GRAPH_KEY_BUCKET = 256
 class AttentionPlan(StepPlan):
     """Which rows of a step are single decoded tokens and which belong to prompt portions, and the
     portions cut into tiles of 64 and of 128 query rows, longest key range first; the same for
-    every attention layer of the step.  Words: [decoded rows | portion rows | (entry, first row)
-    per 64-row tile | the same per 128-row tile]."""
+    every attention layer of the step.  Words: [decoded rows | portion rows (only beside decoded rows) |
+    (entry, first row) per 64-row tile | the same per 128-row tile]."""
 
     def __init__(self, entry_start, entry_pos0, for_graph: bool = False, device=None):
         dec, pre, tiles = [], [], []
@@ -59,17 +59,20 @@ class AttentionPlan(StepPlan):
         self.n_wide_tiles = len(wide)
         if for_graph:
             self.max_decode_keys = -(-self.max_decode_keys // GRAPH_KEY_BUCKET) * GRAPH_KEY_BUCKET
-        self.words = dec + pre + [v for t in tiles for v in t] + [v for t in wide for v in t]
+        # (the portions' rows are listed only beside decoded rows: alone they are the rows 0..n-1, and two
+        # steps of portions that differ in a few tokens then have the same words' layout and one graph)
+        self.n_listed_rows = len(pre) if dec else 0
+        self.words = dec + (pre if dec else []) + [v for t in tiles for v in t] + [v for t in wide for v in t]
         if device is not None:
             self.bind(torch.tensor(self.words, dtype=torch.int32, device=device) if self.words else None)
 
     def graph_key(self) -> tuple:
-        return (self.n_decode, self.n_prefill_rows, self.n_tiles, self.n_wide_tiles, self.max_decode_keys)
+        return (self.n_decode, self.n_listed_rows, self.n_tiles, self.n_wide_tiles, self.max_decode_keys)
 
     def bind(self, buf) -> None:
         """``buf``: a device int32 tensor holding ``self.words``."""
-        nd, npre = self.n_decode, self.n_prefill_rows
-        all_decode = npre == 0
+        nd, npre = self.n_decode, self.n_listed_rows
+        all_decode = self.n_prefill_rows == 0
         # rows 0..n-1 in order need no index list
         self.decode_rows = None if all_decode or nd == 0 else buf[:nd]
         self.prefill_rows = None if nd == 0 or npre == 0 else buf[nd:nd + npre]

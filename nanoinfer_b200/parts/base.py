@@ -271,7 +271,11 @@ class KVCacheView:
 @dataclass
 class StepContext:
     """The rows of one step.  Row t is token ``tokens[t]`` at position ``positions[t]`` of batch
-    entry ``row_entry[t]``; an entry's rows are consecutive and in order."""
+    entry ``row_entry[t]``; an entry's rows are consecutive and in order.  Behind the last entry's rows
+    there may be rows of no request (``row_entry[t] == -1``, token 0 at position 0): the step function
+    fills a step up with them so that its shape repeats.  They pass through every row-wise part like
+    any row; a part that keeps something per request (keys and values, state) leaves them out, and
+    nobody reads what they produce.  ``entry_start[-1]`` is the number of rows that belong to requests."""
     n_rows: int
     n_entries: int
     max_rows: int                # the most rows a step may bring: scratch is sized for it

@@ -267,13 +267,56 @@ def test_batches_padded_to_a_graph_shape_give_the_same_logits(dtype, model_dirs,
     padded, runner = run(True)
     exact, runner_exact = run(False)
     assert runner.padded_steps == 12 and runner_exact.padded_steps == 0
-    assert runner.graph_replays >= 10 and len(runner._graphs) == 1
+    assert runner.graph_replays >= 10 and sum(1 for k in runner._graphs if k[0] == k[1]) == 1   # (T == E: single tokens)
     tol = 1e-4 if dtype == torch.float32 else 6e-2
     for i in range(11):
         ref = plain_logits(d, prompts[i] + more[i])
         for t, (a, b) in enumerate(zip(padded[i], exact[i])):
             assert (a - ref[len(prompts[i]) + t]).abs().max() <= tol
             assert (a - b).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_prompts_of_nearly_one_length_share_a_graph(dtype, model_dirs, plain_logits):
+    """Prompts of 67, 70, 75, 80 and 66 tokens, each a step of its own: the step function fills every one up
+    to 80 rows with rows of no request, so that the second is captured and the others replay its graph.
+    Logits at the prompts' ends and at places inside them, and the tokens decoded afterwards (the cache
+    holds exactly each request's keys), are those of the plain implementation; a step that is not
+    filled up gives the same."""
+    from nanoinfer_b200 import load_model
+    from nanoinfer_b200.cache import CacheManager
+    from nanoinfer_b200.engine import ModelRunner, StepItem
+    tol = 1e-4 if dtype == torch.float32 else 6e-2
+    d = model_dirs("A", dtype)
+    m = load_model(d, dtype, "cuda")
+    lens = [67, 70, 75, 80, 66]
+    toks = [random_tokens(512, n + 6, 700 + i) for i, n in enumerate(lens)]
+    want = [plain_logits(d, t) for t in toks]
+    cache = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=5 * 96, max_requests=5, page_size=16,
+                         dtype=dtype, device=torch.device("cuda"), max_positions=m.max_positions, padding=True)
+    runner = ModelRunner(m, cache, max_rows=128, max_entries=8)
+    reqs = [cache.open_request() for _ in lens]
+    for i, n in enumerate(lens):
+        places = [0, 15, 16, n - 1]
+        out = runner.step([StepItem(reqs[i], toks[i][:n], places)])
+        for k, p in enumerate(places):
+            diff = float((out[k].float().cpu() - want[i][p]).abs().max())
+            assert diff <= tol, f"prompt of {n} tokens, position {p}: {diff:.3e}"
+    assert runner.row_padded_steps == 4 and runner.graph_replays >= 3          # (80 rows need no filling)
+    assert sum(1 for k in runner._graphs if k[0] == 80) == 1
+    for t in range(6):                                                         # then all five decode side by side
+        out = runner.step([StepItem(reqs[i], [toks[i][lens[i] + t]], [0]) for i in range(5)])
+        for i in range(5):
+            diff = float((out[i].float().cpu() - want[i][lens[i] + t]).abs().max())
+            assert diff <= tol, f"request {i}, decoded token {t}: {diff:.3e}"
+    cache.check()
+    # the same first prompt through a step function without graphs (nothing is filled up): the same logits
+    cache2 = CacheManager(m.kv_needs(), m.state_needs(), max_tokens=96, max_requests=1, page_size=16,
+                          dtype=dtype, device=torch.device("cuda"), max_positions=m.max_positions)
+    plain_runner = ModelRunner(m, cache2, max_rows=128, max_entries=1, use_graphs=False)
+    out = plain_runner.step([StepItem(cache2.open_request(), toks[0][:67], [66])])
+    assert plain_runner.row_padded_steps == 0
+    assert float((out[0].float().cpu() - want[0][66]).abs().max()) <= tol
 
 
 def test_sampling_with_seeds_is_reproducible_and_independent_of_the_batch(model_dirs):

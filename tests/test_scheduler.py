@@ -55,6 +55,49 @@ def test_decode_rows_first_and_prompts_share_the_rest():
     assert [(i.request.id, i.n_tokens, i.samples) for i in items] == [(a.id, 1, True), (b.id, 1, True), (c.id, 20, True)]
 
 
+def test_a_lone_short_portion_takes_turns_with_the_decoded_tokens():
+    """With ``portions_alone`` a single short prompt portion beside decoded tokens runs as a step of its
+    own, then the decoded tokens as one of theirs: never two portion steps in a row while tokens wait,
+    and nothing of this for two portions at once, for a long one, or without the switch."""
+    cache, s = setup(max_tokens=2048, max_batch=4, max_rows=512, budget=512, max_positions=600)
+    s.portions_alone = True
+    a = s.add([1] * 5, SamplingParams(max_new_tokens=40))
+    run_step(cache, s)                                             # a is prefilled (alone anyway)
+    b = s.add([2] * 30, SamplingParams(max_new_tokens=20))
+    kinds = []
+    for _ in range(3):
+        items, _ = run_step(cache, s)
+        kinds.append([(i.request.id, i.n_tokens) for i in items])
+    # the portion alone (it is the whole prompt: b has its first token), then both decode together
+    assert kinds == [[(b.id, 30)], [(a.id, 1), (b.id, 1)], [(a.id, 1), (b.id, 1)]]
+    # two arrivals one after the other: portion, tokens, portion, tokens
+    c = s.add([3] * 40, SamplingParams(max_new_tokens=5))
+    items, _ = run_step(cache, s)
+    assert [(i.request.id, i.n_tokens) for i in items] == [(c.id, 40)]
+    d = s.add([4] * 20, SamplingParams(max_new_tokens=5))
+    items, _ = run_step(cache, s)                                  # the tokens' turn: d waits a step
+    assert sorted((i.request.id, i.n_tokens) for i in items) == sorted([(a.id, 1), (b.id, 1), (c.id, 1)])
+    items, _ = run_step(cache, s)
+    assert [(i.request.id, i.n_tokens) for i in items] == [(d.id, 20)]
+    while s.has_work():
+        run_step(cache, s)
+    # a long portion, and two portions at once, share their step with the decoded tokens as before
+    cache, s = setup(max_tokens=4096, max_batch=4, max_rows=1024, budget=1024, max_positions=600)
+    s.portions_alone = True
+    a = s.add([1] * 5, SamplingParams(max_new_tokens=40))
+    run_step(cache, s)
+    b = s.add([2] * 300, SamplingParams(max_new_tokens=2))
+    items, _ = run_step(cache, s)
+    assert [(i.request.id, i.n_tokens) for i in items] == [(a.id, 1), (b.id, 300)]
+    c = s.add([3] * 30, SamplingParams(max_new_tokens=2))
+    d = s.add([4] * 30, SamplingParams(max_new_tokens=2))
+    items, _ = run_step(cache, s)
+    assert [(i.request.id, i.n_tokens) for i in items] == [(a.id, 1), (b.id, 1), (c.id, 30), (d.id, 30)]
+    while s.has_work():
+        run_step(cache, s)
+    assert cache.pages_used() == [0]
+
+
 def test_row_limit_bounds_the_budget():
     cache, s = setup(max_tokens=1024, max_batch=4, max_rows=10, budget=100)
     a = s.add([1] * 3, SamplingParams(max_new_tokens=50))
